@@ -1,0 +1,396 @@
+#!/usr/bin/env python
+"""Benchmark of the ug hot path on B200 through the C ABI.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One JSON line on rank 0.  A "step" is one pass of the hot path over one batch
+of seeded synthetic input.  Timing: CUDA events on the library's own stream
+(the stream its kernels run on), W warm-up steps, K timed steps bracketed by a
+barrier and a device synchronisation, maximum over ranks.  Units (rows,
+sequences) are partitioned across ranks with no collective: every rank works
+on its own full-size batch (weak scaling).
+
+``--impl reference`` times the reference's CPU path (the oracle restatement of
+ug-core's CPU backend; the Rust sources cannot be compiled in this image) on a
+bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return {"hbm": float(d["hbm_gbs"]), "bf16": float(d["bf16_tflops"]),
+                    "bf16_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    "source": "measured"}
+        except Exception:
+            pass
+    return {"hbm": FALLBACK_HBM_GBS, "bf16": FALLBACK_BF16_TFLOPS, "bf16_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi during the timed region."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                mhz.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(mhz)) if mhz else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+# ----------------------------------------------------------------- workloads
+class RmsSiluWorkload:
+    """Config 2: out = rms_norm(x) * w * silu(gate), f32 [8192, 4096] per GPU."""
+    name = "rms_norm_silu_gate f32 [8192,4096] (config 2), rows partitioned across GPUs"
+    metric = "effective HBM GB/s, fused rms_norm*silu(gate) (row-op bandwidth as in the softmax GB/s metric)"
+    unit = "GB/s"
+    dtype = "f32"
+    bound = "hbm"
+    rows, cols = 8192, 4096
+
+    def __init__(self, rank):
+        from ug_b200 import synth
+        # every rank owns its own 8192-row partition, seeded by rank
+        self.x = synth.normal(1 + 1000 * rank, (self.rows, self.cols))
+        self.gate = synth.normal(2 + 1000 * rank, (self.rows, self.cols))
+        self.w = synth.uniform(3, (self.cols,), 0.5, 1.5)
+        self.eps = 1e-5
+        # x + gate read, w read, out written (bytes); GB/s = bytes / time
+        self.bytes_per_step = 3 * self.rows * self.cols * 4 + self.cols * 4
+        self.h2d_bytes = 2 * self.rows * self.cols * 4 + self.cols * 4
+        self.d2h_bytes = self.rows * self.cols * 4
+        self.launches_per_step = 1
+
+    def setup(self, dev):
+        from ug_b200 import DType
+        self.dev = dev
+        self.xs = dev.slice_from_values(self.x)
+        self.gs = dev.slice_from_values(self.gate)
+        self.ws = dev.slice_from_values(self.w)
+        self.out = dev.allocate_uninit(DType.F32, self.rows * self.cols)
+
+    def step(self):
+        self.dev.rms_norm_silu_gate(self.xs, self.ws, self.gs, self.out, self.rows, self.cols, self.eps)
+
+    def units(self, seconds, n_ranks):
+        return n_ranks * self.bytes_per_step / seconds / 1e9
+
+    def setup_e2e(self):
+        import ctypes as C
+        from ug_b200._lib import lib
+        self._pin = []
+        def pinned(arr):
+            p = C.c_void_p()
+            assert lib.ugb_host_alloc(arr.nbytes, C.byref(p)) == 0
+            buf = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(arr.size,))
+            buf[:] = arr.ravel()
+            self._pin.append(p)
+            return p, buf
+        self.px, _ = pinned(self.x)
+        self.pg, _ = pinned(self.gate)
+        self.pw, _ = pinned(self.w)
+        self.po, self.out_host = pinned(np.zeros(self.rows * self.cols, np.float32))
+
+    def e2e_step(self):
+        from ug_b200 import DType
+        from ug_b200._lib import lib
+        d, f32 = self.dev, int(DType.F32)
+        d._check(lib.ugb_h2d_async(self.xs._h, self.px, self.rows * self.cols, f32))
+        d._check(lib.ugb_h2d_async(self.gs._h, self.pg, self.rows * self.cols, f32))
+        d._check(lib.ugb_h2d_async(self.ws._h, self.pw, self.cols, f32))
+        self.step()
+        d._check(lib.ugb_d2h_async(self.out._h, self.po, self.rows * self.cols, f32))
+        d.synchronize()
+
+    def teardown_e2e(self):
+        from ug_b200._lib import lib
+        for p in self._pin:
+            lib.ugb_host_free(p)
+
+    def check(self):
+        """Parity of the timed kernel's output against the oracle on a row subset."""
+        import oracle
+        got = self.out.to_vec().reshape(self.rows, self.cols)[:16]
+        ref = oracle.gen_rms_norm_silu_gate(self.x, self.w, self.gate, self.eps, rows=(0, 16))[:16]
+        return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1e-20)))
+
+    def cpu_sample(self, budget_s):
+        """ug CPU backend (emitted C, one thread) on a bounded row sample; returns GB/s."""
+        import oracle
+        rows = 64
+        t0 = time.perf_counter()
+        oracle.gen_rms_norm_silu_gate(self.x, self.w, self.gate, self.eps, rows=(0, rows))
+        per_row = (time.perf_counter() - t0) / rows
+        rows = int(max(64, min(self.rows, budget_s / per_row)))
+        t0 = time.perf_counter()
+        oracle.gen_rms_norm_silu_gate(self.x, self.w, self.gate, self.eps, rows=(0, rows))
+        dt = time.perf_counter() - t0
+        gbs = rows * self.cols * 12 / dt / 1e9
+        return gbs, 1, f"{rows} of {self.rows} rows, emitted-C kernel of ug's CPU backend, 1 thread, {dt:.1f} s"
+
+    def config(self):
+        return {"workload": self.name, "rows_per_gpu": self.rows, "cols": self.cols,
+                "l2": "inputs larger than L2 (403 MB touched per step vs 126 MB L2)"}
+
+
+class SoftmaxWorkload(RmsSiluWorkload):
+    """Config 1 scaled to HBM size: softmax f32 rows of 4096, 32768 rows per GPU."""
+    name = "custom_softmax f32 [32768,4096] (config 1 row shape, 32x rows so the batch exceeds L2)"
+    metric = "softmax effective GB/s (rows*cols*8 bytes / time)"
+    rows, cols = 32768, 4096
+
+    def __init__(self, rank):
+        from ug_b200 import synth
+        self.x = synth.normal(0 + 1000 * rank, (self.rows, self.cols), 2.0)
+        self.bytes_per_step = 2 * self.rows * self.cols * 4
+        self.h2d_bytes = self.d2h_bytes = self.rows * self.cols * 4
+        self.launches_per_step = 1
+
+    def setup(self, dev):
+        from ug_b200 import DType
+        self.dev = dev
+        self.xs = dev.slice_from_values(self.x)
+        self.out = dev.allocate_uninit(DType.F32, self.rows * self.cols)
+
+    def step(self):
+        self.dev.custom_softmax(self.xs, self.out, self.rows, self.cols)
+
+    def setup_e2e(self):
+        import ctypes as C
+        from ug_b200._lib import lib
+        self._pin = []
+        for attr, arr in (("px", self.x), ("po", np.zeros(self.rows * self.cols, np.float32))):
+            p = C.c_void_p()
+            assert lib.ugb_host_alloc(arr.nbytes, C.byref(p)) == 0
+            np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(arr.size,))[:] = arr.ravel()
+            setattr(self, attr, p)
+            self._pin.append(p)
+
+    def e2e_step(self):
+        from ug_b200 import DType
+        from ug_b200._lib import lib
+        d, f32 = self.dev, int(DType.F32)
+        d._check(lib.ugb_h2d_async(self.xs._h, self.px, self.rows * self.cols, f32))
+        self.step()
+        d._check(lib.ugb_d2h_async(self.out._h, self.po, self.rows * self.cols, f32))
+        d.synchronize()
+
+    def check(self):
+        import oracle
+        got = self.out.to_vec().reshape(self.rows, self.cols)[:64]
+        ref = oracle.custom_softmax(self.x[:64])
+        return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1e-30)))
+
+    def cpu_sample(self, budget_s):
+        import oracle
+        rows = 32
+        t0 = time.perf_counter()
+        oracle.gen_softmax(self.x, rows=(0, rows))
+        per_row = (time.perf_counter() - t0) / rows
+        rows = int(max(32, min(self.rows, budget_s / per_row)))
+        t0 = time.perf_counter()
+        oracle.gen_softmax(self.x, rows=(0, rows))
+        dt = time.perf_counter() - t0
+        return rows * self.cols * 8 / dt / 1e9, 1, \
+            f"{rows} of {self.rows} rows, two emitted-C kernels of ug's CPU backend, 1 thread, {dt:.1f} s"
+
+    def config(self):
+        return {"workload": self.name, "rows_per_gpu": self.rows, "cols": self.cols,
+                "l2": "inputs larger than L2 (1.07 GB touched per step vs 126 MB L2)"}
+
+
+WORKLOADS = {"rms_silu": RmsSiluWorkload, "softmax": SoftmaxWorkload}
+DEFAULT_WORKLOAD = "rms_silu"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ug_b200", choices=["ug_b200", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    import ug_b200
+    dev = ug_b200.Device(local_rank)
+    wl = WORKLOADS[args.workload](rank)
+    wl.setup(dev)
+
+    def barrier():
+        dev.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        wl.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    n0 = dev.launch_count
+    barrier()
+    dev.timer_begin()
+    for _ in range(args.steps):
+        wl.step()
+    dev.timer_end()
+    ms = dev.timer_elapsed_ms()
+    barrier()
+    launches = dev.launch_count - n0
+
+    # end to end: host buffers in, host buffers out, copies inside the timed region
+    wl.setup_e2e()
+    for _ in range(2):
+        wl.e2e_step()
+    e2e_steps = max(3, min(args.steps, 10))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        wl.e2e_step()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    wl.teardown_e2e()
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = t.tolist()
+
+    if rank == 0:
+        peaks = measured_peaks()
+        sec = ms / 1e3
+        value = wl.units(sec, world)
+        launch_s = sec / (args.steps * wl.launches_per_step)
+        achieved = wl.bytes_per_step / wl.launches_per_step / launch_s / 1e9
+        line = {
+            "metric": wl.metric, "value": round(value, 2), "unit": wl.unit, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+            "data": "synthetic (seeded Philox, shapes and distributions of the named config)",
+            "config": wl.config(),
+            "e2e": {"value": round(wl.units(e2e_s / e2e_steps, world), 3), "unit": wl.unit,
+                    "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes,
+                    "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": {"bound": wl.bound, "achieved": round(achieved, 1), "peak": peaks["hbm"],
+                         "unit": "GB/s", "frac": round(achieved / peaks["hbm"], 4),
+                         "traffic": None, "peak_source": peaks["source"]},
+            "parity_max_rel_err": wl.check(),
+        }
+        if not args.no_cpu_baseline:
+            v, cores, sample = wl.cpu_sample(args.cpu_seconds)
+            line["cpu_baseline"] = {"value": round(v, 4), "unit": wl.unit, "cores": cores,
+                                    "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def reference_arm(args):
+    """The reference's own CPU implementation of the path (oracle port), bounded sample per step."""
+    wl = WORKLOADS[args.workload](0)
+    per_step = max(1.0, min(20.0, 120.0 / (args.steps + args.warmup)))
+    vals, cores, sample = [], 1, ""
+    for i in range(args.warmup + args.steps):
+        v, cores, sample = wl.cpu_sample(per_step)
+        if i >= args.warmup:
+            vals.append(v)
+    value = float(np.mean(vals))
+    line = {
+        "impl": "reference", "metric": wl.metric, "value": round(value, 4), "unit": wl.unit,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": None,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+        "data": "synthetic (seeded Philox, shapes and distributions of the named config)",
+        "config": wl.config(),
+        "cpu_baseline": {"value": round(value, 4), "unit": wl.unit, "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(value, 4), "unit": wl.unit, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

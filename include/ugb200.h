@@ -1,0 +1,193 @@
+/* ugb200 -- C ABI of the B200 (sm_100a) execution backend for ug.
+ *
+ * Every entry point is plain C: opaque handles, raw pointers and sizes, an
+ * int32 status as the return value (0 = success).  Nothing here throws or
+ * aborts across the boundary; the text of the last failure on a device is
+ * kept per device and read with ugb_last_error().  A Rust `impl ug::Device`
+ * binds exactly these symbols (see INTEGRATION.md for the binding).
+ *
+ * Threading model (ug-cuda/src/runtime.rs:80-85,163-169): one stream per
+ * device handle, launches are asynchronous and ordered on that stream, only
+ * device->host copies and ugb_sync block.  Calls on ONE device handle must be
+ * serialised by the caller; different handles are independent.
+ *
+ * There is no CPU fallback: every compute entry point launches a CUDA kernel
+ * or fails with a status.
+ */
+#ifndef UGB200_H
+#define UGB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define UGB_API __attribute__((visibility("default")))
+#else
+#define UGB_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ugb_device ugb_device;
+typedef struct ugb_slice ugb_slice;
+typedef struct ugb_func ugb_func;
+
+/* ug::DType, same order as ug-core/src/dtype.rs:4-11. */
+typedef enum {
+  UGB_BF16 = 0,
+  UGB_F16 = 1,
+  UGB_F32 = 2,
+  UGB_I32 = 3,
+  UGB_I64 = 4
+} ugb_dtype;
+
+typedef enum {
+  UGB_OK = 0,
+  UGB_ERR_INVALID = 1,     /* null handle, bad enum value, bad argument          */
+  UGB_ERR_DTYPE = 2,       /* dtype mismatch (runtime.rs:113-117,376,390)        */
+  UGB_ERR_SHAPE = 3,       /* length / layout mismatch (gemm.rs:32,42,65,73)     */
+  UGB_ERR_CUDA = 4,        /* a CUDA runtime/driver call failed                  */
+  UGB_ERR_OOM = 5,         /* device allocation failed                           */
+  UGB_ERR_UNSUPPORTED = 6, /* valid request this backend does not cover          */
+  UGB_ERR_TIMEOUT = 7,     /* a bounded device-side wait gave up                 */
+  UGB_ERR_COMPILE = 8      /* run-time compilation of an SSA kernel failed       */
+} ugb_status;
+
+/* ------------------------------------------------------------------ device */
+
+/* ug_cuda::Device::new (ug-cuda/src/runtime.rs:163-169): binds device
+ * `ordinal`, creates its stream.  On failure *out is NULL and
+ * ugb_last_error(NULL) holds the message. */
+UGB_API int32_t ugb_device_create(int32_t ordinal, ugb_device **out);
+UGB_API int32_t ugb_device_destroy(ugb_device *dev);
+/* Message of the last failed call on `dev` (or of the last failed
+ * ugb_device_create when dev is NULL).  Valid until the next call on it. */
+UGB_API const char *ugb_last_error(const ugb_device *dev);
+/* ug::Device::synchronize (ug-core/src/lib.rs:55; runtime.rs:204-207).  Also
+ * reads the device-side status word and reports UGB_ERR_TIMEOUT if a kernel
+ * gave up on a bounded wait since the previous sync. */
+UGB_API int32_t ugb_sync(ugb_device *dev);
+/* ug::Device::use_grid (lib.rs:72; runtime.rs:346-348): always 1. */
+UGB_API int32_t ugb_use_grid(void);
+UGB_API int32_t ugb_device_ordinal(const ugb_device *dev);
+/* The CUDA stream (cudaStream_t) all work of this device is ordered on;
+ * ug_cuda::Device::cudarc_stream (runtime.rs:171-173). */
+UGB_API void *ugb_device_stream(const ugb_device *dev);
+/* Number of kernels this library has launched on `dev` since creation. */
+UGB_API uint64_t ugb_launch_count(const ugb_device *dev);
+
+/* ------------------------------------------------------------------ memory */
+
+/* ug::Device::allocate_uninit (lib.rs:53; runtime.rs:216-241): `len` ELEMENTS
+ * of `dtype`, contents undefined.  len == 0 is legal (the KV cache starts as
+ * a 0-element buffer, ug-llama/src/model.rs:192-193). */
+UGB_API int32_t ugb_alloc(ugb_device *dev, int32_t dtype, size_t len, ugb_slice **out);
+/* Drop of a Slice (stream-ordered free). */
+UGB_API int32_t ugb_free(ugb_slice *s);
+/* Wraps device memory owned by the caller (never freed by this library). */
+UGB_API int32_t ugb_wrap(ugb_device *dev, void *device_ptr, int32_t dtype, size_t len, ugb_slice **out);
+/* ug::Slice::len / dtype (lib.rs:33-34), device_ptr (runtime.rs:137-161). */
+UGB_API size_t ugb_slice_len(const ugb_slice *s);
+UGB_API int32_t ugb_slice_dtype(const ugb_slice *s);
+UGB_API void *ugb_slice_ptr(const ugb_slice *s);
+/* ug::Slice::copy_host_to_device (lib.rs:35; runtime.rs:367-379): `dtype` is
+ * the host element type and must equal the slice's, `len` must equal the
+ * slice length.  Blocks until the host buffer may be reused. */
+UGB_API int32_t ugb_h2d(ugb_slice *dst, const void *src, size_t len, int32_t dtype);
+/* ug::Slice::copy_device_to_host (lib.rs:36; runtime.rs:381-393): blocks
+ * until the data is in `dst`. */
+UGB_API int32_t ugb_d2h(const ugb_slice *src, void *dst, size_t len, int32_t dtype);
+/* Asynchronous variants for pinned host memory: ordered on the device stream,
+ * return without waiting.  The host buffer must stay valid until ugb_sync. */
+UGB_API int32_t ugb_h2d_async(ugb_slice *dst, const void *pinned_src, size_t len, int32_t dtype);
+UGB_API int32_t ugb_d2h_async(const ugb_slice *src, void *pinned_dst, size_t len, int32_t dtype);
+/* Page-locked host buffers for the asynchronous copies. */
+UGB_API int32_t ugb_host_alloc(size_t bytes, void **out);
+UGB_API int32_t ugb_host_free(void *p);
+
+/* ------------------------------------------------------------------ timing */
+
+/* CUDA-event stopwatch on the device's own stream (the stream every kernel
+ * of this library runs on).  begin/end record events; elapsed waits for the
+ * end event and returns milliseconds. */
+UGB_API int32_t ugb_timer_begin(ugb_device *dev);
+UGB_API int32_t ugb_timer_end(ugb_device *dev);
+UGB_API int32_t ugb_timer_elapsed_ms(ugb_device *dev, float *ms);
+
+/* --------------------------------------------- ug-llama Device trait (ops) */
+/* trait ug_llama::Device (ug-llama/src/main.rs:22-28).  Argument order is the
+ * order the reference's custom-op closures receive their slices in: inputs in
+ * call order, destination last (ug-llama/src/cuda_ops.rs:26-28,128,165). All
+ * slices are F32 except `pos` (I32). */
+
+/* custom_softmax (cuda_ops.rs:149-174, cpu_ops.rs:6-31): max-subtracted
+ * softmax over rows of `n_cols`.  src may equal dst. */
+UGB_API int32_t ugb_softmax(ugb_device *dev, const ugb_slice *src, ugb_slice *dst, size_t n_rows,
+                    size_t n_cols);
+/* causal_mask (cpu_ops.rs:33-56; the reference CUDA backend bails,
+ * cuda_ops.rs:176-178): [bh, s1, s2], keeps i2 <= i1, writes -inf above. */
+UGB_API int32_t ugb_causal_mask(ugb_device *dev, const ugb_slice *src, ugb_slice *dst, size_t bh,
+                        size_t s1, size_t s2);
+/* rope (cuda_ops.rs:58-96, cpu_ops.rs:91-127): half rotation on [b,h,t,d];
+ * table row pos[0] + i_t; cos/sin are [max_pos, d/2]. */
+UGB_API int32_t ugb_rope(ugb_device *dev, const ugb_slice *src, const ugb_slice *cos,
+                 const ugb_slice *sin, const ugb_slice *pos, ugb_slice *dst, size_t b, size_t h,
+                 size_t t, size_t d);
+/* rope_i (cpu_ops.rs:58-89; the reference's ropei.cu does not compile):
+ * interleaved pairs (2i, 2i+1). */
+UGB_API int32_t ugb_rope_i(ugb_device *dev, const ugb_slice *src, const ugb_slice *cos,
+                   const ugb_slice *sin, const ugb_slice *pos, ugb_slice *dst, size_t b,
+                   size_t h, size_t t, size_t d);
+/* cat (cuda_ops.rs:98-147, cpu_ops.rs:129-167) on the flattened views
+ * lhs [d1, d2_l], rhs [d1, d2_r] -> dst [d1, d2_l + d2_r].  Bit-exact copy. */
+UGB_API int32_t ugb_cat(ugb_device *dev, const ugb_slice *lhs, const ugb_slice *rhs, ugb_slice *dst,
+                size_t d1, size_t d2_l, size_t d2_r);
+
+/* ------------------------------------------------------- ug::Device::matmul */
+
+/* ug::Device::matmul (ug-core/src/lib.rs:61-69; ug-cuda/src/gemm.rs:292-332):
+ * dst[b, m, n] = lhs[b, m, k] . rhs[b, k, n], dst row-major contiguous.  The
+ * operand layouts are passed the way ug::Layout holds them: `rank` dims and
+ * element strides plus an element offset.  The same layout rules as
+ * gemm_config (gemm.rs:8-83) apply: each operand's last two dims must be
+ * row-major or its transpose, the leading dims must collapse to one batch
+ * stride (0 is allowed: a shared operand); anything else is UGB_ERR_SHAPE
+ * ("non contiguous matmul").  dst, lhs and rhs must share one dtype out of
+ * BF16 / F16 / F32 (UGB_ERR_DTYPE otherwise); accumulation is fp32.  bf16
+ * operands with a row-major lhs run on the tcgen05 tensor-core kernel. */
+UGB_API int32_t ugb_matmul(ugb_device *dev, ugb_slice *dst, const ugb_slice *lhs,
+                           const ugb_slice *rhs, size_t b, size_t m, size_t n, size_t k,
+                           int32_t rank, const size_t *lhs_dims, const size_t *lhs_strides,
+                           size_t lhs_off, const size_t *rhs_dims, const size_t *rhs_strides,
+                           size_t rhs_off);
+
+/* ------------------------------------------------- fused row operators (new) */
+/* The reference reaches these through generated kernels; the new backend
+ * gives them one fused launch each (single read, single write). */
+
+/* rms_norm (ug-llama/src/model.rs:65-78): y = x / sqrt(mean(x^2) + eps) * alpha,
+ * rows of n_cols, alpha [n_cols]. */
+UGB_API int32_t ugb_rms_norm(ugb_device *dev, const ugb_slice *x, const ugb_slice *alpha, ugb_slice *dst,
+                     size_t n_rows, size_t n_cols, float eps);
+/* rms_norm(x) * alpha * silu(gate) (model.rs:65-78 and :103-109). */
+UGB_API int32_t ugb_rms_norm_silu_gate(ugb_device *dev, const ugb_slice *x, const ugb_slice *alpha,
+                               const ugb_slice *gate, ugb_slice *dst, size_t n_rows,
+                               size_t n_cols, float eps);
+/* silu(gate) * up (model.rs:103-109,160-168), n elements. */
+UGB_API int32_t ugb_silu_mul(ugb_device *dev, const ugb_slice *gate, const ugb_slice *up, ugb_slice *dst,
+                     size_t n);
+/* elementwise a + b (residual adds, model.rs:263,267), n elements. */
+UGB_API int32_t ugb_add(ugb_device *dev, const ugb_slice *a, const ugb_slice *b, ugb_slice *dst,
+                size_t n);
+/* index_select (model.rs:32-63): dst[r, :] = emb[ids[r], :], emb [vocab, h]
+ * F32, ids I32 [n_ids].  Ids outside [0, vocab) are reported as
+ * UGB_ERR_INVALID at the next ugb_sync and their rows are left untouched. */
+UGB_API int32_t ugb_index_select(ugb_device *dev, const ugb_slice *emb, const ugb_slice *ids,
+                         ugb_slice *dst, size_t n_ids, size_t h, size_t vocab);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* UGB200_H */

@@ -1,0 +1,289 @@
+// Fused row operators: softmax, rms_norm, rms_norm * silu(gate).
+//
+// The reference reaches these either through a one-warp-per-row, three-pass
+// kernel (ug-llama/src/softmax.cu:8-54) or through generated kernels whose
+// reductions are re-run per output element (ug-core/src/lower_op.rs:364-391).
+// Here each row is read from HBM exactly once with 128-bit loads, kept in
+// registers (or, for rows that do not fit, in shared memory), reduced with
+// warp shuffles plus one shared-memory stage, and written once.
+//
+// Three code paths, chosen on the host from n_cols and pointer alignment:
+//   warp-per-row   n_cols <= 1024, multiple of 4     (many short rows)
+//   CTA-per-row    n_cols <= 8192, multiple of 4     (row in registers)
+//   general        anything else                      (row in shared memory when
+//                  it fits, otherwise re-read from global memory)
+#include <cfloat>
+
+#include "ugb_internal.h"
+
+namespace {
+
+enum RowOp { OP_SOFTMAX = 0, OP_RMS = 1, OP_RMS_SILU = 2 };
+
+struct RowArgs {
+  const float *x;      // [n_rows, n_cols]
+  const float *alpha;  // [n_cols]            (rms)
+  const float *gate;   // [n_rows, n_cols]    (rms_silu)
+  float *y;            // [n_rows, n_cols]
+  size_t n_rows;
+  int n_cols;
+  float inv_d;
+  float eps;
+};
+
+__device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float4 *p, float4 v) { __stcs(p, v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <int THREADS, bool IS_MAX>
+__device__ __forceinline__ float block_reduce(float v, float *sm) {
+  v = IS_MAX ? warp_max(v) : warp_sum(v);
+  constexpr int W = THREADS / 32;
+  if constexpr (W == 1) return v;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();  // previous use of sm is over
+  if (l == 0) sm[w] = v;
+  __syncthreads();
+  float r = (l < W) ? sm[l] : (IS_MAX ? -INFINITY : 0.0f);
+  return IS_MAX ? warp_max(r) : warp_sum(r);
+}
+
+// silu(g) = g / (exp(-g) + 1), ug-llama/src/model.rs:103-109.
+__device__ __forceinline__ float silu(float g) { return g / (expf(-g) + 1.0f); }
+
+// ---- row held in registers; LANES threads cooperate on one row ------------
+// LANES == 32: one warp per row, THREADS/32 rows per CTA.
+// LANES == THREADS: one CTA per row.
+template <int OP, int VPT, int THREADS, int LANES>
+__global__ void __launch_bounds__(THREADS) row_reg_kernel(RowArgs a) {
+  __shared__ float sm[32];
+  constexpr int ROWS_PER_CTA = THREADS / LANES;
+  const int lane = threadIdx.x % LANES;
+  const int sub = threadIdx.x / LANES;
+  const int nvec = a.n_cols >> 2;
+  for (size_t row = (size_t)blockIdx.x * ROWS_PER_CTA + sub; row < a.n_rows;
+       row += (size_t)gridDim.x * ROWS_PER_CTA) {
+    const float4 *xr = reinterpret_cast<const float4 *>(a.x + row * a.n_cols);
+    float4 *yr = reinterpret_cast<float4 *>(a.y + row * a.n_cols);
+    float4 v[VPT];
+    float4 g[OP == OP_RMS_SILU ? VPT : 1];
+    const float pad = OP == OP_SOFTMAX ? -INFINITY : 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = lane + i * LANES;
+      v[i] = c < nvec ? ld_stream(xr + c) : make_float4(pad, pad, pad, pad);
+    }
+    if constexpr (OP == OP_RMS_SILU) {
+      const float4 *gr = reinterpret_cast<const float4 *>(a.gate + row * a.n_cols);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int c = lane + i * LANES;
+        g[i] = c < nvec ? ld_stream(gr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    if constexpr (OP == OP_SOFTMAX) {
+      float m = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+      m = LANES == 32 ? warp_max(m) : block_reduce<THREADS, true>(m, sm);
+      float s = 0.0f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        v[i].x = expf(v[i].x - m);
+        v[i].y = expf(v[i].y - m);
+        v[i].z = expf(v[i].z - m);
+        v[i].w = expf(v[i].w - m);
+        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+      }
+      s = LANES == 32 ? warp_sum(s) : block_reduce<THREADS, false>(s, sm);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int c = lane + i * LANES;
+        if (c < nvec) st_stream(yr + c, make_float4(v[i].x / s, v[i].y / s, v[i].z / s, v[i].w / s));
+      }
+    } else {
+      float ss = 0.0f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i)
+        ss += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+      ss = LANES == 32 ? warp_sum(ss) : block_reduce<THREADS, false>(ss, sm);
+      const float m = sqrtf(ss * a.inv_d + a.eps);
+      const float4 *al = reinterpret_cast<const float4 *>(a.alpha);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int c = lane + i * LANES;
+        if (c < nvec) {
+          const float4 w = __ldg(al + c);
+          float4 o = make_float4(v[i].x / m * w.x, v[i].y / m * w.y, v[i].z / m * w.z, v[i].w / m * w.w);
+          if constexpr (OP == OP_RMS_SILU) {
+            o.x *= silu(g[i].x);
+            o.y *= silu(g[i].y);
+            o.z *= silu(g[i].z);
+            o.w *= silu(g[i].w);
+          }
+          st_stream(yr + c, o);
+        }
+      }
+    }
+  }
+}
+
+// ---- general path: any n_cols, any alignment -------------------------------
+// The row is cached in dynamic shared memory when `cache_cols >= n_cols`;
+// otherwise every pass re-reads global memory (softmax then parks exp(x - max)
+// in the destination and rescales it in place, each thread touching only the
+// elements it wrote itself).
+template <int OP, int THREADS>
+__global__ void __launch_bounds__(THREADS) row_general_kernel(RowArgs a, int cache_cols) {
+  extern __shared__ float row_cache[];
+  __shared__ float sm[32];
+  const bool cached = cache_cols >= a.n_cols;
+  for (size_t row = blockIdx.x; row < a.n_rows; row += gridDim.x) {
+    const float *xr = a.x + row * a.n_cols;
+    float *yr = a.y + row * a.n_cols;
+    if constexpr (OP == OP_SOFTMAX) {
+      float m = -INFINITY;
+      for (int c = threadIdx.x; c < a.n_cols; c += THREADS) {
+        const float v = xr[c];
+        if (cached) row_cache[c] = v;
+        m = fmaxf(m, v);
+      }
+      m = block_reduce<THREADS, true>(m, sm);
+      float s = 0.0f;
+      for (int c = threadIdx.x; c < a.n_cols; c += THREADS) {
+        const float e = expf((cached ? row_cache[c] : xr[c]) - m);
+        if (cached) row_cache[c] = e; else yr[c] = e;
+        s += e;
+      }
+      s = block_reduce<THREADS, false>(s, sm);
+      for (int c = threadIdx.x; c < a.n_cols; c += THREADS) yr[c] = (cached ? row_cache[c] : yr[c]) / s;
+    } else {
+      float ss = 0.0f;
+      for (int c = threadIdx.x; c < a.n_cols; c += THREADS) {
+        const float v = xr[c];
+        if (cached) row_cache[c] = v;
+        ss += v * v;
+      }
+      ss = block_reduce<THREADS, false>(ss, sm);
+      const float m = sqrtf(ss * a.inv_d + a.eps);
+      for (int c = threadIdx.x; c < a.n_cols; c += THREADS) {
+        float o = (cached ? row_cache[c] : xr[c]) / m * a.alpha[c];
+        if constexpr (OP == OP_RMS_SILU) o *= silu(a.gate[row * a.n_cols + c]);
+        yr[c] = o;
+      }
+    }
+    __syncthreads();  // row_cache is reused by the next row
+  }
+}
+
+template <int OP, int VPT>
+int32_t launch_reg(ugb_device *dev, const RowArgs &a, bool warp_rows) {
+  constexpr int THREADS = 256;
+  if (warp_rows) {
+    size_t ctas = (a.n_rows + 7) / 8;
+    size_t cap = (size_t)dev->sm_count * 32;
+    unsigned grid = (unsigned)(ctas < cap ? ctas : cap);
+    row_reg_kernel<OP, VPT, THREADS, 32><<<grid, THREADS, 0, dev->stream>>>(a);
+  } else {
+    size_t cap = (size_t)dev->sm_count * 64;
+    unsigned grid = (unsigned)(a.n_rows < cap ? a.n_rows : cap);
+    row_reg_kernel<OP, VPT, THREADS, THREADS><<<grid, THREADS, 0, dev->stream>>>(a);
+  }
+  return ugb_after_launch(dev, "row_reg_kernel");
+}
+
+template <int OP>
+int32_t launch_row(ugb_device *dev, const RowArgs &a) {
+  if (a.n_rows == 0 || a.n_cols == 0) return UGB_OK;  // zero-size launches are no-ops
+  bool vec = (a.n_cols % 4 == 0) && ((uintptr_t)a.x % 16 == 0) && ((uintptr_t)a.y % 16 == 0) &&
+             (a.alpha == nullptr || (uintptr_t)a.alpha % 16 == 0) &&
+             (a.gate == nullptr || (uintptr_t)a.gate % 16 == 0);
+  const int nvec = a.n_cols / 4;
+  if (vec && a.n_cols <= 1024 && a.n_rows >= 8) {
+    // one warp per row, VPT float4 per lane
+    if (nvec <= 32) return launch_reg<OP, 1>(dev, a, true);
+    if (nvec <= 64) return launch_reg<OP, 2>(dev, a, true);
+    if (nvec <= 128) return launch_reg<OP, 4>(dev, a, true);
+    return launch_reg<OP, 8>(dev, a, true);
+  }
+  if (vec && a.n_cols <= 8192) {
+    if (nvec <= 256) return launch_reg<OP, 1>(dev, a, false);
+    if (nvec <= 512) return launch_reg<OP, 2>(dev, a, false);
+    if (nvec <= 1024) return launch_reg<OP, 4>(dev, a, false);
+    return launch_reg<OP, 8>(dev, a, false);
+  }
+  constexpr int THREADS = 512;
+  const size_t max_cache = 160 * 1024;
+  size_t need = (size_t)a.n_cols * sizeof(float);
+  int cache_cols = need <= max_cache ? a.n_cols : 0;
+  size_t smem = cache_cols ? need : 0;
+  auto k = row_general_kernel<OP, THREADS>;
+  if (smem > 48 * 1024)
+    UGB_CUDA(dev, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)max_cache));
+  size_t cap = (size_t)dev->sm_count * 4;
+  unsigned grid = (unsigned)(a.n_rows < cap ? a.n_rows : cap);
+  k<<<grid, THREADS, smem, dev->stream>>>(a, cache_cols);
+  return ugb_after_launch(dev, "row_general_kernel");
+}
+
+int32_t check_rows(ugb_device *dev, size_t n_rows, size_t n_cols) {
+  UGB_REQUIRE(dev, n_cols < (1ull << 31), UGB_ERR_SHAPE, "row length %zu exceeds 2^31-1", n_cols);
+  UGB_REQUIRE(dev, n_cols == 0 || n_rows <= SIZE_MAX / n_cols, UGB_ERR_SHAPE, "rows*cols overflows");
+  return UGB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t ugb_softmax(ugb_device *dev, const ugb_slice *src, ugb_slice *dst, size_t n_rows,
+                    size_t n_cols) {
+  if (!dev) return UGB_ERR_INVALID;
+  int32_t rc = check_rows(dev, n_rows, n_cols);
+  if (rc) return rc;
+  UGB_SLICE(dev, src, UGB_F32, n_rows * n_cols);
+  UGB_SLICE(dev, dst, UGB_F32, n_rows * n_cols);
+  RowArgs a{(const float *)src->ptr, nullptr, nullptr, (float *)dst->ptr, n_rows, (int)n_cols, 0.f, 0.f};
+  return launch_row<OP_SOFTMAX>(dev, a);
+}
+
+int32_t ugb_rms_norm(ugb_device *dev, const ugb_slice *x, const ugb_slice *alpha, ugb_slice *dst,
+                     size_t n_rows, size_t n_cols, float eps) {
+  if (!dev) return UGB_ERR_INVALID;
+  int32_t rc = check_rows(dev, n_rows, n_cols);
+  if (rc) return rc;
+  UGB_SLICE(dev, x, UGB_F32, n_rows * n_cols);
+  UGB_SLICE(dev, alpha, UGB_F32, n_cols);
+  UGB_SLICE(dev, dst, UGB_F32, n_rows * n_cols);
+  // 1/d is rounded to f32 once, like the constant node of model.rs:71-74.
+  RowArgs a{(const float *)x->ptr, (const float *)alpha->ptr, nullptr, (float *)dst->ptr, n_rows,
+            (int)n_cols, n_cols ? 1.0f / (float)n_cols : 0.f, eps};
+  return launch_row<OP_RMS>(dev, a);
+}
+
+int32_t ugb_rms_norm_silu_gate(ugb_device *dev, const ugb_slice *x, const ugb_slice *alpha,
+                               const ugb_slice *gate, ugb_slice *dst, size_t n_rows,
+                               size_t n_cols, float eps) {
+  if (!dev) return UGB_ERR_INVALID;
+  int32_t rc = check_rows(dev, n_rows, n_cols);
+  if (rc) return rc;
+  UGB_SLICE(dev, x, UGB_F32, n_rows * n_cols);
+  UGB_SLICE(dev, alpha, UGB_F32, n_cols);
+  UGB_SLICE(dev, gate, UGB_F32, n_rows * n_cols);
+  UGB_SLICE(dev, dst, UGB_F32, n_rows * n_cols);
+  RowArgs a{(const float *)x->ptr, (const float *)alpha->ptr, (const float *)gate->ptr,
+            (float *)dst->ptr, n_rows, (int)n_cols, n_cols ? 1.0f / (float)n_cols : 0.f, eps};
+  return launch_row<OP_RMS_SILU>(dev, a);
+}
+
+}  // extern "C"

@@ -1,0 +1,98 @@
+// Internal definitions shared by the translation units of libugb200.so.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "../../include/ugb200.h"
+
+// Device-side status word layout (one per device handle, read at ugb_sync).
+struct ugb_status_word {
+  unsigned int code;    // 0 = ok, otherwise a ugb_status value
+  unsigned int detail;  // kernel-specific (bad index, wait site, ...)
+};
+
+struct ugb_device {
+  int ordinal = 0;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
+  ugb_status_word *status_dev = nullptr;  // device memory
+  uint64_t launches = 0;
+  int sm_count = 148;
+  size_t smem_optin = 0;
+  std::string last_error;
+  void *gemm_state = nullptr;  // owned by the GEMM translation unit
+};
+
+struct ugb_slice {
+  ugb_device *dev = nullptr;
+  void *ptr = nullptr;
+  size_t len = 0;  // elements
+  int32_t dtype = UGB_F32;
+  bool owned = true;
+};
+
+static inline size_t ugb_dtype_size(int32_t dt) {
+  switch (dt) {
+    case UGB_BF16:
+    case UGB_F16:
+      return 2;
+    case UGB_F32:
+    case UGB_I32:
+      return 4;
+    case UGB_I64:
+      return 8;
+    default:
+      return 0;
+  }
+}
+static inline const char *ugb_dtype_name(int32_t dt) {
+  switch (dt) {
+    case UGB_BF16: return "BF16";
+    case UGB_F16: return "F16";
+    case UGB_F32: return "F32";
+    case UGB_I32: return "I32";
+    case UGB_I64: return "I64";
+    default: return "?";
+  }
+}
+
+// Records a formatted message on the device handle and returns `code`.
+int32_t ugb_fail(ugb_device *dev, int32_t code, const char *fmt, ...);
+// Checks the launch error of the kernel just enqueued and counts it.
+int32_t ugb_after_launch(ugb_device *dev, const char *what);
+
+#define UGB_CUDA(dev, call)                                                           \
+  do {                                                                                \
+    cudaError_t e__ = (call);                                                         \
+    if (e__ != cudaSuccess)                                                           \
+      return ugb_fail((dev), e__ == cudaErrorMemoryAllocation ? UGB_ERR_OOM : UGB_ERR_CUDA, \
+                      "%s failed: %s", #call, cudaGetErrorString(e__));               \
+  } while (0)
+
+#define UGB_REQUIRE(dev, cond, code, ...) \
+  do {                                    \
+    if (!(cond)) return ugb_fail((dev), (code), __VA_ARGS__); \
+  } while (0)
+
+// Common argument checks for typed slices.
+static inline int32_t ugb_check_slice(ugb_device *dev, const ugb_slice *s, int32_t dtype,
+                                      size_t min_len, const char *name) {
+  if (!s) return ugb_fail(dev, UGB_ERR_INVALID, "%s: null slice", name);
+  if (s->dev != dev) return ugb_fail(dev, UGB_ERR_INVALID, "%s: slice belongs to another device", name);
+  if (s->dtype != dtype)
+    return ugb_fail(dev, UGB_ERR_DTYPE, "dtype mismatch for %s, expected %s, got %s", name,
+                    ugb_dtype_name(dtype), ugb_dtype_name(s->dtype));
+  if (s->len < min_len)
+    return ugb_fail(dev, UGB_ERR_SHAPE, "%s: slice holds %zu elements, %zu needed", name, s->len,
+                    min_len);
+  return UGB_OK;
+}
+#define UGB_SLICE(dev, s, dtype, min_len)                                 \
+  do {                                                                    \
+    int32_t rc__ = ugb_check_slice((dev), (s), (dtype), (min_len), #s);   \
+    if (rc__ != UGB_OK) return rc__;                                      \
+  } while (0)
