@@ -106,3 +106,64 @@ def test_matmul_errors(dev):
     with pytest.raises(UgError) as e:      # dst too small
         dev.matmul(f, f, f, (2, 8, 8, 8), contiguous((2, 8, 8)), contiguous((2, 8, 8)))
     assert e.value.code == 3
+
+
+# ---- tcgen05 tensor-core path (bf16, row-major lhs, m*n >= 128*64) ---------
+TC_SHAPES = [
+    # bs, m, n, k, transpose_rhs
+    (1, 128, 256, 64, True), (1, 128, 256, 64, False),        # one tile, one k block
+    (1, 128, 256, 512, True), (1, 128, 256, 512, False),      # pipeline wraps (8 k blocks, 4 stages)
+    (1, 256, 512, 256, True), (1, 256, 512, 256, False),      # 2x2 tiles
+    (1, 200, 264, 200, True), (1, 200, 264, 200, False),      # ragged m, n, k tails
+    (1, 64, 2048, 2048, True),                                # decode-shaped projection
+    (3, 160, 320, 136, True), (3, 160, 320, 136, False),      # per-batch rhs
+    (1, 2048, 1024, 1024, True), (1, 1024, 2048, 1024, False),  # many tiles per CTA (persistent loop)
+]
+
+
+@pytest.mark.parametrize("bs,m,n,k,t", TC_SHAPES)
+def test_bf16_tensor_core_matmul(dev, bs, m, n, k, t):
+    a = oracle.round_bf16(synth.normal(920 + m, (bs, m, k), 0.5))
+    b = oracle.round_bf16(synth.normal(921 + n, (bs, n, k) if t else (bs, k, n), 0.5))
+    got = gpu_matmul(dev, a, b, t, DType.BF16)
+    ref = oracle.matmul(a, b, transpose_rhs=t)
+    err = np.abs(got - ref) / np.maximum(np.abs(ref), 0.05 * np.abs(ref).max())
+    assert err.max() < 2e-2
+    # and the mean error must look like bf16 rounding of an exact f32 sum, not like a dropped k block
+    assert np.abs(got - oracle.round_bf16(ref)).mean() < 2e-3 * np.abs(ref).mean()
+
+
+def test_bf16_shared_weight_batch_is_flattened(dev):
+    # [b, m, k] x shared [n, k] weight (batch stride 0), the Linear::fwd shape for b > 1
+    bs, m, n, k = 4, 96, 256, 128
+    a = oracle.round_bf16(synth.normal(930, (bs, m, k), 0.5))
+    w = oracle.round_bf16(synth.normal(931, (n, k), 0.5))
+    sa = dev.slice_from_values(synth.to_bf16_bits(a), bf16=True)
+    sw = dev.slice_from_values(synth.to_bf16_bits(w), bf16=True)
+    dst = dev.allocate_uninit(DType.BF16, bs * m * n)
+    dev.matmul(dst, sa, sw, (bs, m, n, k), contiguous((bs, m, k)), ([bs, k, n], [0, 1, k], 0))
+    dev.synchronize()
+    got = synth.bf16_bits_to_f32(dst.to_vec()).reshape(bs, m, n)
+    ref = oracle.matmul(a, w, transpose_rhs=True)
+    assert np.max(np.abs(got - ref)) / np.abs(ref).max() < 2e-2
+
+
+def test_bf16_config3_full_size_sampled_rows_and_linearity(dev):
+    """Config 3: A [16,512,4096] x B [4096,4096] ([k,n] layout), bf16, fp32 accumulate."""
+    bs, m, n, k = 16, 512, 4096, 4096
+    a = oracle.round_bf16(synth.normal(4, (bs, m, k), 0.02))
+    b = oracle.round_bf16(synth.normal(5, (k, n), 0.02))
+    sa = dev.slice_from_values(synth.to_bf16_bits(a), bf16=True)
+    sb = dev.slice_from_values(synth.to_bf16_bits(b), bf16=True)
+    dst = dev.allocate_uninit(DType.BF16, bs * m * n)
+    dev.matmul(dst, sa, sb, (bs, m, n, k), contiguous((bs, m, k)), ([bs, k, n], [0, n, 1], 0))
+    dev.synchronize()
+    got = synth.bf16_bits_to_f32(dst.to_vec()).reshape(bs * m, n)
+    rows = np.r_[0:8, 127:130, 4095:4098, 8184:8192]           # tile edges, batch edges, last rows
+    ref = oracle.matmul(a.reshape(bs * m, k)[rows], b)
+    err = np.abs(got[rows] - ref) / np.maximum(np.abs(ref), 0.05 * np.abs(ref).max())
+    assert err.max() < 2e-2
+    # size-independent property over the whole output: (1^T A) B == 1^T (A B) column sums
+    col_ref = (a.reshape(-1, k).astype(np.float64).sum(0)) @ b.astype(np.float64)
+    col_got = got.astype(np.float64).sum(0)
+    assert np.max(np.abs(col_got - col_ref)) < 5e-3 * np.abs(col_ref).max() + 0.5
