@@ -255,7 +255,106 @@ class SoftmaxWorkload(RmsSiluWorkload):
                 "l2": "inputs larger than L2 (1.07 GB touched per step vs 126 MB L2)"}
 
 
-WORKLOADS = {"rms_silu": RmsSiluWorkload, "softmax": SoftmaxWorkload}
+class GemmWorkload:
+    """Config 3: A bf16 [16,512,4096] x B bf16 [4096,4096] ([k,n]), fp32 accumulate, bf16 out."""
+    name = "bf16 matmul [16,512,4096] x [4096,4096] (config 3), batch partitioned across GPUs"
+    metric = "bf16 GEMM TFLOP/s (2*b*m*n*k / time), fp32 accumulate"
+    unit = "TFLOP/s"
+    dtype = "bf16"
+    bound = "tensor"
+    bs, m, n, k = 16, 512, 4096, 4096
+
+    def __init__(self, rank):
+        from ug_b200 import synth
+        self.a = synth.to_bf16_bits(synth.normal(4 + 1000 * rank, (self.bs, self.m, self.k), 0.02))
+        self.b = synth.to_bf16_bits(synth.normal(5, (self.k, self.n), 0.02))
+        self.flops_per_step = 2 * self.bs * self.m * self.n * self.k
+        self.h2d_bytes = self.a.nbytes + self.b.nbytes
+        self.d2h_bytes = self.bs * self.m * self.n * 2
+        self.launches_per_step = 1
+        # operands + result (201 MB) exceed L2 only marginally: rotate over 3 A / C buffers
+        self.rot = 3
+
+    def setup(self, dev):
+        from ug_b200 import DType
+        self.dev = dev
+        self.a_s = [dev.slice_from_values(self.a, bf16=True) for _ in range(self.rot)]
+        self.b_s = dev.slice_from_values(self.b, bf16=True)
+        self.c_s = [dev.allocate_uninit(DType.BF16, self.bs * self.m * self.n) for _ in range(self.rot)]
+        self.i = 0
+        bs, m, n, k = self.bs, self.m, self.n, self.k
+        self.lhs_l = ([bs, m, k], [m * k, k, 1], 0)
+        self.rhs_l = ([bs, k, n], [0, n, 1], 0)
+
+    def step(self):
+        j = self.i % self.rot
+        self.i += 1
+        self.dev.matmul(self.c_s[j], self.a_s[j], self.b_s, (self.bs, self.m, self.n, self.k),
+                        self.lhs_l, self.rhs_l)
+
+    def units(self, seconds, n_ranks):
+        return n_ranks * self.flops_per_step / seconds / 1e12
+
+    def setup_e2e(self):
+        import ctypes as C
+        from ug_b200._lib import lib
+        self._pin = []
+        def pinned(arr):
+            p = C.c_void_p()
+            assert lib.ugb_host_alloc(arr.nbytes, C.byref(p)) == 0
+            np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint16)), shape=(arr.size,))[:] = arr.ravel()
+            self._pin.append(p)
+            return p
+        self.pa, self.pb = pinned(self.a), pinned(self.b)
+        self.pc = pinned(np.zeros(self.bs * self.m * self.n, np.uint16))
+
+    def e2e_step(self):
+        from ug_b200 import DType
+        from ug_b200._lib import lib
+        d, bf = self.dev, int(DType.BF16)
+        d._check(lib.ugb_h2d_async(self.a_s[0]._h, self.pa, self.a.size, bf))
+        d._check(lib.ugb_h2d_async(self.b_s._h, self.pb, self.b.size, bf))
+        self.dev.matmul(self.c_s[0], self.a_s[0], self.b_s, (self.bs, self.m, self.n, self.k),
+                        self.lhs_l, self.rhs_l)
+        d._check(lib.ugb_d2h_async(self.c_s[0]._h, self.pc, self.bs * self.m * self.n, bf))
+        d.synchronize()
+
+    def teardown_e2e(self):
+        from ug_b200._lib import lib
+        for p in self._pin:
+            lib.ugb_host_free(p)
+
+    def check(self):
+        import oracle
+        from ug_b200 import synth
+        got = synth.bf16_bits_to_f32(self.c_s[0].to_vec()).reshape(self.bs * self.m, self.n)[:32]
+        ref = oracle.matmul(synth.bf16_bits_to_f32(self.a).reshape(-1, self.k)[:32],
+                            synth.bf16_bits_to_f32(self.b))
+        return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 0.05 * np.abs(ref).max())))
+
+    def cpu_sample(self, budget_s):
+        """f32 GEMM stand-in for crate gemm 0.18.0 on bf16-rounded inputs, all host threads."""
+        import oracle
+        from ug_b200 import synth
+        a = synth.bf16_bits_to_f32(self.a).reshape(-1, self.k)
+        b = synth.bf16_bits_to_f32(self.b)
+        rows = 64
+        t0 = time.perf_counter()
+        oracle.matmul(a[:rows], b)
+        per_row = (time.perf_counter() - t0) / rows
+        rows = int(max(64, min(a.shape[0], budget_s / per_row)))
+        t0 = time.perf_counter()
+        oracle.matmul(a[:rows], b)
+        dt = time.perf_counter() - t0
+        return 2 * rows * self.n * self.k / dt / 1e12, os.cpu_count(), \
+            f"{rows} of {a.shape[0]} lhs rows, f32 GEMM stand-in for crate gemm, {os.cpu_count()} threads, {dt:.1f} s"
+
+    def config(self):
+        return {"workload": self.name, "batch_per_gpu": self.bs, "m": self.m, "n": self.n, "k": self.k,
+                "l2": "rotates over 3 lhs/result buffer pairs (604 MB) so that no operand tile is L2-resident from the previous step"}
+
+
+WORKLOADS = {"rms_silu": RmsSiluWorkload, "softmax": SoftmaxWorkload, "gemm": GemmWorkload}
 DEFAULT_WORKLOAD = "rms_silu"
 
 
@@ -339,7 +438,10 @@ def main():
         sec = ms / 1e3
         value = wl.units(sec, world)
         launch_s = sec / (args.steps * wl.launches_per_step)
-        achieved = wl.bytes_per_step / wl.launches_per_step / launch_s / 1e9
+        if wl.bound == "hbm":
+            achieved, peak, runit = wl.bytes_per_step / wl.launches_per_step / launch_s / 1e9, peaks["hbm"], "GB/s"
+        else:
+            achieved, peak, runit = wl.flops_per_step / wl.launches_per_step / launch_s / 1e12, peaks["bf16"], "TFLOP/s"
         line = {
             "metric": wl.metric, "value": round(value, 2), "unit": wl.unit, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5),
@@ -351,8 +453,8 @@ def main():
                     "steps": e2e_steps},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"bound": wl.bound, "achieved": round(achieved, 1), "peak": peaks["hbm"],
-                         "unit": "GB/s", "frac": round(achieved / peaks["hbm"], 4),
+            "roofline": {"bound": wl.bound, "achieved": round(achieved, 1), "peak": peak,
+                         "unit": runit, "frac": round(achieved / peak, 4),
                          "traffic": None, "peak_source": peaks["source"]},
             "parity_max_rel_err": wl.check(),
         }
