@@ -187,6 +187,66 @@ UGB_API int32_t ugb_add(ugb_device *dev, const ugb_slice *a, const ugb_slice *b,
 UGB_API int32_t ugb_index_select(ugb_device *dev, const ugb_slice *emb, const ugb_slice *ids,
                          ugb_slice *dst, size_t n_ids, size_t h, size_t vocab);
 
+
+/* ------------------------------------------- ug-llama Model::fwd (decode step) */
+/* The reference builds one lazy graph per token from Model::fwd
+ * (ug-llama/src/model.rs:298-374) and runs ~27 launches per layer; this entry
+ * point family runs the same operator chain for one new token per sequence as
+ * a fixed, fused kernel sequence captured in a CUDA graph.  Weights and the KV
+ * cache are bf16, reductions and the residual stream fp32.  Batch rows are
+ * independent sequences that share one position (the reference reads pos[0]
+ * for every row, ug-llama/src/cpu_ops.rs:67-71). */
+typedef struct ugb_llama ugb_llama;
+
+/* ug_llama::model::Config (ug-llama/src/model.rs:10-30). */
+typedef struct {
+  int32_t hidden;           /* hidden_size                  */
+  int32_t layers;           /* num_hidden_layers            */
+  int32_t n_heads;          /* num_attention_heads          */
+  int32_t n_kv_heads;       /* num_key_value_heads          */
+  int32_t head_dim;         /* hidden_size / n_heads        */
+  int32_t ffn;              /* intermediate_size            */
+  int32_t vocab;            /* vocab_size                   */
+  int32_t max_pos;          /* max_position_embeddings      */
+  float rope_theta;
+  float rms_eps;
+  int32_t rope_interleaved; /* rope_interleaved (0 / 1)     */
+} ugb_llama_config;
+
+enum { UGB_LLAMA_LOGITS = 0, UGB_LLAMA_NEXT_TOKENS = 1, UGB_LLAMA_HIDDEN = 2 };
+
+/* Model::new + Cache::new (model.rs:183-198,298-363): allocates weights, the
+ * RoPE tables (model.rs:278-295) and a KV cache for `batch` sequences of up to
+ * `t_max` positions.  tie_word_embeddings is assumed, as in model.rs:315-319. */
+UGB_API int32_t ugb_llama_create(ugb_device *dev, const ugb_llama_config *cfg, int32_t batch,
+                                 int32_t t_max, ugb_llama **out);
+UGB_API int32_t ugb_llama_destroy(ugb_llama *m);
+/* One tensor by its safetensors name (model.rs:313-346), e.g.
+ * "model.layers.3.self_attn.q_proj.weight".  Matrices: BF16, or F32 rounded to
+ * bf16 (round to nearest even).  Norm weights: F32.  Shapes are checked like
+ * Linear::new / RmsNorm::new do (model.rs:120-122,142-144). */
+UGB_API int32_t ugb_llama_load_weight(ugb_llama *m, const char *name, const ugb_slice *w);
+/* Tuning knobs: "splits_qkv", "splits_o", "splits_down" (split-K factors of the
+ * projections) and "att_splits" (KV slices per sequence and KV head), 1..8. */
+UGB_API int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value);
+/* Sets the number of cached positions (0 = empty cache); cache contents at
+ * positions >= pos are ignored by later steps. */
+UGB_API int32_t ugb_llama_reset(ugb_llama *m, int32_t pos);
+UGB_API int32_t ugb_llama_position(const ugb_llama *m);
+UGB_API int32_t ugb_llama_kv_positions(const ugb_llama *m);
+/* Model::fwd for seq_len == 1, n_steps times.  With `tokens` (I32 [batch],
+ * n_steps must be 1) the step consumes those ids; with NULL each step
+ * consumes the argmax of the previous step's logits (greedy decoding, ties to
+ * the lowest id).  Asynchronous; results are read with ugb_llama_read. */
+UGB_API int32_t ugb_llama_decode(ugb_llama *m, const ugb_slice *tokens, int32_t n_steps);
+/* Blocking read of the last step's logits (f32 [batch, vocab]), next tokens
+ * (i32 [batch]) or final residual stream (f32 [batch, hidden]); len in elements. */
+UGB_API int32_t ugb_llama_read(ugb_llama *m, int32_t what, void *host_dst, size_t len);
+/* Blocking read of one layer's K (which = 0) or V (1) cache, bf16
+ * [batch, n_kv_heads, ugb_llama_kv_positions, head_dim]. */
+UGB_API int32_t ugb_llama_read_kv(ugb_llama *m, int32_t layer, int32_t which, void *host_dst,
+                                  size_t len);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,420 @@
+// Device kernels of the fused Llama decode step (one new token per sequence).
+//
+// They restate, fused and in bf16 storage / fp32 arithmetic, the operator
+// chain of ug-llama/src/model.rs:203-269 between the matmuls:
+//   embed_gather        index_select (model.rs:32-63)
+//   reduce_rmsnorm      residual add (model.rs:263,267) + rms_norm (model.rs:65-78)
+//   rope_append         split/transpose + rope (cpu_ops.rs:58-127) + cat into the KV cache (model.rs:226-230)
+//   decode_attention    repeat + q.kT + scale + softmax + .v + head merge (model.rs:231-245)
+//   argmax_rows         greedy pick (the reference samples on the host, main.rs:151-152)
+// All of them are HBM- or latency-bound; the attention kernel streams the KV
+// cache once with 16-byte cp.async copies and does its two small contractions
+// on mma.sync tiles (m16n8k16, 8 query heads of one KV group padded to 16).
+#pragma once
+#include <cuda_bf16.h>
+
+#include "ugb_internal.h"
+
+namespace ugb_decode {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// x[b, :] = float(embed[tok[b], :]).  One CTA per row; ids outside the table
+// raise the status word and leave the row untouched.
+__global__ void __launch_bounds__(256)
+embed_gather_kernel(const __nv_bfloat16 *__restrict__ embed, const int *__restrict__ tok,
+                    float *__restrict__ x, int hidden, int vocab, ugb_status_word *status) {
+  const int b = blockIdx.x;
+  const int id = tok[b];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0 && atomicCAS(&status->code, 0u, (unsigned)UGB_ERR_INVALID) == 0u) status->detail = b;
+    return;
+  }
+  const uint4 *src = reinterpret_cast<const uint4 *>(embed + (size_t)id * hidden);
+  float4 *dst = reinterpret_cast<float4 *>(x + (size_t)b * hidden);
+  for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) {
+    const uint4 v = __ldg(src + c);
+    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v);
+    const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]);
+    const float2 f2 = __bfloat1622float2(h[2]), f3 = __bfloat1622float2(h[3]);
+    dst[2 * c] = make_float4(f0.x, f0.y, f1.x, f1.y);
+    dst[2 * c + 1] = make_float4(f2.x, f2.y, f3.x, f3.y);
+  }
+}
+
+// x[b, :] += sum_s part[s][b][:]   (split-K partials of the previous projection,
+// summed in a fixed order), then xn = bf16(x / sqrt(mean(x^2) + eps) * alpha).
+// One CTA of 256 threads per row; hidden <= 8192, hidden % 4 == 0.
+template <int VPT>
+__global__ void __launch_bounds__(256)
+reduce_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ part, int n_part,
+                      size_t part_stride, const float *__restrict__ alpha,
+                      __nv_bfloat16 *__restrict__ xn, int hidden, float inv_d, float eps) {
+  __shared__ float sm[8];
+  const int b = blockIdx.x;
+  const int nvec = hidden >> 2;
+  float4 *xr = reinterpret_cast<float4 *>(x + (size_t)b * hidden);
+  float4 v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * 256;
+    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < nvec) {
+      v[i] = xr[c];
+      for (int s = 0; s < n_part; ++s) {
+        const float4 p = __ldcs(reinterpret_cast<const float4 *>(part + s * part_stride + (size_t)b * hidden) + c);
+        v[i].x += p.x; v[i].y += p.y; v[i].z += p.z; v[i].w += p.w;
+      }
+      if (n_part > 0) xr[c] = v[i];
+      ss += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = (threadIdx.x & 31) < 8 ? sm[threadIdx.x & 31] : 0.f;
+  tot = warp_sum(tot);
+  const float m = sqrtf(tot * inv_d + eps);
+  uint2 *out = reinterpret_cast<uint2 *>(xn + (size_t)b * hidden);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < nvec) {
+      const float4 w = __ldg(reinterpret_cast<const float4 *>(alpha) + c);
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v[i].x / m * w.x, v[i].y / m * w.y);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(v[i].z / m * w.z, v[i].w / m * w.w);
+      out[c] = make_uint2(*(uint32_t *)&lo, *(uint32_t *)&hi);
+    }
+  }
+}
+
+// qkv[b, :] = sum_s part[s][b][:]  (fp32), then
+//   q  -> rope -> bf16 q_out[b][head][d]
+//   k  -> rope -> bf16 K cache [b][kvh][pos][d]
+//   v  ->         bf16 V cache [b][kvh][pos][d]
+// pos is read from device memory (every sequence of the batch sits at the same
+// position, the reference's pos[0] convention, cpu_ops.rs:67-71).  One CTA per
+// sequence, one thread per rotation pair.
+__global__ void __launch_bounds__(256)
+rope_append_kernel(const float *__restrict__ part, int n_part, size_t part_stride,
+                   const float *__restrict__ cos_, const float *__restrict__ sin_,
+                   const int *__restrict__ pos_p, __nv_bfloat16 *__restrict__ q_out,
+                   __nv_bfloat16 *__restrict__ kcache, __nv_bfloat16 *__restrict__ vcache,
+                   int n_heads, int n_kv, int hd, int t_max, int interleaved) {
+  const int b = blockIdx.x;
+  const int pos = *pos_p;
+  const int half = hd >> 1;
+  const int qkv_dim = (n_heads + 2 * n_kv) * hd;
+  const float *row = part + (size_t)b * qkv_dim;
+  auto ld = [&](int col) {
+    float a = 0.f;
+    for (int s = 0; s < n_part; ++s) a += row[s * part_stride + col];
+    return a;
+  };
+  const int n_rot_heads = n_heads + n_kv;
+  for (int it = threadIdx.x; it < n_rot_heads * half; it += blockDim.x) {
+    const int head = it / half, i = it - head * half;
+    const int i1 = interleaved ? 2 * i : i;
+    const int i2 = interleaved ? 2 * i + 1 : i + half;
+    const float x1 = ld(head * hd + i1), x2 = ld(head * hd + i2);
+    const float c = cos_[(size_t)pos * half + i], s = sin_[(size_t)pos * half + i];
+    const float y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
+    const float y2 = __fadd_rn(__fmul_rn(x1, s), __fmul_rn(x2, c));
+    __nv_bfloat16 *dst = head < n_heads
+        ? q_out + ((size_t)b * n_heads + head) * hd
+        : kcache + (((size_t)b * n_kv + (head - n_heads)) * t_max + pos) * hd;
+    dst[i1] = __float2bfloat16_rn(y1);
+    dst[i2] = __float2bfloat16_rn(y2);
+  }
+  for (int it = threadIdx.x; it < n_kv * hd; it += blockDim.x) {
+    const int head = it / hd, i = it - head * hd;
+    vcache[(((size_t)b * n_kv + head) * t_max + pos) * hd + i] =
+        __float2bfloat16_rn(ld((n_heads + n_kv) * hd + it));
+  }
+}
+
+// ------------------------------------------------------------- attention ---
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                 uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t smem, const void *gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *(uint32_t *)&t;
+}
+
+constexpr int ATT_WARPS = 4;
+constexpr int ATT_STAGES = 4;          // 16-key sub-tiles in flight per warp
+constexpr int ATT_SUB = 16;            // keys per sub-tile
+constexpr int ATT_HD = 64;             // head dim (compile-time: fragment layout)
+constexpr int ATT_GROUP = 8;           // query heads per KV head (<= 8, padded to the 16-row tile)
+constexpr int ATT_SUB_BYTES = ATT_SUB * ATT_HD * 2;   // 2 KiB per K or V sub-tile
+constexpr int ATT_RING_BYTES = ATT_WARPS * ATT_STAGES * 2 * ATT_SUB_BYTES;   // dynamic shared memory
+
+// Flash-decode for one new query position per sequence, grouped-query heads.
+//   grid = (n_split, n_kv, batch), 128 threads.
+// CTA (sp, kvh, b) covers the sp-th slice of the T = pos + 1 cached positions of
+// sequence b, KV head kvh, for the `group` query heads that share it.  Each warp
+// walks its own 16-key sub-tiles (a private cp.async ring, no CTA barrier in the
+// loop) with a private online-softmax state; the four states are merged through
+// shared memory, written as a partial (m, l, O) and the last CTA of a (b, kvh)
+// to finish combines the partials of all slices into the bf16 output
+//   out[b][head][d]   (= the transposed + merged layout o_proj consumes).
+// K frags use a permuted k index (dims 16t+4s.. for lane t, step s) so that a
+// lane's operands are two contiguous 16-byte pieces of a row; Q uses the same
+// permutation.  V frags come from ldmatrix.trans on the staged sub-tile.
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+decode_attention_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restrict__ kcache,
+                        const __nv_bfloat16 *__restrict__ vcache, const int *__restrict__ pos_p,
+                        float *__restrict__ part_o, float *__restrict__ part_ml,
+                        unsigned int *__restrict__ counters, __nv_bfloat16 *__restrict__ out,
+                        int n_heads, int n_kv, int group, int t_max, float scale) {
+  extern __shared__ __align__(128) uint8_t att_smem[];                     // the cp.async ring, 64 KiB
+  uint8_t (*ring)[ATT_STAGES][2][ATT_SUB_BYTES] =
+      reinterpret_cast<uint8_t (*)[ATT_STAGES][2][ATT_SUB_BYTES]>(att_smem);
+  __shared__ float merge_o[ATT_WARPS][ATT_GROUP][ATT_HD];
+  __shared__ float merge_ml[ATT_WARPS][ATT_GROUP][2];
+  __shared__ int is_last;
+
+  const int sp = blockIdx.x, n_split = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int T = *pos_p + 1;
+  const int n_sub = (T + ATT_SUB - 1) / ATT_SUB;
+  const int sub_per_split = (n_sub + n_split - 1) / n_split;
+  const int sub_lo = sp * sub_per_split;
+  const int sub_hi = min(n_sub, sub_lo + sub_per_split);
+
+  const __nv_bfloat16 *kbase = kcache + ((size_t)b * n_kv + kvh) * (size_t)t_max * ATT_HD;
+  const __nv_bfloat16 *vbase = vcache + ((size_t)b * n_kv + kvh) * (size_t)t_max * ATT_HD;
+
+  // Q fragments (rows >= group are zero padding)
+  uint32_t qa[8];
+  {
+    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+    if (g < group) {
+      const uint4 *qp = reinterpret_cast<const uint4 *>(q + ((size_t)b * n_heads + kvh * group + g) * ATT_HD + 16 * t);
+      lo = __ldg(qp);
+      hi = __ldg(qp + 1);
+    }
+    qa[0] = lo.x; qa[1] = lo.y; qa[2] = lo.z; qa[3] = lo.w;
+    qa[4] = hi.x; qa[5] = hi.y; qa[6] = hi.z; qa[7] = hi.w;
+  }
+
+  auto issue = [&](int sub, int stage) {
+    // 16 keys x 128 B for K and for V: 4 + 4 chunks of 16 B per lane, XOR-swizzled rows
+    const uint32_t ks = (uint32_t)__cvta_generic_to_shared(&ring[warp][stage][0][0]);
+    const uint32_t vs = (uint32_t)__cvta_generic_to_shared(&ring[warp][stage][1][0]);
+    const char *kg = reinterpret_cast<const char *>(kbase + (size_t)sub * ATT_SUB * ATT_HD);
+    const char *vg = reinterpret_cast<const char *>(vbase + (size_t)sub * ATT_SUB * ATT_HD);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = lane + 32 * i, key = c >> 3, ch = c & 7;
+      const uint32_t so = key * 128 + ((ch ^ (key & 7)) << 4);
+      cp_async16(ks + so, kg + c * 16);
+      cp_async16(vs + so, vg + c * 16);
+    }
+  };
+
+  float m_run = -INFINITY, l_run = 0.f;   // row g (this lane's query head)
+  float o[8][4];
+#pragma unroll
+  for (int d = 0; d < 8; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+
+  // prologue: fill the ring
+  const int first = sub_lo + warp;
+#pragma unroll
+  for (int s = 0; s < ATT_STAGES - 1; ++s) {
+    const int sub = first + s * ATT_WARPS;
+    if (sub < sub_hi) issue(sub, s);
+    cp_async_commit();
+  }
+  int stage = 0;
+  for (int sub = first; sub < sub_hi; sub += ATT_WARPS) {
+    {
+      const int nxt = sub + (ATT_STAGES - 1) * ATT_WARPS;
+      const int nstage = (stage + ATT_STAGES - 1) % ATT_STAGES;
+      if (nxt < sub_hi) issue(nxt, nstage);
+      cp_async_commit();
+    }
+    cp_async_wait<ATT_STAGES - 1>();
+    __syncwarp();
+    const uint8_t *ks = &ring[warp][stage][0][0];
+    const uint32_t vs = (uint32_t)__cvta_generic_to_shared(&ring[warp][stage][1][0]);
+
+    // S = Q . K^T for 16 keys: two n-tiles of 8 keys
+    float s_acc[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      s_acc[j][0] = s_acc[j][1] = s_acc[j][2] = s_acc[j][3] = 0.f;
+      const int key = 8 * j + g;
+      const uint4 k0 = *reinterpret_cast<const uint4 *>(ks + key * 128 + (((2 * t) ^ (key & 7)) << 4));
+      const uint4 k1 = *reinterpret_cast<const uint4 *>(ks + key * 128 + (((2 * t + 1) ^ (key & 7)) << 4));
+      mma_bf16_16x8x16(s_acc[j], qa[0], 0u, qa[1], 0u, k0.x, k0.y);
+      mma_bf16_16x8x16(s_acc[j], qa[2], 0u, qa[3], 0u, k0.z, k0.w);
+      mma_bf16_16x8x16(s_acc[j], qa[4], 0u, qa[5], 0u, k1.x, k1.y);
+      mma_bf16_16x8x16(s_acc[j], qa[6], 0u, qa[7], 0u, k1.z, k1.w);
+    }
+    // scale, mask keys >= T, online softmax on row g (values [j][0], [j][1])
+    const int key0 = sub * ATT_SUB;
+    float sv[4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = key0 + 8 * j + 2 * t + e;
+        sv[2 * j + e] = key < T ? s_acc[j][e] * scale : -INFINITY;
+      }
+    float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);             // finite: key0 < T for every sub-tile visited
+    const float alpha = __expf(m_run - m_new);
+    float p[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) p[e] = __expf(sv[e] - m_new);
+    l_run = l_run * alpha + ((p[0] + p[1]) + (p[2] + p[3]));
+    m_run = m_new;
+#pragma unroll
+    for (int d = 0; d < 8; ++d) { o[d][0] *= alpha; o[d][1] *= alpha; }
+    const uint32_t pa0 = pack_bf16(p[0], p[1]), pa2 = pack_bf16(p[2], p[3]);
+
+    // O += P . V : 8 n-tiles of 8 dims, k = 16 keys; B frags by ldmatrix.trans
+#pragma unroll
+    for (int d = 0; d < 8; d += 2) {
+      const int mi = lane >> 3, ri = lane & 7;
+      const int key = ri + 8 * (mi & 1), ch = d + (mi >> 1);
+      const uint32_t addr = vs + key * 128 + ((ch ^ (key & 7)) << 4);
+      uint32_t r0, r1, r2, r3;
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+      mma_bf16_16x8x16(o[d], pa0, 0u, pa2, 0u, r0, r1);
+      mma_bf16_16x8x16(o[d + 1], pa0, 0u, pa2, 0u, r2, r3);
+    }
+    __syncwarp();
+    stage = (stage + 1) % ATT_STAGES;
+  }
+  cp_async_wait<0>();
+
+  // l is a per-lane partial over this lane's key columns: finish the row sum
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+
+  // ---- merge the four warps of this CTA -----------------------------------
+  if (g < ATT_GROUP) {
+#pragma unroll
+    for (int d = 0; d < 8; ++d) {
+      merge_o[warp][g][8 * d + 2 * t] = o[d][0];
+      merge_o[warp][g][8 * d + 2 * t + 1] = o[d][1];
+    }
+    if (t == 0) { merge_ml[warp][g][0] = m_run; merge_ml[warp][g][1] = l_run; }
+  }
+  __syncthreads();
+  const size_t slot = ((size_t)b * n_kv + kvh) * n_split + sp;
+  for (int idx = threadIdx.x; idx < ATT_GROUP * ATT_HD; idx += blockDim.x) {
+    const int h = idx / ATT_HD, dd = idx - h * ATT_HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) mm = fmaxf(mm, merge_ml[w][h][0]);
+    float acc = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) {
+      const float f = merge_ml[w][h][0] == -INFINITY ? 0.f : __expf(merge_ml[w][h][0] - mm);
+      acc += merge_o[w][h][dd] * f;
+      ll += merge_ml[w][h][1] * f;
+    }
+    part_o[(slot * ATT_GROUP + h) * ATT_HD + dd] = acc;
+    if (dd == 0) { part_ml[(slot * ATT_GROUP + h) * 2] = mm; part_ml[(slot * ATT_GROUP + h) * 2 + 1] = ll; }
+  }
+  // ---- last CTA of this (b, kvh) combines the slices ------------------------
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(&counters[(size_t)b * n_kv + kvh], 1u);
+    is_last = (prev == (unsigned)n_split - 1u);
+    if (is_last) counters[(size_t)b * n_kv + kvh] = 0u;   // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const size_t slot0 = ((size_t)b * n_kv + kvh) * n_split;
+  for (int idx = threadIdx.x; idx < group * ATT_HD; idx += blockDim.x) {
+    const int h = idx / ATT_HD, dd = idx - h * ATT_HD;
+    float mm = -INFINITY;
+    for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, __ldcg(&part_ml[((slot0 + s) * ATT_GROUP + h) * 2]));
+    float acc = 0.f, ll = 0.f;
+    for (int s = 0; s < n_split; ++s) {
+      const float ms = __ldcg(&part_ml[((slot0 + s) * ATT_GROUP + h) * 2]);
+      const float f = ms == -INFINITY ? 0.f : __expf(ms - mm);
+      acc += __ldcg(&part_o[((slot0 + s) * ATT_GROUP + h) * ATT_HD + dd]) * f;
+      ll += __ldcg(&part_ml[((slot0 + s) * ATT_GROUP + h) * 2 + 1]) * f;
+    }
+    out[((size_t)b * n_heads + kvh * group + h) * ATT_HD + dd] = __float2bfloat16_rn(acc / ll);
+  }
+}
+
+// next[b] = argmax_j logits[b, j] (ties -> lowest index); thread 0 of CTA 0 also
+// advances the shared position counter.  One CTA of 256 threads per row.
+__global__ void __launch_bounds__(256)
+argmax_rows_kernel(const float *__restrict__ logits, int vocab, int *__restrict__ next, int *pos_p) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const int b = blockIdx.x;
+  const float *row = logits + (size_t)b * vocab;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int j = threadIdx.x; j < vocab; j += blockDim.x) {
+    const float v = row[j];
+    if (v > best || (v == best && j < bi)) { best = v; bi = j; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = threadIdx.x < 8 ? sv[threadIdx.x] : -INFINITY;
+    bi = threadIdx.x < 8 ? si[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (threadIdx.x == 0) {
+      next[b] = bi == 0x7fffffff ? 0 : bi;
+      if (b == 0) *pos_p = *pos_p + 1;
+    }
+  }
+}
+
+// cos/sin tables [max_pos, hd/2]: angle = float(pos) * inv_freq[i] as one f32
+// product (the [max,1].[1,d/2] matmul of model.rs:291), then precise cosf/sinf.
+__global__ void rope_table_kernel(const float *__restrict__ inv_freq, float *__restrict__ cos_,
+                                  float *__restrict__ sin_, int max_pos, int half) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= max_pos * half) return;
+  const float ang = __fmul_rn((float)(i / half), inv_freq[i % half]);
+  cos_[i] = cosf(ang);
+  sin_[i] = sinf(ang);
+}
+
+}  // namespace ugb_decode

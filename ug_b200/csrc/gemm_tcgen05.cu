@@ -28,24 +28,35 @@
 
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int STAGES = 4, ACC_STAGES = 2;
+constexpr int BM = 128, BK = 64;
+constexpr int ACC_STAGES = 2;
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;          // 16 KiB
-constexpr int B_BYTES = BN * BK * 2;          // 32 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int TMEM_COLS = ACC_STAGES * BN;    // 512 (all of TMEM)
 constexpr int THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
+
+// Tile shapes.  BN = 256 for compute-bound products (4 stages of 48 KiB);
+// BN = 64 for skinny, weight-streaming products (m <= 128: 8 stages of 24 KiB
+// keep ~190 KiB of loads in flight per SM and N/64 CTAs spread the weight
+// matrix over the SMs).
+template <int BN> struct Cfg {
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = BN == 256 ? 4 : 8;
+  static constexpr int TMEM_COLS = ACC_STAGES * BN;   // 512 or 128 (powers of two)
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 
 struct Params {
   int M, N, K, batch;
   int tiles_m, tiles_n, k_blocks;
+  int splits, kb_per_split;   // split-K: split s covers k blocks [s*kb_per_split, ...)
   int b_batched;          // 0: B shared by all batch steps
   int b_is_nk;            // 1: B [n,k] (k-major), 0: B [k,n] (n-major)
-  long long c_batch;      // elements between batch steps of C
-  __nv_bfloat16 *C;
+  int epi;                // UGB_EPI_*
+  long long c_batch;      // output elements between batch steps
+  long long c_split;      // output elements between split-K partials
+  void *C;
   ugb_status_word *status;
 };
 
@@ -143,8 +154,12 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major)
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+  constexpr int STAGES = Cfg<BN>::STAGES;
+  constexpr int STAGE_BYTES = Cfg<BN>::STAGE_BYTES;
+  constexpr int TMEM_COLS = Cfg<BN>::TMEM_COLS;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128-byte swizzle pattern repeats every 1024 bytes
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -180,7 +195,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
 
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
-  const int n_tiles = tiles_per_batch * p.batch;
+  const int tiles_per_split = tiles_per_batch * p.batch;
+  const int n_tiles = tiles_per_split * p.splits;
 
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer --
@@ -189,11 +205,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t phase = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-        const int bi = tile / tiles_per_batch;
-        const int r = tile - bi * tiles_per_batch;
+        const int sp = tile / tiles_per_split;
+        const int ts = tile - sp * tiles_per_split;
+        const int bi = ts / tiles_per_batch;
+        const int r = ts - bi * tiles_per_batch;
         const int m0 = (r % p.tiles_m) * BM, n0 = (r / p.tiles_m) * BN;
         const int bz = p.b_batched ? bi : 0;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int kb0 = sp * p.kb_per_split;
+        const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&empty[stage]), phase ^ 1u, abort_flag, p.status, 1)) { alive = false; break; }
           const uint32_t bar = smem_u32(&full[stage]);
           mbar_expect_tx(bar, STAGE_BYTES);
@@ -201,10 +221,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t b_dst = a_dst + A_BYTES;
           tma_load_3d(a_dst, &tmA, bar, kb * BK, m0, bi);
           if (p.b_is_nk) {
-            tma_load_3d(b_dst, &tmB, bar, kb * BK, n0, bz);          // box {64 k, 256 n}
+            tma_load_3d(b_dst, &tmB, bar, kb * BK, n0, bz);          // box {64 k, BN n}
           } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c)                         // 4 boxes {64 n, 64 k}
+            for (int c = 0; c < BN / 64; ++c)                         // BN/64 boxes {64 n, 64 k}
               tma_load_3d(b_dst + c * (64 * BK * 2), &tmB, bar, n0 + c * 64, kb * BK, bz);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -219,10 +239,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t phase = 0, acc_phase = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+        const int sp = tile / tiles_per_split;
+        const int kb0 = sp * p.kb_per_split;
+        const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1u, abort_flag, p.status, 2)) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&full[stage]), phase, abort_flag, p.status, 3)) { alive = false; break; }
           tcgen05_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
@@ -236,7 +259,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // apart (SBO); a k step of 16 moves 16 rows of 128 B.
             const uint64_t b_desc = p.b_is_nk ? make_smem_desc(b_addr + j * (UMMA_K * 2), 0, 1024)
                                               : make_smem_desc(b_addr + j * (UMMA_K * 128), 64 * BK * 2, 1024);
-            umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0 ? 1u : 0u);
+            umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&empty[stage]));      // frees the smem stage when the MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -252,30 +275,58 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-      const int bi = tile / tiles_per_batch;
-      const int r = tile - bi * tiles_per_batch;
+      const int sp = tile / tiles_per_split;
+      const int ts = tile - sp * tiles_per_split;
+      const int bi = ts / tiles_per_batch;
+      const int r = ts - bi * tiles_per_batch;
       const int m0 = (r % p.tiles_m) * BM, n0 = (r / p.tiles_m) * BN;
       if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, abort_flag, p.status, 4)) break;
       tcgen05_fence_after();
       const int row = m0 + quad * 32 + lane;
-      __nv_bfloat16 *crow = p.C + (long long)bi * p.c_batch + (long long)row * p.N + n0;
+      const long long out_off = (long long)sp * p.c_split + (long long)bi * p.c_batch;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
         tmem_ld_wait();
         if (row < p.M) {
+          const int col0 = n0 + c * 32;
+          if (p.epi == UGB_EPI_BF16) {
+            __nv_bfloat16 *crow = (__nv_bfloat16 *)p.C + out_off + (long long)row * p.N + col0;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int col = n0 + c * 32 + q * 8;
-            if (col < p.N) {                          // N % 8 == 0: a chunk of 8 is all in or all out
-              uint4 o;
-              __nv_bfloat162 t;
-              t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])); o.x = *(uint32_t *)&t;
-              t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])); o.y = *(uint32_t *)&t;
-              t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])); o.z = *(uint32_t *)&t;
-              t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7])); o.w = *(uint32_t *)&t;
-              *reinterpret_cast<uint4 *>(crow + c * 32 + q * 8) = o;
+            for (int q = 0; q < 4; ++q) {
+              if (col0 + q * 8 < p.N) {                // N % 8 == 0: a chunk of 8 is all in or all out
+                uint4 o;
+                __nv_bfloat162 t;
+                t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])); o.x = *(uint32_t *)&t;
+                t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])); o.y = *(uint32_t *)&t;
+                t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])); o.z = *(uint32_t *)&t;
+                t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7])); o.w = *(uint32_t *)&t;
+                *reinterpret_cast<uint4 *>(crow + q * 8) = o;
+              }
+            }
+          } else if (p.epi == UGB_EPI_F32) {
+            float *crow = (float *)p.C + out_off + (long long)row * p.N + col0;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              if (col0 + q * 4 < p.N)
+                *reinterpret_cast<uint4 *>(crow + q * 4) = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+          } else {
+            // UGB_EPI_SILU_MUL_BF16: columns come in (gate, up) pairs; out [M, N/2] bf16
+            __nv_bfloat16 *crow = (__nv_bfloat16 *)p.C + out_off + (long long)row * (p.N / 2) + col0 / 2;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              if (col0 + q * 16 < p.N) {
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float g0 = __uint_as_float(v[q * 16 + e * 4 + 0]), u0 = __uint_as_float(v[q * 16 + e * 4 + 1]);
+                  const float g1 = __uint_as_float(v[q * 16 + e * 4 + 2]), u1 = __uint_as_float(v[q * 16 + e * 4 + 3]);
+                  __nv_bfloat162 t = __floats2bfloat162_rn(g0 / (expf(-g0) + 1.0f) * u0, g1 / (expf(-g1) + 1.0f) * u1);
+                  o[e] = *(uint32_t *)&t;
+                }
+                *reinterpret_cast<uint4 *>(crow + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
             }
           }
         }
@@ -310,7 +361,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 
 struct TcState {
   EncodeTiledFn encode = nullptr;
-  bool attr_set = false;
+  bool attr_set[2] = {false, false};
 };
 
 TcState *state_of(ugb_device *dev) {
@@ -333,18 +384,69 @@ int32_t encode_map(ugb_device *dev, TcState *st, CUtensorMap *map, const void *b
   return UGB_OK;
 }
 
+template <int BN>
+int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_t batch, size_t m) {
+  const size_t n = g.n, k = g.k;
+  if (!st->attr_set[BN == 256]) {
+    UGB_CUDA(dev, cudaFuncSetAttribute(tc_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg<BN>::SMEM_BYTES));
+    st->attr_set[BN == 256] = true;
+  }
+  Params p;
+  p.M = (int)m; p.N = (int)n; p.K = (int)k; p.batch = (int)batch;
+  p.tiles_m = (int)((m + BM - 1) / BM);
+  p.tiles_n = (int)((n + BN - 1) / BN);
+  p.k_blocks = (int)((k + BK - 1) / BK);
+  int splits = g.splits < 1 ? 1 : g.splits;
+  if (splits > p.k_blocks) splits = p.k_blocks;
+  p.kb_per_split = (p.k_blocks + splits - 1) / splits;
+  p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;   // no empty split
+  p.b_batched = (batch > 1 && g.b_batch != 0) ? 1 : 0;
+  p.b_is_nk = g.b_is_nk ? 1 : 0;
+  p.epi = g.epi;
+  const long long out_cols = g.epi == UGB_EPI_SILU_MUL_BF16 ? (long long)n / 2 : (long long)n;
+  p.c_batch = (long long)m * out_cols;
+  p.c_split = (long long)batch * m * out_cols;
+  p.C = g.out;
+  p.status = dev->status_dev;
+
+  CUtensorMap tmA, tmB;
+  int32_t rc = encode_map(dev, st, &tmA, g.a, k, m, batch, k, batch > 1 ? (uint64_t)g.a_batch : m * k, BK, BM);
+  if (rc) return rc;
+  const uint64_t nb = p.b_batched ? batch : 1;
+  const uint64_t bs = p.b_batched ? (uint64_t)g.b_batch : n * k;
+  if (g.b_is_nk) rc = encode_map(dev, st, &tmB, g.b, k, n, nb, k, bs, BK, BN);
+  else rc = encode_map(dev, st, &tmB, g.b, n, k, nb, n, bs, 64, BK);
+  if (rc) return rc;
+
+  const long long n_tiles = (long long)p.tiles_m * p.tiles_n * p.batch * p.splits;
+  const unsigned grid = (unsigned)(n_tiles < dev->sm_count ? n_tiles : dev->sm_count);
+  tc_gemm_kernel<BN><<<grid, THREADS, Cfg<BN>::SMEM_BYTES, dev->stream>>>(tmA, tmB, p);
+  return ugb_after_launch(dev, "tc_gemm_kernel");
+}
+
 }  // namespace
 
-int32_t ugb_tc_gemm_bf16(ugb_device *dev, void *c, const void *a, const void *b_, size_t batch, size_t m,
-                         size_t n, size_t k, long long a_batch, long long b_batch, bool b_is_nk) {
+int ugb_tc_gemm_effective_splits(size_t k, int splits) {
+  const int k_blocks = (int)((k + BK - 1) / BK);
+  if (splits < 1) splits = 1;
+  if (splits > k_blocks) splits = k_blocks;
+  const int per = (k_blocks + splits - 1) / splits;
+  return (k_blocks + per - 1) / per;
+}
+
+int32_t ugb_tc_gemm(ugb_device *dev, const ugb_tc_gemm_args &g) {
+  size_t batch = g.batch, m = g.m;
+  const size_t n = g.n, k = g.k;
   // TMA: 16-byte aligned bases, row strides that are multiples of 16 bytes.
   if (k == 0 || k % 8 != 0 || n % 8 != 0) return UGB_ERR_UNSUPPORTED;
-  if (((uintptr_t)a | (uintptr_t)b_ | (uintptr_t)c) & 15) return UGB_ERR_UNSUPPORTED;
-  if ((a_batch % 8) != 0 || (b_batch % 8) != 0 || a_batch < 0 || b_batch < 0) return UGB_ERR_UNSUPPORTED;
-  if (batch > 1 && a_batch == 0) return UGB_ERR_UNSUPPORTED;
+  if (((uintptr_t)g.a | (uintptr_t)g.b | (uintptr_t)g.out) & 15) return UGB_ERR_UNSUPPORTED;
+  if ((g.a_batch % 8) != 0 || (g.b_batch % 8) != 0 || g.a_batch < 0 || g.b_batch < 0) return UGB_ERR_UNSUPPORTED;
+  if (batch > 1 && g.a_batch == 0) return UGB_ERR_UNSUPPORTED;
   if (m > (1u << 30) || n > (1u << 30) || k > (1u << 30) || batch > 65535) return UGB_ERR_UNSUPPORTED;
-  // Tiny products do not fill a 128 x 256 tile; the strided kernel handles them.
-  if (m * n < 128 * 64 || m < 16) return UGB_ERR_UNSUPPORTED;
+  if (g.epi == UGB_EPI_SILU_MUL_BF16 && n % 16 != 0) return UGB_ERR_UNSUPPORTED;
+  if (g.splits > 1 && g.epi != UGB_EPI_F32) return UGB_ERR_UNSUPPORTED;
+  if (m == 0 || n == 0) return UGB_ERR_UNSUPPORTED;
 
   TcState *st = state_of(dev);
   if (!st->encode) {
@@ -355,39 +457,25 @@ int32_t ugb_tc_gemm_bf16(ugb_device *dev, void *c, const void *a, const void *b_
       return ugb_fail(dev, UGB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
     st->encode = (EncodeTiledFn)fn;
   }
-  if (!st->attr_set) {
-    UGB_CUDA(dev, cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    st->attr_set = true;
-  }
   // A shared B with densely stacked A batches is one tall GEMM.
-  if (batch > 1 && b_batch == 0 && a_batch == (long long)(m * k)) {
+  if (batch > 1 && g.b_batch == 0 && g.a_batch == (long long)(m * k)) {
     m *= batch;
     batch = 1;
   }
-  Params p;
-  p.M = (int)m; p.N = (int)n; p.K = (int)k; p.batch = (int)batch;
-  p.tiles_m = (int)((m + BM - 1) / BM);
-  p.tiles_n = (int)((n + BN - 1) / BN);
-  p.k_blocks = (int)((k + BK - 1) / BK);
-  p.b_batched = (batch > 1 && b_batch != 0) ? 1 : 0;
-  p.b_is_nk = b_is_nk ? 1 : 0;
-  p.c_batch = (long long)(m * n);
-  p.C = (__nv_bfloat16 *)c;
-  p.status = dev->status_dev;
+  int bn = g.bn;
+  if (bn == 0) bn = (m <= 128) ? 64 : 256;
+  if (bn == 64) return launch_tc<64>(dev, st, g, batch, m);
+  return launch_tc<256>(dev, st, g, batch, m);
+}
 
-  CUtensorMap tmA, tmB;
-  int32_t rc = encode_map(dev, st, &tmA, a, k, m, batch, k, batch > 1 ? (uint64_t)a_batch : m * k, BK, BM);
-  if (rc) return rc;
-  const uint64_t nb = p.b_batched ? batch : 1;
-  const uint64_t bs = p.b_batched ? (uint64_t)b_batch : n * k;
-  if (b_is_nk) rc = encode_map(dev, st, &tmB, b_, k, n, nb, k, bs, BK, BN);
-  else rc = encode_map(dev, st, &tmB, b_, n, k, nb, n, bs, 64, BK);
-  if (rc) return rc;
-
-  const long long n_tiles = (long long)p.tiles_m * p.tiles_n * p.batch;
-  const unsigned grid = (unsigned)(n_tiles < dev->sm_count ? n_tiles : dev->sm_count);
-  tc_gemm_kernel<<<grid, THREADS, SMEM_BYTES, dev->stream>>>(tmA, tmB, p);
-  return ugb_after_launch(dev, "tc_gemm_kernel");
+int32_t ugb_tc_gemm_bf16(ugb_device *dev, void *c, const void *a, const void *b_, size_t batch, size_t m,
+                         size_t n, size_t k, long long a_batch, long long b_batch, bool b_is_nk) {
+  ugb_tc_gemm_args g;
+  g.out = c; g.a = a; g.b = b_;
+  g.batch = batch; g.m = m; g.n = n; g.k = k;
+  g.a_batch = a_batch; g.b_batch = b_batch; g.b_is_nk = b_is_nk;
+  g.epi = UGB_EPI_BF16; g.splits = 1; g.bn = 0;
+  return ugb_tc_gemm(dev, g);
 }
 
 void ugb_tc_state_free(ugb_device *dev) {

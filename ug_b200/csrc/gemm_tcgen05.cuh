@@ -2,12 +2,32 @@
 #pragma once
 #include "ugb_internal.h"
 
-// C[b, m, n] (bf16, row-major) = A[b, m, k] (bf16, row-major) x B, fp32
-// accumulation.  `b_is_nk`: B is [n, k] row-major (the matmul_t / weight
-// layout), otherwise [k, n] row-major.  Batch strides in elements (0 = shared
-// operand).  Returns UGB_ERR_UNSUPPORTED (without touching last_error) when
-// the shape does not meet the kernel's alignment rules so that the caller can
-// fall back to the strided kernel.
+// Epilogues applied to the fp32 accumulators.
+enum {
+  UGB_EPI_BF16 = 0,           // out bf16 [b, m, n]
+  UGB_EPI_F32 = 1,            // out f32 [splits, b, m, n]  (split-K partials when splits > 1)
+  UGB_EPI_SILU_MUL_BF16 = 2   // columns are (gate, up) pairs: out bf16 [b, m, n/2] = silu(gate) * up
+};
+
+struct ugb_tc_gemm_args {
+  void *out;
+  const void *a;        // bf16 [b, m, k] row-major
+  const void *b;        // bf16 [n, k] row-major when b_is_nk, else [k, n] row-major
+  size_t batch, m, n, k;
+  long long a_batch, b_batch;   // elements between batch steps (b_batch 0 = shared operand)
+  bool b_is_nk;
+  int epi;              // UGB_EPI_*
+  int splits;           // split-K factor (only with UGB_EPI_F32); the kernel may use fewer
+  int bn;               // tile width: 64, 256, or 0 = choose from m
+};
+
+// Returns UGB_ERR_UNSUPPORTED (without touching last_error) when the shape
+// does not meet the kernel's alignment rules so that the caller can fall back
+// to the strided kernel.
+int32_t ugb_tc_gemm(ugb_device *dev, const ugb_tc_gemm_args &args);
+// Number of partials ugb_tc_gemm writes for a requested split factor.
+int ugb_tc_gemm_effective_splits(size_t k, int splits);
+// C[b, m, n] bf16 = A . B with the default epilogue.
 int32_t ugb_tc_gemm_bf16(ugb_device *dev, void *c, const void *a, const void *b_, size_t batch,
                          size_t m, size_t n, size_t k, long long a_batch, long long b_batch,
                          bool b_is_nk);

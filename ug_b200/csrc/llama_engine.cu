@@ -1,0 +1,416 @@
+// Fused Llama decode engine: the Model::fwd call sites of ug-llama
+// (ug-llama/src/model.rs:298-374) for one new token per sequence, as a fixed
+// sequence of hand-written kernels captured in a CUDA graph.
+//
+// Per layer (model.rs:203-269), 8 launches:
+//   reduce_rmsnorm   residual += previous down-proj partials; rms1 -> bf16
+//   tcgen05 GEMM     fused q|k|v projection, split-K fp32 partials
+//   rope_append      sum partials, rope(q), rope(k), write k/v into the KV cache
+//   decode_attention grouped-query flash-decode over the cache (+ slice merge)
+//   tcgen05 GEMM     o_proj, split-K partials
+//   reduce_rmsnorm   residual += o_proj partials; rms2 -> bf16
+//   tcgen05 GEMM     gate|up projection (rows interleaved), epilogue silu(gate)*up -> bf16
+//   tcgen05 GEMM     down projection, split-K partials
+// then the final norm, the tied lm_head GEMM (fp32 logits) and a row argmax
+// that also advances the position.  Weights and the KV cache are bf16, the
+// residual stream and every reduction are fp32.  Batch rows are independent
+// sequences that share one position (the reference's pos[0] convention).
+//
+// HBM layout per model: weights [layer]{wqkv [(h+2kv)*d, hidden], wo [hidden,
+// hidden], wgu [2*ffn, hidden] (gate row j at 2j, up row j at 2j+1), wdown
+// [hidden, ffn]}, embedding [vocab, hidden]; KV cache K and V each
+// [layer][batch][kv_head][t_max][head_dim] bf16 (t_max rounded up to 16).
+#include <cmath>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "decode_kernels.cuh"
+#include "gemm_tcgen05.cuh"
+
+using namespace ugb_decode;
+
+struct LayerW {
+  __nv_bfloat16 *wqkv = nullptr, *wo = nullptr, *wgu = nullptr, *wdown = nullptr;
+  float *rms1 = nullptr, *rms2 = nullptr;
+};
+
+struct ugb_llama {
+  ugb_device *dev = nullptr;
+  ugb_llama_config cfg{};
+  int batch = 0, t_max = 0;       // t_max padded to a multiple of 16
+  int qkv_dim = 0;
+  std::vector<LayerW> layers;
+  __nv_bfloat16 *embed = nullptr;
+  float *ln_f = nullptr;
+  float *cos = nullptr, *sin = nullptr;
+  __nv_bfloat16 *kcache = nullptr, *vcache = nullptr;
+  size_t kv_layer_stride = 0;     // elements per layer of one cache
+  // activations / scratch
+  float *x = nullptr, *part = nullptr, *logits = nullptr;
+  __nv_bfloat16 *xn = nullptr, *q = nullptr, *att = nullptr, *h = nullptr;
+  float *att_po = nullptr, *att_pml = nullptr;
+  unsigned int *att_cnt = nullptr;
+  int *tok = nullptr, *next = nullptr, *pos = nullptr;
+  int host_pos = 0;
+  // tuning
+  int splits_qkv = 3, splits_o = 4, splits_down = 4, att_splits = 2;
+  size_t part_elems = 0;
+  // graph of one step that reads `next` as its input tokens
+  cudaGraphExec_t graph = nullptr;
+  int graph_nodes = 0;
+  bool warmed = false;
+  std::vector<void *> allocs;
+  size_t loaded = 0;
+};
+
+namespace {
+
+template <typename T>
+int32_t dmalloc(ugb_llama *m, T **p, size_t n, bool zero = false) {
+  ugb_device *dev = m->dev;
+  void *v = nullptr;
+  UGB_CUDA(dev, cudaMalloc(&v, n * sizeof(T) ? n * sizeof(T) : 16));
+  if (zero) UGB_CUDA(dev, cudaMemsetAsync(v, 0, n * sizeof(T), dev->stream));
+  m->allocs.push_back(v);
+  *p = (T *)v;
+  return UGB_OK;
+}
+
+__global__ void f32_to_bf16_kernel(const float *__restrict__ s, __nv_bfloat16 *__restrict__ d, size_t n,
+                                   size_t row_len, size_t dst_pitch) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    d[(i / row_len) * dst_pitch + i % row_len] = __float2bfloat16_rn(s[i]);
+}
+
+// Copies a [rows, cols] matrix (bf16, or f32 rounded to bf16) into `dst` with a
+// destination row pitch in elements (interleaving gate/up uses pitch 2*cols).
+int32_t put_matrix(ugb_llama *m, const ugb_slice *w, __nv_bfloat16 *dst, size_t rows, size_t cols,
+                   size_t dst_pitch, const char *name) {
+  ugb_device *dev = m->dev;
+  UGB_REQUIRE(dev, w->len == rows * cols, UGB_ERR_SHAPE, "unexpected shape for %s: %zu elements, expected (%zu, %zu)",
+              name, w->len, rows, cols);
+  if (w->dtype == UGB_BF16) {
+    UGB_CUDA(dev, cudaMemcpy2DAsync(dst, dst_pitch * 2, w->ptr, cols * 2, cols * 2, rows,
+                                    cudaMemcpyDeviceToDevice, dev->stream));
+  } else if (w->dtype == UGB_F32) {
+    f32_to_bf16_kernel<<<dev->sm_count * 8, 256, 0, dev->stream>>>((const float *)w->ptr, dst, rows * cols, cols, dst_pitch);
+    return ugb_after_launch(dev, "f32_to_bf16_kernel");
+  } else {
+    return ugb_fail(dev, UGB_ERR_DTYPE, "%s: weights must be BF16 or F32", name);
+  }
+  return UGB_OK;
+}
+
+int32_t put_vector(ugb_llama *m, const ugb_slice *w, float *dst, size_t n, const char *name) {
+  ugb_device *dev = m->dev;
+  UGB_REQUIRE(dev, w->len == n, UGB_ERR_SHAPE, "unexpected shape for %s: %zu elements, expected %zu", name, w->len, n);
+  UGB_REQUIRE(dev, w->dtype == UGB_F32, UGB_ERR_DTYPE, "%s: norm weights must be F32", name);
+  UGB_CUDA(dev, cudaMemcpyAsync(dst, w->ptr, n * 4, cudaMemcpyDeviceToDevice, dev->stream));
+  return UGB_OK;
+}
+
+int32_t gemm(ugb_llama *m, void *out, const __nv_bfloat16 *a, const __nv_bfloat16 *w, size_t n, size_t k,
+             int epi, int splits) {
+  ugb_tc_gemm_args g;
+  g.out = out; g.a = a; g.b = w;
+  g.batch = 1; g.m = (size_t)m->batch; g.n = n; g.k = k;
+  g.a_batch = 0; g.b_batch = 0; g.b_is_nk = true;
+  g.epi = epi; g.splits = splits; g.bn = 64;
+  int32_t rc = ugb_tc_gemm(m->dev, g);
+  if (rc == UGB_ERR_UNSUPPORTED)
+    return ugb_fail(m->dev, rc, "decode GEMM m=%d n=%zu k=%zu does not meet the tensor-core kernel's shape rules", m->batch, n, k);
+  return rc;
+}
+
+int32_t launch_reduce_rmsnorm(ugb_llama *m, const float *part, int n_part, const float *alpha) {
+  const int hidden = m->cfg.hidden;
+  const int nvec = hidden / 4;
+  const size_t stride = (size_t)m->batch * hidden;
+  const float inv_d = 1.0f / (float)hidden, eps = m->cfg.rms_eps;
+  dim3 grid(m->batch);
+  cudaStream_t st = m->dev->stream;
+  if (nvec <= 256) reduce_rmsnorm_kernel<1><<<grid, 256, 0, st>>>(m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
+  else if (nvec <= 512) reduce_rmsnorm_kernel<2><<<grid, 256, 0, st>>>(m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
+  else if (nvec <= 1024) reduce_rmsnorm_kernel<4><<<grid, 256, 0, st>>>(m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
+  else reduce_rmsnorm_kernel<8><<<grid, 256, 0, st>>>(m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
+  return ugb_after_launch(m->dev, "reduce_rmsnorm_kernel");
+}
+
+// Enqueues one decode step on the device stream; `tok` holds the input ids.
+int32_t enqueue_step(ugb_llama *m, const int *tok) {
+  ugb_device *dev = m->dev;
+  const ugb_llama_config &c = m->cfg;
+  cudaStream_t st = dev->stream;
+  const int B = m->batch, H = c.hidden;
+  int32_t rc;
+  embed_gather_kernel<<<B, 256, 0, st>>>(m->embed, tok, m->x, H, c.vocab, dev->status_dev);
+  if ((rc = ugb_after_launch(dev, "embed_gather_kernel"))) return rc;
+  const int s_qkv = ugb_tc_gemm_effective_splits(H, m->splits_qkv);
+  const int s_o = ugb_tc_gemm_effective_splits(H, m->splits_o);
+  const int s_down = ugb_tc_gemm_effective_splits(c.ffn, m->splits_down);
+  const float scale = powf((float)c.head_dim, -0.5f);   // model.rs:236
+  for (int l = 0; l < c.layers; ++l) {
+    const LayerW &w = m->layers[l];
+    if ((rc = launch_reduce_rmsnorm(m, m->part, l == 0 ? 0 : s_down, w.rms1))) return rc;
+    if ((rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv))) return rc;
+    __nv_bfloat16 *kc = m->kcache + (size_t)l * m->kv_layer_stride;
+    __nv_bfloat16 *vc = m->vcache + (size_t)l * m->kv_layer_stride;
+    rope_append_kernel<<<B, 256, 0, st>>>(m->part, s_qkv, (size_t)B * m->qkv_dim, m->cos, m->sin, m->pos, m->q, kc, vc,
+                                          c.n_heads, c.n_kv_heads, c.head_dim, m->t_max, c.rope_interleaved);
+    if ((rc = ugb_after_launch(dev, "rope_append_kernel"))) return rc;
+    dim3 agrid(m->att_splits, c.n_kv_heads, B);
+    decode_attention_kernel<<<agrid, ATT_WARPS * 32, ATT_RING_BYTES, st>>>(
+        m->q, kc, vc, m->pos, m->att_po, m->att_pml, m->att_cnt, m->att, c.n_heads, c.n_kv_heads,
+        c.n_heads / c.n_kv_heads, m->t_max, scale);
+    if ((rc = ugb_after_launch(dev, "decode_attention_kernel"))) return rc;
+    if ((rc = gemm(m, m->part, m->att, w.wo, H, H, UGB_EPI_F32, m->splits_o))) return rc;
+    if ((rc = launch_reduce_rmsnorm(m, m->part, s_o, w.rms2))) return rc;
+    if ((rc = gemm(m, m->h, m->xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1))) return rc;
+    if ((rc = gemm(m, m->part, m->h, w.wdown, H, c.ffn, UGB_EPI_F32, m->splits_down))) return rc;
+  }
+  if ((rc = launch_reduce_rmsnorm(m, m->part, s_down, m->ln_f))) return rc;
+  if ((rc = gemm(m, m->logits, m->xn, m->embed, c.vocab, H, UGB_EPI_F32, 1))) return rc;
+  argmax_rows_kernel<<<B, 256, 0, st>>>(m->logits, c.vocab, m->next, m->pos);
+  return ugb_after_launch(dev, "argmax_rows_kernel");
+}
+
+bool ends_with(const std::string &s, const char *suffix) {
+  const size_t n = strlen(suffix);
+  return s.size() >= n && s.compare(s.size() - n, n, suffix) == 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t ugb_llama_create(ugb_device *dev, const ugb_llama_config *cfg, int32_t batch, int32_t t_max,
+                         ugb_llama **out) {
+  if (!dev) return UGB_ERR_INVALID;
+  UGB_REQUIRE(dev, cfg && out, UGB_ERR_INVALID, "ugb_llama_create: null argument");
+  *out = nullptr;
+  const ugb_llama_config &c = *cfg;
+  UGB_REQUIRE(dev, c.hidden > 0 && c.layers > 0 && c.n_heads > 0 && c.n_kv_heads > 0 && c.ffn > 0 && c.vocab > 0,
+              UGB_ERR_INVALID, "ugb_llama_create: non-positive dimension");
+  UGB_REQUIRE(dev, c.head_dim == ATT_HD, UGB_ERR_UNSUPPORTED, "head_dim %d: the decode attention kernel is built for 64", c.head_dim);
+  UGB_REQUIRE(dev, c.n_heads * c.head_dim == c.hidden, UGB_ERR_SHAPE, "n_heads * head_dim != hidden");
+  UGB_REQUIRE(dev, c.n_heads % c.n_kv_heads == 0 && c.n_heads / c.n_kv_heads <= ATT_GROUP, UGB_ERR_UNSUPPORTED,
+              "query heads per KV head must divide evenly and be <= %d", ATT_GROUP);
+  UGB_REQUIRE(dev, c.hidden % 8 == 0 && c.hidden <= 8192 && c.ffn % 8 == 0 && c.vocab % 8 == 0, UGB_ERR_UNSUPPORTED,
+              "hidden, ffn and vocab must be multiples of 8 (hidden <= 8192)");
+  UGB_REQUIRE(dev, batch >= 16 && batch <= 128, UGB_ERR_UNSUPPORTED, "batch %d: the decode GEMMs take 16..128 sequences", batch);
+  UGB_REQUIRE(dev, t_max >= 1 && t_max <= c.max_pos, UGB_ERR_INVALID, "t_max %d outside 1..max_pos %d", t_max, c.max_pos);
+  UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
+
+  ugb_llama *m = new ugb_llama();
+  m->dev = dev;
+  m->cfg = c;
+  m->batch = batch;
+  m->t_max = (t_max + 15) / 16 * 16;
+  m->qkv_dim = (c.n_heads + 2 * c.n_kv_heads) * c.head_dim;
+  m->layers.resize(c.layers);
+  const size_t H = c.hidden, F = c.ffn, B = batch;
+  int32_t rc = UGB_OK;
+#define TRY(e) do { if ((rc = (e)) != UGB_OK) { ugb_llama_destroy(m); return rc; } } while (0)
+  for (auto &w : m->layers) {
+    TRY(dmalloc(m, &w.wqkv, (size_t)m->qkv_dim * H));
+    TRY(dmalloc(m, &w.wo, H * H));
+    TRY(dmalloc(m, &w.wgu, 2 * F * H));
+    TRY(dmalloc(m, &w.wdown, H * F));
+    TRY(dmalloc(m, &w.rms1, H));
+    TRY(dmalloc(m, &w.rms2, H));
+  }
+  TRY(dmalloc(m, &m->embed, (size_t)c.vocab * H));
+  TRY(dmalloc(m, &m->ln_f, H));
+  const size_t half = c.head_dim / 2;
+  TRY(dmalloc(m, &m->cos, (size_t)c.max_pos * half));
+  TRY(dmalloc(m, &m->sin, (size_t)c.max_pos * half));
+  m->kv_layer_stride = B * c.n_kv_heads * (size_t)m->t_max * c.head_dim;
+  TRY(dmalloc(m, &m->kcache, m->kv_layer_stride * c.layers, true));
+  TRY(dmalloc(m, &m->vcache, m->kv_layer_stride * c.layers, true));
+  TRY(dmalloc(m, &m->x, B * H));
+  TRY(dmalloc(m, &m->xn, B * H));
+  TRY(dmalloc(m, &m->q, B * H));
+  TRY(dmalloc(m, &m->att, B * H));
+  TRY(dmalloc(m, &m->h, B * F));
+  const size_t widest = std::max<size_t>(m->qkv_dim, H);
+  m->part_elems = 8 * B * widest;    // up to 8 split-K partials
+  TRY(dmalloc(m, &m->part, m->part_elems));
+  TRY(dmalloc(m, &m->logits, B * c.vocab));
+  const size_t slots = B * c.n_kv_heads * 8;   // up to 8 attention slices
+  TRY(dmalloc(m, &m->att_po, slots * ATT_GROUP * ATT_HD));
+  TRY(dmalloc(m, &m->att_pml, slots * ATT_GROUP * 2));
+  TRY(dmalloc(m, &m->att_cnt, B * c.n_kv_heads, true));
+  TRY(dmalloc(m, &m->tok, B, true));
+  TRY(dmalloc(m, &m->next, B, true));
+  TRY(dmalloc(m, &m->pos, 1, true));
+  // rope tables, model.rs:278-295: theta_i = 1 / theta^(i/d) in f32 on the host
+  {
+    std::vector<float> inv(half);
+    for (size_t i = 0; i < half; ++i) inv[i] = 1.0f / powf(c.rope_theta, (float)(2 * i) / (float)c.head_dim);
+    float *inv_d = nullptr;
+    TRY(dmalloc(m, &inv_d, half));
+    if (cudaMemcpyAsync(inv_d, inv.data(), half * 4, cudaMemcpyHostToDevice, dev->stream) != cudaSuccess ||
+        cudaStreamSynchronize(dev->stream) != cudaSuccess) {
+      ugb_fail(dev, UGB_ERR_CUDA, "rope table upload failed");
+      ugb_llama_destroy(m);
+      return UGB_ERR_CUDA;
+    }
+    const int n = c.max_pos * (int)half;
+    rope_table_kernel<<<(n + 255) / 256, 256, 0, dev->stream>>>(inv_d, m->cos, m->sin, c.max_pos, (int)half);
+    TRY(ugb_after_launch(dev, "rope_table_kernel"));
+  }
+  if (cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_RING_BYTES) != cudaSuccess) {
+    ugb_fail(dev, UGB_ERR_CUDA, "cudaFuncSetAttribute(decode_attention_kernel) failed");
+    ugb_llama_destroy(m);
+    return UGB_ERR_CUDA;
+  }
+#undef TRY
+  *out = m;
+  return UGB_OK;
+}
+
+int32_t ugb_llama_destroy(ugb_llama *m) {
+  if (!m) return UGB_ERR_INVALID;
+  cudaSetDevice(m->dev->ordinal);
+  cudaStreamSynchronize(m->dev->stream);
+  if (m->graph) cudaGraphExecDestroy(m->graph);
+  for (void *p : m->allocs) cudaFree(p);
+  delete m;
+  return UGB_OK;
+}
+
+int32_t ugb_llama_load_weight(ugb_llama *m, const char *name, const ugb_slice *w) {
+  if (!m) return UGB_ERR_INVALID;
+  ugb_device *dev = m->dev;
+  UGB_REQUIRE(dev, name && w, UGB_ERR_INVALID, "ugb_llama_load_weight: null argument");
+  UGB_REQUIRE(dev, w->dev == dev, UGB_ERR_INVALID, "%s: slice belongs to another device", name);
+  const ugb_llama_config &c = m->cfg;
+  const size_t H = c.hidden, F = c.ffn, KV = (size_t)c.n_kv_heads * c.head_dim;
+  const std::string s(name);
+  m->loaded++;
+  if (s == "model.embed_tokens.weight") return put_matrix(m, w, m->embed, c.vocab, H, H, name);
+  if (s == "model.norm.weight") return put_vector(m, w, m->ln_f, H, name);
+  const std::string pre = "model.layers.";
+  if (s.compare(0, pre.size(), pre) == 0) {
+    const size_t dot = s.find('.', pre.size());
+    if (dot != std::string::npos) {
+      const int l = atoi(s.substr(pre.size(), dot - pre.size()).c_str());
+      UGB_REQUIRE(dev, l >= 0 && l < c.layers, UGB_ERR_INVALID, "%s: layer index out of range", name);
+      LayerW &L = m->layers[l];
+      if (ends_with(s, ".input_layernorm.weight")) return put_vector(m, w, L.rms1, H, name);
+      if (ends_with(s, ".post_attention_layernorm.weight")) return put_vector(m, w, L.rms2, H, name);
+      if (ends_with(s, ".self_attn.q_proj.weight")) return put_matrix(m, w, L.wqkv, H, H, H, name);
+      if (ends_with(s, ".self_attn.k_proj.weight")) return put_matrix(m, w, L.wqkv + H * H, KV, H, H, name);
+      if (ends_with(s, ".self_attn.v_proj.weight")) return put_matrix(m, w, L.wqkv + (H + KV) * H, KV, H, H, name);
+      if (ends_with(s, ".self_attn.o_proj.weight")) return put_matrix(m, w, L.wo, H, H, H, name);
+      if (ends_with(s, ".mlp.gate_proj.weight")) return put_matrix(m, w, L.wgu, F, H, 2 * H, name);
+      if (ends_with(s, ".mlp.up_proj.weight")) return put_matrix(m, w, L.wgu + H, F, H, 2 * H, name);
+      if (ends_with(s, ".mlp.down_proj.weight")) return put_matrix(m, w, L.wdown, H, F, F, name);
+    }
+  }
+  m->loaded--;
+  return ugb_fail(dev, UGB_ERR_INVALID, "unknown weight name %s", name);
+}
+
+int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
+  if (!m || !key) return UGB_ERR_INVALID;
+  ugb_device *dev = m->dev;
+  const std::string k(key);
+  UGB_REQUIRE(dev, value >= 1 && value <= 8, UGB_ERR_INVALID, "option %s: value %d outside 1..8", key, value);
+  if (k == "splits_qkv") m->splits_qkv = value;
+  else if (k == "splits_o") m->splits_o = value;
+  else if (k == "splits_down") m->splits_down = value;
+  else if (k == "att_splits") m->att_splits = value;
+  else return ugb_fail(dev, UGB_ERR_INVALID, "unknown option %s", key);
+  if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+  return UGB_OK;
+}
+
+int32_t ugb_llama_reset(ugb_llama *m, int32_t pos) {
+  if (!m) return UGB_ERR_INVALID;
+  ugb_device *dev = m->dev;
+  UGB_REQUIRE(dev, pos >= 0 && pos < m->t_max, UGB_ERR_INVALID, "reset position %d outside 0..%d", pos, m->t_max - 1);
+  UGB_CUDA(dev, cudaMemcpyAsync(m->pos, &pos, 4, cudaMemcpyHostToDevice, dev->stream));
+  UGB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  m->host_pos = pos;
+  return UGB_OK;
+}
+
+int32_t ugb_llama_position(const ugb_llama *m) { return m ? m->host_pos : -1; }
+
+int32_t ugb_llama_decode(ugb_llama *m, const ugb_slice *tokens, int32_t n_steps) {
+  if (!m) return UGB_ERR_INVALID;
+  ugb_device *dev = m->dev;
+  UGB_REQUIRE(dev, n_steps >= 1, UGB_ERR_INVALID, "n_steps must be >= 1");
+  UGB_REQUIRE(dev, tokens == nullptr || n_steps == 1, UGB_ERR_INVALID, "explicit tokens feed exactly one step");
+  UGB_REQUIRE(dev, m->host_pos + n_steps <= m->t_max && m->host_pos + n_steps <= m->cfg.max_pos, UGB_ERR_SHAPE,
+              "decode of %d steps from position %d exceeds the KV cache (%d positions)", n_steps, m->host_pos, m->t_max);
+  UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
+  if (tokens) {
+    UGB_SLICE(dev, tokens, UGB_I32, (size_t)m->batch);
+    UGB_CUDA(dev, cudaMemcpyAsync(m->next, tokens->ptr, (size_t)m->batch * 4, cudaMemcpyDeviceToDevice, dev->stream));
+  }
+  int32_t rc;
+  for (int s = 0; s < n_steps; ++s) {
+    if (!m->warmed) {
+      // first step runs eagerly: it sets kernel attributes, which must not happen inside a capture
+      if ((rc = enqueue_step(m, m->next))) return rc;
+      m->warmed = true;
+    } else {
+      if (!m->graph) {
+        cudaGraph_t g = nullptr;
+        const uint64_t before = dev->launches;
+        UGB_CUDA(dev, cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal));
+        rc = enqueue_step(m, m->next);
+        cudaError_t e = cudaStreamEndCapture(dev->stream, &g);
+        m->graph_nodes = (int)(dev->launches - before);
+        dev->launches = before;
+        if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+        if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "stream capture failed: %s", cudaGetErrorString(e));
+        e = cudaGraphInstantiate(&m->graph, g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+      }
+      UGB_CUDA(dev, cudaGraphLaunch(m->graph, dev->stream));
+      dev->launches += (uint64_t)m->graph_nodes;
+    }
+    m->host_pos++;
+  }
+  return UGB_OK;
+}
+
+int32_t ugb_llama_read(ugb_llama *m, int32_t what, void *host_dst, size_t len) {
+  if (!m) return UGB_ERR_INVALID;
+  ugb_device *dev = m->dev;
+  UGB_REQUIRE(dev, host_dst != nullptr, UGB_ERR_INVALID, "ugb_llama_read: null destination");
+  const void *src = nullptr;
+  size_t n = 0, es = 4;
+  switch (what) {
+    case UGB_LLAMA_LOGITS: src = m->logits; n = (size_t)m->batch * m->cfg.vocab; break;
+    case UGB_LLAMA_NEXT_TOKENS: src = m->next; n = (size_t)m->batch; break;
+    case UGB_LLAMA_HIDDEN: src = m->x; n = (size_t)m->batch * m->cfg.hidden; break;
+    default: return ugb_fail(dev, UGB_ERR_INVALID, "ugb_llama_read: unknown selector %d", what);
+  }
+  UGB_REQUIRE(dev, len == n, UGB_ERR_SHAPE, "ugb_llama_read: destination holds %zu elements, %zu expected", len, n);
+  UGB_CUDA(dev, cudaMemcpyAsync(host_dst, src, n * es, cudaMemcpyDeviceToHost, dev->stream));
+  UGB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  return UGB_OK;
+}
+
+int32_t ugb_llama_read_kv(ugb_llama *m, int32_t layer, int32_t which, void *host_dst, size_t len) {
+  if (!m) return UGB_ERR_INVALID;
+  ugb_device *dev = m->dev;
+  UGB_REQUIRE(dev, layer >= 0 && layer < m->cfg.layers && (which == 0 || which == 1) && host_dst, UGB_ERR_INVALID,
+              "ugb_llama_read_kv: bad argument");
+  UGB_REQUIRE(dev, len == m->kv_layer_stride, UGB_ERR_SHAPE, "ugb_llama_read_kv: destination holds %zu elements, %zu expected",
+              len, m->kv_layer_stride);
+  const __nv_bfloat16 *src = (which == 0 ? m->kcache : m->vcache) + (size_t)layer * m->kv_layer_stride;
+  UGB_CUDA(dev, cudaMemcpyAsync(host_dst, src, len * 2, cudaMemcpyDeviceToHost, dev->stream));
+  UGB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  return UGB_OK;
+}
+
+int32_t ugb_llama_kv_positions(const ugb_llama *m) { return m ? m->t_max : -1; }
+
+}  // extern "C"

@@ -177,7 +177,8 @@ int32_t ugb_matmul(ugb_device *dev, ugb_slice *dst, const ugb_slice *lhs, const 
   const char *lp = (const char *)lhs->ptr + lhs_off * es;
   const char *rp = (const char *)rhs->ptr + rhs_off * es;
 
-  if (dt == UGB_BF16 && !L.transposed) {
+  // Tiny products do not fill a 128-row tensor-core tile; the strided kernel handles them.
+  if (dt == UGB_BF16 && !L.transposed && m >= 16 && m * n >= 128 * 64) {
     // tensor-core path: A [m,k] row-major, B either [n,k] row-major ("TN",
     // matmul_t with a weight) or [k,n] row-major ("NN").
     int32_t trc = ugb_tc_gemm_bf16(dev, dst->ptr, lp, rp, b, m, n, k, L.batch, R.batch, R.transposed);

@@ -1,0 +1,153 @@
+"""Host-side mirror of ug-llama's model API over the fused decode engine.
+
+``Config`` and ``Model`` follow ug-llama/src/model.rs:10-30,298-374: the same
+field names, the same safetensors weight names, ``Model.new`` / ``Model.fwd``.
+``fwd`` covers seq_len == 1 (one new token per sequence); the KV cache that the
+reference threads through ``fwd`` as ``&mut [Cache]`` lives inside the engine.
+"""
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from ._lib import lib
+from .device import DType, UgError
+
+
+@dataclass
+class Config:
+    """ug_llama::model::Config (ug-llama/src/model.rs:10-24)."""
+    hidden_size: int
+    intermediate_size: int
+    max_position_embeddings: int
+    num_attention_heads: int
+    num_key_value_heads: int
+    num_hidden_layers: int
+    vocab_size: int
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    rope_interleaved: bool = False
+    tie_word_embeddings: bool = True
+
+    def head_dim(self):
+        return self.hidden_size // self.num_attention_heads
+
+    @staticmethod
+    def llama_1b():
+        """The Llama-1.1B shape of the benchmark configuration."""
+        return Config(hidden_size=2048, intermediate_size=5632, max_position_embeddings=4096,
+                      num_attention_heads=32, num_key_value_heads=4, num_hidden_layers=22,
+                      vocab_size=32000)
+
+
+class _CConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("hidden", "layers", "n_heads", "n_kv_heads", "head_dim", "ffn",
+                                          "vocab", "max_pos")] + \
+               [("rope_theta", C.c_float), ("rms_eps", C.c_float), ("rope_interleaved", C.c_int32)]
+
+
+def weight_names(cfg):
+    """Tensor names in the order Model::new loads them (model.rs:313-346)."""
+    names = ["model.embed_tokens.weight", "model.norm.weight"]
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}"
+        names += [f"{p}.input_layernorm.weight", f"{p}.post_attention_layernorm.weight",
+                  f"{p}.mlp.gate_proj.weight", f"{p}.mlp.up_proj.weight", f"{p}.mlp.down_proj.weight",
+                  f"{p}.self_attn.q_proj.weight", f"{p}.self_attn.k_proj.weight",
+                  f"{p}.self_attn.v_proj.weight", f"{p}.self_attn.o_proj.weight"]
+    return names
+
+
+def weight_shape(cfg, name):
+    h, f, kv = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim() * cfg.num_key_value_heads
+    if name == "model.embed_tokens.weight":
+        return (cfg.vocab_size, h)
+    if name.endswith("norm.weight"):
+        return (h,)
+    tail = name.split(".")[-2]
+    return {"q_proj": (h, h), "k_proj": (kv, h), "v_proj": (kv, h), "o_proj": (h, h),
+            "gate_proj": (f, h), "up_proj": (f, h), "down_proj": (h, f)}[tail]
+
+
+class Model:
+    """Model::new / Model::fwd for seq_len == 1 over ``batch`` independent sequences."""
+
+    def __init__(self, cfg, dev, batch, t_max):
+        if not cfg.tie_word_embeddings:
+            raise UgError(6, "tie_word_embeddings == false is not supported yet")   # model.rs:318
+        self.cfg, self.dev, self.batch = cfg, dev, batch
+        cc = _CConfig(cfg.hidden_size, cfg.num_hidden_layers, cfg.num_attention_heads,
+                      cfg.num_key_value_heads, cfg.head_dim(), cfg.intermediate_size, cfg.vocab_size,
+                      cfg.max_position_embeddings, cfg.rope_theta, cfg.rms_norm_eps,
+                      int(cfg.rope_interleaved))
+        h = C.c_void_p()
+        dev._check(lib.ugb_llama_create(dev._h, C.byref(cc), batch, t_max, C.byref(h)))
+        self._h = h
+
+    @classmethod
+    def new(cls, cfg, weights, dev, batch, t_max):
+        """``weights``: name -> host array; uint16 arrays are bf16 bit patterns, float32 arrays
+        are norm weights (or matrices to be rounded to bf16 on the device)."""
+        m = cls(cfg, dev, batch, t_max)
+        for name in weight_names(cfg):
+            m.load_weight(name, weights[name])
+        return m
+
+    def load_weight(self, name, arr):
+        arr = np.ascontiguousarray(arr)
+        s = self.dev.slice_from_values(arr.ravel(), bf16=(arr.dtype == np.uint16))
+        self.dev._check(lib.ugb_llama_load_weight(self._h, name.encode(), s._h))
+        self.dev.synchronize()
+
+    def close(self):
+        h, self._h = self._h, None
+        if h:
+            lib.ugb_llama_destroy(h)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_option(self, key, value):
+        self.dev._check(lib.ugb_llama_set_option(self._h, key.encode(), value))
+
+    def reset(self, pos=0):
+        self.dev._check(lib.ugb_llama_reset(self._h, pos))
+
+    @property
+    def position(self):
+        return lib.ugb_llama_position(self._h)
+
+    def fwd(self, tokens):
+        """One step on explicit token ids (int32 [batch] or [batch, 1]); asynchronous."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32).reshape(-1)
+        s = self.dev.slice_from_values(tokens)
+        self.dev._check(lib.ugb_llama_decode(self._h, s._h, 1))
+
+    def decode(self, n_steps):
+        """Greedy decoding: each step feeds the previous step's argmax; asynchronous."""
+        self.dev._check(lib.ugb_llama_decode(self._h, None, n_steps))
+
+    def logits(self):
+        out = np.empty((self.batch, self.cfg.vocab_size), np.float32)
+        self.dev._check(lib.ugb_llama_read(self._h, 0, out.ctypes.data, out.size))
+        return out
+
+    def next_tokens(self):
+        out = np.empty(self.batch, np.int32)
+        self.dev._check(lib.ugb_llama_read(self._h, 1, out.ctypes.data, out.size))
+        return out
+
+    def hidden(self):
+        out = np.empty((self.batch, self.cfg.hidden_size), np.float32)
+        self.dev._check(lib.ugb_llama_read(self._h, 2, out.ctypes.data, out.size))
+        return out
+
+    def kv_cache(self, layer, which):
+        """bf16 bit patterns [batch, n_kv_heads, kv_positions, head_dim] of K (0) or V (1)."""
+        t = lib.ugb_llama_kv_positions(self._h)
+        out = np.empty((self.batch, self.cfg.num_key_value_heads, t, self.cfg.head_dim()), np.uint16)
+        self.dev._check(lib.ugb_llama_read_kv(self._h, layer, which, out.ctypes.data, out.size))
+        return out

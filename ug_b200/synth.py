@@ -49,3 +49,23 @@ def rms_silu_c2(n_rows=8192, n_cols=4096):
     """Config 2: x, gate ~ N(0,1) seeds 1,2; w ~ U(0.5,1.5) seed 3; eps 1e-5."""
     return (normal(1, (n_rows, n_cols)), normal(2, (n_rows, n_cols)),
             uniform(3, (n_cols,), 0.5, 1.5), 1e-5)
+
+
+def llama_weights(cfg, seed_base=100):
+    """Random-init weights of a Llama-shaped model: every matrix ~ N(0, 0.02) rounded to bf16
+    (returned as uint16 bit patterns), seed = seed_base + index of the tensor in load order;
+    norm weights are ones (f32), the usual initialisation."""
+    from .llama import weight_names, weight_shape
+    out = {}
+    for i, name in enumerate(weight_names(cfg)):
+        shape = weight_shape(cfg, name)
+        if len(shape) == 1:
+            out[name] = np.ones(shape, np.float32)
+        else:
+            out[name] = to_bf16_bits(normal(seed_base + i, shape, 0.02))
+    return out
+
+
+def llama_weights_f32(weights):
+    """The f32 view of bf16 weights that load_with_cast BF16 -> F32 produces."""
+    return {k: (bf16_bits_to_f32(v) if v.dtype == np.uint16 else v) for k, v in weights.items()}
