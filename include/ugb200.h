@@ -188,6 +188,21 @@ UGB_API int32_t ugb_index_select(ugb_device *dev, const ugb_slice *emb, const ug
                          ugb_slice *dst, size_t n_ids, size_t h, size_t vocab);
 
 
+/* Grouped-query attention for ONE new query position per sequence: the fused
+ * form of repeat + q.kT + scale (head_dim^-0.5) + softmax + .v + transpose/merge
+ * of Attention::fwd (ug-llama/src/model.rs:231-245) over a preallocated bf16 KV
+ * cache.  q bf16 [b, n_heads, 64]; k, v bf16 [b, n_kv, t_max, 64] of which the
+ * first pos[0] + 1 positions are attended (pos I32 [1], read on the device);
+ * out bf16 [b, n_heads * 64].  head_dim is 64, n_heads / n_kv <= 8, t_max a
+ * multiple of 16, n_slices (1..8) KV slices per (sequence, KV head) run as
+ * separate CTAs.  Cache rows at positions > pos[0] must hold finite values.
+ * Scratch for the per-slice partial results comes from the device's
+ * stream-ordered pool for the duration of the call. */
+UGB_API int32_t ugb_decode_attention(ugb_device *dev, const ugb_slice *q, const ugb_slice *k,
+                                     const ugb_slice *v, const ugb_slice *pos, ugb_slice *out,
+                                     size_t b, size_t n_heads, size_t n_kv, size_t t_max,
+                                     int32_t n_slices);
+
 /* ------------------------------------------- ug-llama Model::fwd (decode step) */
 /* The reference builds one lazy graph per token from Model::fwd
  * (ug-llama/src/model.rs:298-374) and runs ~27 launches per layer; this entry

@@ -25,7 +25,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 // x[b, :] = float(embed[tok[b], :]).  One CTA per row; ids outside the table
 // raise the status word and leave the row untouched.
-__global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(256)
 embed_gather_kernel(const __nv_bfloat16 *__restrict__ embed, const int *__restrict__ tok,
                     float *__restrict__ x, int hidden, int vocab, ugb_status_word *status) {
   const int b = blockIdx.x;
@@ -100,7 +100,7 @@ reduce_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ part, int
 // pos is read from device memory (every sequence of the batch sits at the same
 // position, the reference's pos[0] convention, cpu_ops.rs:67-71).  One CTA per
 // sequence, one thread per rotation pair.
-__global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(256)
 rope_append_kernel(const float *__restrict__ part, int n_part, size_t part_stride,
                    const float *__restrict__ cos_, const float *__restrict__ sin_,
                    const int *__restrict__ pos_p, __nv_bfloat16 *__restrict__ q_out,
@@ -178,7 +178,7 @@ constexpr int ATT_RING_BYTES = ATT_WARPS * ATT_STAGES * 2 * ATT_SUB_BYTES;   // 
 // K frags use a permuted k index (dims 16t+4s.. for lane t, step s) so that a
 // lane's operands are two contiguous 16-byte pieces of a row; Q uses the same
 // permutation.  V frags come from ldmatrix.trans on the staged sub-tile.
-__global__ void __launch_bounds__(ATT_WARPS * 32)
+static __global__ void __launch_bounds__(ATT_WARPS * 32)
 decode_attention_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restrict__ kcache,
                         const __nv_bfloat16 *__restrict__ vcache, const int *__restrict__ pos_p,
                         float *__restrict__ part_o, float *__restrict__ part_ml,
@@ -370,7 +370,7 @@ decode_attention_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16
 
 // next[b] = argmax_j logits[b, j] (ties -> lowest index); thread 0 of CTA 0 also
 // advances the shared position counter.  One CTA of 256 threads per row.
-__global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(256)
 argmax_rows_kernel(const float *__restrict__ logits, int vocab, int *__restrict__ next, int *pos_p) {
   __shared__ float sv[8];
   __shared__ int si[8];
@@ -408,7 +408,7 @@ argmax_rows_kernel(const float *__restrict__ logits, int vocab, int *__restrict_
 
 // cos/sin tables [max_pos, hd/2]: angle = float(pos) * inv_freq[i] as one f32
 // product (the [max,1].[1,d/2] matmul of model.rs:291), then precise cosf/sinf.
-__global__ void rope_table_kernel(const float *__restrict__ inv_freq, float *__restrict__ cos_,
+static __global__ void rope_table_kernel(const float *__restrict__ inv_freq, float *__restrict__ cos_,
                                   float *__restrict__ sin_, int max_pos, int half) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= max_pos * half) return;
