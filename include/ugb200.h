@@ -203,6 +203,30 @@ UGB_API int32_t ugb_decode_attention(ugb_device *dev, const ugb_slice *q, const 
                                      size_t b, size_t n_heads, size_t n_kv, size_t t_max,
                                      int32_t n_slices);
 
+/* ugb_decode_attention for callers that cannot allocate device memory.  It has
+ * no counterpart in the reference.  Some hosts of this library give every byte
+ * of the GPU to their own pool when they start (an inference server with a
+ * pre-sized KV arena, a framework's caching allocator), so a driver allocation
+ * made later fails or fragments their arena; others call from a
+ * latency-critical thread where an allocator call may take a lock or
+ * synchronise the device.  This variant takes its scratch (per-slice partial
+ * results and completion counters) from a fixed array inside the library
+ * instead: it calls no cudaMalloc / cudaFree and no allocating routine.
+ * Arguments, results and errors are those of ugb_decode_attention, plus:
+ *  - limit: b * n_kv * n_slices <= 2048, otherwise UGB_ERR_SHAPE (the array is
+ *    about 4.1 MiB and every GPU that loads the library holds it until exit);
+ *  - the first call on each device looks the array's device address up
+ *    (one-time set-up); make that call before starting any stream capture;
+ *  - all calls on a device share the one array, which keeps the previous
+ *    call's contents; each call clears the counters it needs.  Two calls that
+ *    overlap on the GPU (different streams or device handles of one GPU) race
+ *    on it: serialise them. */
+UGB_API int32_t ugb_decode_attention_noalloc(ugb_device *dev, const ugb_slice *q,
+                                             const ugb_slice *k, const ugb_slice *v,
+                                             const ugb_slice *pos, ugb_slice *out, size_t b,
+                                             size_t n_heads, size_t n_kv, size_t t_max,
+                                             int32_t n_slices);
+
 /* ------------------------------------------- ug-llama Model::fwd (decode step) */
 /* The reference builds one lazy graph per token from Model::fwd
  * (ug-llama/src/model.rs:298-374) and runs ~27 launches per layer; this entry

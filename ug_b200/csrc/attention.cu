@@ -44,9 +44,55 @@ int32_t launch_attention(ugb_device *dev, const ugb_slice *q, const ugb_slice *k
   return ugb_after_launch(dev, "decode_attention_kernel");
 }
 
+// ---- fixed scratch for callers that must not allocate ----------------------
+// Room for NOALLOC_MAX_SLOTS (sequence, KV head, slice) partial results and as
+// many completion counters.  Every GPU that loads this library carries the
+// array (about 4.1 MiB) until the process exits.
+constexpr size_t NOALLOC_MAX_SLOTS = 2048;
+constexpr size_t NOALLOC_O_BYTES = NOALLOC_MAX_SLOTS * ATT_GROUP * ATT_HD * sizeof(float);
+constexpr size_t NOALLOC_ML_BYTES = NOALLOC_MAX_SLOTS * ATT_GROUP * 2 * sizeof(float);
+constexpr size_t NOALLOC_CNT_BYTES = NOALLOC_MAX_SLOTS * sizeof(unsigned int);
+static __device__ __align__(256) unsigned char g_att_scratch[NOALLOC_O_BYTES + NOALLOC_ML_BYTES + NOALLOC_CNT_BYTES];
+
+// DEVICE address of g_att_scratch on each device ordinal.  In host code the
+// name g_att_scratch is only a handle for the runtime, never a pointer a
+// kernel may be given: the address has to be asked for, per device.
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static unsigned char *g_att_scratch_addr[NOALLOC_MAX_DEVICES] = {};
+
 }  // namespace
 
 extern "C" {
+
+int32_t ugb_decode_attention_noalloc(ugb_device *dev, const ugb_slice *q, const ugb_slice *k,
+                                     const ugb_slice *v, const ugb_slice *pos, ugb_slice *out, size_t b,
+                                     size_t n_heads, size_t n_kv, size_t t_max, int32_t n_slices) {
+  if (!dev) return UGB_ERR_INVALID;
+  int32_t rc = check_attention_args(dev, q, k, v, pos, out, b, n_heads, n_kv, t_max, n_slices);
+  if (rc) return rc;
+  const size_t slots = b * n_kv * (size_t)n_slices;
+  UGB_REQUIRE(dev, slots <= NOALLOC_MAX_SLOTS, UGB_ERR_SHAPE,
+              "decode_attention_noalloc: batch * n_kv * n_slices = %zu exceeds the fixed scratch of %zu slots; "
+              "use fewer slices or ugb_decode_attention", slots, NOALLOC_MAX_SLOTS);
+  UGB_REQUIRE(dev, dev->ordinal >= 0 && dev->ordinal < NOALLOC_MAX_DEVICES, UGB_ERR_UNSUPPORTED,
+              "decode_attention_noalloc: device ordinal %d beyond %d", dev->ordinal, NOALLOC_MAX_DEVICES);
+  if (b == 0) return UGB_OK;
+  UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
+  if (!g_att_scratch_addr[dev->ordinal]) {
+    // one-time set-up on this device (it is the current device here)
+    void *p = nullptr;
+    UGB_CUDA(dev, cudaGetSymbolAddress(&p, g_att_scratch));
+    g_att_scratch_addr[dev->ordinal] = (unsigned char *)p;
+  }
+  unsigned char *base = g_att_scratch_addr[dev->ordinal];
+  float *part_o = (float *)base;
+  float *part_ml = (float *)(base + NOALLOC_O_BYTES);
+  unsigned int *counters = (unsigned int *)(base + NOALLOC_O_BYTES + NOALLOC_ML_BYTES);
+  // The array keeps whatever the previous call left: the counters must start at
+  // zero (the partial results are fully rewritten before they are read).
+  UGB_CUDA(dev, cudaMemsetAsync(counters, 0, b * n_kv * sizeof(unsigned int), dev->stream));
+  return launch_attention(dev, q, k, v, pos, out, b, n_heads, n_kv, t_max, n_slices, part_o, part_ml, counters);
+}
 
 int32_t ugb_decode_attention(ugb_device *dev, const ugb_slice *q, const ugb_slice *k, const ugb_slice *v,
                              const ugb_slice *pos, ugb_slice *out, size_t b, size_t n_heads, size_t n_kv,
