@@ -128,8 +128,8 @@ class RmsSiluWorkload:
     def step(self):
         self.dev.rms_norm_silu_gate(self.xs, self.ws, self.gs, self.out, self.rows, self.cols, self.eps)
 
-    def units(self, seconds, n_ranks):
-        return n_ranks * self.bytes_per_step / seconds / 1e9
+    def units(self, step_seconds, n_ranks):
+        return n_ranks * self.bytes_per_step / step_seconds / 1e9
 
     def setup_e2e(self):
         import ctypes as C
@@ -292,8 +292,8 @@ class GemmWorkload:
         self.dev.matmul(self.c_s[j], self.a_s[j], self.b_s, (self.bs, self.m, self.n, self.k),
                         self.lhs_l, self.rhs_l)
 
-    def units(self, seconds, n_ranks):
-        return n_ranks * self.flops_per_step / seconds / 1e12
+    def units(self, step_seconds, n_ranks):
+        return n_ranks * self.flops_per_step / step_seconds / 1e12
 
     def setup_e2e(self):
         import ctypes as C
@@ -354,30 +354,189 @@ class GemmWorkload:
                 "l2": "rotates over 3 lhs/result buffer pairs (604 MB) so that no operand tile is L2-resident from the previous step"}
 
 
-WORKLOADS = {"rms_silu": RmsSiluWorkload, "softmax": SoftmaxWorkload, "gemm": GemmWorkload}
-DEFAULT_WORKLOAD = "rms_silu"
+class DecodeWorkload:
+    """Config 5: Llama-1.1B shape, 64 sequences per GPU, KV cache pre-filled to 2048 positions
+    from seeded random prompts, greedy decoding; sequences partitioned across GPUs."""
+    name = ("Llama-1.1B-shape greedy decode (dim 2048, 22 layers, 32q/4kv heads, ffn 5632, vocab 32000, "
+            "bf16 weights + bf16 KV), 64 sequences per GPU, cache pre-filled to 2048 positions")
+    metric = "tokens/s, Llama-1.1B-shape decode (batch 64 per GPU, KV depth 2048+)"
+    unit = "tokens/s"
+    dtype = "bf16"
+    bound = "hbm"
+    batch, prefill = 64, 2048
+    step_is_graph = True
+
+    def __init__(self, rank, prefill=None, layers=None, fast_prefill=False):
+        self.fast_prefill = fast_prefill
+        from ug_b200 import synth
+        from ug_b200.llama import Config
+        self.cfg = Config.llama_1b()
+        if layers:
+            self.cfg.num_hidden_layers = layers
+        if prefill is not None:
+            self.prefill = prefill
+        self.rank = rank
+        self.weights = synth.llama_weights(self.cfg)            # replicated on every GPU
+        self.prompts = synth.tokens(8 + 1000 * rank, (self.batch, self.prefill), self.cfg.vocab_size)
+        c = self.cfg
+        per_layer = (c.hidden_size * (c.hidden_size + 2 * c.num_key_value_heads * c.head_dim())
+                     + c.hidden_size * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
+        self.weight_bytes = 2 * (per_layer * c.num_hidden_layers + c.vocab_size * c.hidden_size)
+        self.kv_bytes_per_pos = c.num_hidden_layers * 2 * c.num_key_value_heads * c.head_dim() * 2
+        self.h2d_bytes = self.batch * 4
+        self.d2h_bytes = self.batch * 4
+        self.launches_per_step = 1 + 8 * c.num_hidden_layers + 3
+
+    def setup(self, dev, total_steps=256):
+        from ug_b200.llama import Model
+        self.dev = dev
+        self.t_max = self.prefill + total_steps + 16
+        self.model = Model.new(self.cfg, self.weights, dev, self.batch, self.t_max)
+        self.model.reset(0)
+        if self.fast_prefill:
+            self.model.fwd(self.prompts[:, 0])
+            self.model.reset(self.prefill)
+        else:
+            # pre-fill: the prompts go through the same decode step, one position per step (untimed)
+            for i in range(self.prefill):
+                self.model.fwd(self.prompts[:, i])
+        dev.synchronize()
+        self.steps_done = 0
+
+    def step(self):
+        self.model.decode(1)
+        self.steps_done += 1
+
+    def mean_depth(self, first_pos, n_steps):
+        return first_pos + (n_steps - 1) / 2.0 + 1
+
+    def step_bytes(self, depth):
+        return self.weight_bytes + self.kv_bytes_per_pos * depth * self.batch
+
+    def units(self, seconds_per_step_total, n_ranks):
+        raise NotImplementedError
+
+    def setup_e2e(self):
+        import ctypes as C
+        from ug_b200 import DType
+        from ug_b200._lib import lib
+        self._pin = []
+        for attr in ("p_in", "p_out"):
+            p = C.c_void_p()
+            assert lib.ugb_host_alloc(self.batch * 4, C.byref(p)) == 0
+            setattr(self, attr, p)
+            self._pin.append(p)
+        self.tok_slice = self.dev.allocate_uninit(DType.I32, self.batch)
+        self.out_slice = None
+        self.host_in = np.ctypeslib.as_array(C.cast(self.p_in, C.POINTER(C.c_int32)), shape=(self.batch,))
+        self.host_out = np.ctypeslib.as_array(C.cast(self.p_out, C.POINTER(C.c_int32)), shape=(self.batch,))
+        self.host_in[:] = self.model.next_tokens()
+
+    def e2e_step(self):
+        """One step the way a caller with host buffers drives it: token ids host -> device,
+        the decode step, chosen ids device -> host, every step."""
+        from ug_b200 import DType
+        from ug_b200._lib import lib
+        d = self.dev
+        d._check(lib.ugb_h2d_async(self.tok_slice._h, self.p_in, self.batch, int(DType.I32)))
+        d._check(lib.ugb_llama_decode(self.model._h, self.tok_slice._h, 1))
+        d._check(lib.ugb_llama_read(self.model._h, 1, self.p_out, self.batch))     # blocking D2H
+        self.host_in[:] = self.host_out
+        self.steps_done += 1
+
+    def teardown_e2e(self):
+        from ug_b200._lib import lib
+        for p in self._pin:
+            lib.ugb_host_free(p)
+
+    def check(self):
+        """Logit parity against the CPU oracle of ug-llama on the same weights: 4 teacher-forced
+        positions from an empty cache, 2 sequences (max |diff| / max |logit|)."""
+        ref = self._oracle()
+        caches = {b: ref.new_cache() for b in (0, self.batch - 1)}
+        worst = 0.0
+        self.model.reset(0)
+        for i in range(4):
+            self.model.fwd(self.prompts[:, i])
+            got = self.model.logits()
+            for b, cache in caches.items():
+                want = ref.fwd(self.prompts[b:b + 1, i:i + 1], i, cache)[0, 0]
+                worst = max(worst, float(np.max(np.abs(got[b] - want)) / np.max(np.abs(want))))
+        return worst
+
+    def _oracle(self):
+        if getattr(self, "_ref", None) is None:
+            from oracle import llama_ref as R
+            from ug_b200 import synth
+            self._ref = R.Model(R.Config(**self.cfg.__dict__), synth.llama_weights_f32(self.weights))
+        return self._ref
+
+    def cpu_sample(self, budget_s):
+        """ug-llama's forward on the CPU oracle: one sequence, one new token per step, against a
+        cache of `prefill` positions filled with N(0,1) keys/values (the cost of a step does not
+        depend on the cached values); tokens/s of that single sequence."""
+        from ug_b200 import synth
+        c = self.cfg
+        ref = self._oracle()
+        cache = [[synth.normal(50 + l, (1, c.num_key_value_heads, self.prefill, c.head_dim())),
+                  synth.normal(90 + l, (1, c.num_key_value_heads, self.prefill, c.head_dim()))]
+                 for l in range(c.num_hidden_layers)]
+        tok = np.array([[1]], np.int32)
+        ref.fwd(tok, self.prefill, cache)                       # warm-up
+        n, t0 = 0, time.perf_counter()
+        while True:
+            logits = ref.fwd(tok, self.prefill + 1 + n, cache)
+            tok = np.array([[int(logits[0, 0].argmax())]], np.int32)
+            n += 1
+            dt = time.perf_counter() - t0
+            if dt > budget_s or n >= 64:
+                break
+        return n / dt, os.cpu_count(), (f"{n} greedy tokens of 1 sequence at KV depth {self.prefill}+, oracle of "
+                                        f"ug-llama's CPU path (f32, GEMM stand-in on {os.cpu_count()} threads), {dt:.1f} s")
+
+    def config(self):
+        return {"workload": self.name, "sequences_per_gpu": self.batch, "prefill": self.prefill,
+                "layers": self.cfg.num_hidden_layers, "fast_prefill": self.fast_prefill,
+                "l2": "inputs larger than L2 (2.07 GB weights + ~3 GB KV cache read per step vs 126 MB L2)"}
+
+
+WORKLOADS = {"rms_silu": RmsSiluWorkload, "softmax": SoftmaxWorkload, "gemm": GemmWorkload,
+             "decode": DecodeWorkload}
+DEFAULT_WORKLOAD = "decode"
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ug_b200", choices=["ug_b200", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prefill", type=int, default=None, help="decode: cached positions before timing")
+    ap.add_argument("--layers", type=int, default=None, help="decode: layer count (profiling of small cases)")
+    ap.add_argument("--fast-prefill", action="store_true",
+                    help="decode, profiling aid: place the cache at --prefill positions without running the "
+                         "prompts (the cache then holds zeros); not a valid benchmark configuration")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.steps is None:
+        args.steps = 128 if args.workload == "decode" else 50
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
 
+    def make_workload(r):
+        if args.workload == "decode":
+            return DecodeWorkload(r, prefill=args.prefill, layers=args.layers, fast_prefill=args.fast_prefill)
+        return WORKLOADS[args.workload](r)
+
     if args.impl == "reference":
         if rank != 0:
             return 0
-        return reference_arm(args)
+        return reference_arm(args, make_workload(0))
 
     import torch
     import torch.distributed as dist
@@ -388,8 +547,12 @@ def main():
 
     import ug_b200
     dev = ug_b200.Device(local_rank)
-    wl = WORKLOADS[args.workload](rank)
-    wl.setup(dev)
+    wl = make_workload(rank)
+    e2e_steps = max(3, min(args.steps, 10 if args.workload != "decode" else 32))
+    if args.workload == "decode":
+        wl.setup(dev, total_steps=args.warmup + args.steps + e2e_steps + 8)
+    else:
+        wl.setup(dev)
 
     def barrier():
         dev.synchronize()
@@ -405,6 +568,7 @@ def main():
         sampler.start()
         time.sleep(0.3)
     n0 = dev.launch_count
+    first_pos = wl.model.position if args.workload == "decode" else 0
     barrier()
     dev.timer_begin()
     for _ in range(args.steps):
@@ -418,11 +582,11 @@ def main():
     wl.setup_e2e()
     for _ in range(2):
         wl.e2e_step()
-    e2e_steps = max(3, min(args.steps, 10))
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         wl.e2e_step()
+    dev.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -435,20 +599,39 @@ def main():
 
     if rank == 0:
         peaks = measured_peaks()
-        sec = ms / 1e3
-        value = wl.units(sec, world)
-        launch_s = sec / (args.steps * wl.launches_per_step)
-        if wl.bound == "hbm":
-            achieved, peak, runit = wl.bytes_per_step / wl.launches_per_step / launch_s / 1e9, peaks["hbm"], "GB/s"
+        step_s = ms / 1e3 / args.steps
+        extra = {}
+        if args.workload == "decode":
+            value = world * wl.batch / step_s
+            e2e_value = world * wl.batch / (e2e_s / e2e_steps)
+            depth = wl.mean_depth(first_pos, args.steps)
+            achieved, peak, runit = wl.step_bytes(depth) / step_s / 1e9, peaks["hbm"], "GB/s"
+            # per-kernel share of one step, each kernel type timed alone over all layers (CUDA events)
+            kern = {}
+            for name in wl.model.KERNELS:
+                kern[name] = round(wl.model.time_kernel(name, 20), 4)
+            att_bytes = wl.kv_bytes_per_pos * wl.model.position * wl.batch
+            extra["kernels_ms_per_step"] = kern
+            extra["roofline_scope"] = ("whole decode step (one CUDA graph of %d kernels): weight bytes + KV bytes "
+                                       "at the mean cache depth %.0f" % (wl.launches_per_step, depth))
+            extra["decode_attention_roofline"] = {
+                "achieved": round(att_bytes / (kern["decode_attention"] / 1e3) / 1e9, 1), "peak": peaks["hbm"],
+                "unit": "GB/s", "frac": round(att_bytes / (kern["decode_attention"] / 1e3) / 1e9 / peaks["hbm"], 4)}
         else:
-            achieved, peak, runit = wl.flops_per_step / wl.launches_per_step / launch_s / 1e12, peaks["bf16"], "TFLOP/s"
+            value = wl.units(step_s, world)
+            e2e_value = wl.units(e2e_s / e2e_steps, world)
+            launch_s = step_s / wl.launches_per_step
+            if wl.bound == "hbm":
+                achieved, peak, runit = wl.bytes_per_step / wl.launches_per_step / launch_s / 1e9, peaks["hbm"], "GB/s"
+            else:
+                achieved, peak, runit = wl.flops_per_step / wl.launches_per_step / launch_s / 1e12, peaks["bf16"], "TFLOP/s"
         line = {
             "metric": wl.metric, "value": round(value, 2), "unit": wl.unit, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
             "data": "synthetic (seeded Philox, shapes and distributions of the named config)",
             "config": wl.config(),
-            "e2e": {"value": round(wl.units(e2e_s / e2e_steps, world), 3), "unit": wl.unit,
+            "e2e": {"value": round(e2e_value, 3), "unit": wl.unit,
                     "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes,
                     "steps": e2e_steps},
             "gpu_launches": int(launches),
@@ -456,8 +639,9 @@ def main():
             "roofline": {"bound": wl.bound, "achieved": round(achieved, 1), "peak": peak,
                          "unit": runit, "frac": round(achieved / peak, 4),
                          "traffic": None, "peak_source": peaks["source"]},
-            "parity_max_rel_err": wl.check(),
         }
+        line.update(extra)
+        line["parity_max_rel_err"] = wl.check()
         if not args.no_cpu_baseline:
             v, cores, sample = wl.cpu_sample(args.cpu_seconds)
             line["cpu_baseline"] = {"value": round(v, 4), "unit": wl.unit, "cores": cores,
@@ -469,10 +653,9 @@ def main():
     return 0
 
 
-def reference_arm(args):
+def reference_arm(args, wl):
     """The reference's own CPU implementation of the path (oracle port), bounded sample per step."""
-    wl = WORKLOADS[args.workload](0)
-    per_step = max(1.0, min(20.0, 120.0 / (args.steps + args.warmup)))
+    per_step = max(0.5, min(20.0, 120.0 / (args.steps + args.warmup)))
     vals, cores, sample = [], 1, ""
     for i in range(args.warmup + args.steps):
         v, cores, sample = wl.cpu_sample(per_step)

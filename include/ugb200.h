@@ -266,7 +266,9 @@ UGB_API int32_t ugb_llama_destroy(ugb_llama *m);
  * Linear::new / RmsNorm::new do (model.rs:120-122,142-144). */
 UGB_API int32_t ugb_llama_load_weight(ugb_llama *m, const char *name, const ugb_slice *w);
 /* Tuning knobs: "splits_qkv", "splits_o", "splits_down" (split-K factors of the
- * projections) and "att_splits" (KV slices per sequence and KV head), 1..8. */
+ * projections) and "att_splits" (KV slices per sequence and KV head), 1..8;
+ * "bn_qkv", "bn_o", "bn_gate_up", "bn_down", "bn_lm_head" (GEMM tile width:
+ * 64, 128 or 256). */
 UGB_API int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value);
 /* Sets the number of cached positions (0 = empty cache); cache contents at
  * positions >= pos are ignored by later steps. */
@@ -285,6 +287,19 @@ UGB_API int32_t ugb_llama_read(ugb_llama *m, int32_t what, void *host_dst, size_
  * [batch, n_kv_heads, ugb_llama_kv_positions, head_dim]. */
 UGB_API int32_t ugb_llama_read_kv(ugb_llama *m, int32_t layer, int32_t which, void *host_dst,
                                   size_t len);
+
+/* Measurement aid: runs ONE kernel type of the decode step over all layers
+ * (the cache must hold at least one position), `iters` passes after one
+ * warm-up pass, timed with CUDA events on the device stream; returns
+ * milliseconds per pass (= per decode step's worth of that kernel; the
+ * lm_head GEMM runs once per pass).  Activations are scratch afterwards; the
+ * KV cache and the position are left as they were. */
+enum {
+  UGB_LLAMA_K_QKV = 0, UGB_LLAMA_K_ATTENTION = 1, UGB_LLAMA_K_O = 2, UGB_LLAMA_K_GATE_UP = 3,
+  UGB_LLAMA_K_DOWN = 4, UGB_LLAMA_K_LM_HEAD = 5
+};
+UGB_API int32_t ugb_llama_time_kernel(ugb_llama *m, int32_t which, int32_t iters,
+                                      float *ms_per_pass);
 
 #ifdef __cplusplus
 }

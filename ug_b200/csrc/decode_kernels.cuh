@@ -98,8 +98,9 @@ reduce_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ part, int
 //   k  -> rope -> bf16 K cache [b][kvh][pos][d]
 //   v  ->         bf16 V cache [b][kvh][pos][d]
 // pos is read from device memory (every sequence of the batch sits at the same
-// position, the reference's pos[0] convention, cpu_ops.rs:67-71).  One CTA per
-// sequence, one thread per rotation pair.
+// position, the reference's pos[0] convention, cpu_ops.rs:67-71).  grid =
+// (batch, ceil(items / 256)): one thread per rotation pair or per v element, so
+// that all of a thread's loads are independent and issued at once.
 static __global__ void __launch_bounds__(256)
 rope_append_kernel(const float *__restrict__ part, int n_part, size_t part_stride,
                    const float *__restrict__ cos_, const float *__restrict__ sin_,
@@ -107,34 +108,35 @@ rope_append_kernel(const float *__restrict__ part, int n_part, size_t part_strid
                    __nv_bfloat16 *__restrict__ kcache, __nv_bfloat16 *__restrict__ vcache,
                    int n_heads, int n_kv, int hd, int t_max, int interleaved) {
   const int b = blockIdx.x;
-  const int pos = *pos_p;
+  const int it = blockIdx.y * blockDim.x + threadIdx.x;
   const int half = hd >> 1;
+  const int n_rot = (n_heads + n_kv) * half;
   const int qkv_dim = (n_heads + 2 * n_kv) * hd;
   const float *row = part + (size_t)b * qkv_dim;
-  auto ld = [&](int col) {
-    float a = 0.f;
-    for (int s = 0; s < n_part; ++s) a += row[s * part_stride + col];
-    return a;
-  };
-  const int n_rot_heads = n_heads + n_kv;
-  for (int it = threadIdx.x; it < n_rot_heads * half; it += blockDim.x) {
+  const int pos = *pos_p;
+  if (it < n_rot) {
     const int head = it / half, i = it - head * half;
     const int i1 = interleaved ? 2 * i : i;
     const int i2 = interleaved ? 2 * i + 1 : i + half;
-    const float x1 = ld(head * hd + i1), x2 = ld(head * hd + i2);
-    const float c = cos_[(size_t)pos * half + i], s = sin_[(size_t)pos * half + i];
-    const float y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
-    const float y2 = __fadd_rn(__fmul_rn(x1, s), __fmul_rn(x2, c));
+    float x1 = 0.f, x2 = 0.f;
+    for (int s = 0; s < n_part; ++s) {
+      x1 += row[s * part_stride + head * hd + i1];
+      x2 += row[s * part_stride + head * hd + i2];
+    }
+    const float c = cos_[(size_t)pos * half + i], sn = sin_[(size_t)pos * half + i];
+    const float y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn));
+    const float y2 = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, c));
     __nv_bfloat16 *dst = head < n_heads
         ? q_out + ((size_t)b * n_heads + head) * hd
         : kcache + (((size_t)b * n_kv + (head - n_heads)) * t_max + pos) * hd;
     dst[i1] = __float2bfloat16_rn(y1);
     dst[i2] = __float2bfloat16_rn(y2);
-  }
-  for (int it = threadIdx.x; it < n_kv * hd; it += blockDim.x) {
-    const int head = it / hd, i = it - head * hd;
-    vcache[(((size_t)b * n_kv + head) * t_max + pos) * hd + i] =
-        __float2bfloat16_rn(ld((n_heads + n_kv) * hd + it));
+  } else if (it < n_rot + n_kv * hd) {
+    const int e = it - n_rot;
+    const int head = e / hd, i = e - head * hd;
+    float x = 0.f;
+    for (int s = 0; s < n_part; ++s) x += row[s * part_stride + (n_heads + n_kv) * hd + e];
+    vcache[(((size_t)b * n_kv + head) * t_max + pos) * hd + i] = __float2bfloat16_rn(x);
   }
 }
 
@@ -159,12 +161,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 }
 
 constexpr int ATT_WARPS = 4;
-constexpr int ATT_STAGES = 4;          // 16-key sub-tiles in flight per warp
+constexpr int ATT_STAGES = 3;          // 16-key sub-tiles in flight per warp (default ring depth)
 constexpr int ATT_SUB = 16;            // keys per sub-tile
 constexpr int ATT_HD = 64;             // head dim (compile-time: fragment layout)
 constexpr int ATT_GROUP = 8;           // query heads per KV head (<= 8, padded to the 16-row tile)
 constexpr int ATT_SUB_BYTES = ATT_SUB * ATT_HD * 2;   // 2 KiB per K or V sub-tile
-constexpr int ATT_RING_BYTES = ATT_WARPS * ATT_STAGES * 2 * ATT_SUB_BYTES;   // dynamic shared memory
+constexpr int att_ring_bytes(int stages) { return ATT_WARPS * stages * 2 * ATT_SUB_BYTES; }   // dynamic shared memory
+constexpr int ATT_RING_BYTES = att_ring_bytes(ATT_STAGES);
 
 // Flash-decode for one new query position per sequence, grouped-query heads.
 //   grid = (n_split, n_kv, batch), 128 threads.
@@ -178,15 +181,16 @@ constexpr int ATT_RING_BYTES = ATT_WARPS * ATT_STAGES * 2 * ATT_SUB_BYTES;   // 
 // K frags use a permuted k index (dims 16t+4s.. for lane t, step s) so that a
 // lane's operands are two contiguous 16-byte pieces of a row; Q uses the same
 // permutation.  V frags come from ldmatrix.trans on the staged sub-tile.
-static __global__ void __launch_bounds__(ATT_WARPS * 32)
-decode_attention_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restrict__ kcache,
+template <int NSTAGE>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restrict__ kcache,
                         const __nv_bfloat16 *__restrict__ vcache, const int *__restrict__ pos_p,
                         float *__restrict__ part_o, float *__restrict__ part_ml,
                         unsigned int *__restrict__ counters, __nv_bfloat16 *__restrict__ out,
                         int n_heads, int n_kv, int group, int t_max, float scale) {
   extern __shared__ __align__(128) uint8_t att_smem[];                     // the cp.async ring, 64 KiB
-  uint8_t (*ring)[ATT_STAGES][2][ATT_SUB_BYTES] =
-      reinterpret_cast<uint8_t (*)[ATT_STAGES][2][ATT_SUB_BYTES]>(att_smem);
+  uint8_t (*ring)[NSTAGE][2][ATT_SUB_BYTES] =
+      reinterpret_cast<uint8_t (*)[NSTAGE][2][ATT_SUB_BYTES]>(att_smem);
   __shared__ float merge_o[ATT_WARPS][ATT_GROUP][ATT_HD];
   __shared__ float merge_ml[ATT_WARPS][ATT_GROUP][2];
   __shared__ int is_last;
@@ -239,7 +243,7 @@ decode_attention_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16
   // prologue: fill the ring
   const int first = sub_lo + warp;
 #pragma unroll
-  for (int s = 0; s < ATT_STAGES - 1; ++s) {
+  for (int s = 0; s < NSTAGE - 1; ++s) {
     const int sub = first + s * ATT_WARPS;
     if (sub < sub_hi) issue(sub, s);
     cp_async_commit();
@@ -247,12 +251,12 @@ decode_attention_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16
   int stage = 0;
   for (int sub = first; sub < sub_hi; sub += ATT_WARPS) {
     {
-      const int nxt = sub + (ATT_STAGES - 1) * ATT_WARPS;
-      const int nstage = (stage + ATT_STAGES - 1) % ATT_STAGES;
+      const int nxt = sub + (NSTAGE - 1) * ATT_WARPS;
+      const int nstage = (stage + NSTAGE - 1) % NSTAGE;
       if (nxt < sub_hi) issue(nxt, nstage);
       cp_async_commit();
     }
-    cp_async_wait<ATT_STAGES - 1>();
+    cp_async_wait<NSTAGE - 1>();
     __syncwarp();
     const uint8_t *ks = &ring[warp][stage][0][0];
     const uint32_t vs = (uint32_t)__cvta_generic_to_shared(&ring[warp][stage][1][0]);
@@ -307,7 +311,7 @@ decode_attention_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16
       mma_bf16_16x8x16(o[d + 1], pa0, 0u, pa2, 0u, r2, r3);
     }
     __syncwarp();
-    stage = (stage + 1) % ATT_STAGES;
+    stage = (stage + 1) % NSTAGE;
   }
   cp_async_wait<0>();
 
@@ -368,36 +372,41 @@ decode_attention_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16
   }
 }
 
+#define decode_attention_kernel decode_attention_kernel_t<ATT_STAGES>
+
 // next[b] = argmax_j logits[b, j] (ties -> lowest index); thread 0 of CTA 0 also
-// advances the shared position counter.  One CTA of 256 threads per row.
-static __global__ void __launch_bounds__(256)
+// advances the shared position counter.  One CTA of 1024 threads per row,
+// 128-bit loads (vocab % 4 == 0).
+static __global__ void __launch_bounds__(1024)
 argmax_rows_kernel(const float *__restrict__ logits, int vocab, int *__restrict__ next, int *pos_p) {
-  __shared__ float sv[8];
-  __shared__ int si[8];
+  __shared__ float sv[32];
+  __shared__ int si[32];
   const int b = blockIdx.x;
-  const float *row = logits + (size_t)b * vocab;
+  const float4 *row = reinterpret_cast<const float4 *>(logits + (size_t)b * vocab);
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int j = threadIdx.x; j < vocab; j += blockDim.x) {
-    const float v = row[j];
-    if (v > best || (v == best && j < bi)) { best = v; bi = j; }
+  auto upd = [&](float v, int j) { if (v > best || (v == best && j < bi)) { best = v; bi = j; } };
+  for (int j = threadIdx.x; j < vocab / 4; j += blockDim.x) {
+    const float4 v = __ldcs(row + j);
+    upd(v.x, 4 * j); upd(v.y, 4 * j + 1); upd(v.z, 4 * j + 2); upd(v.w, 4 * j + 3);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
     const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    upd(ov, oi);
   }
   if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
   __syncthreads();
   if (threadIdx.x < 32) {
-    best = threadIdx.x < 8 ? sv[threadIdx.x] : -INFINITY;
-    bi = threadIdx.x < 8 ? si[threadIdx.x] : 0x7fffffff;
+    const int nw = blockDim.x >> 5;
+    best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
+    bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
 #pragma unroll
-    for (int o = 4; o > 0; o >>= 1) {
+    for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, best, o);
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+      upd(ov, oi);
     }
     if (threadIdx.x == 0) {
       next[b] = bi == 0x7fffffff ? 0 : bi;

@@ -42,8 +42,8 @@ constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
 template <int BN> struct Cfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = BN == 256 ? 4 : 8;
-  static constexpr int TMEM_COLS = ACC_STAGES * BN;   // 512 or 128 (powers of two)
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = ACC_STAGES * BN;   // 512, 256 or 128 (powers of two)
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
@@ -54,6 +54,7 @@ struct Params {
   int b_batched;          // 0: B shared by all batch steps
   int b_is_nk;            // 1: B [n,k] (k-major), 0: B [k,n] (n-major)
   int epi;                // UGB_EPI_*
+  int stage_tx;           // bytes one pipeline stage receives (A box + B box)
   long long c_batch;      // output elements between batch steps
   long long c_split;      // output elements between split-K partials
   void *C;
@@ -81,7 +82,11 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
+#ifdef UGB_MBAR_TEST_WAIT
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+#else
       "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+#endif
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
@@ -216,7 +221,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&empty[stage]), phase ^ 1u, abort_flag, p.status, 1)) { alive = false; break; }
           const uint32_t bar = smem_u32(&full[stage]);
-          mbar_expect_tx(bar, STAGE_BYTES);
+          mbar_expect_tx(bar, (uint32_t)p.stage_tx);
           const uint32_t a_dst = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t b_dst = a_dst + A_BYTES;
           tma_load_3d(a_dst, &tmA, bar, kb * BK, m0, bi);
@@ -322,7 +327,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int e = 0; e < 4; ++e) {
                   const float g0 = __uint_as_float(v[q * 16 + e * 4 + 0]), u0 = __uint_as_float(v[q * 16 + e * 4 + 1]);
                   const float g1 = __uint_as_float(v[q * 16 + e * 4 + 2]), u1 = __uint_as_float(v[q * 16 + e * 4 + 3]);
-                  __nv_bfloat162 t = __floats2bfloat162_rn(g0 / (expf(-g0) + 1.0f) * u0, g1 / (expf(-g1) + 1.0f) * u1);
+                  // ex2.approx-based exp and approximate division: ~1e-6 relative, far below the bf16 output step
+                  __nv_bfloat162 t = __floats2bfloat162_rn(__fdividef(g0, __expf(-g0) + 1.0f) * u0,
+                                                           __fdividef(g1, __expf(-g1) + 1.0f) * u1);
                   o[e] = *(uint32_t *)&t;
                 }
                 *reinterpret_cast<uint4 *>(crow + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -361,7 +368,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 
 struct TcState {
   EncodeTiledFn encode = nullptr;
-  bool attr_set[2] = {false, false};
+  bool attr_set[3] = {false, false, false};
 };
 
 TcState *state_of(ugb_device *dev) {
@@ -387,10 +394,11 @@ int32_t encode_map(ugb_device *dev, TcState *st, CUtensorMap *map, const void *b
 template <int BN>
 int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_t batch, size_t m) {
   const size_t n = g.n, k = g.k;
-  if (!st->attr_set[BN == 256]) {
+  constexpr int slot = BN == 256 ? 2 : (BN == 128 ? 1 : 0);
+  if (!st->attr_set[slot]) {
     UGB_CUDA(dev, cudaFuncSetAttribute(tc_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg<BN>::SMEM_BYTES));
-    st->attr_set[BN == 256] = true;
+    st->attr_set[slot] = true;
   }
   Params p;
   p.M = (int)m; p.N = (int)n; p.K = (int)k; p.batch = (int)batch;
@@ -411,7 +419,11 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   p.status = dev->status_dev;
 
   CUtensorMap tmA, tmB;
-  int32_t rc = encode_map(dev, st, &tmA, g.a, k, m, batch, k, batch > 1 ? (uint64_t)g.a_batch : m * k, BK, BM);
+  // With m <= 64 the A box is 64 rows: the upper half of the 128-row smem tile is never written, the
+  // accumulator rows 64..127 it feeds are never stored, and the TMA unit moves half the bytes.
+  const uint32_t a_rows = m <= 64 ? 64 : BM;
+  p.stage_tx = (int)(a_rows * BK * 2) + Cfg<BN>::B_BYTES;
+  int32_t rc = encode_map(dev, st, &tmA, g.a, k, m, batch, k, batch > 1 ? (uint64_t)g.a_batch : m * k, BK, a_rows);
   if (rc) return rc;
   const uint64_t nb = p.b_batched ? batch : 1;
   const uint64_t bs = p.b_batched ? (uint64_t)g.b_batch : n * k;
@@ -465,6 +477,7 @@ int32_t ugb_tc_gemm(ugb_device *dev, const ugb_tc_gemm_args &g) {
   int bn = g.bn;
   if (bn == 0) bn = (m <= 128) ? 64 : 256;
   if (bn == 64) return launch_tc<64>(dev, st, g, batch, m);
+  if (bn == 128) return launch_tc<128>(dev, st, g, batch, m);
   return launch_tc<256>(dev, st, g, batch, m);
 }
 

@@ -18,7 +18,7 @@ struct ugb_tc_gemm_args {
   bool b_is_nk;
   int epi;              // UGB_EPI_*
   int splits;           // split-K factor (only with UGB_EPI_F32); the kernel may use fewer
-  int bn;               // tile width: 64, 256, or 0 = choose from m
+  int bn;               // tile width: 64, 128, 256, or 0 = choose from m
 };
 
 // Returns UGB_ERR_UNSUPPORTED (without touching last_error) when the shape

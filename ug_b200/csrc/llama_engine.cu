@@ -54,7 +54,8 @@ struct ugb_llama {
   int *tok = nullptr, *next = nullptr, *pos = nullptr;
   int host_pos = 0;
   // tuning
-  int splits_qkv = 3, splits_o = 4, splits_down = 4, att_splits = 2;
+  int splits_qkv = 3, splits_o = 4, splits_down = 4, att_splits = 1, att_stages = 3;
+  int bn_qkv = 64, bn_o = 64, bn_gate_up = 128, bn_down = 64, bn_lm_head = 256;   // GEMM tile widths
   size_t part_elems = 0;
   // graph of one step that reads `next` as its input tokens
   cudaGraphExec_t graph = nullptr;
@@ -111,12 +112,12 @@ int32_t put_vector(ugb_llama *m, const ugb_slice *w, float *dst, size_t n, const
 }
 
 int32_t gemm(ugb_llama *m, void *out, const __nv_bfloat16 *a, const __nv_bfloat16 *w, size_t n, size_t k,
-             int epi, int splits) {
+             int epi, int splits, int bn) {
   ugb_tc_gemm_args g;
   g.out = out; g.a = a; g.b = w;
   g.batch = 1; g.m = (size_t)m->batch; g.n = n; g.k = k;
   g.a_batch = 0; g.b_batch = 0; g.b_is_nk = true;
-  g.epi = epi; g.splits = splits; g.bn = 64;
+  g.epi = epi; g.splits = splits; g.bn = bn;
   int32_t rc = ugb_tc_gemm(m->dev, g);
   if (rc == UGB_ERR_UNSUPPORTED)
     return ugb_fail(m->dev, rc, "decode GEMM m=%d n=%zu k=%zu does not meet the tensor-core kernel's shape rules", m->batch, n, k);
@@ -137,6 +138,25 @@ int32_t launch_reduce_rmsnorm(ugb_llama *m, const float *part, int n_part, const
   return ugb_after_launch(m->dev, "reduce_rmsnorm_kernel");
 }
 
+int32_t launch_attention(ugb_llama *m, const __nv_bfloat16 *kc, const __nv_bfloat16 *vc, float scale) {
+  const ugb_llama_config &c = m->cfg;
+  dim3 grid(m->att_splits, c.n_kv_heads, m->batch);
+  cudaStream_t st = m->dev->stream;
+#define UGB_ATT_LAUNCH(NS)                                                                                   \
+  decode_attention_kernel_t<NS><<<grid, ATT_WARPS * 32, att_ring_bytes(NS), st>>>(                            \
+      m->q, kc, vc, m->pos, m->att_po, m->att_pml, m->att_cnt, m->att, c.n_heads, c.n_kv_heads,               \
+      c.n_heads / c.n_kv_heads, m->t_max, scale)
+  switch (m->att_stages) {
+    case 2: UGB_ATT_LAUNCH(2); break;
+    case 4: UGB_ATT_LAUNCH(4); break;
+    case 5: UGB_ATT_LAUNCH(5); break;
+    case 6: UGB_ATT_LAUNCH(6); break;
+    default: UGB_ATT_LAUNCH(3); break;
+  }
+#undef UGB_ATT_LAUNCH
+  return ugb_after_launch(m->dev, "decode_attention_kernel");
+}
+
 // Enqueues one decode step on the device stream; `tok` holds the input ids.
 int32_t enqueue_step(ugb_llama *m, const int *tok) {
   ugb_device *dev = m->dev;
@@ -153,25 +173,22 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
   for (int l = 0; l < c.layers; ++l) {
     const LayerW &w = m->layers[l];
     if ((rc = launch_reduce_rmsnorm(m, m->part, l == 0 ? 0 : s_down, w.rms1))) return rc;
-    if ((rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv))) return rc;
+    if ((rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv))) return rc;
     __nv_bfloat16 *kc = m->kcache + (size_t)l * m->kv_layer_stride;
     __nv_bfloat16 *vc = m->vcache + (size_t)l * m->kv_layer_stride;
-    rope_append_kernel<<<B, 256, 0, st>>>(m->part, s_qkv, (size_t)B * m->qkv_dim, m->cos, m->sin, m->pos, m->q, kc, vc,
+    const int rope_items = (c.n_heads + c.n_kv_heads) * c.head_dim / 2 + c.n_kv_heads * c.head_dim;
+    rope_append_kernel<<<dim3(B, (rope_items + 255) / 256), 256, 0, st>>>(m->part, s_qkv, (size_t)B * m->qkv_dim, m->cos, m->sin, m->pos, m->q, kc, vc,
                                           c.n_heads, c.n_kv_heads, c.head_dim, m->t_max, c.rope_interleaved);
     if ((rc = ugb_after_launch(dev, "rope_append_kernel"))) return rc;
-    dim3 agrid(m->att_splits, c.n_kv_heads, B);
-    decode_attention_kernel<<<agrid, ATT_WARPS * 32, ATT_RING_BYTES, st>>>(
-        m->q, kc, vc, m->pos, m->att_po, m->att_pml, m->att_cnt, m->att, c.n_heads, c.n_kv_heads,
-        c.n_heads / c.n_kv_heads, m->t_max, scale);
-    if ((rc = ugb_after_launch(dev, "decode_attention_kernel"))) return rc;
-    if ((rc = gemm(m, m->part, m->att, w.wo, H, H, UGB_EPI_F32, m->splits_o))) return rc;
+    if ((rc = launch_attention(m, kc, vc, scale))) return rc;
+    if ((rc = gemm(m, m->part, m->att, w.wo, H, H, UGB_EPI_F32, m->splits_o, m->bn_o))) return rc;
     if ((rc = launch_reduce_rmsnorm(m, m->part, s_o, w.rms2))) return rc;
-    if ((rc = gemm(m, m->h, m->xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1))) return rc;
-    if ((rc = gemm(m, m->part, m->h, w.wdown, H, c.ffn, UGB_EPI_F32, m->splits_down))) return rc;
+    if ((rc = gemm(m, m->h, m->xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, m->bn_gate_up))) return rc;
+    if ((rc = gemm(m, m->part, m->h, w.wdown, H, c.ffn, UGB_EPI_F32, m->splits_down, m->bn_down))) return rc;
   }
   if ((rc = launch_reduce_rmsnorm(m, m->part, s_down, m->ln_f))) return rc;
-  if ((rc = gemm(m, m->logits, m->xn, m->embed, c.vocab, H, UGB_EPI_F32, 1))) return rc;
-  argmax_rows_kernel<<<B, 256, 0, st>>>(m->logits, c.vocab, m->next, m->pos);
+  if ((rc = gemm(m, m->logits, m->xn, m->embed, c.vocab, H, UGB_EPI_F32, 1, m->bn_lm_head))) return rc;
+  argmax_rows_kernel<<<B, 1024, 0, st>>>(m->logits, c.vocab, m->next, m->pos);
   return ugb_after_launch(dev, "argmax_rows_kernel");
 }
 
@@ -260,7 +277,11 @@ int32_t ugb_llama_create(ugb_device *dev, const ugb_llama_config *cfg, int32_t b
     rope_table_kernel<<<(n + 255) / 256, 256, 0, dev->stream>>>(inv_d, m->cos, m->sin, c.max_pos, (int)half);
     TRY(ugb_after_launch(dev, "rope_table_kernel"));
   }
-  if (cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_RING_BYTES) != cudaSuccess) {
+  if (cudaFuncSetAttribute(decode_attention_kernel_t<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, att_ring_bytes(2)) != cudaSuccess ||
+      cudaFuncSetAttribute(decode_attention_kernel_t<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, att_ring_bytes(3)) != cudaSuccess ||
+      cudaFuncSetAttribute(decode_attention_kernel_t<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, att_ring_bytes(4)) != cudaSuccess ||
+      cudaFuncSetAttribute(decode_attention_kernel_t<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, att_ring_bytes(5)) != cudaSuccess ||
+      cudaFuncSetAttribute(decode_attention_kernel_t<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, att_ring_bytes(6)) != cudaSuccess) {
     ugb_fail(dev, UGB_ERR_CUDA, "cudaFuncSetAttribute(decode_attention_kernel) failed");
     ugb_llama_destroy(m);
     return UGB_ERR_CUDA;
@@ -317,11 +338,24 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
   if (!m || !key) return UGB_ERR_INVALID;
   ugb_device *dev = m->dev;
   const std::string k(key);
+  if (k.compare(0, 3, "bn_") == 0) {
+    UGB_REQUIRE(dev, value == 64 || value == 128 || value == 256, UGB_ERR_INVALID, "option %s: tile width must be 64, 128 or 256", key);
+    if (k == "bn_qkv") m->bn_qkv = value;
+    else if (k == "bn_o") m->bn_o = value;
+    else if (k == "bn_gate_up") m->bn_gate_up = value;
+    else if (k == "bn_down") m->bn_down = value;
+    else if (k == "bn_lm_head") m->bn_lm_head = value;
+    else return ugb_fail(dev, UGB_ERR_INVALID, "unknown option %s", key);
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    m->warmed = false;   // a tile width used for the first time sets a kernel attribute: run one step eagerly
+    return UGB_OK;
+  }
   UGB_REQUIRE(dev, value >= 1 && value <= 8, UGB_ERR_INVALID, "option %s: value %d outside 1..8", key, value);
   if (k == "splits_qkv") m->splits_qkv = value;
   else if (k == "splits_o") m->splits_o = value;
   else if (k == "splits_down") m->splits_down = value;
   else if (k == "att_splits") m->att_splits = value;
+  else if (k == "att_stages") m->att_stages = value < 2 ? 2 : (value > 6 ? 6 : value);
   else return ugb_fail(dev, UGB_ERR_INVALID, "unknown option %s", key);
   if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
   return UGB_OK;
@@ -408,6 +442,50 @@ int32_t ugb_llama_read_kv(ugb_llama *m, int32_t layer, int32_t which, void *host
   const __nv_bfloat16 *src = (which == 0 ? m->kcache : m->vcache) + (size_t)layer * m->kv_layer_stride;
   UGB_CUDA(dev, cudaMemcpyAsync(host_dst, src, len * 2, cudaMemcpyDeviceToHost, dev->stream));
   UGB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  return UGB_OK;
+}
+
+int32_t ugb_llama_time_kernel(ugb_llama *m, int32_t which, int32_t iters, float *ms_per_pass) {
+  if (!m) return UGB_ERR_INVALID;
+  ugb_device *dev = m->dev;
+  UGB_REQUIRE(dev, ms_per_pass && iters >= 1, UGB_ERR_INVALID, "ugb_llama_time_kernel: bad argument");
+  UGB_REQUIRE(dev, m->host_pos >= 1, UGB_ERR_INVALID, "ugb_llama_time_kernel: the cache is empty");
+  const ugb_llama_config &c = m->cfg;
+  const int B = m->batch, H = c.hidden;
+  const float scale = powf((float)c.head_dim, -0.5f);
+  int32_t rc = UGB_OK;
+  // the kernels read the device-side position; during timing it must name the last cached position
+  const int last = m->host_pos - 1;
+  UGB_CUDA(dev, cudaMemcpyAsync(m->pos, &last, 4, cudaMemcpyHostToDevice, dev->stream));
+  for (int it = -1; it < iters && rc == UGB_OK; ++it) {    // it == -1: untimed warm-up pass
+    if (it == 0) UGB_CUDA(dev, cudaEventRecord(dev->ev_begin, dev->stream));
+    for (int l = 0; l < c.layers && rc == UGB_OK; ++l) {
+      const LayerW &w = m->layers[l];
+      switch (which) {
+        case UGB_LLAMA_K_QKV: rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv); break;
+        case UGB_LLAMA_K_ATTENTION: {
+          rc = launch_attention(m, m->kcache + (size_t)l * m->kv_layer_stride,
+                                m->vcache + (size_t)l * m->kv_layer_stride, scale);
+          break;
+        }
+        case UGB_LLAMA_K_O: rc = gemm(m, m->part, m->att, w.wo, H, H, UGB_EPI_F32, m->splits_o, m->bn_o); break;
+        case UGB_LLAMA_K_GATE_UP: rc = gemm(m, m->h, m->xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, m->bn_gate_up); break;
+        case UGB_LLAMA_K_DOWN: rc = gemm(m, m->part, m->h, w.wdown, H, c.ffn, UGB_EPI_F32, m->splits_down, m->bn_down); break;
+        case UGB_LLAMA_K_LM_HEAD:
+          if (l == 0) rc = gemm(m, m->logits, m->xn, m->embed, c.vocab, H, UGB_EPI_F32, 1, m->bn_lm_head);
+          break;
+        default: rc = ugb_fail(dev, UGB_ERR_INVALID, "ugb_llama_time_kernel: unknown kernel %d", which);
+      }
+    }
+  }
+  const int cur = m->host_pos;
+  cudaMemcpyAsync(m->pos, &cur, 4, cudaMemcpyHostToDevice, dev->stream);
+  if (rc) return rc;
+  UGB_CUDA(dev, cudaEventRecord(dev->ev_end, dev->stream));
+  UGB_CUDA(dev, cudaEventSynchronize(dev->ev_end));
+  float ms = 0.f;
+  UGB_CUDA(dev, cudaEventElapsedTime(&ms, dev->ev_begin, dev->ev_end));
+  *ms_per_pass = ms / (float)iters;
   return UGB_OK;
 }
 

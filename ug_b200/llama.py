@@ -151,3 +151,12 @@ class Model:
         out = np.empty((self.batch, self.cfg.num_key_value_heads, t, self.cfg.head_dim()), np.uint16)
         self.dev._check(lib.ugb_llama_read_kv(self._h, layer, which, out.ctypes.data, out.size))
         return out
+
+    KERNELS = {"qkv_gemm": 0, "decode_attention": 1, "o_gemm": 2, "gate_up_gemm": 3, "down_gemm": 4,
+               "lm_head_gemm": 5}
+
+    def time_kernel(self, name, iters=20):
+        """Milliseconds one decode step spends in kernel type ``name`` (all layers), CUDA events."""
+        ms = C.c_float()
+        self.dev._check(lib.ugb_llama_time_kernel(self._h, self.KERNELS[name], iters, C.byref(ms)))
+        return ms.value

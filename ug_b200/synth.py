@@ -28,11 +28,12 @@ def tokens(seed, shape, vocab):
 def to_bf16_bits(x):
     """f32 -> bf16 bit patterns (uint16), round to nearest even."""
     x = np.ascontiguousarray(x, dtype=np.float32)
-    u = x.view(np.uint32).astype(np.uint64)
-    rounded = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    u = x.view(np.uint32)
+    # 32-bit wrap-around can only touch NaN bit patterns, which are handled separately below
+    rounded = ((u + (np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1)))) >> np.uint32(16)).astype(np.uint16)
     nan = np.isnan(x)
     if nan.any():
-        rounded[nan] = ((u[nan] >> 16) | 0x40).astype(np.uint16)
+        rounded[nan] = ((u[nan] >> np.uint32(16)) | np.uint32(0x40)).astype(np.uint16)
     return rounded
 
 
@@ -55,15 +56,21 @@ def llama_weights(cfg, seed_base=100):
     """Random-init weights of a Llama-shaped model: every matrix ~ N(0, 0.02) rounded to bf16
     (returned as uint16 bit patterns), seed = seed_base + index of the tensor in load order;
     norm weights are ones (f32), the usual initialisation."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+
     from .llama import weight_names, weight_shape
-    out = {}
-    for i, name in enumerate(weight_names(cfg)):
+
+    def one(item):
+        i, name = item
         shape = weight_shape(cfg, name)
         if len(shape) == 1:
-            out[name] = np.ones(shape, np.float32)
-        else:
-            out[name] = to_bf16_bits(normal(seed_base + i, shape, 0.02))
-    return out
+            return name, np.ones(shape, np.float32)
+        return name, to_bf16_bits(normal(seed_base + i, shape, 0.02))
+
+    # every tensor has its own seed, so generating them on several threads changes nothing
+    with ThreadPoolExecutor(max_workers=min(16, os.cpu_count() or 1)) as ex:
+        return dict(ex.map(one, enumerate(weight_names(cfg))))
 
 
 def llama_weights_f32(weights):
