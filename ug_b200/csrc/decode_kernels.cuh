@@ -28,6 +28,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 static __global__ void __launch_bounds__(256)
 embed_gather_kernel(const __nv_bfloat16 *__restrict__ embed, const int *__restrict__ tok,
                     float *__restrict__ x, int hidden, int vocab, ugb_status_word *status) {
+  ugb_pdl_trigger();
+  ugb_pdl_wait();
   const int b = blockIdx.x;
   const int id = tok[b];
   if (id < 0 || id >= vocab) {
@@ -55,6 +57,8 @@ reduce_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ part, int
                       size_t part_stride, const float *__restrict__ alpha,
                       __nv_bfloat16 *__restrict__ xn, int hidden, float inv_d, float eps) {
   __shared__ float sm[8];
+  ugb_pdl_trigger();
+  ugb_pdl_wait();
   const int b = blockIdx.x;
   const int nvec = hidden >> 2;
   float4 *xr = reinterpret_cast<float4 *>(x + (size_t)b * hidden);
@@ -107,6 +111,8 @@ rope_append_kernel(const float *__restrict__ part, int n_part, size_t part_strid
                    const int *__restrict__ pos_p, __nv_bfloat16 *__restrict__ q_out,
                    __nv_bfloat16 *__restrict__ kcache, __nv_bfloat16 *__restrict__ vcache,
                    int n_heads, int n_kv, int hd, int t_max, int interleaved) {
+  ugb_pdl_trigger();
+  ugb_pdl_wait();
   const int b = blockIdx.x;
   const int it = blockIdx.y * blockDim.x + threadIdx.x;
   const int half = hd >> 1;
@@ -195,6 +201,8 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat
   __shared__ float merge_ml[ATT_WARPS][ATT_GROUP][2];
   __shared__ int is_last;
 
+  ugb_pdl_trigger();
+  ugb_pdl_wait();
   const int sp = blockIdx.x, n_split = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -381,6 +389,8 @@ static __global__ void __launch_bounds__(1024)
 argmax_rows_kernel(const float *__restrict__ logits, int vocab, int *__restrict__ next, int *pos_p) {
   __shared__ float sv[32];
   __shared__ int si[32];
+  ugb_pdl_trigger();
+  ugb_pdl_wait();
   const int b = blockIdx.x;
   const float4 *row = reinterpret_cast<const float4 *>(logits + (size_t)b * vocab);
   float best = -INFINITY;

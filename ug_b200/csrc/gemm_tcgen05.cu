@@ -28,23 +28,26 @@
 
 namespace {
 
-constexpr int BM = 128, BK = 64;
+constexpr int BK = 64;
 constexpr int ACC_STAGES = 2;
 constexpr int UMMA_K = 16;
-constexpr int A_BYTES = BM * BK * 2;          // 16 KiB
 constexpr int THREADS = 192;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
 
-// Tile shapes.  BN = 256 for compute-bound products (4 stages of 48 KiB);
-// BN = 64 for skinny, weight-streaming products (m <= 128: 8 stages of 24 KiB
-// keep ~190 KiB of loads in flight per SM and N/64 CTAs spread the weight
-// matrix over the SMs).
-template <int BN> struct Cfg {
+// Tile shapes.  BM = 128 (one accumulator row per TMEM lane) for tall products;
+// BM = 64 when m <= 64 (decode: the activation tile is half the size, so the
+// shared-memory ring holds more stages and more weight bytes are in flight per
+// SM; the 64 accumulator rows then sit on 16 lanes of each TMEM lane quadrant).
+// BN = 256 for compute-bound products, 64 / 128 for weight streaming.  The ring
+// takes as many stages as fit in 220 KiB (at most 12).
+template <int BM, int BN> struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int FIT = (220 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = FIT > 12 ? 12 : FIT;
   static constexpr int TMEM_COLS = ACC_STAGES * BN;   // 512, 256 or 128 (powers of two)
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
 struct Params {
@@ -55,6 +58,7 @@ struct Params {
   int b_is_nk;            // 1: B [n,k] (k-major), 0: B [k,n] (n-major)
   int epi;                // UGB_EPI_*
   int stage_tx;           // bytes one pipeline stage receives (A box + B box)
+  int b_static;           // 1: no kernel on the stream writes B (weights): it may be fetched before ugb_pdl_wait
   long long c_batch;      // output elements between batch steps
   long long c_split;      // output elements between split-K partials
   void *C;
@@ -159,12 +163,13 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major)
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-template <int BN>
+template <int BM, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
-  constexpr int STAGES = Cfg<BN>::STAGES;
-  constexpr int STAGE_BYTES = Cfg<BN>::STAGE_BYTES;
-  constexpr int TMEM_COLS = Cfg<BN>::TMEM_COLS;
+  constexpr int STAGES = Cfg<BM, BN>::STAGES;
+  constexpr int STAGE_BYTES = Cfg<BM, BN>::STAGE_BYTES;
+  constexpr int A_BYTES = Cfg<BM, BN>::A_BYTES;
+  constexpr int TMEM_COLS = Cfg<BM, BN>::TMEM_COLS;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128-byte swizzle pattern repeats every 1024 bytes
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -198,6 +203,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) ugb_pdl_trigger();   // the next kernel on the stream may begin its preamble
 
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int tiles_per_split = tiles_per_batch * p.batch;
@@ -209,6 +215,41 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
+      auto issue_b = [&](uint32_t b_dst, uint32_t bar, int kb, int n0, int bz) {
+        if (p.b_is_nk) {
+          tma_load_3d(b_dst, &tmB, bar, kb * BK, n0, bz);            // box {64 k, BN n}
+        } else {
+#pragma unroll
+          for (int c = 0; c < BN / 64; ++c)                           // BN/64 boxes {64 n, 64 k}
+            tma_load_3d(b_dst + c * (64 * BK * 2), &tmB, bar, n0 + c * 64, kb * BK, bz);
+        }
+      };
+      // Preamble: the B operand of the first tile (weights in the decode step) is
+      // written by no kernel of the stream, so its first stages are requested
+      // before waiting for the preceding kernel; A follows once that kernel is done.
+      int pre = 0;
+      {
+        const int tile = blockIdx.x;
+        const int sp = tile / tiles_per_split;
+        const int ts = tile - sp * tiles_per_split;
+        const int bi = ts / tiles_per_batch;
+        const int r = ts - bi * tiles_per_batch;
+        const int m0 = (r % p.tiles_m) * BM, n0 = (r / p.tiles_m) * BN;
+        const int bz = p.b_batched ? bi : 0;
+        const int kb0 = sp * p.kb_per_split;
+        const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+        pre = p.b_static ? min(STAGES, kb1 - kb0) : 0;
+        for (int i = 0; i < pre; ++i) {
+          const uint32_t bar = smem_u32(&full[i]);
+          mbar_expect_tx(bar, (uint32_t)p.stage_tx);
+          issue_b(smem_u32(smem + i * STAGE_BYTES) + A_BYTES, bar, kb0 + i, n0, bz);
+        }
+        ugb_pdl_wait();
+        for (int i = 0; i < pre; ++i)
+          tma_load_3d(smem_u32(smem + i * STAGE_BYTES), &tmA, smem_u32(&full[i]), (kb0 + i) * BK, m0, bi);
+        stage = pre % STAGES;
+        phase = pre == STAGES ? 1u : 0u;
+      }
       for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
         const int sp = tile / tiles_per_split;
         const int ts = tile - sp * tiles_per_split;
@@ -218,20 +259,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int bz = p.b_batched ? bi : 0;
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0 + (tile == (int)blockIdx.x ? pre : 0); kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&empty[stage]), phase ^ 1u, abort_flag, p.status, 1)) { alive = false; break; }
           const uint32_t bar = smem_u32(&full[stage]);
           mbar_expect_tx(bar, (uint32_t)p.stage_tx);
           const uint32_t a_dst = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t b_dst = a_dst + A_BYTES;
           tma_load_3d(a_dst, &tmA, bar, kb * BK, m0, bi);
-          if (p.b_is_nk) {
-            tma_load_3d(b_dst, &tmB, bar, kb * BK, n0, bz);          // box {64 k, BN n}
-          } else {
-#pragma unroll
-            for (int c = 0; c < BN / 64; ++c)                         // BN/64 boxes {64 n, 64 k}
-              tma_load_3d(b_dst + c * (64 * BK * 2), &tmB, bar, n0 + c * 64, kb * BK, bz);
-          }
+          issue_b(a_dst + A_BYTES, bar, kb, n0, bz);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -287,14 +321,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int m0 = (r % p.tiles_m) * BM, n0 = (r / p.tiles_m) * BN;
       if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, abort_flag, p.status, 4)) break;
       tcgen05_fence_after();
-      const int row = m0 + quad * 32 + lane;
+      // BM = 128: accumulator row = TMEM lane.  BM = 64: rows 16q..16q+15 sit on lanes 0..15 of quadrant q.
+      const bool row_lane = BM == 128 || lane < 16;
+      const int row = BM == 128 ? m0 + quad * 32 + lane : m0 + quad * 16 + lane;
       const long long out_off = (long long)sp * p.c_split + (long long)bi * p.c_batch;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
         tmem_ld_wait();
-        if (row < p.M) {
+        if (row_lane && row < p.M) {
           const int col0 = n0 + c * 32;
           if (p.epi == UGB_EPI_BF16) {
             __nv_bfloat16 *crow = (__nv_bfloat16 *)p.C + out_off + (long long)row * p.N + col0;
@@ -368,7 +404,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 
 struct TcState {
   EncodeTiledFn encode = nullptr;
-  bool attr_set[3] = {false, false, false};
+  bool attr_set[6] = {false, false, false, false, false, false};
 };
 
 TcState *state_of(ugb_device *dev) {
@@ -391,13 +427,13 @@ int32_t encode_map(ugb_device *dev, TcState *st, CUtensorMap *map, const void *b
   return UGB_OK;
 }
 
-template <int BN>
+template <int BM, int BN>
 int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_t batch, size_t m) {
   const size_t n = g.n, k = g.k;
-  constexpr int slot = BN == 256 ? 2 : (BN == 128 ? 1 : 0);
+  constexpr int slot = (BN == 256 ? 2 : (BN == 128 ? 1 : 0)) + (BM == 64 ? 3 : 0);
   if (!st->attr_set[slot]) {
-    UGB_CUDA(dev, cudaFuncSetAttribute(tc_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       Cfg<BN>::SMEM_BYTES));
+    UGB_CUDA(dev, cudaFuncSetAttribute(tc_gemm_kernel<BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg<BM, BN>::SMEM_BYTES));
     st->attr_set[slot] = true;
   }
   Params p;
@@ -412,6 +448,7 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   p.b_batched = (batch > 1 && g.b_batch != 0) ? 1 : 0;
   p.b_is_nk = g.b_is_nk ? 1 : 0;
   p.epi = g.epi;
+  p.b_static = g.b_static ? 1 : 0;
   const long long out_cols = g.epi == UGB_EPI_SILU_MUL_BF16 ? (long long)n / 2 : (long long)n;
   p.c_batch = (long long)m * out_cols;
   p.c_split = (long long)batch * m * out_cols;
@@ -419,11 +456,8 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   p.status = dev->status_dev;
 
   CUtensorMap tmA, tmB;
-  // With m <= 64 the A box is 64 rows: the upper half of the 128-row smem tile is never written, the
-  // accumulator rows 64..127 it feeds are never stored, and the TMA unit moves half the bytes.
-  const uint32_t a_rows = m <= 64 ? 64 : BM;
-  p.stage_tx = (int)(a_rows * BK * 2) + Cfg<BN>::B_BYTES;
-  int32_t rc = encode_map(dev, st, &tmA, g.a, k, m, batch, k, batch > 1 ? (uint64_t)g.a_batch : m * k, BK, a_rows);
+  p.stage_tx = Cfg<BM, BN>::STAGE_BYTES;
+  int32_t rc = encode_map(dev, st, &tmA, g.a, k, m, batch, k, batch > 1 ? (uint64_t)g.a_batch : m * k, BK, BM);
   if (rc) return rc;
   const uint64_t nb = p.b_batched ? batch : 1;
   const uint64_t bs = p.b_batched ? (uint64_t)g.b_batch : n * k;
@@ -433,7 +467,9 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
 
   const long long n_tiles = (long long)p.tiles_m * p.tiles_n * p.batch * p.splits;
   const unsigned grid = (unsigned)(n_tiles < dev->sm_count ? n_tiles : dev->sm_count);
-  tc_gemm_kernel<BN><<<grid, THREADS, Cfg<BN>::SMEM_BYTES, dev->stream>>>(tmA, tmB, p);
+  cudaError_t le = ugb_launch(tc_gemm_kernel<BM, BN>, dim3(grid), dim3(THREADS), Cfg<BM, BN>::SMEM_BYTES, dev->stream,
+                              g.pdl, tmA, tmB, p);
+  if (le != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of tc_gemm_kernel failed: %s", cudaGetErrorString(le));
   return ugb_after_launch(dev, "tc_gemm_kernel");
 }
 
@@ -476,9 +512,14 @@ int32_t ugb_tc_gemm(ugb_device *dev, const ugb_tc_gemm_args &g) {
   }
   int bn = g.bn;
   if (bn == 0) bn = (m <= 128) ? 64 : 256;
-  if (bn == 64) return launch_tc<64>(dev, st, g, batch, m);
-  if (bn == 128) return launch_tc<128>(dev, st, g, batch, m);
-  return launch_tc<256>(dev, st, g, batch, m);
+  if (m <= 64) {
+    if (bn == 64) return launch_tc<64, 64>(dev, st, g, batch, m);
+    if (bn == 128) return launch_tc<64, 128>(dev, st, g, batch, m);
+    return launch_tc<64, 256>(dev, st, g, batch, m);
+  }
+  if (bn == 64) return launch_tc<128, 64>(dev, st, g, batch, m);
+  if (bn == 128) return launch_tc<128, 128>(dev, st, g, batch, m);
+  return launch_tc<128, 256>(dev, st, g, batch, m);
 }
 
 int32_t ugb_tc_gemm_bf16(ugb_device *dev, void *c, const void *a, const void *b_, size_t batch, size_t m,
@@ -487,7 +528,7 @@ int32_t ugb_tc_gemm_bf16(ugb_device *dev, void *c, const void *a, const void *b_
   g.out = c; g.a = a; g.b = b_;
   g.batch = batch; g.m = m; g.n = n; g.k = k;
   g.a_batch = a_batch; g.b_batch = b_batch; g.b_is_nk = b_is_nk;
-  g.epi = UGB_EPI_BF16; g.splits = 1; g.bn = 0;
+  g.epi = UGB_EPI_BF16; g.splits = 1; g.bn = 0; g.b_static = false; g.pdl = false;
   return ugb_tc_gemm(dev, g);
 }
 

@@ -19,6 +19,8 @@ struct ugb_tc_gemm_args {
   int epi;              // UGB_EPI_*
   int splits;           // split-K factor (only with UGB_EPI_F32); the kernel may use fewer
   int bn;               // tile width: 64, 128, 256, or 0 = choose from m
+  bool b_static;        // no kernel on the stream writes b (weights): fetch it before waiting for the predecessor
+  bool pdl;             // launch with programmatic stream serialization (see ugb_launch)
 };
 
 // Returns UGB_ERR_UNSUPPORTED (without touching last_error) when the shape

@@ -54,8 +54,10 @@ struct ugb_llama {
   int *tok = nullptr, *next = nullptr, *pos = nullptr;
   int host_pos = 0;
   // tuning
-  int splits_qkv = 3, splits_o = 4, splits_down = 4, att_splits = 1, att_stages = 3;
-  int bn_qkv = 64, bn_o = 64, bn_gate_up = 128, bn_down = 64, bn_lm_head = 256;   // GEMM tile widths
+  int splits_qkv = 3, splits_o = 4, splits_down = 8, att_splits = 1, att_stages = 3;
+  int pdl = 1;                    // programmatic dependent launch between the kernels of a step
+  int skip = 0;                   // measurement aid: bit mask of kernel types left out of the step
+  int bn_qkv = 64, bn_o = 64, bn_gate_up = 128, bn_down = 128, bn_lm_head = 256;   // GEMM tile widths
   size_t part_elems = 0;
   // graph of one step that reads `next` as its input tokens
   cudaGraphExec_t graph = nullptr;
@@ -117,7 +119,7 @@ int32_t gemm(ugb_llama *m, void *out, const __nv_bfloat16 *a, const __nv_bfloat1
   g.out = out; g.a = a; g.b = w;
   g.batch = 1; g.m = (size_t)m->batch; g.n = n; g.k = k;
   g.a_batch = 0; g.b_batch = 0; g.b_is_nk = true;
-  g.epi = epi; g.splits = splits; g.bn = bn;
+  g.epi = epi; g.splits = splits; g.bn = bn; g.b_static = true; g.pdl = m->pdl != 0;
   int32_t rc = ugb_tc_gemm(m->dev, g);
   if (rc == UGB_ERR_UNSUPPORTED)
     return ugb_fail(m->dev, rc, "decode GEMM m=%d n=%zu k=%zu does not meet the tensor-core kernel's shape rules", m->batch, n, k);
@@ -131,10 +133,13 @@ int32_t launch_reduce_rmsnorm(ugb_llama *m, const float *part, int n_part, const
   const float inv_d = 1.0f / (float)hidden, eps = m->cfg.rms_eps;
   dim3 grid(m->batch);
   cudaStream_t st = m->dev->stream;
-  if (nvec <= 256) reduce_rmsnorm_kernel<1><<<grid, 256, 0, st>>>(m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
-  else if (nvec <= 512) reduce_rmsnorm_kernel<2><<<grid, 256, 0, st>>>(m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
-  else if (nvec <= 1024) reduce_rmsnorm_kernel<4><<<grid, 256, 0, st>>>(m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
-  else reduce_rmsnorm_kernel<8><<<grid, 256, 0, st>>>(m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
+  const bool pdl = m->pdl != 0;
+  cudaError_t e;
+  if (nvec <= 256) e = ugb_launch(reduce_rmsnorm_kernel<1>, grid, dim3(256), 0, st, pdl, m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
+  else if (nvec <= 512) e = ugb_launch(reduce_rmsnorm_kernel<2>, grid, dim3(256), 0, st, pdl, m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
+  else if (nvec <= 1024) e = ugb_launch(reduce_rmsnorm_kernel<4>, grid, dim3(256), 0, st, pdl, m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
+  else e = ugb_launch(reduce_rmsnorm_kernel<8>, grid, dim3(256), 0, st, pdl, m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
+  if (e != cudaSuccess) return ugb_fail(m->dev, UGB_ERR_CUDA, "launch of reduce_rmsnorm_kernel failed: %s", cudaGetErrorString(e));
   return ugb_after_launch(m->dev, "reduce_rmsnorm_kernel");
 }
 
@@ -142,10 +147,11 @@ int32_t launch_attention(ugb_llama *m, const __nv_bfloat16 *kc, const __nv_bfloa
   const ugb_llama_config &c = m->cfg;
   dim3 grid(m->att_splits, c.n_kv_heads, m->batch);
   cudaStream_t st = m->dev->stream;
+  cudaError_t e = cudaSuccess;
 #define UGB_ATT_LAUNCH(NS)                                                                                   \
-  decode_attention_kernel_t<NS><<<grid, ATT_WARPS * 32, att_ring_bytes(NS), st>>>(                            \
-      m->q, kc, vc, m->pos, m->att_po, m->att_pml, m->att_cnt, m->att, c.n_heads, c.n_kv_heads,               \
-      c.n_heads / c.n_kv_heads, m->t_max, scale)
+  e = ugb_launch(decode_attention_kernel_t<NS>, grid, dim3(ATT_WARPS * 32), att_ring_bytes(NS), st,           \
+                 m->pdl != 0, m->q, kc, vc, m->pos, m->att_po, m->att_pml, m->att_cnt, m->att, c.n_heads,     \
+                 c.n_kv_heads, c.n_heads / c.n_kv_heads, m->t_max, scale)
   switch (m->att_stages) {
     case 2: UGB_ATT_LAUNCH(2); break;
     case 4: UGB_ATT_LAUNCH(4); break;
@@ -154,6 +160,7 @@ int32_t launch_attention(ugb_llama *m, const __nv_bfloat16 *kc, const __nv_bfloa
     default: UGB_ATT_LAUNCH(3); break;
   }
 #undef UGB_ATT_LAUNCH
+  if (e != cudaSuccess) return ugb_fail(m->dev, UGB_ERR_CUDA, "launch of decode_attention_kernel failed: %s", cudaGetErrorString(e));
   return ugb_after_launch(m->dev, "decode_attention_kernel");
 }
 
@@ -164,7 +171,9 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
   cudaStream_t st = dev->stream;
   const int B = m->batch, H = c.hidden;
   int32_t rc;
-  embed_gather_kernel<<<B, 256, 0, st>>>(m->embed, tok, m->x, H, c.vocab, dev->status_dev);
+  const bool pdl = m->pdl != 0;
+  cudaError_t e = ugb_launch(embed_gather_kernel, dim3(B), dim3(256), 0, st, pdl, m->embed, tok, m->x, H, c.vocab, dev->status_dev);
+  if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of embed_gather_kernel failed: %s", cudaGetErrorString(e));
   if ((rc = ugb_after_launch(dev, "embed_gather_kernel"))) return rc;
   const int s_qkv = ugb_tc_gemm_effective_splits(H, m->splits_qkv);
   const int s_o = ugb_tc_gemm_effective_splits(H, m->splits_o);
@@ -172,23 +181,27 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
   const float scale = powf((float)c.head_dim, -0.5f);   // model.rs:236
   for (int l = 0; l < c.layers; ++l) {
     const LayerW &w = m->layers[l];
-    if ((rc = launch_reduce_rmsnorm(m, m->part, l == 0 ? 0 : s_down, w.rms1))) return rc;
-    if ((rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv))) return rc;
+    if (!(m->skip & 1) && (rc = launch_reduce_rmsnorm(m, m->part, l == 0 ? 0 : s_down, w.rms1))) return rc;
+    if (!(m->skip & 2) && (rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv))) return rc;
     __nv_bfloat16 *kc = m->kcache + (size_t)l * m->kv_layer_stride;
     __nv_bfloat16 *vc = m->vcache + (size_t)l * m->kv_layer_stride;
     const int rope_items = (c.n_heads + c.n_kv_heads) * c.head_dim / 2 + c.n_kv_heads * c.head_dim;
-    rope_append_kernel<<<dim3(B, (rope_items + 255) / 256), 256, 0, st>>>(m->part, s_qkv, (size_t)B * m->qkv_dim, m->cos, m->sin, m->pos, m->q, kc, vc,
-                                          c.n_heads, c.n_kv_heads, c.head_dim, m->t_max, c.rope_interleaved);
+    if (!(m->skip & 4))
+    e = ugb_launch(rope_append_kernel, dim3(B, (rope_items + 255) / 256), dim3(256), 0, st, pdl, m->part, s_qkv,
+                   (size_t)B * m->qkv_dim, m->cos, m->sin, m->pos, m->q, kc, vc, c.n_heads, c.n_kv_heads, c.head_dim,
+                   m->t_max, c.rope_interleaved);
+    if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of rope_append_kernel failed: %s", cudaGetErrorString(e));
     if ((rc = ugb_after_launch(dev, "rope_append_kernel"))) return rc;
-    if ((rc = launch_attention(m, kc, vc, scale))) return rc;
-    if ((rc = gemm(m, m->part, m->att, w.wo, H, H, UGB_EPI_F32, m->splits_o, m->bn_o))) return rc;
-    if ((rc = launch_reduce_rmsnorm(m, m->part, s_o, w.rms2))) return rc;
-    if ((rc = gemm(m, m->h, m->xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, m->bn_gate_up))) return rc;
-    if ((rc = gemm(m, m->part, m->h, w.wdown, H, c.ffn, UGB_EPI_F32, m->splits_down, m->bn_down))) return rc;
+    if (!(m->skip & 8) && (rc = launch_attention(m, kc, vc, scale))) return rc;
+    if (!(m->skip & 16) && (rc = gemm(m, m->part, m->att, w.wo, H, H, UGB_EPI_F32, m->splits_o, m->bn_o))) return rc;
+    if (!(m->skip & 1) && (rc = launch_reduce_rmsnorm(m, m->part, s_o, w.rms2))) return rc;
+    if (!(m->skip & 32) && (rc = gemm(m, m->h, m->xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, m->bn_gate_up))) return rc;
+    if (!(m->skip & 64) && (rc = gemm(m, m->part, m->h, w.wdown, H, c.ffn, UGB_EPI_F32, m->splits_down, m->bn_down))) return rc;
   }
   if ((rc = launch_reduce_rmsnorm(m, m->part, s_down, m->ln_f))) return rc;
-  if ((rc = gemm(m, m->logits, m->xn, m->embed, c.vocab, H, UGB_EPI_F32, 1, m->bn_lm_head))) return rc;
-  argmax_rows_kernel<<<B, 1024, 0, st>>>(m->logits, c.vocab, m->next, m->pos);
+  if (!(m->skip & 128) && (rc = gemm(m, m->logits, m->xn, m->embed, c.vocab, H, UGB_EPI_F32, 1, m->bn_lm_head))) return rc;
+  e = ugb_launch(argmax_rows_kernel, dim3(B), dim3(1024), 0, st, pdl, m->logits, c.vocab, m->next, m->pos);
+  if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of argmax_rows_kernel failed: %s", cudaGetErrorString(e));
   return ugb_after_launch(dev, "argmax_rows_kernel");
 }
 
@@ -338,6 +351,16 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
   if (!m || !key) return UGB_ERR_INVALID;
   ugb_device *dev = m->dev;
   const std::string k(key);
+  if (k == "measure_skip_mask") {   // measurement aid: results of a step are meaningless while it is non-zero
+    m->skip = value;
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    return UGB_OK;
+  }
+  if (k == "pdl") {
+    m->pdl = value != 0;
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    return UGB_OK;
+  }
   if (k.compare(0, 3, "bn_") == 0) {
     UGB_REQUIRE(dev, value == 64 || value == 128 || value == 256, UGB_ERR_INVALID, "option %s: tile width must be 64, 128 or 256", key);
     if (k == "bn_qkv") m->bn_qkv = value;
@@ -460,7 +483,7 @@ int32_t ugb_llama_time_kernel(ugb_llama *m, int32_t which, int32_t iters, float 
   for (int it = -1; it < iters && rc == UGB_OK; ++it) {    // it == -1: untimed warm-up pass
     if (it == 0) UGB_CUDA(dev, cudaEventRecord(dev->ev_begin, dev->stream));
     for (int l = 0; l < c.layers && rc == UGB_OK; ++l) {
-      const LayerW &w = m->layers[l];
+      const LayerW &w = m->layers[(m->skip & 256) ? 0 : l];   // bit 8: reuse layer 0 (weights stay in L2)
       switch (which) {
         case UGB_LLAMA_K_QKV: rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv); break;
         case UGB_LLAMA_K_ATTENTION: {

@@ -96,3 +96,33 @@ static inline int32_t ugb_check_slice(ugb_device *dev, const ugb_slice *s, int32
     int32_t rc__ = ugb_check_slice((dev), (s), (dtype), (min_len), #s);   \
     if (rc__ != UGB_OK) return rc__;                                      \
   } while (0)
+
+// ---- programmatic dependent launch ------------------------------------------
+// A kernel launched with ugb_launch(..., pdl = true) may start while the kernel
+// before it on the stream is still running.  It must execute ugb_pdl_wait()
+// before it reads or writes anything an earlier kernel touches (the wait returns
+// once the preceding kernel has completed and its writes are visible); what it
+// does before that (barrier set-up, TMEM allocation, loads of weights that no
+// kernel writes) overlaps the predecessor's tail.  ugb_pdl_trigger() lets the
+// NEXT kernel on the stream begin its own preamble.  Both are no-ops in a
+// kernel launched the ordinary way.
+#ifdef __CUDACC__
+__device__ __forceinline__ void ugb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void ugb_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t ugb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              bool pdl, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
