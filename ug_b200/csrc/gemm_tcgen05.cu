@@ -58,6 +58,7 @@ struct Params {
   int b_is_nk;            // 1: B [n,k] (k-major), 0: B [k,n] (n-major)
   int epi;                // UGB_EPI_*
   int stage_tx;           // bytes one pipeline stage receives (A box + B box)
+  int n_fast;             // tile order: 1 = n-tiles vary fastest (a wave re-reads B, the smaller operand)
   int b_static;           // 1: no kernel on the stream writes B (weights): it may be fetched before ugb_pdl_wait
   long long c_batch;      // output elements between batch steps
   long long c_split;      // output elements between split-K partials
@@ -234,7 +235,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int ts = tile - sp * tiles_per_split;
         const int bi = ts / tiles_per_batch;
         const int r = ts - bi * tiles_per_batch;
-        const int m0 = (r % p.tiles_m) * BM, n0 = (r / p.tiles_m) * BN;
+        const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * BM, n0 = (p.n_fast ? r % p.tiles_n : r / p.tiles_m) * BN;
         const int bz = p.b_batched ? bi : 0;
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
@@ -255,7 +256,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int ts = tile - sp * tiles_per_split;
         const int bi = ts / tiles_per_batch;
         const int r = ts - bi * tiles_per_batch;
-        const int m0 = (r % p.tiles_m) * BM, n0 = (r / p.tiles_m) * BN;
+        const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * BM, n0 = (p.n_fast ? r % p.tiles_n : r / p.tiles_m) * BN;
         const int bz = p.b_batched ? bi : 0;
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
@@ -318,7 +319,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int ts = tile - sp * tiles_per_split;
       const int bi = ts / tiles_per_batch;
       const int r = ts - bi * tiles_per_batch;
-      const int m0 = (r % p.tiles_m) * BM, n0 = (r / p.tiles_m) * BN;
+      const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * BM, n0 = (p.n_fast ? r % p.tiles_n : r / p.tiles_m) * BN;
       if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, abort_flag, p.status, 4)) break;
       tcgen05_fence_after();
       // BM = 128: accumulator row = TMEM lane.  BM = 64: rows 16q..16q+15 sit on lanes 0..15 of quadrant q.
@@ -449,6 +450,9 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   p.b_is_nk = g.b_is_nk ? 1 : 0;
   p.epi = g.epi;
   p.b_static = g.b_static ? 1 : 0;
+  // Consecutive tiles run in the same wave.  The operand that is walked completely by every wave is read
+  // from L2 again and again, so it should be the smaller one: B (n x k) when n <= m, otherwise A.
+  p.n_fast = n <= m ? 1 : 0;
   const long long out_cols = g.epi == UGB_EPI_SILU_MUL_BF16 ? (long long)n / 2 : (long long)n;
   p.c_batch = (long long)m * out_cols;
   p.c_split = (long long)batch * m * out_cols;
