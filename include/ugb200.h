@@ -145,6 +145,71 @@ UGB_API int32_t ugb_rope_i(ugb_device *dev, const ugb_slice *src, const ugb_slic
 UGB_API int32_t ugb_cat(ugb_device *dev, const ugb_slice *lhs, const ugb_slice *rhs, ugb_slice *dst,
                 size_t d1, size_t d2_l, size_t d2_r);
 
+/* ---------------------------------------------- ug::Device::compile / run */
+/* The SSA kernel IR crosses the boundary verbatim: one ugb_ssa_instr per
+ * ssa::Instr (ug-core/src/lang.rs:690-709), a variable being the line number
+ * of the instruction that defines it (lang.rs:611-636). */
+typedef enum {
+  UGB_SSA_DEFINE_ACC = 0,   /* cst                                   DefineAcc(Const)            */
+  UGB_SSA_DEFINE_GLOBAL,    /* index, dtype                          DefineGlobal{index,dtype}   */
+  UGB_SSA_DEFINE_LOCAL,     /* index = size, dtype                   DefineLocal{size,dtype}     */
+  UGB_SSA_SPECIAL,          /* op = UGB_SSA_THREAD_IDX | BLOCK_IDX   Special                     */
+  UGB_SSA_CONST,            /* cst                                   Const(Const)                */
+  UGB_SSA_UNARY,            /* op = UGB_UNARY_*, a0, dtype           Unary{op,arg,dtype}         */
+  UGB_SSA_BINARY,           /* op = UGB_BINARY_*, a0, a1, dtype      Binary{op,lhs,rhs,dtype}    */
+  UGB_SSA_RANGE,            /* a0 = lo, a1 = up, index = step, v0    Range{lo,up,step,end_idx}   */
+  UGB_SSA_LOAD,             /* v0 = src, a0 = offset, dtype          Load{src,offset,dtype}      */
+  UGB_SSA_ASSIGN,           /* v0 = dst, a0 = src                    Assign{dst,src}             */
+  UGB_SSA_END_RANGE,        /* v0 = start_idx                        EndRange{start_idx}         */
+  UGB_SSA_IF,               /* a0 = cond, v0 = end_idx               If{cond,end_idx}            */
+  UGB_SSA_END_IF,           /*                                       EndIf                       */
+  UGB_SSA_STORE,            /* v0 = dst, a0 = offset, a1 = value     Store{dst,offset,value,..}  */
+  UGB_SSA_BARRIER,          /*                                       Barrier                     */
+  UGB_SSA_REDUCE_LOCAL      /* op = UGB_REDUCE_*, a0, dtype          ReduceLocal{op,arg,dtype}   */
+} ugb_ssa_kind;
+enum { UGB_SSA_THREAD_IDX = 0, UGB_SSA_BLOCK_IDX = 1 };
+enum { UGB_UNARY_ID = 0, UGB_UNARY_EXP, UGB_UNARY_SIN, UGB_UNARY_COS, UGB_UNARY_NEG, UGB_UNARY_SQRT, UGB_UNARY_CAST };
+enum { UGB_BINARY_ADD = 0, UGB_BINARY_SUB, UGB_BINARY_MUL, UGB_BINARY_DIV, UGB_BINARY_MOD, UGB_BINARY_MIN, UGB_BINARY_MAX };
+enum { UGB_REDUCE_SUM = 0, UGB_REDUCE_MAX, UGB_REDUCE_MIN };
+
+/* ssa::A (lang.rs:642-646): a variable, or an inline constant whose bit
+ * pattern sits in the low bits of `value` (f32: 32 bits, bf16/f16: 16 bits). */
+typedef struct {
+  int32_t is_var;
+  int32_t dtype;  /* constants only */
+  int64_t value;  /* variable id, or constant bits */
+} ugb_ssa_arg;
+
+typedef struct {
+  int32_t kind;   /* ugb_ssa_kind */
+  int32_t dtype;
+  int32_t op;
+  int32_t reserved;
+  int64_t index;
+  int64_t v0;
+  ugb_ssa_arg a0, a1;
+  ugb_ssa_arg cst;
+} ugb_ssa_instr;
+
+/* ug::Device::compile (lib.rs:56; ug-cuda/src/runtime.rs:247-264) with the
+ * kernel's LaunchConfig (lang.rs:34-45).  The kernel's pointer arguments are
+ * its DefineGlobal instructions in index order.  Errors in the IR or in the
+ * run-time compilation are UGB_ERR_COMPILE with the compiler log in the
+ * message. */
+UGB_API int32_t ugb_compile(ugb_device *dev, const ugb_ssa_instr *instrs, size_t n_instrs,
+                            uint32_t grid_dim, uint32_t block_dim, uint32_t shared_mem,
+                            const char *name, ugb_func **out);
+UGB_API int32_t ugb_func_free(ugb_func *f);
+/* The CUDA C this backend generated for the kernel (inspection, tests). */
+UGB_API const char *ugb_func_source(const ugb_func *f);
+/* ug::Device::run (lib.rs:60; runtime.rs:266-332): launches asynchronously on
+ * the device stream.  One slice per pointer argument, any number of them (the
+ * reference accepts 1 to 5); dtypes are checked; a zero grid or block
+ * dimension is a no-op (runtime.rs:269-277).  Loads and stores that fall
+ * outside the slice they address are skipped and reported as UGB_ERR_SHAPE
+ * by the next ugb_sync. */
+UGB_API int32_t ugb_run(ugb_device *dev, ugb_func *f, ugb_slice *const *args, size_t n_args);
+
 /* ------------------------------------------------------- ug::Device::matmul */
 
 /* ug::Device::matmul (ug-core/src/lib.rs:61-69; ug-cuda/src/gemm.rs:292-332):

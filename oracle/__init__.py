@@ -219,3 +219,50 @@ def gen_add(a, b):
     y = np.empty_like(a)
     _gen.ug_gen_add(_p(a), _p(b), _p(y), a.size)
     return y
+
+
+# ------------------------------------------------- CPU backend as a host-layer device
+class CpuOps:
+    """ug-llama's CPU operators (ug-llama/src/cpu_ops.rs) on slices of the oracle CPU device."""
+
+    def __init__(self, lib):
+        self._lib = lib
+
+    def _arr(self, raw, n, dtype=np.float32):
+        p = self._lib.oracle_cpu_slice_ptr(raw)
+        if not p:
+            raise ValueError("not a CPU slice")
+        ct = C.c_float if dtype == np.float32 else C.c_int32
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(ct)), shape=(max(n, 1),))[:n]
+
+    def softmax(self, src, dst, n_rows, n_cols):
+        n = n_rows * n_cols
+        _ops.ug_custom_softmax_f32(_p(self._arr(src, n)), _p(self._arr(dst, n)), n_rows, n_cols)
+
+    def causal_mask(self, src, dst, bh, s1, s2):
+        n = bh * s1 * s2
+        _ops.ug_causal_mask_f32(_p(self._arr(src, n)), _p(self._arr(dst, n)), bh, s1, s2)
+
+    def rope(self, interleaved, src, cos, sin, pos, dst, b, h, t, d):
+        n = b * h * t * d
+        fn = _ops.ug_rope_i_f32 if interleaved else _ops.ug_rope_f32
+        from ug_b200.lazy import host
+        nc = host.ugh_slice_len(cos)
+        fn(_p(self._arr(src, n)), _p(self._arr(cos, nc)), _p(self._arr(sin, nc)),
+           _p(self._arr(pos, 1, np.int32), _i32p), _p(self._arr(dst, n)), b, h, t, d)
+
+    def cat(self, lhs, rhs, dst, d1, d2_l, d2_r):
+        _ops.ug_cat_f32(_p(self._arr(lhs, d1 * d2_l)), _p(self._arr(rhs, d1 * d2_r)),
+                        _p(self._arr(dst, d1 * (d2_l + d2_r))), d1, d2_l, d2_r)
+
+
+def cpu_host_device():
+    """ug-core's CPU backend (oracle/cpu_device.cpp) as a ``ug_b200.lazy.HostDevice``."""
+    from ug_b200 import lazy
+    lib = C.CDLL(_build.build_cpu_device())
+    lib.oracle_cpu_device_new.restype = C.c_void_p
+    lib.oracle_cpu_slice_ptr.restype = C.c_void_p
+    lib.oracle_cpu_slice_ptr.argtypes = [C.c_void_p]
+    dev = lazy.HostDevice.adopt(lib.oracle_cpu_device_new(), CpuOps(lib))
+    dev._cpu_lib = lib
+    return dev

@@ -67,5 +67,27 @@ def build(verbose=False):
     return gen_so, ops_so
 
 
+def build_cpu_device(verbose=False):
+    """ug-core's CPU backend behind the C++ ug::Device interface of the host layer (cpu_device.cpp),
+    with the GEMM stand-in of ug_cpu_ops.c compiled in under its own arithmetic flags."""
+    os.makedirs(OUT, exist_ok=True)
+    tag = _cpu_tag()
+    so = os.path.join(OUT, f"liboracle_cpudev_{tag}.so")
+    cpp = os.path.join(HERE, "cpu_device.cpp")
+    ops = os.path.join(HERE, "ug_cpu_ops.c")
+    host_hdrs = [os.path.join(HERE, "..", "ug_b200", "csrc", "host", n)
+                 for n in ("ug_core.hpp", "ug_lower.hpp", "ug_graph.hpp")]
+    if _needs(so, [cpp, ops, __file__] + host_hdrs):
+        obj = os.path.join(OUT, f"ug_cpu_ops_{tag}.o")
+        c1 = ["gcc", "-c", ops, "-O3", "-march=native", "-fno-fast-math", "-ffp-contract=off", "-fopenmp", "-fPIC", "-o", obj]
+        c2 = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", cpp, obj, "-o", so, "-fopenmp", "-ldl"]
+        for c in (c1, c2):
+            if verbose:
+                print(" ".join(c))
+            subprocess.check_call(c)
+    return so
+
+
 if __name__ == "__main__":
     print(build(verbose=True))
+    print(build_cpu_device(verbose=True))

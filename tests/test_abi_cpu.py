@@ -43,3 +43,11 @@ def test_null_handles_are_rejected():
     assert lib.ugb_free(None) != 0
     assert lib.ugb_softmax(None, None, None, 1, 1) != 0
     assert lib.ugb_matmul(None, None, None, None, 1, 1, 1, 1, 2, None, None, 0, None, None, 0) != 0
+
+
+def test_host_layer_library_exports_its_header():
+    from ug_b200 import lazy
+    protos = _lib.parse_header(lazy.HOST_HEADER)
+    assert len(protos) >= 40
+    lib = C.CDLL(lazy.HOST_LIB)
+    assert not [n for n in protos if not hasattr(lib, n)]

@@ -1,0 +1,224 @@
+"""The host layer on the B200 device, and raw SSA kernels through
+ugb_compile / ugb_run.  The lazy-graph cases are the reference's fixtures
+(tests/lazy_cases.py); graph results are compared with the same graphs run on
+the CPU oracle device (fp32 reductions <= 1e-5 relative, copies bit-exact)."""
+import numpy as np
+import pytest
+
+import lazy_cases as cases
+import oracle
+from conftest import rel_err
+from oracle import llama_ref as R
+from ug_b200 import DType, UgError, synth
+from ug_b200.lazy import LB, BinaryOp as B, HostDevice, ReduceOp as Rd, Schedule, UnaryOp as U, ssa
+from ug_b200.llama import Config
+
+pytestmark = pytest.mark.gpu
+I = ssa.instr
+
+
+@pytest.fixture(scope="module")
+def hdev(dev):
+    return HostDevice(dev)
+
+
+@pytest.fixture(scope="module")
+def cpu():
+    return oracle.cpu_host_device()
+
+
+@pytest.fixture(params=["b200_policy", "reference_policy"])
+def policy(request, hdev):
+    hdev.set_launch_policy(request.param == "reference_policy")
+    yield request.param
+    hdev.set_launch_policy(False)
+
+
+@pytest.mark.parametrize("case", ["add", "mm", "cat", "schedule_one_kernel", "lb_copy", "schedule_broadcast",
+                                  "lb_layout", "lb_set", "errors", "cache_hits"])
+def test_reference_fixtures(hdev, policy, case):
+    getattr(cases, case)(hdev)
+    hdev.synchronize()
+
+
+def test_custom_ops(hdev, dev):
+    ones = dev.slice_from_values(np.ones(6, np.float32))
+
+    def add_one(s):
+        dev.add(hdev.ops._s(s[0]), ones, hdev.ops._s(s[1]), 6)
+
+    def add_one_ip(s):
+        dev.add(hdev.ops._s(s[0]), ones, hdev.ops._s(s[0]), 6)
+    cases.custom_ops(hdev, add_one, add_one_ip)
+
+
+def test_layout_chain(hdev, policy):
+    cases.layout_chain(hdev, synth.normal(1, (2, 5, 16)))
+
+
+@pytest.mark.parametrize("rows,cols", [(2, 4), (6, 300), (64, 256), (33, 1024), (5, 4096), (3, 777)])
+def test_graph_softmax_and_rms_silu_match_the_cpu_backend(hdev, cpu, policy, rows, cols):
+    if policy == "reference_policy" and rows * cols * cols > 2 ** 24:
+        pytest.skip("the reference launch shape re-runs the reduction per element: too slow to be useful")
+    x = synth.normal(2 + cols, (rows, cols), 2.0)
+    assert rel_err(cases.graph_softmax(hdev, x), cases.graph_softmax(cpu, x)) < 1e-5
+    g = synth.normal(3 + cols, (rows, cols))
+    w = synth.uniform(4 + cols, (cols,), 0.5, 1.5)
+    got, items = cases.graph_rms_silu(hdev, x, w, g)
+    want, _ = cases.graph_rms_silu(cpu, x, w, g)
+    assert items == ["Kernel"]
+    assert rel_err(got, want, 1e-20) < 1e-5
+
+
+def test_b200_policy_hoists_row_reductions(hdev):
+    """This backend's lowering of a row softmax: one block per row, 256 threads striding the row, the max /
+    sum evaluated once per row by a block reduction (the reference's shape re-runs them per element)."""
+    hdev.set_launch_policy(False)
+    x = LB.copy(synth.normal(5, (64, 1000)), (64, 1000), hdev)
+    from ug_b200 import llama_graph as G
+    s = Schedule.create_one(G.softmax(x))
+    assert s.items() == ["Kernel", "Kernel"]
+    ours, ref = s.ssa_text(0, policy=1), s.ssa_text(0, policy=0)
+    assert "launch grid=64 block=256" in ours and ours.count("reduce_local.max") == 1
+    assert "reduce_local" not in ref
+    pure_map = Schedule.create_one(x.unary(U.Exp).binary(B.Mul, x))
+    assert "launch grid=250 block=256" in pure_map.ssa_text(0, policy=1)     # 64000 elements, one thread each
+    assert "launch grid=1 block=1" in pure_map.ssa_text(0, policy=0)         # the reference: a single thread
+
+
+def test_llama_graph_on_b200_matches_the_cpu_oracle(hdev):
+    from ug_b200 import llama_graph as G
+    cfg = Config(hidden_size=64, intermediate_size=96, max_position_embeddings=32, num_attention_heads=4,
+                 num_key_value_heads=2, num_hidden_layers=2, vocab_size=50)
+    w = synth.llama_weights_f32(synth.llama_weights(cfg))
+    ref = R.Model(R.Config(**cfg.__dict__), w, custom_softmax_op=False)
+    toks = synth.tokens(6, (1, 7), cfg.vocab_size)
+    for custom in (False, True):
+        model = G.Model(cfg, w, hdev, custom_softmax_op=custom)
+        cache, rcache = model.new_cache(), ref.new_cache()
+        for lo, hi in ((0, 5), (5, 6), (6, 7)):
+            t = LB.copy(toks[:, lo:hi], (1, hi - lo), hdev)
+            pos = LB.copy(np.array([[lo]], np.int32), (1, 1), hdev)
+            got = model.fwd(t, pos, cache).data_vec().reshape(1, hi - lo, cfg.vocab_size)
+            want = ref.fwd(toks[:, lo:hi], lo, rcache)
+            assert np.max(np.abs(got - want)) < 1e-4 * np.abs(want).max()    # f32 everywhere, GEMM order differs
+
+
+# ------------------------------------------------------- raw SSA kernels ----
+def test_ssa_simple_add_reference_vector(dev):
+    # ug-core/src/samples.rs:10-28 run as ug-core/tests/cpu_tests.rs:3-16 does: [3,1,4,1,5,9] + [1..6]
+    i32 = DType.I32
+    k = [I("DefineGlobal", i32, index=0), I("DefineGlobal", i32, index=1), I("DefineGlobal", i32, index=2),
+         I("Range", a0=ssa.i32(0), a1=ssa.i32(6), index=1, v0=8),
+         I("Load", i32, v0=1, a0=3), I("Load", i32, v0=2, a0=3),
+         I("Binary", i32, op=B.Add, a0=4, a1=5), I("Store", i32, v0=0, a0=3, a1=6), I("EndRange", v0=3)]
+    f = dev.compile(k, name="foo")
+    v1 = dev.slice_from_values(np.zeros(6, np.int32))
+    v2 = dev.slice_from_values(np.array([3, 1, 4, 1, 5, 9], np.int32))
+    v3 = dev.slice_from_values(np.array([1, 2, 3, 4, 5, 6], np.int32))
+    dev.run(f, [v1, v2, v3])
+    dev.synchronize()
+    assert np.array_equal(v1.to_vec(), [4, 3, 7, 5, 10, 15])
+    assert '__global__ void ug_foo_' in f.source
+
+
+def test_ssa_dotprod_reference_vector(dev):
+    # ug-core/src/samples.rs:30-52 with the operands of ug-core/tests/basic_tests.rs:15-26 -> 12.0
+    f32 = DType.F32
+    k = [I("DefineGlobal", f32, index=0), I("DefineGlobal", f32, index=1), I("DefineGlobal", f32, index=2),
+         I("Const", cst=ssa.i32(0)), I("Const", cst=ssa.i32(2)), I("DefineAcc", cst=ssa.f32(0.0)),
+         I("Range", a0=3, a1=4, index=1, v0=12), I("Load", f32, v0=1, a0=6), I("Load", f32, v0=2, a0=6),
+         I("Binary", f32, op=B.Mul, a0=7, a1=8), I("Binary", f32, op=B.Add, a0=9, a1=5), I("Assign", v0=5, a0=10),
+         I("EndRange", v0=6), I("Store", f32, v0=0, a0=3, a1=5)]
+    f = dev.compile(k)
+    a = dev.slice_from_values(np.zeros(1, np.float32))
+    b = dev.slice_from_values(np.array([3., 4.5], np.float32))
+    c = dev.slice_from_values(np.array([1., 2.], np.float32))
+    dev.run(f, [a, b, c])
+    dev.synchronize()
+    assert a.to_vec()[0] == 12.0
+
+
+def softmax_reduce_kernel(dim2):
+    # ug-core/src/samples.rs:164-187: one block per row, one thread per column, two ReduceLocal
+    f32, i32 = DType.F32, DType.I32
+    return [I("DefineGlobal", f32, index=0), I("DefineGlobal", f32, index=1),
+            I("Special", i32, op=1), I("Special", i32, op=0),
+            I("Binary", i32, op=B.Mul, a0=2, a1=ssa.i32(dim2)), I("Binary", i32, op=B.Add, a0=4, a1=3),
+            I("Load", f32, v0=0, a0=5), I("ReduceLocal", f32, op=Rd.Max, a0=6),
+            I("Binary", f32, op=B.Sub, a0=6, a1=7), I("Unary", f32, op=U.Exp, a0=8),
+            I("ReduceLocal", f32, op=Rd.Sum, a0=9), I("Binary", f32, op=B.Div, a0=9, a1=10),
+            I("Store", f32, v0=1, a0=5, a1=11)]
+
+
+def test_ssa_softmax_reduce_reference_vector(dev):
+    # ug-core/tests/basic_tests.rs:91-116
+    x = np.array([0., 1., 2., 3., 2., 1., 2., 1.], np.float32)
+    gold = np.array([0.032058604, 0.08714432, 0.23688284, 0.6439143, 0.3655293, 0.13447072, 0.3655293, 0.13447072], np.float32)
+    f = dev.compile(softmax_reduce_kernel(4), grid_dim=2, block_dim=4)
+    src, dst = dev.slice_from_values(x), dev.allocate_uninit(DType.F32, 8)
+    dev.run(f, [src, dst])
+    dev.synchronize()
+    assert rel_err(dst.to_vec(), gold) < 3e-7
+
+
+@pytest.mark.parametrize("rows,cols", [(7, 32), (5, 100), (3, 1000), (2, 1024)])
+def test_ssa_softmax_reduce_any_block_size(dev, rows, cols):
+    x = synth.normal(20 + cols, (rows, cols), 2.0)
+    f = dev.compile(softmax_reduce_kernel(cols), grid_dim=rows, block_dim=cols)
+    src, dst = dev.slice_from_values(x), dev.allocate_uninit(DType.F32, x.size)
+    dev.run(f, [src, dst])
+    dev.synchronize()
+    assert rel_err(dst.to_vec().reshape(x.shape), oracle.custom_softmax(x)) < 1e-5
+
+
+def test_ssa_shared_memory_and_barrier(dev):
+    # DefineLocal + Barrier: reverse each block of 64 values through shared memory
+    f32, i32 = DType.F32, DType.I32
+    k = [I("DefineGlobal", f32, index=0), I("DefineGlobal", f32, index=1), I("DefineLocal", f32, index=64),
+         I("Special", i32, op=1), I("Special", i32, op=0),
+         I("Binary", i32, op=B.Mul, a0=3, a1=ssa.i32(64)), I("Binary", i32, op=B.Add, a0=5, a1=4),
+         I("Load", f32, v0=0, a0=6), I("Store", f32, v0=2, a0=4, a1=7), I("Barrier"),
+         I("Binary", i32, op=B.Sub, a0=ssa.i32(63), a1=4), I("Load", f32, v0=2, a0=10), I("Store", f32, v0=1, a0=6, a1=11)]
+    f = dev.compile(k, grid_dim=3, block_dim=64)
+    x = synth.normal(30, (3, 64))
+    src, dst = dev.slice_from_values(x), dev.allocate_uninit(DType.F32, x.size)
+    dev.run(f, [src, dst])
+    dev.synchronize()
+    assert np.array_equal(dst.to_vec().reshape(3, 64), x[:, ::-1])
+
+
+def test_ssa_out_of_range_access_is_reported_not_faulted(dev):
+    i32 = DType.I32
+    k = [I("DefineGlobal", i32, index=0), I("Const", cst=ssa.i32(7)), I("Store", i32, v0=0, a0=ssa.i32(1000), a1=1),
+         I("Store", i32, v0=0, a0=ssa.i32(2), a1=1)]
+    f = dev.compile(k)
+    s = dev.slice_from_values(np.zeros(4, np.int32))
+    dev.run(f, [s])
+    with pytest.raises(UgError) as e:
+        dev.synchronize()
+    assert e.value.code == 3
+    assert np.array_equal(s.to_vec(), [0, 0, 7, 0])       # the in-range store happened, the other was skipped
+    dev.synchronize()
+
+
+def test_ssa_errors(dev):
+    i32 = DType.I32
+    with pytest.raises(UgError) as e:       # arguments out of order (lang.rs:742-745)
+        dev.compile([I("DefineGlobal", i32, index=1)])
+    assert e.value.code == 8
+    with pytest.raises(UgError) as e:
+        dev.compile([I("DefineGlobal", i32, index=0), I("Range", a0=ssa.i32(0), a1=ssa.i32(2), index=1, v0=2)])
+    assert e.value.code == 8 and "unmatched" in e.value.msg
+    f = dev.compile([I("DefineGlobal", i32, index=0)])
+    fl = dev.allocate_uninit(DType.F32, 4)
+    with pytest.raises(UgError) as e:       # dtype of a kernel argument
+        dev.run(f, [fl])
+    assert e.value.code == 2
+    with pytest.raises(UgError) as e:       # arity
+        dev.run(f, [])
+    assert e.value.code == 1
+    z = dev.compile([I("DefineGlobal", i32, index=0)], grid_dim=0, block_dim=32)
+    n0 = dev.launch_count
+    dev.run(z, [dev.allocate_uninit(DType.I32, 4)])        # zero launch dimension: a no-op (runtime.rs:269-277)
+    assert dev.launch_count == n0

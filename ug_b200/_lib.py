@@ -16,6 +16,7 @@ HEADER = os.path.join(HERE, "..", "include", "ugb200.h")
 _CTYPES = {
     "int32_t": C.c_int32,
     "uint64_t": C.c_uint64,
+    "uint32_t": C.c_uint32,
     "size_t": C.c_size_t,
     "float": C.c_float,
     "void": None,
@@ -40,7 +41,7 @@ def parse_header(path=HEADER):
     text = open(path).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     protos = {}
-    for m in re.finditer(r"UGB_API\s+([^;(]+?)\s*\b(ugb_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S):
+    for m in re.finditer(r"UGB_API\s+([^;(]+?)\s*\b(ug[bh]_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S):
         ret, name, params = m.group(1), m.group(2), m.group(3)
         params = [p.strip() for p in params.replace("\n", " ").split(",")]
         if params == ["void"]:

@@ -63,7 +63,28 @@ def build(force=False, verbose=False):
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
         if verbose:
             print(f"linked {LIB}")
+    build_host(force=force or bool(jobs), verbose=verbose)
     return LIB
+
+
+HOST_DIR = os.path.join(CSRC, "host")
+HOST_LIB = os.path.join(HERE, "libughost.so")
+
+
+def build_host(force=False, verbose=False):
+    """g++ build of the host layer (lazy graph, scheduler, lowering) against libugb200.so."""
+    srcs = sorted(glob.glob(os.path.join(HOST_DIR, "*.cpp")))
+    deps = srcs + glob.glob(os.path.join(HOST_DIR, "*.hpp")) + glob.glob(os.path.join(HERE, "..", "include", "*.h")) + [LIB]
+    if not (force or _stale(HOST_LIB, deps)):
+        return HOST_LIB
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall", "-Wextra"] + srcs + \
+          ["-o", HOST_LIB, "-L" + HERE, "-lugb200", "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"host layer build failed:\n{r.stdout}\n{r.stderr}")
+    if verbose:
+        print(f"linked {HOST_LIB}")
+    return HOST_LIB
 
 
 if __name__ == "__main__":

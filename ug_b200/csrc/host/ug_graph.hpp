@@ -1,0 +1,179 @@
+// The backend contract and the lazy graph above it: restatement of
+// ug-core/src/lib.rs:29-73 (Slice / Device), lazy_buffer.rs (LazyBuffer, Op),
+// schedule.rs (Schedule, ScheduleItem, CompiledSchedule) and cache.rs.
+#pragma once
+#include "ug_lower.hpp"
+
+namespace ug {
+
+// ug::Slice (lib.rs:29-47)
+struct Slice {
+  virtual ~Slice() = default;
+  virtual DType dtype() const = 0;
+  virtual size_t len() const = 0;
+  virtual void copy_host_to_device(const void *src, size_t len, DType dtype) = 0;
+  virtual void copy_device_to_host(void *dst, size_t len, DType dtype) const = 0;
+  bool is_empty() const { return len() == 0; }
+};
+
+struct Func {
+  virtual ~Func() = default;
+};
+
+// How Schedule::compile picks the launch shape of a fused kernel.
+enum class LaunchPolicy {
+  Sequential,     // use_grid() == false: default Opts, every dim a sequential loop (the CPU backend)
+  ReferenceGrid,  // schedule.rs:162-188 as written
+  B200            // reduce-aware shapes of this backend (see choose_opts in ug_graph.cpp)
+};
+
+// ug::Device (lib.rs:49-73)
+struct Device {
+  virtual ~Device() = default;
+  virtual std::unique_ptr<Slice> allocate_uninit(DType dtype, size_t len) = 0;
+  virtual void synchronize() = 0;
+  virtual std::shared_ptr<Func> compile(const ssa::Kernel &kernel, const std::string *name) = 0;
+  virtual void run(Func &f, std::vector<Slice *> &args) = 0;
+  virtual void matmul(Slice &dst, const Slice &lhs, const Slice &rhs, size_t b, size_t m, size_t n, size_t k,
+                      const Layout &lhs_l, const Layout &rhs_l) = 0;
+  virtual bool use_grid() const = 0;
+  virtual LaunchPolicy launch_policy() const { return use_grid() ? LaunchPolicy::ReferenceGrid : LaunchPolicy::Sequential; }
+};
+
+using CustomF = std::function<void(std::vector<Slice *> &)>;
+
+struct LazyBufferInner;
+// LazyBuffer<D> (lazy_buffer.rs:86-112): a shared handle on a node of the op DAG.
+struct LazyBuffer {
+  std::shared_ptr<LazyBufferInner> p;
+  LazyBufferInner *operator->() const { return p.get(); }
+  explicit operator bool() const { return (bool)p; }
+
+  // builders, lazy_buffer.rs:229-765
+  LazyBuffer unary(UnaryOp op) const;
+  LazyBuffer cast(DType dtype) const;
+  LazyBuffer binary(BinaryOp op, const LazyBuffer &rhs) const;
+  LazyBuffer reduce(ReduceOp op, long dim) const;
+  LazyBuffer matmul(const LazyBuffer &rhs) const { return matmul_(rhs, false); }
+  LazyBuffer matmul_t(const LazyBuffer &rhs) const { return matmul_(rhs, true); }
+  LazyBuffer matmul_(const LazyBuffer &rhs, bool transpose) const;
+  LazyBuffer split_dim(long dim, size_t size1, size_t size2) const;
+  LazyBuffer merge_dims(long dim) const;
+  LazyBuffer squeeze(long dim) const;
+  LazyBuffer unsqueeze(long dim) const;
+  LazyBuffer reshape(const Shape &s) const;
+  LazyBuffer narrow(long dim, size_t offset, size_t length) const;
+  LazyBuffer broadcast(const Shape &s) const;
+  LazyBuffer transpose(long dim1, long dim2) const;
+  LazyBuffer custom_ip(CustomF f, std::vector<LazyBuffer> args) const;
+  LazyBuffer set(const LazyBuffer &values) const;
+  LazyBuffer set_l(const LazyBuffer &values, const Layout &dst_layout) const;
+
+  static LazyBuffer alloc_uninit(DType dtype, const Shape &s, Device *dev);
+  static LazyBuffer cst(Const c, const Shape &s, Device *dev);
+  static LazyBuffer copy(const void *data, size_t len, DType dtype, const Shape &s, Device *dev);
+  static LazyBuffer from_slice(std::unique_ptr<Slice> data, const Shape &s, Device *dev);
+  static LazyBuffer custom(CustomF f, std::vector<LazyBuffer> args, const Shape &s, DType dtype, Device *dev);
+  static LazyBuffer ssa(ssa::Kernel k, std::vector<LazyBuffer> args, const Shape &s, DType dtype, Device *dev);
+  static LazyBuffer cat(const std::vector<LazyBuffer> &args, long dim);
+
+  bool in_place_op() const;
+  bool realized() const;
+  void realize() const;
+  void maybe_allocate_uninit() const;
+  void data_vec(void *dst, size_t len, DType dtype) const;
+};
+
+// The storage cell shared by clones and by in-place ops (Arc<RefCell<Option<Slice>>>).
+struct DataCell {
+  std::unique_ptr<Slice> slice;
+};
+
+// lazy_buffer.rs:51-83
+struct Op {
+  enum Kind { Unary, Binary, MatMul, Reduce, Const, Value, Layout, Reshape, Custom, CustomIp, Ssa, Set } kind = Value;
+  UnaryOp uop;
+  BinaryOp bop = BinaryOp::Add;
+  ReduceOp rop = ReduceOp::Sum;
+  size_t reduce_dim = 0;
+  ug::Const cst;
+  op::LayoutOp lop;
+  size_t b = 0, m = 0, n = 0, k = 0;
+  bool transpose = false;
+  CustomF f;
+  ssa::Kernel ssa_kernel;
+  ug::Layout dst_layout;
+  LazyBuffer a0, a1;                // operand(s): arg | lhs, rhs | src, values
+  std::vector<LazyBuffer> args;     // Custom / CustomIp / Ssa
+};
+
+struct LazyBufferInner {
+  size_t id;
+  std::shared_ptr<DataCell> data;
+  Op op;
+  DType dtype;
+  Shape shape;
+  Device *device;
+  size_t rank() const { return shape.size(); }
+};
+
+// ------------------------------------------------------------- schedule ----
+using Args = std::vector<std::pair<ArgId, LazyBuffer>>;
+
+struct ScheduleItem {  // schedule.rs:42-60
+  enum Kind { Kernel, MatMul, Custom, Ssa } kind = Kernel;
+  // Kernel
+  op::AstP ast;
+  std::pair<ArgId, LazyBuffer> dst;
+  bool has_dst_layout = false;
+  Layout dst_layout;
+  // MatMul
+  LazyBuffer mm_dst, lhs, rhs;
+  size_t b = 0, m = 0, n = 0, k = 0;
+  bool transpose = false;
+  // Custom / Ssa
+  CustomF f;
+  ssa::Kernel ssa_kernel;
+  Args args;
+
+  op::Kernel kernel() const;  // schedule.rs:23-39
+};
+
+struct CompilationCache {  // cache.rs:73-101
+  std::map<NormalizedKernel, std::shared_ptr<Func>> op_cache;
+  std::map<std::vector<ssa::Instr>, std::shared_ptr<Func>> ssa_cache;
+  size_t hits = 0, misses = 0;
+};
+
+struct CompiledFunc {  // schedule.rs:209-227
+  enum Kind { Kernel, MatMul, Custom } kind = Kernel;
+  std::shared_ptr<Func> func;
+  Args args;
+  LazyBuffer dst, lhs, rhs;
+  size_t b = 0, m = 0, n = 0, k = 0;
+  bool transpose = false;
+  CustomF f;
+};
+
+struct CompiledSchedule {
+  std::vector<CompiledFunc> funcs;
+  Device *device = nullptr;
+  void run() const;  // schedule.rs:233-306
+};
+
+struct Schedule {
+  std::vector<ScheduleItem> items;
+  std::map<ArgId, LazyBuffer> per_arg_id;
+  Device *device = nullptr;
+
+  static Schedule create(const std::vector<LazyBuffer> &buffers);  // schedule.rs:78-101
+  static Schedule create_one(const LazyBuffer &b) { return create({b}); }
+  CompiledSchedule compile() const { CompilationCache c; return compile_with_cache(c); }
+  CompiledSchedule compile_with_cache(CompilationCache &cache) const;  // schedule.rs:115-207
+};
+
+// Launch shapes: the reference's heuristic and this backend's.
+Opts reference_opts(const op::Kernel &optimized);
+Opts b200_opts(const op::Kernel &optimized);
+
+}  // namespace ug

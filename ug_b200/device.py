@@ -66,7 +66,7 @@ class Slice:
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
-        if h and lib is not None and getattr(self.device, "_h", None):
+        if h and lib is not None and getattr(self.device, "_h", None) and not getattr(self, "_borrowed", False):
             lib.ugb_free(h)
 
     @property
@@ -102,6 +102,22 @@ class Slice:
         out = np.empty(len(self), dtype=np_dtype(self.dtype))
         self.copy_device_to_host(out)
         return out
+
+
+class Func:
+    """ug::Device::Func: a compiled SSA kernel with its launch configuration."""
+
+    def __init__(self, device, handle):
+        self.device, self._h = device, handle
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h and lib is not None and getattr(self.device, "_h", None):
+            lib.ugb_func_free(h)
+
+    @property
+    def source(self):
+        return (lib.ugb_func_source(self._h) or b"").decode()
 
 
 class Device:
@@ -143,6 +159,21 @@ class Device:
 
     def synchronize(self):
         self._check(lib.ugb_sync(self._h))
+
+    def compile(self, instrs, grid_dim=1, block_dim=1, shared_mem=0, name=None):
+        """ug::Device::compile: ``instrs`` is a list of ``ug_b200.lazy.SsaInstr`` (ssa::Instr in wire
+        form); the launch shape is the kernel's LaunchConfig (ug-core/src/lang.rs:34-45)."""
+        from .lazy import SsaInstr
+        arr = (SsaInstr * max(len(instrs), 1))(*instrs)
+        h = C.c_void_p()
+        self._check(lib.ugb_compile(self._h, arr, len(instrs), grid_dim, block_dim, shared_mem,
+                                    name.encode() if name else None, C.byref(h)))
+        return Func(self, h)
+
+    def run(self, func, args):
+        """ug::Device::run: one slice per pointer argument of the kernel."""
+        arr = (C.c_void_p * max(len(args), 1))(*[a._h for a in args])
+        self._check(lib.ugb_run(self._h, func._h, arr, len(args)))
 
     @property
     def launch_count(self):
