@@ -237,6 +237,24 @@ class SoftmaxWorkload(RmsSiluWorkload):
         ref = oracle.custom_softmax(self.x[:64])
         return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1e-30)))
 
+    def reference_cuda_gbs(self, steps=20):
+        """The reference's own softmax.cu (one warp per row, three passes; oracle/_ref) on the same buffers."""
+        import oracle
+        from ug_b200._lib import lib
+        ref = oracle.reference_cuda()
+        if ref is None:
+            return None
+        stream = lib.ugb_device_stream(self.dev._h)
+        run = lambda: ref.ugref_softmax_f32(self.xs.device_ptr, self.out.device_ptr, self.rows, self.cols, stream)
+        for _ in range(3):
+            run()
+        self.dev.synchronize()
+        self.dev.timer_begin()
+        for _ in range(steps):
+            run()
+        self.dev.timer_end()
+        return self.bytes_per_step * steps / (self.dev.timer_elapsed_ms() / 1e3) / 1e9
+
     def cpu_sample(self, budget_s):
         import oracle
         rows = 32
@@ -641,6 +659,11 @@ def main():
                          "traffic": None, "peak_source": peaks["source"]},
         }
         line.update(extra)
+        if hasattr(wl, "reference_cuda_gbs"):
+            g = wl.reference_cuda_gbs()
+            line["reference_cuda_kernel"] = None if g is None else {
+                "value": round(g, 1), "unit": "GB/s", "what": "ug-llama/src/softmax.cu compiled as is (fast-math), "
+                "launched as ug-llama/src/cuda_ops.rs does, same buffers"}
         line["parity_max_rel_err"] = wl.check()
         if not args.no_cpu_baseline:
             v, cores, sample = wl.cpu_sample(args.cpu_seconds)

@@ -266,3 +266,19 @@ def cpu_host_device():
     dev = lazy.HostDevice.adopt(lib.oracle_cpu_device_new(), CpuOps(lib))
     dev._cpu_lib = lib
     return dev
+
+
+# ------------------------------------- the reference's own CUDA kernels (oracle/_ref)
+def reference_cuda():
+    """ctypes handle on oracle/_ref/libugref_cuda.so (the reference's softmax.cu / rope.cu / cat.cu
+    compiled where they lie by oracle/build_ref.py), or None when it was not built."""
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref", "libugref_cuda.so")
+    if not os.path.exists(path):
+        return None
+    lib = C.CDLL(path)
+    vp, ci, cu = C.c_void_p, C.c_int, C.c_uint
+    lib.ugref_softmax_f32.argtypes = [vp, vp, ci, ci, vp]
+    lib.ugref_rope_f32.argtypes = [vp, vp, vp, vp, vp, cu, cu, cu, cu, vp]
+    lib.ugref_cat_f32.argtypes = [vp, vp, vp, cu, cu, cu, vp]
+    return lib
