@@ -542,9 +542,8 @@ def main():
     if args.steps is None:
         args.steps = 128 if args.workload == "decode" else 50
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
+    from ug_b200.dist import env_rank
+    rank, local_rank, world = env_rank()
 
     def make_workload(r):
         if args.workload == "decode":
@@ -556,12 +555,8 @@ def main():
             return 0
         return reference_arm(args, make_workload(0))
 
-    import torch
-    import torch.distributed as dist
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    from ug_b200.dist import Group
+    group = Group(backend="nccl" if world > 1 else None)
 
     import ug_b200
     dev = ug_b200.Device(local_rank)
@@ -574,9 +569,7 @@ def main():
 
     def barrier():
         dev.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+        group.barrier()
 
     for _ in range(args.warmup):
         wl.step()
@@ -610,10 +603,7 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     wl.teardown_e2e()
 
-    if world > 1:
-        t = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_s = t.tolist()
+    ms, e2e_s = group.max([ms, e2e_s])      # the slowest rank defines the step
 
     if rank == 0:
         peaks = measured_peaks()
@@ -670,9 +660,7 @@ def main():
             line["cpu_baseline"] = {"value": round(v, 4), "unit": wl.unit, "cores": cores,
                                     "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    group.close()
     return 0
 
 
