@@ -415,9 +415,8 @@ class DecodeWorkload:
             self.model.fwd(self.prompts[:, 0])
             self.model.reset(self.prefill)
         else:
-            # pre-fill: the prompts go through the same decode step, one position per step (untimed)
-            for i in range(self.prefill):
-                self.model.fwd(self.prompts[:, i])
+            # pre-fill (untimed): the prompts go through the causal prefill path
+            self.model.prefill(self.prompts)
         dev.synchronize()
         self.steps_done = 0
 
@@ -518,8 +517,105 @@ class DecodeWorkload:
                 "l2": "inputs larger than L2 (2.07 GB weights + ~3 GB KV cache read per step vs 126 MB L2)"}
 
 
+class PrefillWorkload(DecodeWorkload):
+    """Config 4: Llama-1.1B shape, 8 sequences x 512 prompt positions per GPU through the causal
+    prefill path (Model::fwd with seq_len > 1), last-position logits and next tokens as the result."""
+    name = ("Llama-1.1B-shape prefill (dim 2048, 22 layers, 32q/4kv heads, ffn 5632, vocab 32000, bf16 weights + "
+            "bf16 KV), 8 sequences x 512 positions per GPU")
+    metric = "tokens/s, Llama-1.1B-shape prefill (8 x 512 per GPU)"
+    unit = "tokens/s"
+    dtype = "bf16"
+    bound = "tensor"
+    sustained_peak = True          # ~200 kernels per step, seconds of back-to-back GEMMs: sustained bf16 figure
+    batch, prefill = 8, 512
+    step_is_graph = False
+
+    def __init__(self, rank, prefill=None, layers=None, fast_prefill=False):
+        super().__init__(rank, prefill=prefill, layers=layers)
+        c = self.cfg
+        t = self.prefill
+        rows = self.batch * t
+        # projections: 2 flops per weight per row (lm_head on the last position only);
+        # attention: QK^T and PV over the causal half, 4 * head_dim flops per (query, key, head)
+        self.flops_per_step = (2 * rows * (self.weight_bytes // 2 - c.vocab_size * c.hidden_size)
+                               + 2 * self.batch * c.vocab_size * c.hidden_size
+                               + c.num_hidden_layers * 4 * c.head_dim() * c.num_attention_heads * self.batch * t * (t + 1) // 2)
+        self.h2d_bytes = rows * 4
+        self.d2h_bytes = self.batch * 4
+        self.launches_per_step = 1 + 9 * c.num_hidden_layers + 3
+
+    def setup(self, dev):
+        from ug_b200 import DType
+        from ug_b200.llama import Model
+        self.dev = dev
+        self.model = Model.new(self.cfg, self.weights, dev, self.batch, self.prefill)
+        self.tok_dev = dev.slice_from_values(self.prompts.reshape(-1))
+        dev.synchronize()
+
+    def step(self):
+        self.model.reset(0)
+        self.model.prefill(self.tok_dev)
+
+    def units(self, step_seconds, n_ranks):
+        return n_ranks * self.batch * self.prefill / step_seconds
+
+    def setup_e2e(self):
+        import ctypes as C
+        from ug_b200._lib import lib
+        n = self.batch * self.prefill
+        self._pin = []
+        for attr, cnt in (("p_in", n), ("p_out", self.batch)):
+            p = C.c_void_p()
+            assert lib.ugb_host_alloc(cnt * 4, C.byref(p)) == 0
+            setattr(self, attr, p)
+            self._pin.append(p)
+        self.host_in = np.ctypeslib.as_array(C.cast(self.p_in, C.POINTER(C.c_int32)), shape=(n,))
+        self.host_in[:] = self.prompts.reshape(-1)
+
+    def e2e_step(self):
+        """Prompt ids host -> device, the prefill, chosen next ids device -> host."""
+        from ug_b200 import DType
+        from ug_b200._lib import lib
+        d = self.dev
+        d._check(lib.ugb_h2d_async(self.tok_dev._h, self.p_in, self.batch * self.prefill, int(DType.I32)))
+        self.model.reset(0)
+        d._check(lib.ugb_llama_prefill(self.model._h, self.tok_dev._h, self.prefill, 0))
+        d._check(lib.ugb_llama_read(self.model._h, 1, self.p_out, self.batch))     # blocking D2H
+
+    def check(self):
+        """Last-position logits of a prefill of the first 48 prompt positions against the CPU oracle of
+        ug-llama on the same weights, one sequence (max |diff| / max |logit|)."""
+        n = min(48, self.prefill)
+        ref = self._oracle()
+        want = ref.fwd(self.prompts[3:4, :n], 0, ref.new_cache())[0, -1]
+        self.model.reset(0)
+        self.model.prefill(self.prompts[:, :n])
+        got = self.model.logits()
+        return float(np.max(np.abs(got[3] - want)) / np.max(np.abs(want)))
+
+    def cpu_sample(self, budget_s):
+        """ug-llama's forward on the CPU oracle over the first positions of one prompt; tokens/s."""
+        ref = self._oracle()
+        n = 32
+        ref.fwd(self.prompts[:1, :8], 0, ref.new_cache())          # warm-up
+        done, t0 = 0, time.perf_counter()
+        while True:
+            ref.fwd(self.prompts[:1, :n], 0, ref.new_cache())
+            done += n
+            dt = time.perf_counter() - t0
+            if dt > budget_s or done >= 512:
+                break
+        return done / dt, os.cpu_count(), (f"{done} prompt positions in blocks of {n} (one sequence), oracle of ug-llama's "
+                                           f"CPU path (f32, GEMM stand-in on {os.cpu_count()} threads), {dt:.1f} s")
+
+    def config(self):
+        return {"workload": self.name, "sequences_per_gpu": self.batch, "prompt_positions": self.prefill,
+                "layers": self.cfg.num_hidden_layers,
+                "l2": "inputs larger than L2 (2.07 GB of weights read per step vs 126 MB L2)"}
+
+
 WORKLOADS = {"rms_silu": RmsSiluWorkload, "softmax": SoftmaxWorkload, "gemm": GemmWorkload,
-             "decode": DecodeWorkload}
+             "decode": DecodeWorkload, "prefill": PrefillWorkload}
 DEFAULT_WORKLOAD = "decode"
 
 
@@ -546,8 +642,8 @@ def main():
     rank, local_rank, world = env_rank()
 
     def make_workload(r):
-        if args.workload == "decode":
-            return DecodeWorkload(r, prefill=args.prefill, layers=args.layers, fast_prefill=args.fast_prefill)
+        if args.workload in ("decode", "prefill"):
+            return WORKLOADS[args.workload](r, prefill=args.prefill, layers=args.layers, fast_prefill=args.fast_prefill)
         return WORKLOADS[args.workload](r)
 
     if args.impl == "reference":
@@ -632,7 +728,8 @@ def main():
             if wl.bound == "hbm":
                 achieved, peak, runit = wl.bytes_per_step / wl.launches_per_step / launch_s / 1e9, peaks["hbm"], "GB/s"
             else:
-                achieved, peak, runit = wl.flops_per_step / wl.launches_per_step / launch_s / 1e12, peaks["bf16"], "TFLOP/s"
+                tpeak = peaks["bf16_sustained"] if getattr(wl, "sustained_peak", False) else peaks["bf16"]
+                achieved, peak, runit = wl.flops_per_step / wl.launches_per_step / launch_s / 1e12, tpeak, "TFLOP/s"
         line = {
             "metric": wl.metric, "value": round(value, 2), "unit": wl.unit, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5),

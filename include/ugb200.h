@@ -317,7 +317,7 @@ typedef struct {
   int32_t rope_interleaved; /* rope_interleaved (0 / 1)     */
 } ugb_llama_config;
 
-enum { UGB_LLAMA_LOGITS = 0, UGB_LLAMA_NEXT_TOKENS = 1, UGB_LLAMA_HIDDEN = 2 };
+enum { UGB_LLAMA_LOGITS = 0, UGB_LLAMA_NEXT_TOKENS = 1, UGB_LLAMA_HIDDEN = 2, UGB_LLAMA_PREFILL_LOGITS = 3 };
 
 /* Model::new + Cache::new (model.rs:183-198,298-363): allocates weights, the
  * RoPE tables (model.rs:278-295) and a KV cache for `batch` sequences of up to
@@ -333,7 +333,7 @@ UGB_API int32_t ugb_llama_load_weight(ugb_llama *m, const char *name, const ugb_
 /* Tuning knobs: "splits_qkv", "splits_o", "splits_down" (split-K factors of the
  * projections) and "att_splits" (KV slices per sequence and KV head), 1..8;
  * "bn_qkv", "bn_o", "bn_gate_up", "bn_down", "bn_lm_head" (GEMM tile width:
- * 64, 128 or 256). */
+ * 64, 128 or 256); "prefill_rows" (64..65536, see ugb_llama_prefill). */
 UGB_API int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value);
 /* Sets the number of cached positions (0 = empty cache); cache contents at
  * positions >= pos are ignored by later steps. */
@@ -345,8 +345,22 @@ UGB_API int32_t ugb_llama_kv_positions(const ugb_llama *m);
  * consumes the argmax of the previous step's logits (greedy decoding, ties to
  * the lowest id).  Asynchronous; results are read with ugb_llama_read. */
 UGB_API int32_t ugb_llama_decode(ugb_llama *m, const ugb_slice *tokens, int32_t n_steps);
+/* Model::fwd for seq_len == t > 1 (model.rs:365-374 with the causal mask of
+ * Attention::fwd, model.rs:231-245): consumes `tokens` (I32 [batch, t]), appends
+ * t positions to the KV cache of every sequence and leaves the logits of the
+ * LAST position in the place ugb_llama_decode leaves them, so that
+ * ugb_llama_decode(m, NULL, n) continues greedily from there.  The block is
+ * processed in chunks of positions bounded by option "prefill_rows" (rows =
+ * batch * positions per chunk, default 8192; set it before the first call);
+ * the projections run on the same tensor-core GEMM as decode with m = rows,
+ * attention is a causal flash kernel over the cache.  With all_logits != 0 the
+ * logits of every position are kept too (f32 [batch, t, vocab], the tensor
+ * Model::fwd returns) and read with UGB_LLAMA_PREFILL_LOGITS.  Asynchronous. */
+UGB_API int32_t ugb_llama_prefill(ugb_llama *m, const ugb_slice *tokens, int32_t t,
+                                  int32_t all_logits);
 /* Blocking read of the last step's logits (f32 [batch, vocab]), next tokens
- * (i32 [batch]) or final residual stream (f32 [batch, hidden]); len in elements. */
+ * (i32 [batch]), final residual stream (f32 [batch, hidden]) or the logits of
+ * the last all_logits prefill (f32 [batch, t, vocab]); len in elements. */
 UGB_API int32_t ugb_llama_read(ugb_llama *m, int32_t what, void *host_dst, size_t len);
 /* Blocking read of one layer's K (which = 0) or V (1) cache, bf16
  * [batch, n_kv_heads, ugb_llama_kv_positions, head_dim]. */

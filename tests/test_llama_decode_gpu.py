@@ -154,5 +154,16 @@ def test_engine_errors(dev):
     with pytest.raises(UgError):
         Model(Config(**{**TINY, "hidden_size": 96, "num_attention_heads": 2}), dev, 16, 32)   # head_dim 48
     with pytest.raises(UgError):
-        Model(cfg, dev, 4, 32)                                           # batch below the GEMM tile rule
+        Model(cfg, dev, 129, 32)                                         # more sequences than one GEMM row tile
     m.close()
+
+
+@pytest.mark.parametrize("batch", [1, 5])
+def test_decode_small_batches(dev, batch):
+    """Fewer sequences than the 16 rows of an MMA row group: the unused rows are zero-filled tiles."""
+    cfg = Config(**TINY)
+    gpu, ref = make(cfg, dev, batch, 64)
+    prompts = synth.tokens(17, (batch, 12), cfg.vocab_size)
+    worst, _ = run_teacher_forced(gpu, ref, prompts, check_seqs=sorted({0, batch - 1}))
+    assert worst < TOL
+    gpu.close()

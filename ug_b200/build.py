@@ -18,7 +18,7 @@ LIB = os.path.join(HERE, "libugb200.so")
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-CFLAGS = (["-DUGB_MBAR_TEST_WAIT"] if os.environ.get("UGB_TW") else []) + ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden",
+CFLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden",
           "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 
 

@@ -23,15 +23,18 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// x[b, :] = float(embed[tok[b], :]).  One CTA per row; ids outside the table
-// raise the status word and leave the row untouched.
+// x[r, :] = float(embed[id(r), :]) for row r = (sequence s, step i) = (r / t, r % t),
+// id(r) = tok[s * tok_stride + tok_off + i] (decode: t = 1, tok_stride = 1, tok_off = 0).
+// One CTA per row; ids outside the table raise the status word and leave the row
+// untouched.
 static __global__ void __launch_bounds__(256)
 embed_gather_kernel(const __nv_bfloat16 *__restrict__ embed, const int *__restrict__ tok,
-                    float *__restrict__ x, int hidden, int vocab, ugb_status_word *status) {
+                    float *__restrict__ x, int hidden, int vocab, ugb_status_word *status,
+                    int t, int tok_stride, int tok_off) {
   ugb_pdl_trigger();
   ugb_pdl_wait();
   const int b = blockIdx.x;
-  const int id = tok[b];
+  const int id = tok[(size_t)(b / t) * tok_stride + tok_off + b % t];
   if (id < 0 || id >= vocab) {
     if (threadIdx.x == 0 && atomicCAS(&status->code, 0u, (unsigned)UGB_ERR_INVALID) == 0u) status->detail = b;
     return;
@@ -97,29 +100,31 @@ reduce_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ part, int
   }
 }
 
-// qkv[b, :] = sum_s part[s][b][:]  (fp32), then
-//   q  -> rope -> bf16 q_out[b][head][d]
+// Row r = (sequence b, step i) = (r / t, r % t) of a block of t new positions per
+// sequence (decode: t = 1).  qkv[r, :] = sum_s part[s][r][:]  (fp32), then
+//   q  -> rope -> bf16 q_out[r][head][d]
 //   k  -> rope -> bf16 K cache [b][kvh][pos][d]
 //   v  ->         bf16 V cache [b][kvh][pos][d]
-// pos is read from device memory (every sequence of the batch sits at the same
-// position, the reference's pos[0] convention, cpu_ops.rs:67-71).  grid =
-// (batch, ceil(items / 256)): one thread per rotation pair or per v element, so
-// that all of a thread's loads are independent and issued at once.
+// with pos = *pos_p + pos_off + i: the base position is read from device memory
+// (every sequence of the batch sits at the same position, the reference's pos[0]
+// convention, cpu_ops.rs:67-71).  grid = (rows, ceil(items / 256)): one thread
+// per rotation pair or per v element, so that all of a thread's loads are
+// independent and issued at once.
 static __global__ void __launch_bounds__(256)
 rope_append_kernel(const float *__restrict__ part, int n_part, size_t part_stride,
                    const float *__restrict__ cos_, const float *__restrict__ sin_,
                    const int *__restrict__ pos_p, __nv_bfloat16 *__restrict__ q_out,
                    __nv_bfloat16 *__restrict__ kcache, __nv_bfloat16 *__restrict__ vcache,
-                   int n_heads, int n_kv, int hd, int t_max, int interleaved) {
+                   int n_heads, int n_kv, int hd, int t_max, int interleaved, int t, int pos_off) {
   ugb_pdl_trigger();
   ugb_pdl_wait();
-  const int b = blockIdx.x;
+  const int r = blockIdx.x, b = r / t;
   const int it = blockIdx.y * blockDim.x + threadIdx.x;
   const int half = hd >> 1;
   const int n_rot = (n_heads + n_kv) * half;
   const int qkv_dim = (n_heads + 2 * n_kv) * hd;
-  const float *row = part + (size_t)b * qkv_dim;
-  const int pos = *pos_p;
+  const float *row = part + (size_t)r * qkv_dim;
+  const int pos = *pos_p + pos_off + r % t;
   if (it < n_rot) {
     const int head = it / half, i = it - head * half;
     const int i1 = interleaved ? 2 * i : i;
@@ -133,7 +138,7 @@ rope_append_kernel(const float *__restrict__ part, int n_part, size_t part_strid
     const float y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn));
     const float y2 = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, c));
     __nv_bfloat16 *dst = head < n_heads
-        ? q_out + ((size_t)b * n_heads + head) * hd
+        ? q_out + ((size_t)r * n_heads + head) * hd
         : kcache + (((size_t)b * n_kv + (head - n_heads)) * t_max + pos) * hd;
     dst[i1] = __float2bfloat16_rn(y1);
     dst[i2] = __float2bfloat16_rn(y2);
@@ -434,6 +439,173 @@ static __global__ void rope_table_kernel(const float *__restrict__ inv_freq, flo
   const float ang = __fmul_rn((float)(i / half), inv_freq[i % half]);
   cos_[i] = cosf(ang);
   sin_[i] = sinf(ang);
+}
+
+}  // namespace ugb_decode
+
+namespace ugb_decode {
+
+// ------------------------------------------------------ prefill attention ---
+// Causal grouped-query attention for a block of `t` new positions per sequence
+// (Attention::fwd with seq_len > 1: repeat + q.kT + scale + causal_mask + softmax
+// + .v + head merge, ug-llama/src/model.rs:231-245, without materialising the
+// [b, h, t, T] score tensor).  Query i attends the cached positions
+// 0 .. pos0 + i (the reference's causal_mask assumes pos0 == 0,
+// ug-llama/src/cpu_ops.rs:33-56; a non-empty cache is the natural extension).
+//   q    bf16 [b, t, n_heads, 64]          (rope already applied)
+//   k, v bf16 [b, n_kv, t_max, 64]         (positions < pos0 + t are valid)
+//   out  bf16 [b, t, n_heads * 64]
+// grid (ceil(t / 64), n_heads, b), 128 threads: a CTA owns 64 queries of one
+// head, a warp 16 of them; K / V tiles of 64 keys are staged by cp.async in a
+// two-deep shared-memory ring; both contractions run on mma.sync m16n8k16 bf16
+// tiles with an online softmax in fp32 registers.
+constexpr int PF_BQ = 64, PF_BKV = 64;
+
+static __global__ void __launch_bounds__(128)
+prefill_attention_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restrict__ kcache,
+                         const __nv_bfloat16 *__restrict__ vcache, __nv_bfloat16 *__restrict__ out, int t, int pos0,
+                         int n_heads, int n_kv, int t_max, float scale) {
+  __shared__ __align__(128) uint8_t ks[2][PF_BKV * 128];
+  __shared__ __align__(128) uint8_t vs[2][PF_BKV * 128];
+  const int q0 = blockIdx.x * PF_BQ, head = blockIdx.y, b = blockIdx.z;
+  const int kvh = head / (n_heads / n_kv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  const __nv_bfloat16 *kbase = kcache + ((size_t)b * n_kv + kvh) * (size_t)t_max * ATT_HD;
+  const __nv_bfloat16 *vbase = vcache + ((size_t)b * n_kv + kvh) * (size_t)t_max * ATT_HD;
+
+  // rows of this lane: r_lo = q0 + 16*warp + g, r_hi = r_lo + 8 (query indexes inside the block of t)
+  const int r_lo = q0 + 16 * warp + g, r_hi = r_lo + 8;
+  uint32_t qa[4][4];
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    const int c = 16 * s + 2 * tq;
+    auto ld = [&](int row, int col) -> uint32_t {
+      if (row >= t) return 0u;
+      return *reinterpret_cast<const uint32_t *>(q + (((size_t)b * t + row) * n_heads + head) * ATT_HD + col);
+    };
+    qa[s][0] = ld(r_lo, c);
+    qa[s][1] = ld(r_hi, c);
+    qa[s][2] = ld(r_lo, c + 8);
+    qa[s][3] = ld(r_hi, c + 8);
+  }
+
+  const int last_q = min(q0 + PF_BQ, t) - 1;                 // last query of this CTA
+  const int n_keys = pos0 + last_q + 1;                       // keys any query of this CTA may attend
+  const int n_tiles = (n_keys + PF_BKV - 1) / PF_BKV;
+
+  auto issue = [&](int tile, int stage) {
+    const uint32_t kd = (uint32_t)__cvta_generic_to_shared(&ks[stage][0]);
+    const uint32_t vd = (uint32_t)__cvta_generic_to_shared(&vs[stage][0]);
+    const char *kg = reinterpret_cast<const char *>(kbase + (size_t)tile * PF_BKV * ATT_HD);
+    const char *vg = reinterpret_cast<const char *>(vbase + (size_t)tile * PF_BKV * ATT_HD);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {                              // 64 keys x 8 chunks of 16 B = 512 chunks, 4 per thread
+      const int c = threadIdx.x + 128 * i, key = c >> 3, ch = c & 7;
+      const uint32_t so = key * 128 + ((ch ^ (key & 7)) << 4);
+      if (tile * PF_BKV + key < t_max) {
+        cp_async16(kd + so, kg + c * 16);
+        cp_async16(vd + so, vg + c * 16);
+      } else {                                                 // past the end of the cache: zeros, masked below
+        *reinterpret_cast<uint4 *>(&ks[stage][so]) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4 *>(&vs[stage][so]) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    cp_async_commit();
+  };
+
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  float o[8][4];
+#pragma unroll
+  for (int d = 0; d < 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+  if (n_tiles > 0) issue(0, 0);
+  for (int j = 0; j < n_tiles; ++j) {
+    cp_async_wait<0>();
+    __syncthreads();                                           // tile j landed; everyone is done with tile j-1
+    if (j + 1 < n_tiles) issue(j + 1, (j + 1) & 1);
+    const uint32_t kd = (uint32_t)__cvta_generic_to_shared(&ks[j & 1][0]);
+    const uint32_t vd = (uint32_t)__cvta_generic_to_shared(&vs[j & 1][0]);
+
+    // S = Q K^T : 8 n-tiles of 8 keys
+    float s_acc[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      s_acc[n][0] = s_acc[n][1] = s_acc[n][2] = s_acc[n][3] = 0.f;
+#pragma unroll
+      for (int sp = 0; sp < 2; ++sp) {                         // two k-steps per ldmatrix.x4
+        const int mi = lane >> 3, ri = lane & 7;
+        const int key = 8 * n + ri, ch = 4 * sp + mi;          // matrices: dim chunks 4sp .. 4sp+3 of keys 8n..8n+7
+        uint32_t r0, r1, r2, r3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(kd + key * 128 + ((ch ^ (key & 7)) << 4)));
+        mma_bf16_16x8x16(s_acc[n], qa[2 * sp][0], qa[2 * sp][1], qa[2 * sp][2], qa[2 * sp][3], r0, r1);
+        mma_bf16_16x8x16(s_acc[n], qa[2 * sp + 1][0], qa[2 * sp + 1][1], qa[2 * sp + 1][2], qa[2 * sp + 1][3], r2, r3);
+      }
+    }
+    // scale + causal mask (key <= pos0 + query), online softmax for the two rows of this lane
+    const int key0 = j * PF_BKV;
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = key0 + 8 * n + 2 * tq + e;
+        s_acc[n][e] = key <= pos0 + r_lo ? s_acc[n][e] * scale : -INFINITY;
+        s_acc[n][2 + e] = key <= pos0 + r_hi ? s_acc[n][2 + e] * scale : -INFINITY;
+        mx_lo = fmaxf(mx_lo, s_acc[n][e]);
+        mx_hi = fmaxf(mx_hi, s_acc[n][2 + e]);
+      }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    // a row with nothing to attend yet in this tile keeps max = -inf: use 0 as the reference point
+    const float ref_lo = mn_lo == -INFINITY ? 0.f : mn_lo, ref_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+    const float a_lo = __expf(m_lo - ref_lo), a_hi = __expf(m_hi - ref_hi);
+    float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      s_acc[n][0] = __expf(s_acc[n][0] - ref_lo); s_acc[n][1] = __expf(s_acc[n][1] - ref_lo);
+      s_acc[n][2] = __expf(s_acc[n][2] - ref_hi); s_acc[n][3] = __expf(s_acc[n][3] - ref_hi);
+      sum_lo += s_acc[n][0] + s_acc[n][1];
+      sum_hi += s_acc[n][2] + s_acc[n][3];
+    }
+    l_lo = l_lo * a_lo + sum_lo; l_hi = l_hi * a_hi + sum_hi;
+    m_lo = mn_lo; m_hi = mn_hi;
+#pragma unroll
+    for (int d = 0; d < 8; ++d) { o[d][0] *= a_lo; o[d][1] *= a_lo; o[d][2] *= a_hi; o[d][3] *= a_hi; }
+
+    // O += P V : k = 64 keys in 4 steps of 16, 8 n-tiles of 8 dims
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const uint32_t pa0 = pack_bf16(s_acc[2 * kk][0], s_acc[2 * kk][1]), pa1 = pack_bf16(s_acc[2 * kk][2], s_acc[2 * kk][3]);
+      const uint32_t pa2 = pack_bf16(s_acc[2 * kk + 1][0], s_acc[2 * kk + 1][1]), pa3 = pack_bf16(s_acc[2 * kk + 1][2], s_acc[2 * kk + 1][3]);
+#pragma unroll
+      for (int d = 0; d < 8; d += 2) {
+        const int mi = lane >> 3, ri = lane & 7;
+        const int key = 16 * kk + ri + 8 * (mi & 1), ch = d + (mi >> 1);
+        uint32_t r0, r1, r2, r3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(vd + key * 128 + ((ch ^ (key & 7)) << 4)));
+        mma_bf16_16x8x16(o[d], pa0, pa1, pa2, pa3, r0, r1);
+        mma_bf16_16x8x16(o[d + 1], pa0, pa1, pa2, pa3, r2, r3);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+#pragma unroll
+  for (int d = 0; d < 8; ++d) {
+    const int col = head * ATT_HD + 8 * d + 2 * tq;
+    if (r_lo < t)
+      *reinterpret_cast<uint32_t *>(out + ((size_t)b * t + r_lo) * ((size_t)n_heads * ATT_HD) + col) = pack_bf16(o[d][0] * inv_lo, o[d][1] * inv_lo);
+    if (r_hi < t)
+      *reinterpret_cast<uint32_t *>(out + ((size_t)b * t + r_hi) * ((size_t)n_heads * ATT_HD) + col) = pack_bf16(o[d][2] * inv_hi, o[d][3] * inv_hi);
+  }
 }
 
 }  // namespace ugb_decode

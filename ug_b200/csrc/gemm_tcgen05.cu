@@ -87,11 +87,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-#ifdef UGB_MBAR_TEST_WAIT
-      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-#else
       "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-#endif
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
@@ -454,7 +450,7 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   // from L2 again and again, so it should be the smaller one: B (n x k) when n <= m, otherwise A.
   p.n_fast = n <= m ? 1 : 0;
   const long long out_cols = g.epi == UGB_EPI_SILU_MUL_BF16 ? (long long)n / 2 : (long long)n;
-  p.c_batch = (long long)m * out_cols;
+  p.c_batch = g.c_batch ? g.c_batch : (long long)m * out_cols;
   p.c_split = (long long)batch * m * out_cols;
   p.C = g.out;
   p.status = dev->status_dev;
@@ -510,7 +506,8 @@ int32_t ugb_tc_gemm(ugb_device *dev, const ugb_tc_gemm_args &g) {
     st->encode = (EncodeTiledFn)fn;
   }
   // A shared B with densely stacked A batches is one tall GEMM.
-  if (batch > 1 && g.b_batch == 0 && g.a_batch == (long long)(m * k)) {
+  const long long dense_c = (long long)m * (long long)(g.epi == UGB_EPI_SILU_MUL_BF16 ? n / 2 : n);
+  if (batch > 1 && g.b_batch == 0 && g.a_batch == (long long)(m * k) && (g.c_batch == 0 || g.c_batch == dense_c)) {
     m *= batch;
     batch = 1;
   }

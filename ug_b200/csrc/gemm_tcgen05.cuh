@@ -15,6 +15,7 @@ struct ugb_tc_gemm_args {
   const void *b;        // bf16 [n, k] row-major when b_is_nk, else [k, n] row-major
   size_t batch, m, n, k;
   long long a_batch, b_batch;   // elements between batch steps (b_batch 0 = shared operand)
+  long long c_batch = 0;        // output elements between batch steps; 0 = dense (m * output columns)
   bool b_is_nk;
   int epi;              // UGB_EPI_*
   int splits;           // split-K factor (only with UGB_EPI_F32); the kernel may use fewer

@@ -65,6 +65,17 @@ struct ugb_llama {
   bool warmed = false;
   std::vector<void *> allocs;
   size_t loaded = 0;
+  // prefill workspace, allocated by the first ugb_llama_prefill: activations of one chunk of
+  // pf_rows = batch * pf_chunk rows (pf_chunk positions of every sequence)
+  int pf_rows_max = 8192;         // option prefill_rows: upper bound on rows per chunk
+  int pf_rows = 0, pf_chunk = 0;
+  float *pf_x = nullptr, *pf_f32 = nullptr;            // residual stream; f32 GEMM output (qkv, o, down)
+  __nv_bfloat16 *pf_xn = nullptr, *pf_q = nullptr, *pf_att = nullptr, *pf_h = nullptr;
+  int *pf_tok = nullptr;
+  size_t pf_tok_cap = 0;
+  float *pf_logits = nullptr;     // [batch, pf_logits_t, vocab] when all-position logits were requested
+  int pf_logits_t = 0;
+  size_t pf_logits_cap = 0;
 };
 
 namespace {
@@ -113,34 +124,45 @@ int32_t put_vector(ugb_llama *m, const ugb_slice *w, float *dst, size_t n, const
   return UGB_OK;
 }
 
-int32_t gemm(ugb_llama *m, void *out, const __nv_bfloat16 *a, const __nv_bfloat16 *w, size_t n, size_t k,
-             int epi, int splits, int bn) {
+// out[rows, n] = a[rows, k] . w[n, k]^T on the tensor-core kernel (weights are the static operand).
+int32_t gemm_rows(ugb_llama *m, size_t rows, void *out, const __nv_bfloat16 *a, const __nv_bfloat16 *w, size_t n,
+                  size_t k, int epi, int splits, int bn) {
   ugb_tc_gemm_args g;
   g.out = out; g.a = a; g.b = w;
-  g.batch = 1; g.m = (size_t)m->batch; g.n = n; g.k = k;
+  g.batch = 1; g.m = rows; g.n = n; g.k = k;
   g.a_batch = 0; g.b_batch = 0; g.b_is_nk = true;
   g.epi = epi; g.splits = splits; g.bn = bn; g.b_static = true; g.pdl = m->pdl != 0;
   int32_t rc = ugb_tc_gemm(m->dev, g);
   if (rc == UGB_ERR_UNSUPPORTED)
-    return ugb_fail(m->dev, rc, "decode GEMM m=%d n=%zu k=%zu does not meet the tensor-core kernel's shape rules", m->batch, n, k);
+    return ugb_fail(m->dev, rc, "GEMM m=%zu n=%zu k=%zu does not meet the tensor-core kernel's shape rules", rows, n, k);
   return rc;
 }
 
-int32_t launch_reduce_rmsnorm(ugb_llama *m, const float *part, int n_part, const float *alpha) {
+int32_t gemm(ugb_llama *m, void *out, const __nv_bfloat16 *a, const __nv_bfloat16 *w, size_t n, size_t k,
+             int epi, int splits, int bn) {
+  return gemm_rows(m, (size_t)m->batch, out, a, w, n, k, epi, splits, bn);
+}
+
+int32_t launch_reduce_rmsnorm_rows(ugb_llama *m, int rows, float *x, __nv_bfloat16 *xn, const float *part, int n_part,
+                                   const float *alpha) {
   const int hidden = m->cfg.hidden;
   const int nvec = hidden / 4;
-  const size_t stride = (size_t)m->batch * hidden;
+  const size_t stride = (size_t)rows * hidden;
   const float inv_d = 1.0f / (float)hidden, eps = m->cfg.rms_eps;
-  dim3 grid(m->batch);
+  dim3 grid(rows);
   cudaStream_t st = m->dev->stream;
   const bool pdl = m->pdl != 0;
   cudaError_t e;
-  if (nvec <= 256) e = ugb_launch(reduce_rmsnorm_kernel<1>, grid, dim3(256), 0, st, pdl, m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
-  else if (nvec <= 512) e = ugb_launch(reduce_rmsnorm_kernel<2>, grid, dim3(256), 0, st, pdl, m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
-  else if (nvec <= 1024) e = ugb_launch(reduce_rmsnorm_kernel<4>, grid, dim3(256), 0, st, pdl, m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
-  else e = ugb_launch(reduce_rmsnorm_kernel<8>, grid, dim3(256), 0, st, pdl, m->x, part, n_part, stride, alpha, m->xn, hidden, inv_d, eps);
+  if (nvec <= 256) e = ugb_launch(reduce_rmsnorm_kernel<1>, grid, dim3(256), 0, st, pdl, x, part, n_part, stride, alpha, xn, hidden, inv_d, eps);
+  else if (nvec <= 512) e = ugb_launch(reduce_rmsnorm_kernel<2>, grid, dim3(256), 0, st, pdl, x, part, n_part, stride, alpha, xn, hidden, inv_d, eps);
+  else if (nvec <= 1024) e = ugb_launch(reduce_rmsnorm_kernel<4>, grid, dim3(256), 0, st, pdl, x, part, n_part, stride, alpha, xn, hidden, inv_d, eps);
+  else e = ugb_launch(reduce_rmsnorm_kernel<8>, grid, dim3(256), 0, st, pdl, x, part, n_part, stride, alpha, xn, hidden, inv_d, eps);
   if (e != cudaSuccess) return ugb_fail(m->dev, UGB_ERR_CUDA, "launch of reduce_rmsnorm_kernel failed: %s", cudaGetErrorString(e));
   return ugb_after_launch(m->dev, "reduce_rmsnorm_kernel");
+}
+
+int32_t launch_reduce_rmsnorm(ugb_llama *m, const float *part, int n_part, const float *alpha) {
+  return launch_reduce_rmsnorm_rows(m, m->batch, m->x, m->xn, part, n_part, alpha);
 }
 
 int32_t launch_attention(ugb_llama *m, const __nv_bfloat16 *kc, const __nv_bfloat16 *vc, float scale) {
@@ -172,7 +194,7 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
   const int B = m->batch, H = c.hidden;
   int32_t rc;
   const bool pdl = m->pdl != 0;
-  cudaError_t e = ugb_launch(embed_gather_kernel, dim3(B), dim3(256), 0, st, pdl, m->embed, tok, m->x, H, c.vocab, dev->status_dev);
+  cudaError_t e = ugb_launch(embed_gather_kernel, dim3(B), dim3(256), 0, st, pdl, m->embed, tok, m->x, H, c.vocab, dev->status_dev, 1, 1, 0);
   if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of embed_gather_kernel failed: %s", cudaGetErrorString(e));
   if ((rc = ugb_after_launch(dev, "embed_gather_kernel"))) return rc;
   const int s_qkv = ugb_tc_gemm_effective_splits(H, m->splits_qkv);
@@ -189,7 +211,7 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
     if (!(m->skip & 4))
     e = ugb_launch(rope_append_kernel, dim3(B, (rope_items + 255) / 256), dim3(256), 0, st, pdl, m->part, s_qkv,
                    (size_t)B * m->qkv_dim, m->cos, m->sin, m->pos, m->q, kc, vc, c.n_heads, c.n_kv_heads, c.head_dim,
-                   m->t_max, c.rope_interleaved);
+                   m->t_max, c.rope_interleaved, 1, 0);
     if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of rope_append_kernel failed: %s", cudaGetErrorString(e));
     if ((rc = ugb_after_launch(dev, "rope_append_kernel"))) return rc;
     if (!(m->skip & 8) && (rc = launch_attention(m, kc, vc, scale))) return rc;
@@ -203,6 +225,75 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
   e = ugb_launch(argmax_rows_kernel, dim3(B), dim3(1024), 0, st, pdl, m->logits, c.vocab, m->next, m->pos);
   if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of argmax_rows_kernel failed: %s", cudaGetErrorString(e));
   return ugb_after_launch(dev, "argmax_rows_kernel");
+}
+
+// Activations for one prefill chunk; allocated once, freed with the model.
+int32_t ensure_prefill_workspace(ugb_llama *m) {
+  if (m->pf_rows) return UGB_OK;
+  const ugb_llama_config &c = m->cfg;
+  int chunk = m->pf_rows_max / m->batch;
+  if (chunk < 1) chunk = 1;
+  if (chunk >= PF_BQ) chunk -= chunk % PF_BQ;     // whole query tiles per chunk
+  const size_t rows = (size_t)m->batch * chunk, H = c.hidden, F = c.ffn;
+  int32_t rc;
+  if ((rc = dmalloc(m, &m->pf_x, rows * H))) return rc;
+  if ((rc = dmalloc(m, &m->pf_f32, rows * std::max<size_t>(m->qkv_dim, H)))) return rc;
+  if ((rc = dmalloc(m, &m->pf_xn, rows * H))) return rc;
+  if ((rc = dmalloc(m, &m->pf_q, rows * H))) return rc;
+  if ((rc = dmalloc(m, &m->pf_att, rows * H))) return rc;
+  if ((rc = dmalloc(m, &m->pf_h, rows * F))) return rc;
+  m->pf_chunk = chunk;
+  m->pf_rows = (int)rows;
+  return UGB_OK;
+}
+
+// One chunk of a prefill: positions c0 .. c0 + tc - 1 of a block of t per sequence, cache positions
+// host_pos + c0 onwards.  Rows are ordered (sequence, position).
+int32_t enqueue_prefill_chunk(ugb_llama *m, const int *tok, int t, int c0, int tc, bool all_logits) {
+  ugb_device *dev = m->dev;
+  const ugb_llama_config &c = m->cfg;
+  cudaStream_t st = dev->stream;
+  const int B = m->batch, H = c.hidden, rows = B * tc;
+  const bool pdl = m->pdl != 0;
+  const float scale = powf((float)c.head_dim, -0.5f);   // model.rs:236
+  int32_t rc;
+  cudaError_t e = ugb_launch(embed_gather_kernel, dim3(rows), dim3(256), 0, st, pdl, m->embed, tok, m->pf_x, H, c.vocab,
+                             dev->status_dev, tc, t, c0);
+  if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of embed_gather_kernel failed: %s", cudaGetErrorString(e));
+  if ((rc = ugb_after_launch(dev, "embed_gather_kernel"))) return rc;
+  const int rope_items = (c.n_heads + c.n_kv_heads) * c.head_dim / 2 + c.n_kv_heads * c.head_dim;
+  for (int l = 0; l < c.layers; ++l) {
+    const LayerW &w = m->layers[l];
+    __nv_bfloat16 *kc = m->kcache + (size_t)l * m->kv_layer_stride;
+    __nv_bfloat16 *vc = m->vcache + (size_t)l * m->kv_layer_stride;
+    if ((rc = launch_reduce_rmsnorm_rows(m, rows, m->pf_x, m->pf_xn, m->pf_f32, l == 0 ? 0 : 1, w.rms1))) return rc;
+    if ((rc = gemm_rows(m, rows, m->pf_f32, m->pf_xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, 1, 0))) return rc;
+    e = ugb_launch(rope_append_kernel, dim3(rows, (rope_items + 255) / 256), dim3(256), 0, st, pdl, m->pf_f32, 1,
+                   (size_t)0, m->cos, m->sin, m->pos, m->pf_q, kc, vc, c.n_heads, c.n_kv_heads, c.head_dim, m->t_max,
+                   c.rope_interleaved, tc, c0);
+    if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of rope_append_kernel failed: %s", cudaGetErrorString(e));
+    if ((rc = ugb_after_launch(dev, "rope_append_kernel"))) return rc;
+    prefill_attention_kernel<<<dim3((tc + PF_BQ - 1) / PF_BQ, c.n_heads, B), 128, 0, st>>>(
+        m->pf_q, kc, vc, m->pf_att, tc, m->host_pos + c0, c.n_heads, c.n_kv_heads, m->t_max, scale);
+    if ((rc = ugb_after_launch(dev, "prefill_attention_kernel"))) return rc;
+    if ((rc = gemm_rows(m, rows, m->pf_f32, m->pf_att, w.wo, H, H, UGB_EPI_F32, 1, 0))) return rc;
+    if ((rc = launch_reduce_rmsnorm_rows(m, rows, m->pf_x, m->pf_xn, m->pf_f32, 1, w.rms2))) return rc;
+    if ((rc = gemm_rows(m, rows, m->pf_h, m->pf_xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, 0))) return rc;
+    if ((rc = gemm_rows(m, rows, m->pf_f32, m->pf_h, w.wdown, H, c.ffn, UGB_EPI_F32, 1, 0))) return rc;
+  }
+  if (all_logits) {
+    // final norm of every row, then logits[b, c0 + i, :] for the chunk as one GEMM batched over sequences
+    if ((rc = launch_reduce_rmsnorm_rows(m, rows, m->pf_x, m->pf_xn, m->pf_f32, 1, m->ln_f))) return rc;
+    ugb_tc_gemm_args g;
+    g.out = m->pf_logits + (size_t)c0 * c.vocab; g.a = m->pf_xn; g.b = m->embed;
+    g.batch = (size_t)B; g.m = (size_t)tc; g.n = (size_t)c.vocab; g.k = (size_t)H;
+    g.a_batch = (long long)tc * H; g.b_batch = 0; g.c_batch = (long long)t * c.vocab; g.b_is_nk = true;
+    g.epi = UGB_EPI_F32; g.splits = 1; g.bn = 0; g.b_static = true; g.pdl = pdl;
+    rc = ugb_tc_gemm(dev, g);
+    if (rc == UGB_ERR_UNSUPPORTED) return ugb_fail(dev, rc, "prefill lm_head GEMM does not meet the tensor-core kernel's shape rules");
+    if (rc) return rc;
+  }
+  return UGB_OK;
 }
 
 bool ends_with(const std::string &s, const char *suffix) {
@@ -228,7 +319,7 @@ int32_t ugb_llama_create(ugb_device *dev, const ugb_llama_config *cfg, int32_t b
               "query heads per KV head must divide evenly and be <= %d", ATT_GROUP);
   UGB_REQUIRE(dev, c.hidden % 8 == 0 && c.hidden <= 8192 && c.ffn % 8 == 0 && c.vocab % 8 == 0, UGB_ERR_UNSUPPORTED,
               "hidden, ffn and vocab must be multiples of 8 (hidden <= 8192)");
-  UGB_REQUIRE(dev, batch >= 16 && batch <= 128, UGB_ERR_UNSUPPORTED, "batch %d: the decode GEMMs take 16..128 sequences", batch);
+  UGB_REQUIRE(dev, batch >= 1 && batch <= 128, UGB_ERR_UNSUPPORTED, "batch %d: the decode kernels take 1..128 sequences", batch);
   UGB_REQUIRE(dev, t_max >= 1 && t_max <= c.max_pos, UGB_ERR_INVALID, "t_max %d outside 1..max_pos %d", t_max, c.max_pos);
   UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
 
@@ -310,6 +401,7 @@ int32_t ugb_llama_destroy(ugb_llama *m) {
   cudaStreamSynchronize(m->dev->stream);
   if (m->graph) cudaGraphExecDestroy(m->graph);
   for (void *p : m->allocs) cudaFree(p);
+  if (m->pf_logits) cudaFree(m->pf_logits);
   delete m;
   return UGB_OK;
 }
@@ -359,6 +451,12 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
   if (k == "pdl") {
     m->pdl = value != 0;
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    return UGB_OK;
+  }
+  if (k == "prefill_rows") {
+    UGB_REQUIRE(dev, value >= 64 && value <= 65536, UGB_ERR_INVALID, "option prefill_rows: %d outside 64..65536", value);
+    UGB_REQUIRE(dev, m->pf_rows == 0, UGB_ERR_INVALID, "option prefill_rows must be set before the first prefill");
+    m->pf_rows_max = value;
     return UGB_OK;
   }
   if (k.compare(0, 3, "bn_") == 0) {
@@ -437,6 +535,55 @@ int32_t ugb_llama_decode(ugb_llama *m, const ugb_slice *tokens, int32_t n_steps)
   return UGB_OK;
 }
 
+int32_t ugb_llama_prefill(ugb_llama *m, const ugb_slice *tokens, int32_t t, int32_t all_logits) {
+  if (!m) return UGB_ERR_INVALID;
+  ugb_device *dev = m->dev;
+  UGB_REQUIRE(dev, t >= 1, UGB_ERR_INVALID, "prefill of %d positions", t);
+  UGB_REQUIRE(dev, tokens != nullptr, UGB_ERR_INVALID, "ugb_llama_prefill: null tokens");
+  UGB_SLICE(dev, tokens, UGB_I32, (size_t)m->batch * t);
+  UGB_REQUIRE(dev, m->host_pos + t <= m->t_max && m->host_pos + t <= m->cfg.max_pos, UGB_ERR_SHAPE,
+              "prefill of %d positions from position %d exceeds the KV cache (%d positions)", t, m->host_pos, m->t_max);
+  UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
+  const ugb_llama_config &c = m->cfg;
+  const size_t H = c.hidden;
+  int32_t rc;
+  if ((rc = ensure_prefill_workspace(m))) return rc;
+  if (all_logits) {
+    const size_t need = (size_t)m->batch * t * c.vocab;
+    if (need > m->pf_logits_cap) {
+      UGB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+      if (m->pf_logits) { cudaFree(m->pf_logits); m->pf_logits = nullptr; m->pf_logits_cap = 0; }
+      void *v = nullptr;
+      UGB_CUDA(dev, cudaMalloc(&v, need * sizeof(float)));
+      m->pf_logits = (float *)v;
+      m->pf_logits_cap = need;
+    }
+    m->pf_logits_t = t;
+  }
+  const int *tok = (const int *)tokens->ptr;
+  int tc = 0;
+  for (int c0 = 0; c0 < t; c0 += tc) {
+    tc = std::min(m->pf_chunk, t - c0);
+    if ((rc = enqueue_prefill_chunk(m, tok, t, c0, tc, all_logits != 0))) return rc;
+  }
+  // Last position of every sequence -> the decode-shaped buffers, final norm, lm_head, argmax.
+  UGB_CUDA(dev, cudaMemcpy2DAsync(m->x, H * 4, m->pf_x + (size_t)(tc - 1) * H, (size_t)tc * H * 4, H * 4, m->batch,
+                                  cudaMemcpyDeviceToDevice, dev->stream));
+  if (!all_logits)
+    UGB_CUDA(dev, cudaMemcpy2DAsync(m->part, H * 4, m->pf_f32 + (size_t)(tc - 1) * H, (size_t)tc * H * 4, H * 4, m->batch,
+                                    cudaMemcpyDeviceToDevice, dev->stream));
+  if ((rc = launch_reduce_rmsnorm(m, m->part, all_logits ? 0 : 1, m->ln_f))) return rc;
+  if ((rc = gemm(m, m->logits, m->xn, m->embed, c.vocab, c.hidden, UGB_EPI_F32, 1, m->bn_lm_head))) return rc;
+  const int last = m->host_pos + t - 1;     // argmax_rows_kernel advances the device-side position by one
+  UGB_CUDA(dev, cudaMemcpyAsync(m->pos, &last, 4, cudaMemcpyHostToDevice, dev->stream));
+  cudaError_t e = ugb_launch(argmax_rows_kernel, dim3(m->batch), dim3(1024), 0, dev->stream, false, m->logits, c.vocab,
+                             m->next, m->pos);
+  if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of argmax_rows_kernel failed: %s", cudaGetErrorString(e));
+  if ((rc = ugb_after_launch(dev, "argmax_rows_kernel"))) return rc;
+  m->host_pos += t;
+  return UGB_OK;
+}
+
 int32_t ugb_llama_read(ugb_llama *m, int32_t what, void *host_dst, size_t len) {
   if (!m) return UGB_ERR_INVALID;
   ugb_device *dev = m->dev;
@@ -447,6 +594,9 @@ int32_t ugb_llama_read(ugb_llama *m, int32_t what, void *host_dst, size_t len) {
     case UGB_LLAMA_LOGITS: src = m->logits; n = (size_t)m->batch * m->cfg.vocab; break;
     case UGB_LLAMA_NEXT_TOKENS: src = m->next; n = (size_t)m->batch; break;
     case UGB_LLAMA_HIDDEN: src = m->x; n = (size_t)m->batch * m->cfg.hidden; break;
+    case UGB_LLAMA_PREFILL_LOGITS:
+      UGB_REQUIRE(dev, m->pf_logits && m->pf_logits_t > 0, UGB_ERR_INVALID, "no all-position logits: run ugb_llama_prefill with all_logits first");
+      src = m->pf_logits; n = (size_t)m->batch * m->pf_logits_t * m->cfg.vocab; break;
     default: return ugb_fail(dev, UGB_ERR_INVALID, "ugb_llama_read: unknown selector %d", what);
   }
   UGB_REQUIRE(dev, len == n, UGB_ERR_SHAPE, "ugb_llama_read: destination holds %zu elements, %zu expected", len, n);

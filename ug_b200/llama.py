@@ -121,10 +121,35 @@ class Model:
         return lib.ugb_llama_position(self._h)
 
     def fwd(self, tokens):
-        """One step on explicit token ids (int32 [batch] or [batch, 1]); asynchronous."""
-        tokens = np.ascontiguousarray(tokens, dtype=np.int32).reshape(-1)
-        s = self.dev.slice_from_values(tokens)
+        """Model::fwd on explicit token ids, asynchronous: int32 [batch] or [batch, 1] is one
+        decode step; [batch, t] with t > 1 appends t positions (causal prefill) and keeps the
+        logits of every position for :meth:`prefill_logits`."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        if tokens.ndim == 2 and tokens.shape[1] > 1:
+            return self.prefill(tokens, all_logits=True)
+        s = self.dev.slice_from_values(tokens.reshape(-1))
         self.dev._check(lib.ugb_llama_decode(self._h, s._h, 1))
+
+    def prefill(self, tokens, all_logits=False):
+        """Appends ``tokens`` (int32 [batch, t], host array or device Slice of batch*t ids) to
+        every sequence; :meth:`logits` / :meth:`next_tokens` then refer to the last position."""
+        if isinstance(tokens, np.ndarray) or not hasattr(tokens, "_h"):
+            tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+            if tokens.ndim != 2 or tokens.shape[0] != self.batch:
+                raise UgError(4, f"prefill tokens must be [batch={self.batch}, t], got {tokens.shape}")
+            t = tokens.shape[1]
+            s = self.dev.slice_from_values(tokens.reshape(-1))
+        else:
+            s, t = tokens, tokens.len // self.batch
+        self.dev._check(lib.ugb_llama_prefill(self._h, s._h, t, int(all_logits)))
+        self._prefill_t = t if all_logits else getattr(self, "_prefill_t", 0)
+
+    def prefill_logits(self):
+        """f32 [batch, t, vocab] of the last ``all_logits`` prefill (what Model::fwd returns)."""
+        t = getattr(self, "_prefill_t", 0)
+        out = np.empty((self.batch, t, self.cfg.vocab_size), np.float32)
+        self.dev._check(lib.ugb_llama_read(self._h, 3, out.ctypes.data, out.size))
+        return out
 
     def decode(self, n_steps):
         """Greedy decoding: each step feeds the previous step's argmax; asynchronous."""
