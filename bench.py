@@ -356,6 +356,7 @@ class GemmWorkload:
         from ug_b200 import synth
         a = synth.bf16_bits_to_f32(self.a).reshape(-1, self.k)
         b = synth.bf16_bits_to_f32(self.b)
+        threads = oracle.set_threads(os.cpu_count())
         rows = 64
         t0 = time.perf_counter()
         oracle.matmul(a[:rows], b)
@@ -364,8 +365,8 @@ class GemmWorkload:
         t0 = time.perf_counter()
         oracle.matmul(a[:rows], b)
         dt = time.perf_counter() - t0
-        return 2 * rows * self.n * self.k / dt / 1e12, os.cpu_count(), \
-            f"{rows} of {a.shape[0]} lhs rows, f32 GEMM stand-in for crate gemm, {os.cpu_count()} threads, {dt:.1f} s"
+        return 2 * rows * self.n * self.k / dt / 1e12, threads, \
+            f"{rows} of {a.shape[0]} lhs rows, f32 GEMM stand-in for crate gemm, {threads} threads, {dt:.1f} s"
 
     def config(self):
         return {"workload": self.name, "batch_per_gpu": self.bs, "m": self.m, "n": self.n, "k": self.k,
@@ -483,7 +484,9 @@ class DecodeWorkload:
 
     def _oracle(self):
         if getattr(self, "_ref", None) is None:
+            import oracle
             from oracle import llama_ref as R
+            self.cpu_threads = oracle.set_threads(os.cpu_count())
             from ug_b200 import synth
             self._ref = R.Model(R.Config(**self.cfg.__dict__), synth.llama_weights_f32(self.weights))
         return self._ref
@@ -508,8 +511,8 @@ class DecodeWorkload:
             dt = time.perf_counter() - t0
             if dt > budget_s or n >= 64:
                 break
-        return n / dt, os.cpu_count(), (f"{n} greedy tokens of 1 sequence at KV depth {self.prefill}+, oracle of "
-                                        f"ug-llama's CPU path (f32, GEMM stand-in on {os.cpu_count()} threads), {dt:.1f} s")
+        return n / dt, self.cpu_threads, (f"{n} greedy tokens of 1 sequence at KV depth {self.prefill}+, oracle of "
+                                          f"ug-llama's CPU path (f32, GEMM stand-in on {self.cpu_threads} threads), {dt:.1f} s")
 
     def config(self):
         return {"workload": self.name, "sequences_per_gpu": self.batch, "prefill": self.prefill,
@@ -605,8 +608,8 @@ class PrefillWorkload(DecodeWorkload):
             dt = time.perf_counter() - t0
             if dt > budget_s or done >= 512:
                 break
-        return done / dt, os.cpu_count(), (f"{done} prompt positions in blocks of {n} (one sequence), oracle of ug-llama's "
-                                           f"CPU path (f32, GEMM stand-in on {os.cpu_count()} threads), {dt:.1f} s")
+        return done / dt, self.cpu_threads, (f"{done} prompt positions in blocks of {n} (one sequence), oracle of ug-llama's "
+                                             f"CPU path (f32, GEMM stand-in on {self.cpu_threads} threads), {dt:.1f} s")
 
     def config(self):
         return {"workload": self.name, "sequences_per_gpu": self.batch, "prompt_positions": self.prefill,

@@ -17,6 +17,15 @@ _gen_path, _ops_path = _build.build()
 _gen = C.CDLL(_gen_path)
 _ops = C.CDLL(_ops_path)
 
+_ops.ug_set_threads.restype = C.c_int
+_ops.ug_set_threads.argtypes = [C.c_int]
+
+
+def set_threads(n=0):
+    """Threads of the oracle's row loops and GEMM stand-in (0 = leave as is); returns the count in force."""
+    return int(_ops.ug_set_threads(int(n)))
+
+
 _f32p = C.POINTER(C.c_float)
 _i32p = C.POINTER(C.c_int32)
 _u16p = C.POINTER(C.c_uint16)

@@ -21,6 +21,22 @@
 #include <stddef.h>
 #include <stdint.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* Thread count of the row loops below (rayon uses every core by default;
+ * launchers such as torchrun export OMP_NUM_THREADS=1, which would silently
+ * serialise the oracle).  Returns the count now in force. */
+int ug_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
 
 /* ug-llama/src/cpu_ops.rs:6-31 -- custom_softmax: per row, running max with
  * f32::max, exp(x - max) written to dst, sequential sum of dst, divide. */
