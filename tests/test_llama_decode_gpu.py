@@ -167,3 +167,22 @@ def test_decode_small_batches(dev, batch):
     worst, _ = run_teacher_forced(gpu, ref, prompts, check_seqs=sorted({0, batch - 1}))
     assert worst < TOL
     gpu.close()
+
+
+@pytest.mark.parametrize("bn", [80, 96, 128, 256])
+def test_gemm_tile_widths_agree(dev, bn):
+    """Every projection on another tile width (80 / 96 leave a ragged last tile and a partly used
+    32-column accumulator chunk) reproduces the default configuration's logits."""
+    cfg = Config(**{**TINY, "hidden_size": 256, "num_attention_heads": 4, "intermediate_size": 352})
+    gpu, ref = make(cfg, dev, 16, 64)
+    prompts = synth.tokens(19, (16, 9), cfg.vocab_size)
+    worst, _ = run_teacher_forced(gpu, ref, prompts, check_seqs=[4])
+    assert worst < TOL
+    base = gpu.logits()
+    for key in ("bn_qkv", "bn_o", "bn_gate_up", "bn_down", "bn_lm_head"):
+        gpu.set_option(key, bn)
+    gpu.set_option("gemm_smem_kib", 64)
+    worst, _ = run_teacher_forced(gpu, ref, prompts, check_seqs=[4])
+    assert worst < TOL
+    assert np.max(np.abs(gpu.logits() - base)) < 2e-3 * np.abs(base).max()
+    gpu.close()

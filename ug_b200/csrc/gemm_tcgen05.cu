@@ -46,7 +46,9 @@ template <int BM, int BN> struct Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int FIT = (220 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = FIT > 12 ? 12 : FIT;
-  static constexpr int TMEM_COLS = ACC_STAGES * BN;   // 512, 256 or 128 (powers of two)
+  // TMEM columns between the accumulator stages (a power of two >= BN) and columns allocated
+  static constexpr int ACC_STRIDE = BN <= 64 ? 64 : (BN <= 128 ? 128 : 256);
+  static constexpr int TMEM_COLS = ACC_STAGES * ACC_STRIDE;   // 512, 256 or 128 (powers of two)
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
@@ -60,6 +62,7 @@ struct Params {
   int stage_tx;           // bytes one pipeline stage receives (A box + B box)
   int n_fast;             // tile order: 1 = n-tiles vary fastest (a wave re-reads B, the smaller operand)
   int b_static;           // 1: no kernel on the stream writes B (weights): it may be fetched before ugb_pdl_wait
+  int stages;             // depth of the shared-memory ring in use (2 .. Cfg::STAGES)
   long long c_batch;      // output elements between batch steps
   long long c_split;      // output elements between split-K partials
   void *C;
@@ -163,7 +166,7 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major)
 template <int BM, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
-  constexpr int STAGES = Cfg<BM, BN>::STAGES;
+  const int STAGES = p.stages;
   constexpr int STAGE_BYTES = Cfg<BM, BN>::STAGE_BYTES;
   constexpr int A_BYTES = Cfg<BM, BN>::A_BYTES;
   constexpr int TMEM_COLS = Cfg<BM, BN>::TMEM_COLS;
@@ -280,7 +283,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1u, abort_flag, p.status, 2)) break;
         tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * Cfg<BM, BN>::ACC_STRIDE);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&full[stage]), phase, abort_flag, p.status, 3)) { alive = false; break; }
           tcgen05_fence_after();
@@ -323,9 +326,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int row = BM == 128 ? m0 + quad * 32 + lane : m0 + quad * 16 + lane;
       const long long out_off = (long long)sp * p.c_split + (long long)bi * p.c_batch;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < (BN + 31) / 32; ++c) {      // a tile width that is not a multiple of 32 ends in a partly used chunk
         uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * Cfg<BM, BN>::ACC_STRIDE + c * 32), v);
         tmem_ld_wait();
         if (row_lane && row < p.M) {
           const int col0 = n0 + c * 32;
@@ -333,7 +336,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             __nv_bfloat16 *crow = (__nv_bfloat16 *)p.C + out_off + (long long)row * p.N + col0;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              if (col0 + q * 8 < p.N) {                // N % 8 == 0: a chunk of 8 is all in or all out
+              if (c * 32 + q * 8 < BN && col0 + q * 8 < p.N) {   // BN % 8 == N % 8 == 0: a chunk of 8 is all in or all out
                 uint4 o;
                 __nv_bfloat162 t;
                 t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])); o.x = *(uint32_t *)&t;
@@ -347,14 +350,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             float *crow = (float *)p.C + out_off + (long long)row * p.N + col0;
 #pragma unroll
             for (int q = 0; q < 8; ++q)
-              if (col0 + q * 4 < p.N)
+              if (c * 32 + q * 4 < BN && col0 + q * 4 < p.N)
                 *reinterpret_cast<uint4 *>(crow + q * 4) = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
           } else {
             // UGB_EPI_SILU_MUL_BF16: columns come in (gate, up) pairs; out [M, N/2] bf16
             __nv_bfloat16 *crow = (__nv_bfloat16 *)p.C + out_off + (long long)row * (p.N / 2) + col0 / 2;
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
-              if (col0 + q * 16 < p.N) {
+              if (c * 32 + q * 16 < BN && col0 + q * 16 < p.N) {
                 uint32_t o[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -401,7 +404,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 
 struct TcState {
   EncodeTiledFn encode = nullptr;
-  bool attr_set[6] = {false, false, false, false, false, false};
+  bool attr_set[8] = {false, false, false, false, false, false, false, false};
 };
 
 TcState *state_of(ugb_device *dev) {
@@ -427,7 +430,7 @@ int32_t encode_map(ugb_device *dev, TcState *st, CUtensorMap *map, const void *b
 template <int BM, int BN>
 int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_t batch, size_t m) {
   const size_t n = g.n, k = g.k;
-  constexpr int slot = (BN == 256 ? 2 : (BN == 128 ? 1 : 0)) + (BM == 64 ? 3 : 0);
+  constexpr int slot = BN == 80 ? 6 : BN == 96 ? 7 : (BN == 256 ? 2 : (BN == 128 ? 1 : 0)) + (BM == 64 ? 3 : 0);
   if (!st->attr_set[slot]) {
     UGB_CUDA(dev, cudaFuncSetAttribute(tc_gemm_kernel<BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg<BM, BN>::SMEM_BYTES));
@@ -467,7 +470,16 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
 
   const long long n_tiles = (long long)p.tiles_m * p.tiles_n * p.batch * p.splits;
   const unsigned grid = (unsigned)(n_tiles < dev->sm_count ? n_tiles : dev->sm_count);
-  cudaError_t le = ugb_launch(tc_gemm_kernel<BM, BN>, dim3(grid), dim3(THREADS), Cfg<BM, BN>::SMEM_BYTES, dev->stream,
+  // A shallower ring (smem_kib) leaves room for a second CTA per SM: with programmatic dependent launch
+  // the next kernel's CTAs then become resident, and fetch their weights, while this kernel still runs.
+  int stages = Cfg<BM, BN>::STAGES;
+  if (g.smem_kib > 0) {
+    const int fit = (g.smem_kib * 1024 - 1536) / Cfg<BM, BN>::STAGE_BYTES;
+    stages = fit < 2 ? 2 : (fit > stages ? stages : fit);
+  }
+  p.stages = stages;
+  const size_t smem = (size_t)stages * Cfg<BM, BN>::STAGE_BYTES + 1536;
+  cudaError_t le = ugb_launch(tc_gemm_kernel<BM, BN>, dim3(grid), dim3(THREADS), smem, dev->stream,
                               g.pdl, tmA, tmB, p);
   if (le != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of tc_gemm_kernel failed: %s", cudaGetErrorString(le));
   return ugb_after_launch(dev, "tc_gemm_kernel");
@@ -513,11 +525,15 @@ int32_t ugb_tc_gemm(ugb_device *dev, const ugb_tc_gemm_args &g) {
   }
   int bn = g.bn;
   if (bn == 0) bn = (m <= 128) ? 64 : 256;
+  if (!g.b_is_nk && (bn == 80 || bn == 96)) bn = 128;                  // n-major B is boxed in 64-column pieces
   if (m <= 64) {
     if (bn == 64) return launch_tc<64, 64>(dev, st, g, batch, m);
+    if (bn == 80) return launch_tc<64, 80>(dev, st, g, batch, m);      // widths that split n into close to one
+    if (bn == 96) return launch_tc<64, 96>(dev, st, g, batch, m);      // tile per SM where 64 / 128 do not
     if (bn == 128) return launch_tc<64, 128>(dev, st, g, batch, m);
     return launch_tc<64, 256>(dev, st, g, batch, m);
   }
+  if (bn == 80 || bn == 96) bn = 128;                                  // BM = 128 needs n % 16 == 0 tiles: keep the three sizes
   if (bn == 64) return launch_tc<128, 64>(dev, st, g, batch, m);
   if (bn == 128) return launch_tc<128, 128>(dev, st, g, batch, m);
   return launch_tc<128, 256>(dev, st, g, batch, m);

@@ -19,9 +19,10 @@ struct ugb_tc_gemm_args {
   bool b_is_nk;
   int epi;              // UGB_EPI_*
   int splits;           // split-K factor (only with UGB_EPI_F32); the kernel may use fewer
-  int bn;               // tile width: 64, 128, 256, or 0 = choose from m
+  int bn;               // tile width: 64, 128, 256 (80, 96 too when m <= 64 and b_is_nk), or 0 = choose from m
   bool b_static;        // no kernel on the stream writes b (weights): fetch it before waiting for the predecessor
   bool pdl;             // launch with programmatic stream serialization (see ugb_launch)
+  int smem_kib = 0;     // cap on the shared memory of a CTA (ring depth follows); 0 = as deep as fits in 220 KiB
 };
 
 // Returns UGB_ERR_UNSUPPORTED (without touching last_error) when the shape

@@ -56,6 +56,7 @@ struct ugb_llama {
   // tuning
   int splits_qkv = 3, splits_o = 4, splits_down = 8, att_splits = 1, att_stages = 3;
   int pdl = 1;                    // programmatic dependent launch between the kernels of a step
+  int gemm_smem_kib = 0;          // shared-memory cap of the decode GEMM CTAs (0 = deepest ring)
   int skip = 0;                   // measurement aid: bit mask of kernel types left out of the step
   int bn_qkv = 64, bn_o = 64, bn_gate_up = 128, bn_down = 128, bn_lm_head = 256;   // GEMM tile widths
   size_t part_elems = 0;
@@ -132,6 +133,7 @@ int32_t gemm_rows(ugb_llama *m, size_t rows, void *out, const __nv_bfloat16 *a, 
   g.batch = 1; g.m = rows; g.n = n; g.k = k;
   g.a_batch = 0; g.b_batch = 0; g.b_is_nk = true;
   g.epi = epi; g.splits = splits; g.bn = bn; g.b_static = true; g.pdl = m->pdl != 0;
+  g.smem_kib = rows <= 64 ? m->gemm_smem_kib : 0;
   int32_t rc = ugb_tc_gemm(m->dev, g);
   if (rc == UGB_ERR_UNSUPPORTED)
     return ugb_fail(m->dev, rc, "GEMM m=%zu n=%zu k=%zu does not meet the tensor-core kernel's shape rules", rows, n, k);
@@ -453,6 +455,12 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
     return UGB_OK;
   }
+  if (k == "gemm_smem_kib") {
+    UGB_REQUIRE(dev, value == 0 || (value >= 32 && value <= 220), UGB_ERR_INVALID, "option gemm_smem_kib: %d outside 32..220 (0 = no cap)", value);
+    m->gemm_smem_kib = value;
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    return UGB_OK;
+  }
   if (k == "prefill_rows") {
     UGB_REQUIRE(dev, value >= 64 && value <= 65536, UGB_ERR_INVALID, "option prefill_rows: %d outside 64..65536", value);
     UGB_REQUIRE(dev, m->pf_rows == 0, UGB_ERR_INVALID, "option prefill_rows must be set before the first prefill");
@@ -460,7 +468,8 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
     return UGB_OK;
   }
   if (k.compare(0, 3, "bn_") == 0) {
-    UGB_REQUIRE(dev, value == 64 || value == 128 || value == 256, UGB_ERR_INVALID, "option %s: tile width must be 64, 128 or 256", key);
+    UGB_REQUIRE(dev, value == 64 || value == 80 || value == 96 || value == 128 || value == 256, UGB_ERR_INVALID,
+                "option %s: tile width must be 64, 80, 96, 128 or 256", key);
     if (k == "bn_qkv") m->bn_qkv = value;
     else if (k == "bn_o") m->bn_o = value;
     else if (k == "bn_gate_up") m->bn_gate_up = value;
