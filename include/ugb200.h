@@ -325,6 +325,33 @@ enum { UGB_LLAMA_LOGITS = 0, UGB_LLAMA_NEXT_TOKENS = 1, UGB_LLAMA_HIDDEN = 2, UG
 UGB_API int32_t ugb_llama_create(ugb_device *dev, const ugb_llama_config *cfg, int32_t batch,
                                  int32_t t_max, ugb_llama **out);
 UGB_API int32_t ugb_llama_destroy(ugb_llama *m);
+/* Tensor-parallel variant (no counterpart in the reference, which runs on one
+ * device): rank `tp_rank` of `tp_size` (1..8) keeps the query heads, KV heads
+ * (replicated when tp_size > n_kv_heads), FFN columns and vocabulary slice it
+ * owns; q/k/v/gate/up are column-parallel, o_proj/down_proj row-parallel.  All
+ * ranks are fed the same tokens and hold the same residual stream.  The sums
+ * over ranks are not separate collectives: every rank leaves its fp32 partials
+ * in an exchange block that the peers map (ugb_llama_tp_export ->
+ * ugb_llama_tp_connect, CUDA IPC, one process per GPU), and the kernel that
+ * adds the residual and applies the next RMSNorm reads all ranks' partials
+ * over NVLink in rank order, so the replicas stay bit-identical.  Logits are
+ * vocab-parallel: ugb_llama_read returns this rank's columns
+ * [vocab_offset, vocab_offset + vocab_local) and the greedy choice is made over
+ * (value, id) pairs exchanged the same way.  Waits on peers are bounded (2 s,
+ * then UGB_ERR_TIMEOUT at the next ugb_sync); ranks must issue the same calls.
+ * ugb_llama_load_weight takes whole tensors and keeps the rank's slice. */
+UGB_API int32_t ugb_llama_create_tp(ugb_device *dev, const ugb_llama_config *cfg, int32_t batch,
+                                    int32_t t_max, int32_t tp_rank, int32_t tp_size, ugb_llama **out);
+/* 64-byte CUDA IPC handle of this rank's exchange block. */
+UGB_API int32_t ugb_llama_tp_export(ugb_llama *m, void *handle_out, size_t handle_bytes);
+/* `handles`: tp_size handles in rank order (own entry ignored).  Every rank must
+ * have exported before any rank connects, and connected before any rank steps. */
+UGB_API int32_t ugb_llama_tp_connect(ugb_llama *m, const void *handles, size_t handle_bytes,
+                                     int32_t n_ranks);
+UGB_API int32_t ugb_llama_tp_info(const ugb_llama *m, int32_t *tp_rank, int32_t *tp_size,
+                                  int32_t *vocab_local, int32_t *vocab_offset,
+                                  int32_t *kv_heads_local);
+
 /* One tensor by its safetensors name (model.rs:313-346), e.g.
  * "model.layers.3.self_attn.q_proj.weight".  Matrices: BF16, or F32 rounded to
  * bf16 (round to nearest even).  Norm weights: F32.  Shapes are checked like

@@ -52,3 +52,32 @@ def test_two_gloo_ranks_reduce_timings_and_units(tmp_path):
     assert out.returncode == 0, out.stderr[-2000:]
     line = [l for l in out.stdout.splitlines() if l.startswith("RESULT")]
     assert line == ["RESULT 2 [2.5, 10.0] [65.0]"]
+
+
+def test_tp_shard_partitions_cover_the_model():
+    """Column-parallel q/k/v/gate/up + row-parallel o/down over the shards reproduce the full products."""
+    import numpy as np
+    from ug_b200.dist import tp_shard
+    nh, nkv, ffn, vocab, hd, hidden = 8, 2, 96, 64, 4, 32
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((3, hidden)).astype(np.float64)
+    wq = rng.standard_normal((nh * hd, hidden))
+    wo = rng.standard_normal((hidden, nh * hd))
+    wg = rng.standard_normal((ffn, hidden))
+    wd = rng.standard_normal((hidden, ffn))
+    for size in (1, 2, 4, 8):
+        shards = [tp_shard(nh, nkv, ffn, vocab, r, size) for r in range(size)]
+        assert sorted(h for s in shards for h in range(s["q0"], s["q0"] + s["nq"])) == list(range(nh))
+        assert sorted(f for s in shards for f in range(s["f0"], s["f0"] + s["nf"])) == list(range(ffn))
+        assert sorted(v for s in shards for v in range(s["v0"], s["v0"] + s["nv"])) == list(range(vocab))
+        for s in shards:   # the KV head a query head reads is one the rank holds
+            for h in range(s["q0"], s["q0"] + s["nq"]):
+                assert s["kv0"] <= h // (nh // nkv) < s["kv0"] + s["nkv"]
+        att = sum((x @ wq[s["q0"] * hd:(s["q0"] + s["nq"]) * hd].T) @ wo[:, s["q0"] * hd:(s["q0"] + s["nq"]) * hd].T
+                  for s in shards)
+        assert np.allclose(att, (x @ wq.T) @ wo.T)
+        mlp = sum((x @ wg[s["f0"]:s["f0"] + s["nf"]].T) @ wd[:, s["f0"]:s["f0"] + s["nf"]].T for s in shards)
+        assert np.allclose(mlp, (x @ wg.T) @ wd.T)
+    import pytest
+    with pytest.raises(ValueError):
+        tp_shard(8, 3, 96, 64, 0, 2)

@@ -27,6 +27,7 @@
 
 #include "decode_kernels.cuh"
 #include "gemm_tcgen05.cuh"
+#include "tp_kernels.cuh"
 
 using namespace ugb_decode;
 
@@ -37,8 +38,18 @@ struct LayerW {
 
 struct ugb_llama {
   ugb_device *dev = nullptr;
-  ugb_llama_config cfg{};
+  ugb_llama_config cfg{};         // the whole model (weight shapes, vocabulary range)
+  ugb_llama_config lc{};          // this rank's share: n_heads, n_kv_heads and ffn are the local counts
   int batch = 0, t_max = 0;       // t_max padded to a multiple of 16
+  // tensor parallelism: rank tp_rank of tp_size owns query heads [q0, q0 + lc.n_heads), KV heads
+  // [kv0, kv0 + lc.n_kv_heads) (a KV head is replicated when tp_size > n_kv_heads), FFN columns
+  // [tp_rank * lc.ffn, ...) and logit columns [tp_rank * vl, ...).  tp == false: one rank, plain kernels.
+  bool tp = false;
+  int tp_rank = 0, tp_size = 1, q0 = 0, kv0 = 0, vl = 0;
+  void *tp_block = nullptr;       // exchange block of this rank (header, o / down partials, argmax pairs)
+  size_t tp_off_o = 0, tp_off_down = 0, tp_off_pairs = 0, tp_block_bytes = 0, tp_part_rows = 0;
+  void *tp_peer[TP_MAX] = {};     // every rank's exchange block as mapped here (own included)
+  bool tp_ready = false;
   int qkv_dim = 0;
   std::vector<LayerW> layers;
   __nv_bfloat16 *embed = nullptr;
@@ -93,28 +104,37 @@ int32_t dmalloc(ugb_llama *m, T **p, size_t n, bool zero = false) {
 }
 
 __global__ void f32_to_bf16_kernel(const float *__restrict__ s, __nv_bfloat16 *__restrict__ d, size_t n,
-                                   size_t row_len, size_t dst_pitch) {
+                                   size_t row_len, size_t dst_pitch, size_t src_pitch) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-    d[(i / row_len) * dst_pitch + i % row_len] = __float2bfloat16_rn(s[i]);
+    d[(i / row_len) * dst_pitch + i % row_len] = __float2bfloat16_rn(s[(i / row_len) * src_pitch + i % row_len]);
 }
 
-// Copies a [rows, cols] matrix (bf16, or f32 rounded to bf16) into `dst` with a
-// destination row pitch in elements (interleaving gate/up uses pitch 2*cols).
-int32_t put_matrix(ugb_llama *m, const ugb_slice *w, __nv_bfloat16 *dst, size_t rows, size_t cols,
-                   size_t dst_pitch, const char *name) {
+// Copies rows [row0, row0 + nrows) x columns [col0, col0 + ncols) of a [rows, cols] matrix (bf16, or f32
+// rounded to bf16) into `dst` with a destination row pitch in elements (interleaving gate/up uses
+// pitch 2 * hidden).  The shape check is on the whole tensor, as Linear::new does it (model.rs:142-144);
+// a tensor-parallel rank keeps its slice only.
+int32_t put_sub(ugb_llama *m, const ugb_slice *w, __nv_bfloat16 *dst, size_t rows, size_t cols, size_t row0,
+                size_t nrows, size_t col0, size_t ncols, size_t dst_pitch, const char *name) {
   ugb_device *dev = m->dev;
   UGB_REQUIRE(dev, w->len == rows * cols, UGB_ERR_SHAPE, "unexpected shape for %s: %zu elements, expected (%zu, %zu)",
               name, w->len, rows, cols);
+  const size_t off = row0 * cols + col0;
   if (w->dtype == UGB_BF16) {
-    UGB_CUDA(dev, cudaMemcpy2DAsync(dst, dst_pitch * 2, w->ptr, cols * 2, cols * 2, rows,
+    UGB_CUDA(dev, cudaMemcpy2DAsync(dst, dst_pitch * 2, (const __nv_bfloat16 *)w->ptr + off, cols * 2, ncols * 2, nrows,
                                     cudaMemcpyDeviceToDevice, dev->stream));
   } else if (w->dtype == UGB_F32) {
-    f32_to_bf16_kernel<<<dev->sm_count * 8, 256, 0, dev->stream>>>((const float *)w->ptr, dst, rows * cols, cols, dst_pitch);
+    f32_to_bf16_kernel<<<dev->sm_count * 8, 256, 0, dev->stream>>>((const float *)w->ptr + off, dst, nrows * ncols, ncols,
+                                                                    dst_pitch, cols);
     return ugb_after_launch(dev, "f32_to_bf16_kernel");
   } else {
     return ugb_fail(dev, UGB_ERR_DTYPE, "%s: weights must be BF16 or F32", name);
   }
   return UGB_OK;
+}
+
+int32_t put_matrix(ugb_llama *m, const ugb_slice *w, __nv_bfloat16 *dst, size_t rows, size_t cols,
+                   size_t dst_pitch, const char *name) {
+  return put_sub(m, w, dst, rows, cols, 0, rows, 0, cols, dst_pitch, name);
 }
 
 int32_t put_vector(ugb_llama *m, const ugb_slice *w, float *dst, size_t n, const char *name) {
@@ -167,8 +187,73 @@ int32_t launch_reduce_rmsnorm(ugb_llama *m, const float *part, int n_part, const
   return launch_reduce_rmsnorm_rows(m, m->batch, m->x, m->xn, part, n_part, alpha);
 }
 
+// Where the row-parallel projections leave their fp32 partials: in the exchange block when peers read them.
+enum { RED_NONE = 0, RED_O = 1, RED_DOWN = 2 };
+float *o_out(ugb_llama *m, float *local) { return m->tp ? (float *)((char *)m->tp_block + m->tp_off_o) : local; }
+float *down_out(ugb_llama *m, float *local) { return m->tp ? (float *)((char *)m->tp_block + m->tp_off_down) : local; }
+
+TpPeers tp_peers(const ugb_llama *m, size_t offset) {
+  TpPeers t{};
+  t.rank = m->tp_rank;
+  t.size = m->tp_size;
+  for (int r = 0; r < m->tp_size; ++r) {
+    t.hdr[r] = (TpHeader *)m->tp_peer[r];
+    t.part[r] = (const float *)((const char *)m->tp_peer[r] + offset);
+  }
+  return t;
+}
+
+// x += (sum of the partials of projection `which`), xn = rmsnorm(x) for `rows` rows.  Single rank: the
+// split-K partials in `local`; tensor parallel: every rank's partials, read in place over NVLink.
+int32_t launch_reduce(ugb_llama *m, int rows, float *x, __nv_bfloat16 *xn, int which, const float *local, int n_part,
+                      const float *alpha) {
+  if (!m->tp || which == RED_NONE || n_part == 0) return launch_reduce_rmsnorm_rows(m, rows, x, xn, local, n_part, alpha);
+  if (!m->tp_ready) return ugb_fail(m->dev, UGB_ERR_INVALID, "tensor-parallel model: peers not connected (ugb_llama_tp_connect)");
+  const int hidden = m->cfg.hidden, nvec = hidden / 4;
+  const size_t stride = (size_t)rows * hidden;
+  const float inv_d = 1.0f / (float)hidden, eps = m->cfg.rms_eps;
+  const TpPeers tp = tp_peers(m, which == RED_O ? m->tp_off_o : m->tp_off_down);
+  cudaStream_t st = m->dev->stream;
+  const bool pdl = m->pdl != 0;
+  ugb_status_word *status = m->dev->status_dev;
+  cudaError_t e;
+  if (nvec <= 256) e = ugb_launch(tp_reduce_rmsnorm_kernel<1>, dim3(rows), dim3(256), 0, st, pdl, x, tp, n_part, stride, alpha, xn, hidden, inv_d, eps, status);
+  else if (nvec <= 512) e = ugb_launch(tp_reduce_rmsnorm_kernel<2>, dim3(rows), dim3(256), 0, st, pdl, x, tp, n_part, stride, alpha, xn, hidden, inv_d, eps, status);
+  else if (nvec <= 1024) e = ugb_launch(tp_reduce_rmsnorm_kernel<4>, dim3(rows), dim3(256), 0, st, pdl, x, tp, n_part, stride, alpha, xn, hidden, inv_d, eps, status);
+  else e = ugb_launch(tp_reduce_rmsnorm_kernel<8>, dim3(rows), dim3(256), 0, st, pdl, x, tp, n_part, stride, alpha, xn, hidden, inv_d, eps, status);
+  if (e != cudaSuccess) return ugb_fail(m->dev, UGB_ERR_CUDA, "launch of tp_reduce_rmsnorm_kernel failed: %s", cudaGetErrorString(e));
+  return ugb_after_launch(m->dev, "tp_reduce_rmsnorm_kernel");
+}
+
+// logits[rows, vl] = xn . embed[rank's vocabulary slice]^T (tied lm_head, vocab-parallel), then the greedy
+// choice: plain argmax on one rank, (value, id) pairs exchanged between the ranks otherwise.
+int32_t launch_lm_head_argmax(ugb_llama *m, bool pdl_first) {
+  ugb_device *dev = m->dev;
+  const ugb_llama_config &c = m->lc;
+  int32_t rc;
+  const __nv_bfloat16 *w = m->embed + (size_t)m->tp_rank * m->vl * c.hidden;
+  if (!(m->skip & 128) && (rc = gemm(m, m->logits, m->xn, w, (size_t)m->vl, c.hidden, UGB_EPI_F32, 1, m->bn_lm_head))) return rc;
+  cudaStream_t st = dev->stream;
+  const bool pdl = pdl_first && m->pdl != 0;
+  cudaError_t e;
+  if (!m->tp) {
+    e = ugb_launch(argmax_rows_kernel, dim3(m->batch), dim3(1024), 0, st, pdl, m->logits, m->vl, m->next, m->pos);
+    if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of argmax_rows_kernel failed: %s", cudaGetErrorString(e));
+    return ugb_after_launch(dev, "argmax_rows_kernel");
+  }
+  if (!m->tp_ready) return ugb_fail(dev, UGB_ERR_INVALID, "tensor-parallel model: peers not connected (ugb_llama_tp_connect)");
+  float2 *pairs = (float2 *)((char *)m->tp_block + m->tp_off_pairs);
+  e = ugb_launch(tp_argmax_local_kernel, dim3(m->batch), dim3(1024), 0, st, pdl, m->logits, m->vl, m->tp_rank * m->vl, pairs);
+  if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of tp_argmax_local_kernel failed: %s", cudaGetErrorString(e));
+  if ((rc = ugb_after_launch(dev, "tp_argmax_local_kernel"))) return rc;
+  const TpPeers tp = tp_peers(m, m->tp_off_pairs);
+  e = ugb_launch(tp_argmax_final_kernel, dim3(1), dim3(128), 0, st, m->pdl != 0, tp, m->batch, m->next, m->pos, dev->status_dev);
+  if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of tp_argmax_final_kernel failed: %s", cudaGetErrorString(e));
+  return ugb_after_launch(dev, "tp_argmax_final_kernel");
+}
+
 int32_t launch_attention(ugb_llama *m, const __nv_bfloat16 *kc, const __nv_bfloat16 *vc, float scale) {
-  const ugb_llama_config &c = m->cfg;
+  const ugb_llama_config &c = m->lc;
   dim3 grid(m->att_splits, c.n_kv_heads, m->batch);
   cudaStream_t st = m->dev->stream;
   cudaError_t e = cudaSuccess;
@@ -191,21 +276,22 @@ int32_t launch_attention(ugb_llama *m, const __nv_bfloat16 *kc, const __nv_bfloa
 // Enqueues one decode step on the device stream; `tok` holds the input ids.
 int32_t enqueue_step(ugb_llama *m, const int *tok) {
   ugb_device *dev = m->dev;
-  const ugb_llama_config &c = m->cfg;
+  const ugb_llama_config &c = m->lc;         // this rank's share of heads and FFN columns
   cudaStream_t st = dev->stream;
-  const int B = m->batch, H = c.hidden;
+  const int B = m->batch, H = c.hidden, AW = c.n_heads * c.head_dim;
   int32_t rc;
   const bool pdl = m->pdl != 0;
   cudaError_t e = ugb_launch(embed_gather_kernel, dim3(B), dim3(256), 0, st, pdl, m->embed, tok, m->x, H, c.vocab, dev->status_dev, 1, 1, 0);
   if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of embed_gather_kernel failed: %s", cudaGetErrorString(e));
   if ((rc = ugb_after_launch(dev, "embed_gather_kernel"))) return rc;
   const int s_qkv = ugb_tc_gemm_effective_splits(H, m->splits_qkv);
-  const int s_o = ugb_tc_gemm_effective_splits(H, m->splits_o);
+  const int s_o = ugb_tc_gemm_effective_splits(AW, m->splits_o);
   const int s_down = ugb_tc_gemm_effective_splits(c.ffn, m->splits_down);
   const float scale = powf((float)c.head_dim, -0.5f);   // model.rs:236
+  float *po = o_out(m, m->part), *pd = down_out(m, m->part);
   for (int l = 0; l < c.layers; ++l) {
     const LayerW &w = m->layers[l];
-    if (!(m->skip & 1) && (rc = launch_reduce_rmsnorm(m, m->part, l == 0 ? 0 : s_down, w.rms1))) return rc;
+    if (!(m->skip & 1) && (rc = launch_reduce(m, B, m->x, m->xn, l == 0 ? RED_NONE : RED_DOWN, pd, l == 0 ? 0 : s_down, w.rms1))) return rc;
     if (!(m->skip & 2) && (rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv))) return rc;
     __nv_bfloat16 *kc = m->kcache + (size_t)l * m->kv_layer_stride;
     __nv_bfloat16 *vc = m->vcache + (size_t)l * m->kv_layer_stride;
@@ -217,23 +303,22 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
     if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of rope_append_kernel failed: %s", cudaGetErrorString(e));
     if ((rc = ugb_after_launch(dev, "rope_append_kernel"))) return rc;
     if (!(m->skip & 8) && (rc = launch_attention(m, kc, vc, scale))) return rc;
-    if (!(m->skip & 16) && (rc = gemm(m, m->part, m->att, w.wo, H, H, UGB_EPI_F32, m->splits_o, m->bn_o))) return rc;
-    if (!(m->skip & 1) && (rc = launch_reduce_rmsnorm(m, m->part, s_o, w.rms2))) return rc;
+    if (!(m->skip & 16) && (rc = gemm(m, po, m->att, w.wo, H, AW, UGB_EPI_F32, m->splits_o, m->bn_o))) return rc;
+    if (!(m->skip & 1) && (rc = launch_reduce(m, B, m->x, m->xn, RED_O, po, s_o, w.rms2))) return rc;
     if (!(m->skip & 32) && (rc = gemm(m, m->h, m->xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, m->bn_gate_up))) return rc;
-    if (!(m->skip & 64) && (rc = gemm(m, m->part, m->h, w.wdown, H, c.ffn, UGB_EPI_F32, m->splits_down, m->bn_down))) return rc;
+    if (!(m->skip & 64) && (rc = gemm(m, pd, m->h, w.wdown, H, c.ffn, UGB_EPI_F32, m->splits_down, m->bn_down))) return rc;
   }
-  if ((rc = launch_reduce_rmsnorm(m, m->part, s_down, m->ln_f))) return rc;
-  if (!(m->skip & 128) && (rc = gemm(m, m->logits, m->xn, m->embed, c.vocab, H, UGB_EPI_F32, 1, m->bn_lm_head))) return rc;
-  e = ugb_launch(argmax_rows_kernel, dim3(B), dim3(1024), 0, st, pdl, m->logits, c.vocab, m->next, m->pos);
-  if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of argmax_rows_kernel failed: %s", cudaGetErrorString(e));
-  return ugb_after_launch(dev, "argmax_rows_kernel");
+  if ((rc = launch_reduce(m, B, m->x, m->xn, RED_DOWN, pd, s_down, m->ln_f))) return rc;
+  return launch_lm_head_argmax(m, true);
 }
 
 // Activations for one prefill chunk; allocated once, freed with the model.
 int32_t ensure_prefill_workspace(ugb_llama *m) {
   if (m->pf_rows) return UGB_OK;
-  const ugb_llama_config &c = m->cfg;
-  int chunk = m->pf_rows_max / m->batch;
+  const ugb_llama_config &c = m->lc;
+  int rows_max = m->pf_rows_max;
+  if (m->tp && (size_t)rows_max > m->tp_part_rows) rows_max = (int)m->tp_part_rows;   // the exchange block was sized at creation
+  int chunk = rows_max / m->batch;
   if (chunk < 1) chunk = 1;
   if (chunk >= PF_BQ) chunk -= chunk % PF_BQ;     // whole query tiles per chunk
   const size_t rows = (size_t)m->batch * chunk, H = c.hidden, F = c.ffn;
@@ -253,9 +338,9 @@ int32_t ensure_prefill_workspace(ugb_llama *m) {
 // host_pos + c0 onwards.  Rows are ordered (sequence, position).
 int32_t enqueue_prefill_chunk(ugb_llama *m, const int *tok, int t, int c0, int tc, bool all_logits) {
   ugb_device *dev = m->dev;
-  const ugb_llama_config &c = m->cfg;
+  const ugb_llama_config &c = m->lc;
   cudaStream_t st = dev->stream;
-  const int B = m->batch, H = c.hidden, rows = B * tc;
+  const int B = m->batch, H = c.hidden, rows = B * tc, AW = c.n_heads * c.head_dim;
   const bool pdl = m->pdl != 0;
   const float scale = powf((float)c.head_dim, -0.5f);   // model.rs:236
   int32_t rc;
@@ -264,11 +349,12 @@ int32_t enqueue_prefill_chunk(ugb_llama *m, const int *tok, int t, int c0, int t
   if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of embed_gather_kernel failed: %s", cudaGetErrorString(e));
   if ((rc = ugb_after_launch(dev, "embed_gather_kernel"))) return rc;
   const int rope_items = (c.n_heads + c.n_kv_heads) * c.head_dim / 2 + c.n_kv_heads * c.head_dim;
+  float *po = o_out(m, m->pf_f32), *pd = down_out(m, m->pf_f32);
   for (int l = 0; l < c.layers; ++l) {
     const LayerW &w = m->layers[l];
     __nv_bfloat16 *kc = m->kcache + (size_t)l * m->kv_layer_stride;
     __nv_bfloat16 *vc = m->vcache + (size_t)l * m->kv_layer_stride;
-    if ((rc = launch_reduce_rmsnorm_rows(m, rows, m->pf_x, m->pf_xn, m->pf_f32, l == 0 ? 0 : 1, w.rms1))) return rc;
+    if ((rc = launch_reduce(m, rows, m->pf_x, m->pf_xn, l == 0 ? RED_NONE : RED_DOWN, pd, l == 0 ? 0 : 1, w.rms1))) return rc;
     if ((rc = gemm_rows(m, rows, m->pf_f32, m->pf_xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, 1, 0))) return rc;
     e = ugb_launch(rope_append_kernel, dim3(rows, (rope_items + 255) / 256), dim3(256), 0, st, pdl, m->pf_f32, 1,
                    (size_t)0, m->cos, m->sin, m->pos, m->pf_q, kc, vc, c.n_heads, c.n_kv_heads, c.head_dim, m->t_max,
@@ -278,18 +364,20 @@ int32_t enqueue_prefill_chunk(ugb_llama *m, const int *tok, int t, int c0, int t
     prefill_attention_kernel<<<dim3((tc + PF_BQ - 1) / PF_BQ, c.n_heads, B), 128, 0, st>>>(
         m->pf_q, kc, vc, m->pf_att, tc, m->host_pos + c0, c.n_heads, c.n_kv_heads, m->t_max, scale);
     if ((rc = ugb_after_launch(dev, "prefill_attention_kernel"))) return rc;
-    if ((rc = gemm_rows(m, rows, m->pf_f32, m->pf_att, w.wo, H, H, UGB_EPI_F32, 1, 0))) return rc;
-    if ((rc = launch_reduce_rmsnorm_rows(m, rows, m->pf_x, m->pf_xn, m->pf_f32, 1, w.rms2))) return rc;
+    if ((rc = gemm_rows(m, rows, po, m->pf_att, w.wo, H, AW, UGB_EPI_F32, 1, 0))) return rc;
+    if ((rc = launch_reduce(m, rows, m->pf_x, m->pf_xn, RED_O, po, 1, w.rms2))) return rc;
     if ((rc = gemm_rows(m, rows, m->pf_h, m->pf_xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, 0))) return rc;
-    if ((rc = gemm_rows(m, rows, m->pf_f32, m->pf_h, w.wdown, H, c.ffn, UGB_EPI_F32, 1, 0))) return rc;
+    if ((rc = gemm_rows(m, rows, pd, m->pf_h, w.wdown, H, c.ffn, UGB_EPI_F32, 1, 0))) return rc;
   }
+  // The last down_proj output is folded into the residual stream here (every rank's partial under tensor
+  // parallelism), so that what follows -- all-position logits, the last-position step -- sees the final x.
+  if ((rc = launch_reduce(m, rows, m->pf_x, m->pf_xn, RED_DOWN, pd, 1, m->ln_f))) return rc;
   if (all_logits) {
-    // final norm of every row, then logits[b, c0 + i, :] for the chunk as one GEMM batched over sequences
-    if ((rc = launch_reduce_rmsnorm_rows(m, rows, m->pf_x, m->pf_xn, m->pf_f32, 1, m->ln_f))) return rc;
+    // logits[b, c0 + i, rank's vocabulary slice] for the chunk as one GEMM batched over sequences
     ugb_tc_gemm_args g;
-    g.out = m->pf_logits + (size_t)c0 * c.vocab; g.a = m->pf_xn; g.b = m->embed;
-    g.batch = (size_t)B; g.m = (size_t)tc; g.n = (size_t)c.vocab; g.k = (size_t)H;
-    g.a_batch = (long long)tc * H; g.b_batch = 0; g.c_batch = (long long)t * c.vocab; g.b_is_nk = true;
+    g.out = m->pf_logits + (size_t)c0 * m->vl; g.a = m->pf_xn; g.b = m->embed + (size_t)m->tp_rank * m->vl * H;
+    g.batch = (size_t)B; g.m = (size_t)tc; g.n = (size_t)m->vl; g.k = (size_t)H;
+    g.a_batch = (long long)tc * H; g.b_batch = 0; g.c_batch = (long long)t * m->vl; g.b_is_nk = true;
     g.epi = UGB_EPI_F32; g.splits = 1; g.bn = 0; g.b_static = true; g.pdl = pdl;
     rc = ugb_tc_gemm(dev, g);
     if (rc == UGB_ERR_UNSUPPORTED) return ugb_fail(dev, rc, "prefill lm_head GEMM does not meet the tensor-core kernel's shape rules");
@@ -309,14 +397,34 @@ extern "C" {
 
 int32_t ugb_llama_create(ugb_device *dev, const ugb_llama_config *cfg, int32_t batch, int32_t t_max,
                          ugb_llama **out) {
+  return ugb_llama_create_tp(dev, cfg, batch, t_max, 0, 0, out);
+}
+
+int32_t ugb_llama_create_tp(ugb_device *dev, const ugb_llama_config *cfg, int32_t batch, int32_t t_max,
+                            int32_t tp_rank, int32_t tp_size, ugb_llama **out) {
   if (!dev) return UGB_ERR_INVALID;
   UGB_REQUIRE(dev, cfg && out, UGB_ERR_INVALID, "ugb_llama_create: null argument");
   *out = nullptr;
-  const ugb_llama_config &c = *cfg;
+  const ugb_llama_config &g = *cfg;
+  const bool tp = tp_size >= 1;          // tp_size 0: single rank on the plain kernels
+  const int n_rank = tp ? tp_size : 1;
+  UGB_REQUIRE(dev, n_rank <= TP_MAX && tp_rank >= 0 && tp_rank < n_rank, UGB_ERR_INVALID,
+              "tensor-parallel rank %d of %d (at most %d ranks)", tp_rank, n_rank, TP_MAX);
+  UGB_REQUIRE(dev, g.n_heads > 0 && g.n_kv_heads > 0 && g.ffn > 0 && g.vocab > 0, UGB_ERR_INVALID,
+              "ugb_llama_create: non-positive dimension");
+  UGB_REQUIRE(dev, g.n_heads % n_rank == 0 && (g.n_kv_heads % n_rank == 0 || n_rank % g.n_kv_heads == 0) &&
+                   g.ffn % (8 * n_rank) == 0 && g.vocab % (8 * n_rank) == 0, UGB_ERR_UNSUPPORTED,
+              "%d ranks do not divide heads %d / KV heads %d / ffn %d / vocab %d evenly", n_rank, g.n_heads,
+              g.n_kv_heads, g.ffn, g.vocab);
+  ugb_llama_config c = g;                // local share
+  c.n_heads = g.n_heads / n_rank;
+  c.n_kv_heads = g.n_kv_heads >= n_rank ? g.n_kv_heads / n_rank : 1;
+  c.ffn = g.ffn / n_rank;
+  c.hidden = g.hidden;
   UGB_REQUIRE(dev, c.hidden > 0 && c.layers > 0 && c.n_heads > 0 && c.n_kv_heads > 0 && c.ffn > 0 && c.vocab > 0,
               UGB_ERR_INVALID, "ugb_llama_create: non-positive dimension");
   UGB_REQUIRE(dev, c.head_dim == ATT_HD, UGB_ERR_UNSUPPORTED, "head_dim %d: the decode attention kernel is built for 64", c.head_dim);
-  UGB_REQUIRE(dev, c.n_heads * c.head_dim == c.hidden, UGB_ERR_SHAPE, "n_heads * head_dim != hidden");
+  UGB_REQUIRE(dev, g.n_heads * g.head_dim == g.hidden, UGB_ERR_SHAPE, "n_heads * head_dim != hidden");
   UGB_REQUIRE(dev, c.n_heads % c.n_kv_heads == 0 && c.n_heads / c.n_kv_heads <= ATT_GROUP, UGB_ERR_UNSUPPORTED,
               "query heads per KV head must divide evenly and be <= %d", ATT_GROUP);
   UGB_REQUIRE(dev, c.hidden % 8 == 0 && c.hidden <= 8192 && c.ffn % 8 == 0 && c.vocab % 8 == 0, UGB_ERR_UNSUPPORTED,
@@ -327,7 +435,14 @@ int32_t ugb_llama_create(ugb_device *dev, const ugb_llama_config *cfg, int32_t b
 
   ugb_llama *m = new ugb_llama();
   m->dev = dev;
-  m->cfg = c;
+  m->cfg = g;
+  m->lc = c;
+  m->tp = tp;
+  m->tp_rank = tp_rank;
+  m->tp_size = n_rank;
+  m->q0 = tp_rank * c.n_heads;
+  m->kv0 = tp_rank * g.n_kv_heads / n_rank;
+  m->vl = g.vocab / n_rank;
   m->batch = batch;
   m->t_max = (t_max + 15) / 16 * 16;
   m->qkv_dim = (c.n_heads + 2 * c.n_kv_heads) * c.head_dim;
@@ -337,13 +452,13 @@ int32_t ugb_llama_create(ugb_device *dev, const ugb_llama_config *cfg, int32_t b
 #define TRY(e) do { if ((rc = (e)) != UGB_OK) { ugb_llama_destroy(m); return rc; } } while (0)
   for (auto &w : m->layers) {
     TRY(dmalloc(m, &w.wqkv, (size_t)m->qkv_dim * H));
-    TRY(dmalloc(m, &w.wo, H * H));
+    TRY(dmalloc(m, &w.wo, H * (size_t)c.n_heads * c.head_dim));
     TRY(dmalloc(m, &w.wgu, 2 * F * H));
     TRY(dmalloc(m, &w.wdown, H * F));
     TRY(dmalloc(m, &w.rms1, H));
     TRY(dmalloc(m, &w.rms2, H));
   }
-  TRY(dmalloc(m, &m->embed, (size_t)c.vocab * H));
+  TRY(dmalloc(m, &m->embed, (size_t)g.vocab * H));
   TRY(dmalloc(m, &m->ln_f, H));
   const size_t half = c.head_dim / 2;
   TRY(dmalloc(m, &m->cos, (size_t)c.max_pos * half));
@@ -359,7 +474,7 @@ int32_t ugb_llama_create(ugb_device *dev, const ugb_llama_config *cfg, int32_t b
   const size_t widest = std::max<size_t>(m->qkv_dim, H);
   m->part_elems = 8 * B * widest;    // up to 8 split-K partials
   TRY(dmalloc(m, &m->part, m->part_elems));
-  TRY(dmalloc(m, &m->logits, B * c.vocab));
+  TRY(dmalloc(m, &m->logits, B * (size_t)m->vl));
   const size_t slots = B * c.n_kv_heads * 8;   // up to 8 attention slices
   TRY(dmalloc(m, &m->att_po, slots * ATT_GROUP * ATT_HD));
   TRY(dmalloc(m, &m->att_pml, slots * ATT_GROUP * 2));
@@ -367,6 +482,26 @@ int32_t ugb_llama_create(ugb_device *dev, const ugb_llama_config *cfg, int32_t b
   TRY(dmalloc(m, &m->tok, B, true));
   TRY(dmalloc(m, &m->next, B, true));
   TRY(dmalloc(m, &m->pos, 1, true));
+  if (tp) {
+    // exchange block: header | o_proj partials | down_proj partials | argmax pairs.  Partial buffers hold
+    // up to 8 split-K partials of a decode step or one partial of a prefill chunk, whichever is larger.
+    m->tp_part_rows = std::max<size_t>(8 * B, (size_t)m->pf_rows_max);
+    const size_t part_bytes = m->tp_part_rows * H * sizeof(float);
+    m->tp_off_o = 256;
+    m->tp_off_down = m->tp_off_o + part_bytes;
+    m->tp_off_pairs = m->tp_off_down + part_bytes;
+    m->tp_block_bytes = m->tp_off_pairs + ((B * sizeof(float2) + 255) / 256) * 256;
+    unsigned char *blk = nullptr;
+    TRY(dmalloc(m, &blk, m->tp_block_bytes));
+    if (cudaMemsetAsync(blk, 0, m->tp_block_bytes, dev->stream) != cudaSuccess) {
+      ugb_fail(dev, UGB_ERR_CUDA, "clearing the exchange block failed");
+      ugb_llama_destroy(m);
+      return UGB_ERR_CUDA;
+    }
+    m->tp_block = blk;
+    m->tp_peer[tp_rank] = blk;
+    m->tp_ready = n_rank == 1;
+  }
   // rope tables, model.rs:278-295: theta_i = 1 / theta^(i/d) in f32 on the host
   {
     std::vector<float> inv(half);
@@ -402,6 +537,8 @@ int32_t ugb_llama_destroy(ugb_llama *m) {
   cudaSetDevice(m->dev->ordinal);
   cudaStreamSynchronize(m->dev->stream);
   if (m->graph) cudaGraphExecDestroy(m->graph);
+  for (int r = 0; r < m->tp_size; ++r)
+    if (r != m->tp_rank && m->tp_peer[r]) cudaIpcCloseMemHandle(m->tp_peer[r]);
   for (void *p : m->allocs) cudaFree(p);
   if (m->pf_logits) cudaFree(m->pf_logits);
   delete m;
@@ -414,7 +551,10 @@ int32_t ugb_llama_load_weight(ugb_llama *m, const char *name, const ugb_slice *w
   UGB_REQUIRE(dev, name && w, UGB_ERR_INVALID, "ugb_llama_load_weight: null argument");
   UGB_REQUIRE(dev, w->dev == dev, UGB_ERR_INVALID, "%s: slice belongs to another device", name);
   const ugb_llama_config &c = m->cfg;
-  const size_t H = c.hidden, F = c.ffn, KV = (size_t)c.n_kv_heads * c.head_dim;
+  const ugb_llama_config &lc = m->lc;
+  const size_t H = c.hidden, F = c.ffn, KV = (size_t)c.n_kv_heads * c.head_dim, D = c.head_dim;
+  const size_t QL = (size_t)lc.n_heads * D, KVL = (size_t)lc.n_kv_heads * D, FL = lc.ffn;   // this rank's widths
+  const size_t q_row0 = (size_t)m->q0 * D, kv_row0 = (size_t)m->kv0 * D, f0 = (size_t)m->tp_rank * FL;
   const std::string s(name);
   m->loaded++;
   if (s == "model.embed_tokens.weight") return put_matrix(m, w, m->embed, c.vocab, H, H, name);
@@ -428,13 +568,14 @@ int32_t ugb_llama_load_weight(ugb_llama *m, const char *name, const ugb_slice *w
       LayerW &L = m->layers[l];
       if (ends_with(s, ".input_layernorm.weight")) return put_vector(m, w, L.rms1, H, name);
       if (ends_with(s, ".post_attention_layernorm.weight")) return put_vector(m, w, L.rms2, H, name);
-      if (ends_with(s, ".self_attn.q_proj.weight")) return put_matrix(m, w, L.wqkv, H, H, H, name);
-      if (ends_with(s, ".self_attn.k_proj.weight")) return put_matrix(m, w, L.wqkv + H * H, KV, H, H, name);
-      if (ends_with(s, ".self_attn.v_proj.weight")) return put_matrix(m, w, L.wqkv + (H + KV) * H, KV, H, H, name);
-      if (ends_with(s, ".self_attn.o_proj.weight")) return put_matrix(m, w, L.wo, H, H, H, name);
-      if (ends_with(s, ".mlp.gate_proj.weight")) return put_matrix(m, w, L.wgu, F, H, 2 * H, name);
-      if (ends_with(s, ".mlp.up_proj.weight")) return put_matrix(m, w, L.wgu + H, F, H, 2 * H, name);
-      if (ends_with(s, ".mlp.down_proj.weight")) return put_matrix(m, w, L.wdown, H, F, F, name);
+      // column-parallel: rows of q/k/v/gate/up; row-parallel: columns of o/down
+      if (ends_with(s, ".self_attn.q_proj.weight")) return put_sub(m, w, L.wqkv, H, H, q_row0, QL, 0, H, H, name);
+      if (ends_with(s, ".self_attn.k_proj.weight")) return put_sub(m, w, L.wqkv + QL * H, KV, H, kv_row0, KVL, 0, H, H, name);
+      if (ends_with(s, ".self_attn.v_proj.weight")) return put_sub(m, w, L.wqkv + (QL + KVL) * H, KV, H, kv_row0, KVL, 0, H, H, name);
+      if (ends_with(s, ".self_attn.o_proj.weight")) return put_sub(m, w, L.wo, H, H, 0, H, q_row0, QL, QL, name);
+      if (ends_with(s, ".mlp.gate_proj.weight")) return put_sub(m, w, L.wgu, F, H, f0, FL, 0, H, 2 * H, name);
+      if (ends_with(s, ".mlp.up_proj.weight")) return put_sub(m, w, L.wgu + H, F, H, f0, FL, 0, H, 2 * H, name);
+      if (ends_with(s, ".mlp.down_proj.weight")) return put_sub(m, w, L.wdown, H, F, 0, H, f0, FL, FL, name);
     }
   }
   m->loaded--;
@@ -558,7 +699,7 @@ int32_t ugb_llama_prefill(ugb_llama *m, const ugb_slice *tokens, int32_t t, int3
   int32_t rc;
   if ((rc = ensure_prefill_workspace(m))) return rc;
   if (all_logits) {
-    const size_t need = (size_t)m->batch * t * c.vocab;
+    const size_t need = (size_t)m->batch * t * m->vl;
     if (need > m->pf_logits_cap) {
       UGB_CUDA(dev, cudaStreamSynchronize(dev->stream));
       if (m->pf_logits) { cudaFree(m->pf_logits); m->pf_logits = nullptr; m->pf_logits_cap = 0; }
@@ -575,20 +716,14 @@ int32_t ugb_llama_prefill(ugb_llama *m, const ugb_slice *tokens, int32_t t, int3
     tc = std::min(m->pf_chunk, t - c0);
     if ((rc = enqueue_prefill_chunk(m, tok, t, c0, tc, all_logits != 0))) return rc;
   }
-  // Last position of every sequence -> the decode-shaped buffers, final norm, lm_head, argmax.
+  // Last position of every sequence -> the decode-shaped buffers (x already holds the last down_proj
+  // output), final norm, lm_head, greedy choice.
   UGB_CUDA(dev, cudaMemcpy2DAsync(m->x, H * 4, m->pf_x + (size_t)(tc - 1) * H, (size_t)tc * H * 4, H * 4, m->batch,
                                   cudaMemcpyDeviceToDevice, dev->stream));
-  if (!all_logits)
-    UGB_CUDA(dev, cudaMemcpy2DAsync(m->part, H * 4, m->pf_f32 + (size_t)(tc - 1) * H, (size_t)tc * H * 4, H * 4, m->batch,
-                                    cudaMemcpyDeviceToDevice, dev->stream));
-  if ((rc = launch_reduce_rmsnorm(m, m->part, all_logits ? 0 : 1, m->ln_f))) return rc;
-  if ((rc = gemm(m, m->logits, m->xn, m->embed, c.vocab, c.hidden, UGB_EPI_F32, 1, m->bn_lm_head))) return rc;
-  const int last = m->host_pos + t - 1;     // argmax_rows_kernel advances the device-side position by one
+  if ((rc = launch_reduce(m, m->batch, m->x, m->xn, RED_NONE, m->part, 0, m->ln_f))) return rc;
+  const int last = m->host_pos + t - 1;     // the argmax kernel advances the device-side position by one
   UGB_CUDA(dev, cudaMemcpyAsync(m->pos, &last, 4, cudaMemcpyHostToDevice, dev->stream));
-  cudaError_t e = ugb_launch(argmax_rows_kernel, dim3(m->batch), dim3(1024), 0, dev->stream, false, m->logits, c.vocab,
-                             m->next, m->pos);
-  if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of argmax_rows_kernel failed: %s", cudaGetErrorString(e));
-  if ((rc = ugb_after_launch(dev, "argmax_rows_kernel"))) return rc;
+  if ((rc = launch_lm_head_argmax(m, false))) return rc;
   m->host_pos += t;
   return UGB_OK;
 }
@@ -600,12 +735,12 @@ int32_t ugb_llama_read(ugb_llama *m, int32_t what, void *host_dst, size_t len) {
   const void *src = nullptr;
   size_t n = 0, es = 4;
   switch (what) {
-    case UGB_LLAMA_LOGITS: src = m->logits; n = (size_t)m->batch * m->cfg.vocab; break;
+    case UGB_LLAMA_LOGITS: src = m->logits; n = (size_t)m->batch * m->vl; break;
     case UGB_LLAMA_NEXT_TOKENS: src = m->next; n = (size_t)m->batch; break;
     case UGB_LLAMA_HIDDEN: src = m->x; n = (size_t)m->batch * m->cfg.hidden; break;
     case UGB_LLAMA_PREFILL_LOGITS:
       UGB_REQUIRE(dev, m->pf_logits && m->pf_logits_t > 0, UGB_ERR_INVALID, "no all-position logits: run ugb_llama_prefill with all_logits first");
-      src = m->pf_logits; n = (size_t)m->batch * m->pf_logits_t * m->cfg.vocab; break;
+      src = m->pf_logits; n = (size_t)m->batch * m->pf_logits_t * m->vl; break;
     default: return ugb_fail(dev, UGB_ERR_INVALID, "ugb_llama_read: unknown selector %d", what);
   }
   UGB_REQUIRE(dev, len == n, UGB_ERR_SHAPE, "ugb_llama_read: destination holds %zu elements, %zu expected", len, n);
@@ -632,8 +767,8 @@ int32_t ugb_llama_time_kernel(ugb_llama *m, int32_t which, int32_t iters, float 
   ugb_device *dev = m->dev;
   UGB_REQUIRE(dev, ms_per_pass && iters >= 1, UGB_ERR_INVALID, "ugb_llama_time_kernel: bad argument");
   UGB_REQUIRE(dev, m->host_pos >= 1, UGB_ERR_INVALID, "ugb_llama_time_kernel: the cache is empty");
-  const ugb_llama_config &c = m->cfg;
-  const int B = m->batch, H = c.hidden;
+  const ugb_llama_config &c = m->lc;
+  const int H = c.hidden, AW = c.n_heads * c.head_dim;
   const float scale = powf((float)c.head_dim, -0.5f);
   int32_t rc = UGB_OK;
   // the kernels read the device-side position; during timing it must name the last cached position
@@ -650,11 +785,11 @@ int32_t ugb_llama_time_kernel(ugb_llama *m, int32_t which, int32_t iters, float 
                                 m->vcache + (size_t)l * m->kv_layer_stride, scale);
           break;
         }
-        case UGB_LLAMA_K_O: rc = gemm(m, m->part, m->att, w.wo, H, H, UGB_EPI_F32, m->splits_o, m->bn_o); break;
+        case UGB_LLAMA_K_O: rc = gemm(m, m->part, m->att, w.wo, H, AW, UGB_EPI_F32, m->splits_o, m->bn_o); break;
         case UGB_LLAMA_K_GATE_UP: rc = gemm(m, m->h, m->xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, m->bn_gate_up); break;
         case UGB_LLAMA_K_DOWN: rc = gemm(m, m->part, m->h, w.wdown, H, c.ffn, UGB_EPI_F32, m->splits_down, m->bn_down); break;
         case UGB_LLAMA_K_LM_HEAD:
-          if (l == 0) rc = gemm(m, m->logits, m->xn, m->embed, c.vocab, H, UGB_EPI_F32, 1, m->bn_lm_head);
+          if (l == 0) rc = gemm(m, m->logits, m->xn, m->embed + (size_t)m->tp_rank * m->vl * H, (size_t)m->vl, H, UGB_EPI_F32, 1, m->bn_lm_head);
           break;
         default: rc = ugb_fail(dev, UGB_ERR_INVALID, "ugb_llama_time_kernel: unknown kernel %d", which);
       }
@@ -672,5 +807,52 @@ int32_t ugb_llama_time_kernel(ugb_llama *m, int32_t which, int32_t iters, float 
 }
 
 int32_t ugb_llama_kv_positions(const ugb_llama *m) { return m ? m->t_max : -1; }
+
+int32_t ugb_llama_tp_info(const ugb_llama *m, int32_t *tp_rank, int32_t *tp_size, int32_t *vocab_local,
+                          int32_t *vocab_offset, int32_t *kv_heads_local) {
+  if (!m) return UGB_ERR_INVALID;
+  if (tp_rank) *tp_rank = m->tp_rank;
+  if (tp_size) *tp_size = m->tp_size;
+  if (vocab_local) *vocab_local = m->vl;
+  if (vocab_offset) *vocab_offset = m->tp_rank * m->vl;
+  if (kv_heads_local) *kv_heads_local = m->lc.n_kv_heads;
+  return UGB_OK;
+}
+
+int32_t ugb_llama_tp_export(ugb_llama *m, void *handle_out, size_t handle_bytes) {
+  if (!m) return UGB_ERR_INVALID;
+  ugb_device *dev = m->dev;
+  UGB_REQUIRE(dev, m->tp && m->tp_block, UGB_ERR_INVALID, "ugb_llama_tp_export: not a tensor-parallel model");
+  UGB_REQUIRE(dev, handle_out && handle_bytes == sizeof(cudaIpcMemHandle_t), UGB_ERR_INVALID,
+              "ugb_llama_tp_export: the handle buffer must hold %zu bytes", sizeof(cudaIpcMemHandle_t));
+  UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
+  UGB_CUDA(dev, cudaStreamSynchronize(dev->stream));      // the block has been cleared before anyone maps it
+  cudaIpcMemHandle_t h;
+  UGB_CUDA(dev, cudaIpcGetMemHandle(&h, m->tp_block));
+  memcpy(handle_out, &h, sizeof(h));
+  return UGB_OK;
+}
+
+int32_t ugb_llama_tp_connect(ugb_llama *m, const void *handles, size_t handle_bytes, int32_t n_ranks) {
+  if (!m) return UGB_ERR_INVALID;
+  ugb_device *dev = m->dev;
+  UGB_REQUIRE(dev, m->tp, UGB_ERR_INVALID, "ugb_llama_tp_connect: not a tensor-parallel model");
+  UGB_REQUIRE(dev, handles && handle_bytes == sizeof(cudaIpcMemHandle_t) && n_ranks == m->tp_size, UGB_ERR_INVALID,
+              "ugb_llama_tp_connect: expected %d handles of %zu bytes", m->tp_size, sizeof(cudaIpcMemHandle_t));
+  UGB_REQUIRE(dev, !m->tp_ready || m->tp_size == 1, UGB_ERR_INVALID, "ugb_llama_tp_connect: already connected");
+  UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
+  for (int r = 0; r < m->tp_size; ++r) {
+    if (r == m->tp_rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, (const char *)handles + (size_t)r * handle_bytes, sizeof(h));
+    void *p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "mapping the exchange block of rank %d failed: %s", r, cudaGetErrorString(e));
+    m->tp_peer[r] = p;
+  }
+  m->tp_ready = true;
+  if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+  return UGB_OK;
+}
 
 }  // extern "C"

@@ -4,7 +4,10 @@ The path shards by independent units (sequences, rows, batch entries): every
 rank owns a contiguous range of units and there is no data-path collective.
 `torch.distributed` is used for the rendezvous, the barriers around the timed
 region and the max-over-ranks of the device-side timings only (backend
-``nccl`` on GPUs, ``gloo`` in the CPU tests).
+``nccl`` on GPUs, ``gloo`` in the CPU tests).  The tensor-parallel variant of
+the Llama engine uses it once more, to exchange the 64-byte handles of the
+ranks' exchange blocks (`Group.all_gather_bytes`); its per-step sums run inside
+the engine's own kernels over peer memory.
 """
 import os
 
@@ -21,6 +24,18 @@ def shard_range(n_units, rank, world):
     base, extra = divmod(n_units, world)
     lo = rank * base + min(rank, extra)
     return lo, lo + base + (1 if rank < extra else 0)
+
+
+def tp_shard(n_heads, n_kv_heads, ffn, vocab, rank, size):
+    """What tensor-parallel rank `rank` of `size` owns: query heads [q0, q0 + nq), KV heads
+    [kv0, kv0 + nkv) (one replicated KV head when there are more ranks than KV heads), FFN columns
+    [f0, f0 + nf) and logit columns [v0, v0 + nv).  Mirrors ugb_llama_create_tp."""
+    if n_heads % size or ffn % size or vocab % size or (n_kv_heads % size and size % n_kv_heads):
+        raise ValueError(f"{size} ranks do not divide heads {n_heads} / KV heads {n_kv_heads} / ffn {ffn} / vocab {vocab}")
+    nq, nf, nv = n_heads // size, ffn // size, vocab // size
+    nkv = n_kv_heads // size if n_kv_heads >= size else 1
+    return {"q0": rank * nq, "nq": nq, "kv0": rank * n_kv_heads // size, "nkv": nkv,
+            "f0": rank * nf, "nf": nf, "v0": rank * nv, "nv": nv}
 
 
 def rank_seed(seed, rank):
@@ -67,6 +82,15 @@ class Group:
 
     def sum(self, values):
         return self._reduce(values, self.dist.ReduceOp.SUM)
+
+    def all_gather_bytes(self, payload):
+        """Every rank's `payload` (bytes of one common length), in rank order."""
+        if not self.active:
+            return [bytes(payload)]
+        t = self.torch.tensor(list(payload), dtype=self.torch.uint8, device=self.device)
+        out = [self.torch.empty_like(t) for _ in range(self.world)]
+        self.dist.all_gather(out, t)
+        return [bytes(o.cpu().tolist()) for o in out]
 
     def close(self):
         if self.active and self.dist.is_initialized():

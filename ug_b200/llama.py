@@ -72,26 +72,49 @@ def weight_shape(cfg, name):
 class Model:
     """Model::new / Model::fwd for seq_len == 1 over ``batch`` independent sequences."""
 
-    def __init__(self, cfg, dev, batch, t_max):
+    def __init__(self, cfg, dev, batch, t_max, tp=None):
+        """``tp = (rank, size)`` builds the tensor-parallel variant: this process keeps rank's share of
+        heads, FFN columns and vocabulary; call :meth:`connect` on every rank before the first step."""
         if not cfg.tie_word_embeddings:
             raise UgError(6, "tie_word_embeddings == false is not supported yet")   # model.rs:318
         self.cfg, self.dev, self.batch = cfg, dev, batch
+        self.tp = tp
         cc = _CConfig(cfg.hidden_size, cfg.num_hidden_layers, cfg.num_attention_heads,
                       cfg.num_key_value_heads, cfg.head_dim(), cfg.intermediate_size, cfg.vocab_size,
                       cfg.max_position_embeddings, cfg.rope_theta, cfg.rms_norm_eps,
                       int(cfg.rope_interleaved))
         h = C.c_void_p()
-        dev._check(lib.ugb_llama_create(dev._h, C.byref(cc), batch, t_max, C.byref(h)))
+        if tp is None:
+            dev._check(lib.ugb_llama_create(dev._h, C.byref(cc), batch, t_max, C.byref(h)))
+        else:
+            dev._check(lib.ugb_llama_create_tp(dev._h, C.byref(cc), batch, t_max, tp[0], tp[1], C.byref(h)))
         self._h = h
+        info = [C.c_int32() for _ in range(5)]
+        lib.ugb_llama_tp_info(h, *[C.byref(i) for i in info])
+        self.tp_rank, self.tp_size, self.vocab_local, self.vocab_offset, self.kv_heads_local = (i.value for i in info)
 
     @classmethod
-    def new(cls, cfg, weights, dev, batch, t_max):
+    def new(cls, cfg, weights, dev, batch, t_max, tp=None, group=None):
         """``weights``: name -> host array; uint16 arrays are bf16 bit patterns, float32 arrays
-        are norm weights (or matrices to be rounded to bf16 on the device)."""
-        m = cls(cfg, dev, batch, t_max)
+        are norm weights (or matrices to be rounded to bf16 on the device).  Tensor parallel
+        (``tp``): every rank passes the whole tensors and ``group`` (ug_b200.dist.Group)."""
+        m = cls(cfg, dev, batch, t_max, tp=tp)
         for name in weight_names(cfg):
             m.load_weight(name, weights[name])
+        if tp is not None:
+            m.connect(group)
         return m
+
+    def connect(self, group):
+        """Maps the peers' exchange blocks (collective over ``group``; no-op for one rank)."""
+        if self.tp is None or self.tp_size == 1:
+            return
+        buf = C.create_string_buffer(64)
+        self.dev._check(lib.ugb_llama_tp_export(self._h, buf, 64))
+        handles = b"".join(group.all_gather_bytes(buf.raw))
+        self.dev._check(lib.ugb_llama_tp_connect(self._h, handles, 64, self.tp_size))
+        self.dev.synchronize()
+        group.barrier()          # nobody steps before everybody has mapped everybody
 
     def load_weight(self, name, arr):
         arr = np.ascontiguousarray(arr)
@@ -147,7 +170,7 @@ class Model:
     def prefill_logits(self):
         """f32 [batch, t, vocab] of the last ``all_logits`` prefill (what Model::fwd returns)."""
         t = getattr(self, "_prefill_t", 0)
-        out = np.empty((self.batch, t, self.cfg.vocab_size), np.float32)
+        out = np.empty((self.batch, t, self.vocab_local), np.float32)
         self.dev._check(lib.ugb_llama_read(self._h, 3, out.ctypes.data, out.size))
         return out
 
@@ -156,7 +179,9 @@ class Model:
         self.dev._check(lib.ugb_llama_decode(self._h, None, n_steps))
 
     def logits(self):
-        out = np.empty((self.batch, self.cfg.vocab_size), np.float32)
+        """f32 [batch, vocab]; a tensor-parallel rank returns its columns
+        [vocab_offset, vocab_offset + vocab_local)."""
+        out = np.empty((self.batch, self.vocab_local), np.float32)
         self.dev._check(lib.ugb_llama_read(self._h, 0, out.ctypes.data, out.size))
         return out
 
@@ -173,7 +198,7 @@ class Model:
     def kv_cache(self, layer, which):
         """bf16 bit patterns [batch, n_kv_heads, kv_positions, head_dim] of K (0) or V (1)."""
         t = lib.ugb_llama_kv_positions(self._h)
-        out = np.empty((self.batch, self.cfg.num_key_value_heads, t, self.cfg.head_dim()), np.uint16)
+        out = np.empty((self.batch, self.kv_heads_local, t, self.cfg.head_dim()), np.uint16)
         self.dev._check(lib.ugb_llama_read_kv(self._h, layer, which, out.ctypes.data, out.size))
         return out
 
