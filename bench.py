@@ -385,8 +385,11 @@ class DecodeWorkload:
     batch, prefill = 64, 2048
     step_is_graph = True
 
-    def __init__(self, rank, prefill=None, layers=None, fast_prefill=False):
+    def __init__(self, rank, prefill=None, layers=None, fast_prefill=False, tp=None):
         self.fast_prefill = fast_prefill
+        self.tp = tp                       # (rank, size): tensor-parallel variant, every rank sees the same 64 sequences
+        if tp is not None:
+            rank = 0                       # same prompts on every rank
         from ug_b200 import synth
         from ug_b200.llama import Config
         self.cfg = Config.llama_1b()
@@ -406,11 +409,18 @@ class DecodeWorkload:
         self.d2h_bytes = self.batch * 4
         self.launches_per_step = 1 + 8 * c.num_hidden_layers + 3
 
-    def setup(self, dev, total_steps=256):
+    def setup(self, dev, total_steps=256, group=None):
         from ug_b200.llama import Model
         self.dev = dev
         self.t_max = self.prefill + total_steps + 16
-        self.model = Model.new(self.cfg, self.weights, dev, self.batch, self.t_max)
+        self.model = Model.new(self.cfg, self.weights, dev, self.batch, self.t_max, tp=self.tp, group=group)
+        if self.tp is not None:
+            # per-rank bytes of a step: the rank's share of the layer weights, the whole embedding slice it
+            # multiplies by, and its KV heads
+            n = self.tp[1]
+            c = self.cfg
+            self.weight_bytes = (self.weight_bytes - 2 * c.vocab_size * c.hidden_size) // n + 2 * c.vocab_size * c.hidden_size // n
+            self.kv_bytes_per_pos = self.kv_bytes_per_pos * self.model.kv_heads_local // c.num_key_value_heads
         self.model.reset(0)
         if self.fast_prefill:
             self.model.fwd(self.prompts[:, 0])
@@ -476,10 +486,11 @@ class DecodeWorkload:
         self.model.reset(0)
         for i in range(4):
             self.model.fwd(self.prompts[:, i])
-            got = self.model.logits()
+            got = self.model.logits()                       # a tensor-parallel rank holds its vocabulary slice
+            v0, nv = self.model.vocab_offset, self.model.vocab_local
             for b, cache in caches.items():
                 want = ref.fwd(self.prompts[b:b + 1, i:i + 1], i, cache)[0, 0]
-                worst = max(worst, float(np.max(np.abs(got[b] - want)) / np.max(np.abs(want))))
+                worst = max(worst, float(np.max(np.abs(got[b] - want[v0:v0 + nv])) / np.max(np.abs(want))))
         return worst
 
     def _oracle(self):
@@ -515,7 +526,8 @@ class DecodeWorkload:
                                           f"ug-llama's CPU path (f32, GEMM stand-in on {self.cpu_threads} threads), {dt:.1f} s")
 
     def config(self):
-        return {"workload": self.name, "sequences_per_gpu": self.batch, "prefill": self.prefill,
+        par = {} if self.tp is None else {"parallelism": f"tp{self.tp[1]}", "sequences_total": self.batch}
+        return {"workload": self.name, **par, "sequences_per_gpu": self.batch, "prefill": self.prefill,
                 "layers": self.cfg.num_hidden_layers, "fast_prefill": self.fast_prefill,
                 "l2": "inputs larger than L2 (2.07 GB weights + ~3 GB KV cache read per step vs 126 MB L2)"}
 
@@ -633,6 +645,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--prefill", type=int, default=None, help="decode: cached positions before timing")
     ap.add_argument("--layers", type=int, default=None, help="decode: layer count (profiling of small cases)")
+    ap.add_argument("--tp", action="store_true",
+                    help="decode: tensor-parallel variant -- the ranks share ONE batch of 64 sequences (heads, FFN "
+                         "columns and vocabulary sharded, cross-rank sums inside the engine's kernels over NVLink)")
     ap.add_argument("--fast-prefill", action="store_true",
                     help="decode, profiling aid: place the cache at --prefill positions without running the "
                          "prompts (the cache then holds zeros); not a valid benchmark configuration")
@@ -645,8 +660,11 @@ def main():
     rank, local_rank, world = env_rank()
 
     def make_workload(r):
-        if args.workload in ("decode", "prefill"):
-            return WORKLOADS[args.workload](r, prefill=args.prefill, layers=args.layers, fast_prefill=args.fast_prefill)
+        if args.workload == "decode":
+            return DecodeWorkload(r, prefill=args.prefill, layers=args.layers, fast_prefill=args.fast_prefill,
+                                  tp=(rank, world) if args.tp else None)
+        if args.workload == "prefill":
+            return PrefillWorkload(r, prefill=args.prefill, layers=args.layers)
         return WORKLOADS[args.workload](r)
 
     if args.impl == "reference":
@@ -662,7 +680,7 @@ def main():
     wl = make_workload(rank)
     e2e_steps = max(3, min(args.steps, 10 if args.workload != "decode" else 32))
     if args.workload == "decode":
-        wl.setup(dev, total_steps=args.warmup + args.steps + e2e_steps + 8)
+        wl.setup(dev, total_steps=args.warmup + args.steps + e2e_steps + 8, group=group)
     else:
         wl.setup(dev)
 
@@ -703,21 +721,27 @@ def main():
     wl.teardown_e2e()
 
     ms, e2e_s = group.max([ms, e2e_s])      # the slowest rank defines the step
+    tp = bool(getattr(args, "tp", False)) and args.workload == "decode"
+    kern, att_bytes = {}, 0
+    if rank == 0 and args.workload == "decode":
+        # per-kernel share of one step, each kernel type timed alone over all layers (CUDA events); no exchange inside
+        for name in wl.model.KERNELS:
+            kern[name] = round(wl.model.time_kernel(name, 20), 4)
+        att_bytes = wl.kv_bytes_per_pos * wl.model.position * wl.batch
+    barrier()
+    # under tensor parallelism every engine call is collective: all ranks run the parity check
+    parity = wl.check() if (rank == 0 or tp) else None
 
     if rank == 0:
         peaks = measured_peaks()
         step_s = ms / 1e3 / args.steps
         extra = {}
         if args.workload == "decode":
-            value = world * wl.batch / step_s
-            e2e_value = world * wl.batch / (e2e_s / e2e_steps)
+            n_seq = wl.batch if tp else world * wl.batch      # tensor parallel: one batch shared by all ranks
+            value = n_seq / step_s
+            e2e_value = n_seq / (e2e_s / e2e_steps)
             depth = wl.mean_depth(first_pos, args.steps)
             achieved, peak, runit = wl.step_bytes(depth) / step_s / 1e9, peaks["hbm"], "GB/s"
-            # per-kernel share of one step, each kernel type timed alone over all layers (CUDA events)
-            kern = {}
-            for name in wl.model.KERNELS:
-                kern[name] = round(wl.model.time_kernel(name, 20), 4)
-            att_bytes = wl.kv_bytes_per_pos * wl.model.position * wl.batch
             extra["kernels_ms_per_step"] = kern
             extra["roofline_scope"] = ("whole decode step (one CUDA graph of %d kernels): weight bytes + KV bytes "
                                        "at the mean cache depth %.0f" % (wl.launches_per_step, depth))
@@ -736,7 +760,7 @@ def main():
         line = {
             "metric": wl.metric, "value": round(value, 2), "unit": wl.unit, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+            "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": wl.dtype,
             "data": "synthetic (seeded Philox, shapes and distributions of the named config)",
             "config": wl.config(),
             "e2e": {"value": round(e2e_value, 3), "unit": wl.unit,
@@ -754,7 +778,7 @@ def main():
             line["reference_cuda_kernel"] = None if g is None else {
                 "value": round(g, 1), "unit": "GB/s", "what": "ug-llama/src/softmax.cu compiled as is (fast-math), "
                 "launched as ug-llama/src/cuda_ops.rs does, same buffers"}
-        line["parity_max_rel_err"] = wl.check()
+        line["parity_max_rel_err"] = parity
         if not args.no_cpu_baseline:
             v, cores, sample = wl.cpu_sample(args.cpu_seconds)
             line["cpu_baseline"] = {"value": round(v, 4), "unit": wl.unit, "cores": cores,

@@ -108,8 +108,9 @@ reduce_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ part, int
 // with pos = *pos_p + pos_off + i: the base position is read from device memory
 // (every sequence of the batch sits at the same position, the reference's pos[0]
 // convention, cpu_ops.rs:67-71).  grid = (rows, ceil(items / 256)): one thread
-// per rotation pair or per v element, so that all of a thread's loads are
-// independent and issued at once.
+// per FOUR rotation pairs or four v elements -- 128-bit loads of the fp32
+// sums and of the cos / sin rows, 64- or 128-bit bf16 stores -- so that all of a
+// thread's loads are independent and issued at once.  hd % 8 == 0.
 static __global__ void __launch_bounds__(256)
 rope_append_kernel(const float *__restrict__ part, int n_part, size_t part_stride,
                    const float *__restrict__ cos_, const float *__restrict__ sin_,
@@ -120,34 +121,54 @@ rope_append_kernel(const float *__restrict__ part, int n_part, size_t part_strid
   ugb_pdl_wait();
   const int r = blockIdx.x, b = r / t;
   const int it = blockIdx.y * blockDim.x + threadIdx.x;
-  const int half = hd >> 1;
-  const int n_rot = (n_heads + n_kv) * half;
+  const int half = hd >> 1, quads = half >> 2;          // groups of 4 rotation pairs per head
+  const int n_rot = (n_heads + n_kv) * quads;
   const int qkv_dim = (n_heads + 2 * n_kv) * hd;
   const float *row = part + (size_t)r * qkv_dim;
   const int pos = *pos_p + pos_off + r % t;
-  if (it < n_rot) {
-    const int head = it / half, i = it - head * half;
-    const int i1 = interleaved ? 2 * i : i;
-    const int i2 = interleaved ? 2 * i + 1 : i + half;
-    float x1 = 0.f, x2 = 0.f;
+  auto sum4 = [&](int col) {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < n_part; ++s) {
-      x1 += row[s * part_stride + head * hd + i1];
-      x2 += row[s * part_stride + head * hd + i2];
+      const float4 p = *reinterpret_cast<const float4 *>(row + s * part_stride + col);
+      a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w;
     }
-    const float c = cos_[(size_t)pos * half + i], sn = sin_[(size_t)pos * half + i];
-    const float y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn));
-    const float y2 = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, c));
+    return a;
+  };
+  auto pack2 = [](float lo, float hi) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<uint32_t *>(&v); };
+  if (it < n_rot) {
+    const int head = it / quads, i = (it - head * quads) * 4;          // pairs i .. i + 3 of this head
+    const float4 c = *reinterpret_cast<const float4 *>(cos_ + (size_t)pos * half + i);
+    const float4 sn = *reinterpret_cast<const float4 *>(sin_ + (size_t)pos * half + i);
     __nv_bfloat16 *dst = head < n_heads
         ? q_out + ((size_t)r * n_heads + head) * hd
         : kcache + (((size_t)b * n_kv + (head - n_heads)) * t_max + pos) * hd;
-    dst[i1] = __float2bfloat16_rn(y1);
-    dst[i2] = __float2bfloat16_rn(y2);
-  } else if (it < n_rot + n_kv * hd) {
-    const int e = it - n_rot;
+    // dst[i1] = x1 c - x2 s, dst[i2] = x1 s + x2 c, each product and sum rounded separately (cpu_ops.rs:73-78)
+    if (interleaved) {                                                  // pairs (2i, 2i + 1): 8 contiguous values
+      const float4 u = sum4(head * hd + 2 * i), w = sum4(head * hd + 2 * i + 4);
+      uint4 o;
+      o.x = pack2(__fsub_rn(__fmul_rn(u.x, c.x), __fmul_rn(u.y, sn.x)), __fadd_rn(__fmul_rn(u.x, sn.x), __fmul_rn(u.y, c.x)));
+      o.y = pack2(__fsub_rn(__fmul_rn(u.z, c.y), __fmul_rn(u.w, sn.y)), __fadd_rn(__fmul_rn(u.z, sn.y), __fmul_rn(u.w, c.y)));
+      o.z = pack2(__fsub_rn(__fmul_rn(w.x, c.z), __fmul_rn(w.y, sn.z)), __fadd_rn(__fmul_rn(w.x, sn.z), __fmul_rn(w.y, c.z)));
+      o.w = pack2(__fsub_rn(__fmul_rn(w.z, c.w), __fmul_rn(w.w, sn.w)), __fadd_rn(__fmul_rn(w.z, sn.w), __fmul_rn(w.w, c.w)));
+      *reinterpret_cast<uint4 *>(dst + 2 * i) = o;
+    } else {                                                            // pairs (i, i + hd / 2)
+      const float4 x1 = sum4(head * hd + i), x2 = sum4(head * hd + i + half);
+      uint2 lo, hi;
+      lo.x = pack2(__fsub_rn(__fmul_rn(x1.x, c.x), __fmul_rn(x2.x, sn.x)), __fsub_rn(__fmul_rn(x1.y, c.y), __fmul_rn(x2.y, sn.y)));
+      lo.y = pack2(__fsub_rn(__fmul_rn(x1.z, c.z), __fmul_rn(x2.z, sn.z)), __fsub_rn(__fmul_rn(x1.w, c.w), __fmul_rn(x2.w, sn.w)));
+      hi.x = pack2(__fadd_rn(__fmul_rn(x1.x, sn.x), __fmul_rn(x2.x, c.x)), __fadd_rn(__fmul_rn(x1.y, sn.y), __fmul_rn(x2.y, c.y)));
+      hi.y = pack2(__fadd_rn(__fmul_rn(x1.z, sn.z), __fmul_rn(x2.z, c.z)), __fadd_rn(__fmul_rn(x1.w, sn.w), __fmul_rn(x2.w, c.w)));
+      *reinterpret_cast<uint2 *>(dst + i) = lo;
+      *reinterpret_cast<uint2 *>(dst + i + half) = hi;
+    }
+  } else if (it < n_rot + n_kv * (hd >> 2)) {
+    const int e = (it - n_rot) * 4;                                     // 4 contiguous v values
     const int head = e / hd, i = e - head * hd;
-    float x = 0.f;
-    for (int s = 0; s < n_part; ++s) x += row[s * part_stride + (n_heads + n_kv) * hd + e];
-    vcache[(((size_t)b * n_kv + head) * t_max + pos) * hd + i] = __float2bfloat16_rn(x);
+    const float4 x = sum4((n_heads + n_kv) * hd + e);
+    uint2 o;
+    o.x = pack2(x.x, x.y);
+    o.y = pack2(x.z, x.w);
+    *reinterpret_cast<uint2 *>(vcache + (((size_t)b * n_kv + head) * t_max + pos) * hd + i) = o;
   }
 }
 
@@ -461,7 +482,7 @@ namespace ugb_decode {
 // tiles with an online softmax in fp32 registers.
 constexpr int PF_BQ = 64, PF_BKV = 64;
 
-static __global__ void __launch_bounds__(128)
+static __global__ void __launch_bounds__(128, 4)
 prefill_attention_kernel(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restrict__ kcache,
                          const __nv_bfloat16 *__restrict__ vcache, __nv_bfloat16 *__restrict__ out, int t, int pos0,
                          int n_heads, int n_kv, int t_max, float scale) {

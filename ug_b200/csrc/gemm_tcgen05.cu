@@ -180,6 +180,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int tiles_per_split = tiles_per_batch * p.batch;
+  const int n_tiles = tiles_per_split * p.splits;
+  auto issue_b = [&](uint32_t b_dst, uint32_t bar, int kb, int n0, int bz) {
+    if (p.b_is_nk) {
+      tma_load_3d(b_dst, &tmB, bar, kb * BK, n0, bz);            // box {64 k, BN n}
+    } else {
+#pragma unroll
+      for (int c = 0; c < BN / 64; ++c)                           // BN/64 boxes {64 n, 64 k}
+        tma_load_3d(b_dst + c * (64 * BK * 2), &tmB, bar, n0 + c * 64, kb * BK, bz);
+    }
+  };
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&full[s]), 1);
@@ -193,6 +205,26 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+    // Preamble: the B operand of the first tile (weights in the decode step) is written by no kernel of
+    // the stream, so its first stages are requested right here -- before the TMEM allocation, the CTA
+    // barrier and the wait for the preceding kernel; A follows once that kernel is done.
+    if (p.b_static) {
+      const int tile = blockIdx.x;
+      const int sp = tile / tiles_per_split;
+      const int ts = tile - sp * tiles_per_split;
+      const int bi = ts / tiles_per_batch;
+      const int r = ts - bi * tiles_per_batch;
+      const int n0 = (p.n_fast ? r % p.tiles_n : r / p.tiles_m) * BN;
+      const int bz = p.b_batched ? bi : 0;
+      const int kb0 = sp * p.kb_per_split;
+      const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+      const int pre = min(STAGES, kb1 - kb0);
+      for (int i = 0; i < pre; ++i) {
+        const uint32_t bar = smem_u32(&full[i]);
+        mbar_expect_tx(bar, (uint32_t)p.stage_tx);
+        issue_b(smem_u32(smem + i * STAGE_BYTES) + A_BYTES, bar, kb0 + i, n0, bz);
+      }
+    }
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -205,28 +237,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) ugb_pdl_trigger();   // the next kernel on the stream may begin its preamble
 
-  const int tiles_per_batch = p.tiles_m * p.tiles_n;
-  const int tiles_per_split = tiles_per_batch * p.batch;
-  const int n_tiles = tiles_per_split * p.splits;
-
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer --
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      auto issue_b = [&](uint32_t b_dst, uint32_t bar, int kb, int n0, int bz) {
-        if (p.b_is_nk) {
-          tma_load_3d(b_dst, &tmB, bar, kb * BK, n0, bz);            // box {64 k, BN n}
-        } else {
-#pragma unroll
-          for (int c = 0; c < BN / 64; ++c)                           // BN/64 boxes {64 n, 64 k}
-            tma_load_3d(b_dst + c * (64 * BK * 2), &tmB, bar, n0 + c * 64, kb * BK, bz);
-        }
-      };
-      // Preamble: the B operand of the first tile (weights in the decode step) is
-      // written by no kernel of the stream, so its first stages are requested
-      // before waiting for the preceding kernel; A follows once that kernel is done.
+      // The B halves of the first `pre` stages were requested in the preamble above.
       int pre = 0;
       {
         const int tile = blockIdx.x;
@@ -234,16 +251,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int ts = tile - sp * tiles_per_split;
         const int bi = ts / tiles_per_batch;
         const int r = ts - bi * tiles_per_batch;
-        const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * BM, n0 = (p.n_fast ? r % p.tiles_n : r / p.tiles_m) * BN;
-        const int bz = p.b_batched ? bi : 0;
+        const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * BM;
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         pre = p.b_static ? min(STAGES, kb1 - kb0) : 0;
-        for (int i = 0; i < pre; ++i) {
-          const uint32_t bar = smem_u32(&full[i]);
-          mbar_expect_tx(bar, (uint32_t)p.stage_tx);
-          issue_b(smem_u32(smem + i * STAGE_BYTES) + A_BYTES, bar, kb0 + i, n0, bz);
-        }
         ugb_pdl_wait();
         for (int i = 0; i < pre; ++i)
           tma_load_3d(smem_u32(smem + i * STAGE_BYTES), &tmA, smem_u32(&full[i]), (kb0 + i) * BK, m0, bi);
@@ -434,6 +445,7 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   if (!st->attr_set[slot]) {
     UGB_CUDA(dev, cudaFuncSetAttribute(tc_gemm_kernel<BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg<BM, BN>::SMEM_BYTES));
+
     st->attr_set[slot] = true;
   }
   Params p;

@@ -67,7 +67,7 @@ struct ugb_llama {
   // tuning
   int splits_qkv = 3, splits_o = 4, splits_down = 8, att_splits = 1, att_stages = 3;
   int pdl = 1;                    // programmatic dependent launch between the kernels of a step
-  int gemm_smem_kib = 0;          // shared-memory cap of the decode GEMM CTAs (0 = deepest ring)
+  int gemm_smem_kib = 144;        // shared-memory cap of the decode GEMM CTAs (0 = deepest ring); measured best
   int skip = 0;                   // measurement aid: bit mask of kernel types left out of the step
   int bn_qkv = 64, bn_o = 64, bn_gate_up = 128, bn_down = 128, bn_lm_head = 256;   // GEMM tile widths
   size_t part_elems = 0;
@@ -217,10 +217,10 @@ int32_t launch_reduce(ugb_llama *m, int rows, float *x, __nv_bfloat16 *xn, int w
   const bool pdl = m->pdl != 0;
   ugb_status_word *status = m->dev->status_dev;
   cudaError_t e;
-  if (nvec <= 256) e = ugb_launch(tp_reduce_rmsnorm_kernel<1>, dim3(rows), dim3(256), 0, st, pdl, x, tp, n_part, stride, alpha, xn, hidden, inv_d, eps, status);
-  else if (nvec <= 512) e = ugb_launch(tp_reduce_rmsnorm_kernel<2>, dim3(rows), dim3(256), 0, st, pdl, x, tp, n_part, stride, alpha, xn, hidden, inv_d, eps, status);
-  else if (nvec <= 1024) e = ugb_launch(tp_reduce_rmsnorm_kernel<4>, dim3(rows), dim3(256), 0, st, pdl, x, tp, n_part, stride, alpha, xn, hidden, inv_d, eps, status);
-  else e = ugb_launch(tp_reduce_rmsnorm_kernel<8>, dim3(rows), dim3(256), 0, st, pdl, x, tp, n_part, stride, alpha, xn, hidden, inv_d, eps, status);
+  const dim3 blk(TP_RED_THREADS);
+  if (nvec <= TP_RED_THREADS) e = ugb_launch(tp_reduce_rmsnorm_kernel<1>, dim3(rows), blk, 0, st, pdl, x, tp, n_part, stride, alpha, xn, hidden, inv_d, eps, status);
+  else if (nvec <= 2 * TP_RED_THREADS) e = ugb_launch(tp_reduce_rmsnorm_kernel<2>, dim3(rows), blk, 0, st, pdl, x, tp, n_part, stride, alpha, xn, hidden, inv_d, eps, status);
+  else e = ugb_launch(tp_reduce_rmsnorm_kernel<4>, dim3(rows), blk, 0, st, pdl, x, tp, n_part, stride, alpha, xn, hidden, inv_d, eps, status);
   if (e != cudaSuccess) return ugb_fail(m->dev, UGB_ERR_CUDA, "launch of tp_reduce_rmsnorm_kernel failed: %s", cudaGetErrorString(e));
   return ugb_after_launch(m->dev, "tp_reduce_rmsnorm_kernel");
 }
@@ -295,7 +295,7 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
     if (!(m->skip & 2) && (rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv))) return rc;
     __nv_bfloat16 *kc = m->kcache + (size_t)l * m->kv_layer_stride;
     __nv_bfloat16 *vc = m->vcache + (size_t)l * m->kv_layer_stride;
-    const int rope_items = (c.n_heads + c.n_kv_heads) * c.head_dim / 2 + c.n_kv_heads * c.head_dim;
+    const int rope_items = ((c.n_heads + c.n_kv_heads) * c.head_dim / 2 + c.n_kv_heads * c.head_dim) / 4;   // 4 pairs / values per thread
     if (!(m->skip & 4))
     e = ugb_launch(rope_append_kernel, dim3(B, (rope_items + 255) / 256), dim3(256), 0, st, pdl, m->part, s_qkv,
                    (size_t)B * m->qkv_dim, m->cos, m->sin, m->pos, m->q, kc, vc, c.n_heads, c.n_kv_heads, c.head_dim,
@@ -348,7 +348,7 @@ int32_t enqueue_prefill_chunk(ugb_llama *m, const int *tok, int t, int c0, int t
                              dev->status_dev, tc, t, c0);
   if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of embed_gather_kernel failed: %s", cudaGetErrorString(e));
   if ((rc = ugb_after_launch(dev, "embed_gather_kernel"))) return rc;
-  const int rope_items = (c.n_heads + c.n_kv_heads) * c.head_dim / 2 + c.n_kv_heads * c.head_dim;
+  const int rope_items = ((c.n_heads + c.n_kv_heads) * c.head_dim / 2 + c.n_kv_heads * c.head_dim) / 4;   // 4 pairs / values per thread
   float *po = o_out(m, m->pf_f32), *pd = down_out(m, m->pf_f32);
   for (int l = 0; l < c.layers; ++l) {
     const LayerW &w = m->layers[l];
@@ -501,6 +501,14 @@ int32_t ugb_llama_create_tp(ugb_device *dev, const ugb_llama_config *cfg, int32_
     m->tp_block = blk;
     m->tp_peer[tp_rank] = blk;
     m->tp_ready = n_rank == 1;
+    if (n_rank > 1) {
+      // a rank's projections are 1 / n_rank of the work: fewer split-K partials to fetch from the peers, and
+      // the KV range cut in slices so that the rank's fewer (sequence, KV head) pairs still fill the SMs
+      m->splits_qkv = 7;
+      m->splits_o = 2;
+      m->splits_down = 2;
+      m->att_splits = n_rank < 8 ? n_rank : 8;
+    }
   }
   // rope tables, model.rs:278-295: theta_i = 1 / theta^(i/d) in f32 on the host
   {

@@ -99,13 +99,14 @@ __device__ __forceinline__ void tp_exchange_end(const TpPeers &tp) {
 // then xn = bf16(x / sqrt(mean(x^2) + eps) * alpha)            (Layer::fwd's residual add + RmsNorm::fwd,
 // ug-llama/src/model.rs:65-78,259-269, with the tensor-parallel all-reduce folded in).
 // Every rank adds the same numbers in the same order, so the replicas of x stay bit-identical.
-// One CTA of 256 threads per row; hidden <= 8192, hidden % 4 == 0.
+// One CTA of 512 threads per row; hidden <= 8192, hidden % 4 == 0.
+constexpr int TP_RED_THREADS = 512;
 template <int VPT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(TP_RED_THREADS)
 tp_reduce_rmsnorm_kernel(float *__restrict__ x, TpPeers tp, int n_part, size_t part_stride,
                          const float *__restrict__ alpha, __nv_bfloat16 *__restrict__ xn, int hidden,
                          float inv_d, float eps, ugb_status_word *status) {
-  __shared__ float sm[8];
+  __shared__ float sm[TP_RED_THREADS / 32];
   ugb_pdl_trigger();
   ugb_pdl_wait();
   tp_exchange_begin(tp, status, blockIdx.x == 0);
@@ -114,19 +115,31 @@ tp_reduce_rmsnorm_kernel(float *__restrict__ x, TpPeers tp, int n_part, size_t p
   float4 *xr = reinterpret_cast<float4 *>(x + (size_t)b * hidden);
   float4 v[VPT];
   float ss = 0.f;
+  const int n_loads = tp.size * n_part;        // (rank, partial) pairs, rank-major = the order of the sum
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int c = threadIdx.x + i * 256;
+    const int c = threadIdx.x + i * TP_RED_THREADS;
     v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c < nvec) {
       v[i] = xr[c];
-      for (int r = 0; r < tp.size; ++r) {
-        const float *pr = tp.part[r];
-        for (int s = 0; s < n_part; ++s) {
-          // ld.cv: never served from this SM's L1, whose lines may be from the previous use of the buffer
-          const float4 p = __ldcv(reinterpret_cast<const float4 *>(pr + s * part_stride + (size_t)b * hidden) + c);
-          v[i].x += p.x; v[i].y += p.y; v[i].z += p.z; v[i].w += p.w;
+      // Peer loads cross NVLink (microseconds each): up to 16 are requested before the first is used, so a
+      // thread waits once per batch instead of once per partial.  ld.cv: never served from this SM's L1,
+      // whose lines may be from the buffer's previous use.
+      for (int j0 = 0; j0 < n_loads; j0 += 16) {
+        float4 p[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const int j = j0 + u;
+          if (j < n_loads) {
+            const int r = j / n_part, sp = j - r * n_part;
+            p[u] = __ldcv(reinterpret_cast<const float4 *>(tp.part[r] + (size_t)sp * part_stride + (size_t)b * hidden) + c);
+          } else {
+            p[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
         }
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+          if (j0 + u < n_loads) { v[i].x += p[u].x; v[i].y += p[u].y; v[i].z += p[u].z; v[i].w += p[u].w; }
       }
       xr[c] = v[i];
       ss += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
@@ -136,13 +149,13 @@ tp_reduce_rmsnorm_kernel(float *__restrict__ x, TpPeers tp, int n_part, size_t p
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = ss;
   __syncthreads();
-  float tot = (threadIdx.x & 31) < 8 ? sm[threadIdx.x & 31] : 0.f;
+  float tot = (threadIdx.x & 31) < TP_RED_THREADS / 32 ? sm[threadIdx.x & 31] : 0.f;
   tot = warp_sum(tot);
   const float m = sqrtf(tot * inv_d + eps);
   uint2 *out = reinterpret_cast<uint2 *>(xn + (size_t)b * hidden);
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int c = threadIdx.x + i * 256;
+    const int c = threadIdx.x + i * TP_RED_THREADS;
     if (c < nvec) {
       const float4 w = __ldg(reinterpret_cast<const float4 *>(alpha) + c);
       __nv_bfloat162 lo = __floats2bfloat162_rn(v[i].x / m * w.x, v[i].y / m * w.y);
