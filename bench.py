@@ -407,7 +407,7 @@ class DecodeWorkload:
         self.kv_bytes_per_pos = c.num_hidden_layers * 2 * c.num_key_value_heads * c.head_dim() * 2
         self.h2d_bytes = self.batch * 4
         self.d2h_bytes = self.batch * 4
-        self.launches_per_step = 1 + 8 * c.num_hidden_layers + 3
+        self.launches_per_step = 1 + 7 * c.num_hidden_layers + 3
 
     def setup(self, dev, total_steps=256, group=None):
         from ug_b200.llama import Model

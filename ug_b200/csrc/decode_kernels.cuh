@@ -213,13 +213,27 @@ constexpr int ATT_RING_BYTES = att_ring_bytes(ATT_STAGES);
 // K frags use a permuted k index (dims 16t+4s.. for lane t, step s) so that a
 // lane's operands are two contiguous 16-byte pieces of a row; Q uses the same
 // permutation.  V frags come from ldmatrix.trans on the staged sub-tile.
+// Fused front end (the engine's decode step): with `rope.part` set, q / k / v of the new position are
+// taken from the fp32 split-K partials of the qkv projection ([s][b][(n_heads + 2 n_kv) * 64]) instead
+// of `q`: the CTA sums the partials in order, applies the rotation (each product and sum rounded
+// separately, as ug-llama/src/cpu_ops.rs:73-78), rounds to bf16, and -- the CTA whose slice holds the
+// new position, when `rope.append` -- writes the K / V rows of position pos into the cache before it
+// reads them back with the rest of its slice.  Same arithmetic as rope_append_kernel.
+struct AttRope {
+  const float *part;
+  int n_part;
+  size_t part_stride;
+  const float *cos_, *sin_;
+  int interleaved, append;
+};
+
 template <int NSTAGE>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
-decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat16 *__restrict__ kcache,
-                        const __nv_bfloat16 *__restrict__ vcache, const int *__restrict__ pos_p,
+decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__restrict__ kcache,
+                        __nv_bfloat16 *__restrict__ vcache, const int *__restrict__ pos_p,
                         float *__restrict__ part_o, float *__restrict__ part_ml,
                         unsigned int *__restrict__ counters, __nv_bfloat16 *__restrict__ out,
-                        int n_heads, int n_kv, int group, int t_max, float scale) {
+                        int n_heads, int n_kv, int group, int t_max, float scale, AttRope rope) {
   extern __shared__ __align__(128) uint8_t att_smem[];                     // the cp.async ring, 64 KiB
   uint8_t (*ring)[NSTAGE][2][ATT_SUB_BYTES] =
       reinterpret_cast<uint8_t (*)[NSTAGE][2][ATT_SUB_BYTES]>(att_smem);
@@ -241,9 +255,10 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat
   const __nv_bfloat16 *kbase = kcache + ((size_t)b * n_kv + kvh) * (size_t)t_max * ATT_HD;
   const __nv_bfloat16 *vbase = vcache + ((size_t)b * n_kv + kvh) * (size_t)t_max * ATT_HD;
 
-  // Q fragments (rows >= group are zero padding)
+  // Q fragments (rows >= group are zero padding): lane (g, t) holds dims 16t .. 16t + 15 of query head g.
+  // With the fused front end they are computed after the ring has been filled (below).
   uint32_t qa[8];
-  {
+  if (rope.part == nullptr) {
     uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
     if (g < group) {
       const uint4 *qp = reinterpret_cast<const uint4 *>(q + ((size_t)b * n_heads + kvh * group + g) * ATT_HD + 16 * t);
@@ -253,6 +268,61 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat
     qa[0] = lo.x; qa[1] = lo.y; qa[2] = lo.z; qa[3] = lo.w;
     qa[4] = hi.x; qa[5] = hi.y; qa[6] = hi.z; qa[7] = hi.w;
   }
+  const int half = ATT_HD / 2;
+  const float *rope_row = rope.part ? rope.part + (size_t)b * ((n_heads + 2 * n_kv) * ATT_HD) : nullptr;
+  auto sum4 = [&](int col) {       // all partials requested before the first is used (at most 8 of them)
+    float4 p[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+      p[s] = s < rope.n_part ? __ldcg(reinterpret_cast<const float4 *>(rope_row + s * rope.part_stride + col))
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+      if (s < rope.n_part) { a.x += p[s].x; a.y += p[s].y; a.z += p[s].z; a.w += p[s].w; }
+    return a;
+  };
+  // K / V rows of the new position: written by the warp that will fetch the sub-tile holding them, so
+  // that no CTA barrier is needed -- before the ring is filled when that sub-tile is part of the fill,
+  // otherwise after, with the fill's loads in flight.
+  auto append_kv = [&]() {
+    const int pos = T - 1;
+    const int kcol = (n_heads + kvh) * ATT_HD, vcol = (n_heads + n_kv + kvh) * ATT_HD;
+    __nv_bfloat16 *kd = kcache + (((size_t)b * n_kv + kvh) * t_max + pos) * ATT_HD;
+    __nv_bfloat16 *vd = vcache + (((size_t)b * n_kv + kvh) * t_max + pos) * ATT_HD;
+    if (lane < 8) {                                      // 4 rotation pairs per lane
+      const int i = lane * 4;
+      const float4 c = *reinterpret_cast<const float4 *>(rope.cos_ + (size_t)pos * half + i);
+      const float4 sn = *reinterpret_cast<const float4 *>(rope.sin_ + (size_t)pos * half + i);
+      if (rope.interleaved) {
+        const float4 u = sum4(kcol + 2 * i), w = sum4(kcol + 2 * i + 4);
+        uint4 o;
+        o.x = pack_bf16(__fsub_rn(__fmul_rn(u.x, c.x), __fmul_rn(u.y, sn.x)), __fadd_rn(__fmul_rn(u.x, sn.x), __fmul_rn(u.y, c.x)));
+        o.y = pack_bf16(__fsub_rn(__fmul_rn(u.z, c.y), __fmul_rn(u.w, sn.y)), __fadd_rn(__fmul_rn(u.z, sn.y), __fmul_rn(u.w, c.y)));
+        o.z = pack_bf16(__fsub_rn(__fmul_rn(w.x, c.z), __fmul_rn(w.y, sn.z)), __fadd_rn(__fmul_rn(w.x, sn.z), __fmul_rn(w.y, c.z)));
+        o.w = pack_bf16(__fsub_rn(__fmul_rn(w.z, c.w), __fmul_rn(w.w, sn.w)), __fadd_rn(__fmul_rn(w.z, sn.w), __fmul_rn(w.w, c.w)));
+        *reinterpret_cast<uint4 *>(kd + 2 * i) = o;
+      } else {
+        const float4 x1 = sum4(kcol + i), x2 = sum4(kcol + i + half);
+        uint2 lo, hi;
+        lo.x = pack_bf16(__fsub_rn(__fmul_rn(x1.x, c.x), __fmul_rn(x2.x, sn.x)), __fsub_rn(__fmul_rn(x1.y, c.y), __fmul_rn(x2.y, sn.y)));
+        lo.y = pack_bf16(__fsub_rn(__fmul_rn(x1.z, c.z), __fmul_rn(x2.z, sn.z)), __fsub_rn(__fmul_rn(x1.w, c.w), __fmul_rn(x2.w, sn.w)));
+        hi.x = pack_bf16(__fadd_rn(__fmul_rn(x1.x, sn.x), __fmul_rn(x2.x, c.x)), __fadd_rn(__fmul_rn(x1.y, sn.y), __fmul_rn(x2.y, c.y)));
+        hi.y = pack_bf16(__fadd_rn(__fmul_rn(x1.z, sn.z), __fmul_rn(x2.z, c.z)), __fadd_rn(__fmul_rn(x1.w, sn.w), __fmul_rn(x2.w, c.w)));
+        *reinterpret_cast<uint2 *>(kd + i) = lo;
+        *reinterpret_cast<uint2 *>(kd + i + half) = hi;
+      }
+    } else if (lane < 24) {                              // 4 v values per lane
+      const int i = (lane - 8) * 4;
+      const float4 x = sum4(vcol + i);
+      *reinterpret_cast<uint2 *>(vd + i) = make_uint2(pack_bf16(x.x, x.y), pack_bf16(x.z, x.w));
+    }
+    __threadfence();                                     // in L2 before this warp's cp.async fetches the row
+    __syncwarp();
+  };
+  const int sub_pos = (T - 1) / ATT_SUB;                 // sub-tile of the new position
+  const bool appender = rope.part != nullptr && rope.append && sub_pos >= sub_lo && sub_pos < sub_hi &&
+                        ((sub_pos - sub_lo) & (ATT_WARPS - 1)) == warp;
 
   auto issue = [&](int sub, int stage) {
     // 16 keys x 128 B for K and for V: 4 + 4 chunks of 16 B per lane, XOR-swizzled rows
@@ -276,11 +346,62 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat
 
   // prologue: fill the ring
   const int first = sub_lo + warp;
+  const bool append_first = appender && sub_pos < first + (NSTAGE - 1) * ATT_WARPS;
+  if (append_first) append_kv();
 #pragma unroll
   for (int s = 0; s < NSTAGE - 1; ++s) {
     const int sub = first + s * ATT_WARPS;
     if (sub < sub_hi) issue(sub, s);
     cp_async_commit();
+  }
+  if (appender && !append_first) append_kv();
+  if (rope.part != nullptr) {
+    // ---- this lane's 16 dims of query head g, rotated -------------------------------------------
+    float y[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) y[e] = 0.f;
+    if (g < group) {
+      const int pos = T - 1, qcol = (kvh * group + g) * ATT_HD, d0 = 16 * t;
+      float xa[16];
+#pragma unroll
+      for (int v4 = 0; v4 < 4; ++v4) {
+        const float4 a = sum4(qcol + d0 + 4 * v4);
+        xa[4 * v4] = a.x; xa[4 * v4 + 1] = a.y; xa[4 * v4 + 2] = a.z; xa[4 * v4 + 3] = a.w;
+      }
+      if (rope.interleaved) {                                // pairs (2i, 2i + 1), i = 8t .. 8t + 7: all in this lane
+        float cs[8], sn[8];
+#pragma unroll
+        for (int v4 = 0; v4 < 2; ++v4) {
+          const float4 c4 = *reinterpret_cast<const float4 *>(rope.cos_ + (size_t)pos * half + 8 * t + 4 * v4);
+          const float4 s4 = *reinterpret_cast<const float4 *>(rope.sin_ + (size_t)pos * half + 8 * t + 4 * v4);
+          cs[4 * v4] = c4.x; cs[4 * v4 + 1] = c4.y; cs[4 * v4 + 2] = c4.z; cs[4 * v4 + 3] = c4.w;
+          sn[4 * v4] = s4.x; sn[4 * v4 + 1] = s4.y; sn[4 * v4 + 2] = s4.z; sn[4 * v4 + 3] = s4.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          y[2 * i] = __fsub_rn(__fmul_rn(xa[2 * i], cs[i]), __fmul_rn(xa[2 * i + 1], sn[i]));
+          y[2 * i + 1] = __fadd_rn(__fmul_rn(xa[2 * i], sn[i]), __fmul_rn(xa[2 * i + 1], cs[i]));
+        }
+      } else {                                               // pairs (i, i + 32): the partner dims sit 32 away
+        const int i0 = d0 & (half - 1);                      // rotation index of this lane's first dim
+        float xb[16], cs[16], sn[16];
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          const float4 a = sum4(qcol + (d0 ^ half) + 4 * v4);
+          const float4 c4 = *reinterpret_cast<const float4 *>(rope.cos_ + (size_t)pos * half + i0 + 4 * v4);
+          const float4 s4 = *reinterpret_cast<const float4 *>(rope.sin_ + (size_t)pos * half + i0 + 4 * v4);
+          xb[4 * v4] = a.x; xb[4 * v4 + 1] = a.y; xb[4 * v4 + 2] = a.z; xb[4 * v4 + 3] = a.w;
+          cs[4 * v4] = c4.x; cs[4 * v4 + 1] = c4.y; cs[4 * v4 + 2] = c4.z; cs[4 * v4 + 3] = c4.w;
+          sn[4 * v4] = s4.x; sn[4 * v4 + 1] = s4.y; sn[4 * v4 + 2] = s4.z; sn[4 * v4 + 3] = s4.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 16; ++e)
+          y[e] = d0 < half ? __fsub_rn(__fmul_rn(xa[e], cs[e]), __fmul_rn(xb[e], sn[e]))      // x1 c - x2 s
+                           : __fadd_rn(__fmul_rn(xb[e], sn[e]), __fmul_rn(xa[e], cs[e]));     // x1 s + x2 c
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) qa[e] = pack_bf16(y[2 * e], y[2 * e + 1]);
   }
   int stage = 0;
   for (int sub = first; sub < sub_hi; sub += ATT_WARPS) {
@@ -376,9 +497,14 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, const __nv_bfloat
       acc += merge_o[w][h][dd] * f;
       ll += merge_ml[w][h][1] * f;
     }
+    if (n_split == 1) {      // the only slice: no partials, no counter
+      if (h < group) out[((size_t)b * n_heads + kvh * group + h) * ATT_HD + dd] = __float2bfloat16_rn(acc / ll);
+      continue;
+    }
     part_o[(slot * ATT_GROUP + h) * ATT_HD + dd] = acc;
     if (dd == 0) { part_ml[(slot * ATT_GROUP + h) * 2] = mm; part_ml[(slot * ATT_GROUP + h) * 2 + 1] = ll; }
   }
+  if (n_split == 1) return;
   // ---- last CTA of this (b, kvh) combines the slices ------------------------
   __threadfence();
   __syncthreads();

@@ -252,15 +252,20 @@ int32_t launch_lm_head_argmax(ugb_llama *m, bool pdl_first) {
   return ugb_after_launch(dev, "tp_argmax_final_kernel");
 }
 
-int32_t launch_attention(ugb_llama *m, const __nv_bfloat16 *kc, const __nv_bfloat16 *vc, float scale) {
+// Rope of q and k, append of the new K / V rows and attention over the cache, one kernel per layer.
+// `append` false (kernel timing): the cache is left untouched.
+int32_t launch_attention(ugb_llama *m, __nv_bfloat16 *kc, __nv_bfloat16 *vc, float scale, int n_part, bool append) {
   const ugb_llama_config &c = m->lc;
   dim3 grid(m->att_splits, c.n_kv_heads, m->batch);
   cudaStream_t st = m->dev->stream;
+  AttRope rope;
+  rope.part = m->part; rope.n_part = n_part; rope.part_stride = (size_t)m->batch * m->qkv_dim;
+  rope.cos_ = m->cos; rope.sin_ = m->sin; rope.interleaved = c.rope_interleaved; rope.append = append ? 1 : 0;
   cudaError_t e = cudaSuccess;
 #define UGB_ATT_LAUNCH(NS)                                                                                   \
   e = ugb_launch(decode_attention_kernel_t<NS>, grid, dim3(ATT_WARPS * 32), att_ring_bytes(NS), st,           \
-                 m->pdl != 0, m->q, kc, vc, m->pos, m->att_po, m->att_pml, m->att_cnt, m->att, c.n_heads,     \
-                 c.n_kv_heads, c.n_heads / c.n_kv_heads, m->t_max, scale)
+                 m->pdl != 0, (const __nv_bfloat16 *)nullptr, kc, vc, (const int *)m->pos, m->att_po, m->att_pml, \
+                 m->att_cnt, m->att, c.n_heads, c.n_kv_heads, c.n_heads / c.n_kv_heads, m->t_max, scale, rope)
   switch (m->att_stages) {
     case 2: UGB_ATT_LAUNCH(2); break;
     case 4: UGB_ATT_LAUNCH(4); break;
@@ -295,14 +300,7 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
     if (!(m->skip & 2) && (rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv))) return rc;
     __nv_bfloat16 *kc = m->kcache + (size_t)l * m->kv_layer_stride;
     __nv_bfloat16 *vc = m->vcache + (size_t)l * m->kv_layer_stride;
-    const int rope_items = ((c.n_heads + c.n_kv_heads) * c.head_dim / 2 + c.n_kv_heads * c.head_dim) / 4;   // 4 pairs / values per thread
-    if (!(m->skip & 4))
-    e = ugb_launch(rope_append_kernel, dim3(B, (rope_items + 255) / 256), dim3(256), 0, st, pdl, m->part, s_qkv,
-                   (size_t)B * m->qkv_dim, m->cos, m->sin, m->pos, m->q, kc, vc, c.n_heads, c.n_kv_heads, c.head_dim,
-                   m->t_max, c.rope_interleaved, 1, 0);
-    if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of rope_append_kernel failed: %s", cudaGetErrorString(e));
-    if ((rc = ugb_after_launch(dev, "rope_append_kernel"))) return rc;
-    if (!(m->skip & 8) && (rc = launch_attention(m, kc, vc, scale))) return rc;
+    if (!(m->skip & 8) && (rc = launch_attention(m, kc, vc, scale, s_qkv, true))) return rc;   // rope + append + attention
     if (!(m->skip & 16) && (rc = gemm(m, po, m->att, w.wo, H, AW, UGB_EPI_F32, m->splits_o, m->bn_o))) return rc;
     if (!(m->skip & 1) && (rc = launch_reduce(m, B, m->x, m->xn, RED_O, po, s_o, w.rms2))) return rc;
     if (!(m->skip & 32) && (rc = gemm(m, m->h, m->xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, m->bn_gate_up))) return rc;
@@ -790,7 +788,8 @@ int32_t ugb_llama_time_kernel(ugb_llama *m, int32_t which, int32_t iters, float 
         case UGB_LLAMA_K_QKV: rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv); break;
         case UGB_LLAMA_K_ATTENTION: {
           rc = launch_attention(m, m->kcache + (size_t)l * m->kv_layer_stride,
-                                m->vcache + (size_t)l * m->kv_layer_stride, scale);
+                                m->vcache + (size_t)l * m->kv_layer_stride, scale,
+                                ugb_tc_gemm_effective_splits(H, m->splits_qkv), false);
           break;
         }
         case UGB_LLAMA_K_O: rc = gemm(m, m->part, m->att, w.wo, H, AW, UGB_EPI_F32, m->splits_o, m->bn_o); break;
