@@ -124,12 +124,19 @@ __global__ void __launch_bounds__(THREADS) row_reg_kernel(RowArgs a) {
         const int c = lane + i * LANES;
         if (c < nvec) {
           const float4 w = __ldg(al + c);
-          float4 o = make_float4(v[i].x / m * w.x, v[i].y / m * w.y, v[i].z / m * w.z, v[i].w / m * w.w);
+          float4 o;
           if constexpr (OP == OP_RMS_SILU) {
-            o.x *= silu(g[i].x);
-            o.y *= silu(g[i].y);
-            o.z *= silu(g[i].z);
-            o.w *= silu(g[i].w);
+            // x / m * w * g / (1 + exp(-g)) with one division per element: (x w g) / (m (1 + exp(-g))).
+            // With libm expf and two IEEE divisions per element the kernel is issue-bound (0.85 of the HBM
+            // peak); ex2.approx-based __expf (|error| ~ 2^-21 |g|) and the approximate division (2 ulp) keep
+            // the result within ~6e-7 relative of the oracle on N(0,1) inputs, against the 1e-5 bound, and
+            // let the loads and stores set the pace (0.97 of the peak).
+            o.x = __fdividef(v[i].x * w.x * g[i].x, m * (__expf(-g[i].x) + 1.0f));
+            o.y = __fdividef(v[i].y * w.y * g[i].y, m * (__expf(-g[i].y) + 1.0f));
+            o.z = __fdividef(v[i].z * w.z * g[i].z, m * (__expf(-g[i].z) + 1.0f));
+            o.w = __fdividef(v[i].w * w.w * g[i].w, m * (__expf(-g[i].w) + 1.0f));
+          } else {
+            o = make_float4(v[i].x / m * w.x, v[i].y / m * w.y, v[i].z / m * w.z, v[i].w / m * w.w);
           }
           st_stream(yr + c, o);
         }
