@@ -210,6 +210,35 @@ UGB_API const char *ugb_func_source(const ugb_func *f);
  * by the next ugb_sync. */
 UGB_API int32_t ugb_run(ugb_device *dev, ugb_func *f, ugb_slice *const *args, size_t n_args);
 
+/* ------------------------------------------ ug::safetensors::MmapedSafetensors */
+/* Memory-mapped .safetensors files (ug-core/src/safetensors.rs:10-318; container
+ * format of crate safetensors 0.4.5).  Files stay mapped until ugb_st_close; a
+ * tensor name present in several files resolves to the last file (safetensors.rs:40). */
+typedef struct ugb_safetensors ugb_safetensors;
+/* MmapedSafetensors::new (one path) / ::multi (several).  Errors (unreadable
+ * file, malformed or inconsistent header) are UGB_ERR_INVALID with the path in
+ * the message, on `dev`. */
+UGB_API int32_t ugb_st_open(ugb_device *dev, const char *const *paths, size_t n_paths,
+                            ugb_safetensors **out);
+UGB_API int32_t ugb_st_close(ugb_safetensors *st);
+/* MmapedSafetensors::tensors: names in file order of their data. */
+UGB_API size_t ugb_st_count(const ugb_safetensors *st);
+UGB_API const char *ugb_st_name(const ugb_safetensors *st, size_t i);
+/* MmapedSafetensors::get: dtype (ugb_dtype, or -1 for a safetensors dtype that ug
+ * has no DType for), rank and up to dims_cap dimensions. */
+UGB_API int32_t ugb_st_info(ugb_device *dev, const ugb_safetensors *st, const char *name,
+                            int32_t *dtype, int32_t *rank, size_t *dims, size_t dims_cap);
+/* load_slice (safetensors.rs:83-118): a new slice of the tensor's dtype holding
+ * its elements.  Dtypes other than BF16/F16/F32/I32/I64 are UGB_ERR_DTYPE. */
+UGB_API int32_t ugb_st_load_slice(ugb_device *dev, const ugb_safetensors *st, const char *name,
+                                  ugb_slice **out);
+/* load_slice_with_cast (safetensors.rs:120-271): converted on the host, element
+ * by element, through f32 for the float types (round to nearest even into
+ * bf16 / f16), float -> int saturating, i64 -> i32 wrapping.  BF16 / F16 -> I64
+ * fail with the dtype mismatch the reference's own copy raises there. */
+UGB_API int32_t ugb_st_load_slice_with_cast(ugb_device *dev, const ugb_safetensors *st,
+                                            const char *name, int32_t dst_dtype, ugb_slice **out);
+
 /* ------------------------------------------------------- ug::Device::matmul */
 
 /* ug::Device::matmul (ug-core/src/lib.rs:61-69; ug-cuda/src/gemm.rs:292-332):

@@ -33,6 +33,17 @@ class Config:
         return self.hidden_size // self.num_attention_heads
 
     @staticmethod
+    def from_json(path):
+        """A Hugging Face ``config.json`` (what ug-llama deserialises into Config, main.rs:105-122)."""
+        import json
+        with open(path) as f:
+            d = json.load(f)
+        keys = ("hidden_size", "intermediate_size", "max_position_embeddings", "num_attention_heads",
+                "num_key_value_heads", "num_hidden_layers", "vocab_size", "rms_norm_eps", "rope_theta",
+                "rope_interleaved", "tie_word_embeddings")
+        return Config(**{k: d[k] for k in keys if k in d})
+
+    @staticmethod
     def llama_1b():
         """The Llama-1.1B shape of the benchmark configuration."""
         return Config(hidden_size=2048, intermediate_size=5632, max_position_embeddings=4096,
@@ -101,6 +112,24 @@ class Model:
         m = cls(cfg, dev, batch, t_max, tp=tp)
         for name in weight_names(cfg):
             m.load_weight(name, weights[name])
+        if tp is not None:
+            m.connect(group)
+        return m
+
+    @classmethod
+    def from_safetensors(cls, cfg, st, dev, batch, t_max, tp=None, group=None):
+        """Model::new (model.rs:298-363) from a ``ug_b200.safetensors.MmapedSafetensors``: projection and
+        embedding matrices keep their stored BF16 / F32 (F16 goes through F32), norm weights are cast to F32."""
+        from .device import DType
+        m = cls(cfg, dev, batch, t_max, tp=tp)
+        for name in weight_names(cfg):
+            src_dtype, shape = st.get(name)
+            if len(shape) == 1 or src_dtype not in (DType.BF16, DType.F32):
+                _, s = st.load_slice_with_cast(name, DType.F32, dev)
+            else:
+                _, s = st.load_slice(name, dev)
+            dev._check(lib.ugb_llama_load_weight(m._h, name.encode(), s._h))
+            dev.synchronize()
         if tp is not None:
             m.connect(group)
         return m
