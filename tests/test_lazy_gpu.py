@@ -222,3 +222,74 @@ def test_ssa_errors(dev):
     n0 = dev.launch_count
     dev.run(z, [dev.allocate_uninit(DType.I32, 4)])        # zero launch dimension: a no-op (runtime.rs:269-277)
     assert dev.launch_count == n0
+
+
+def test_ssa_exp_samples(dev):
+    # ug-core/src/samples.rs:52-71 (one element per thread) and :73-99 (a block walks a row in steps of block_size)
+    f32, i32 = DType.F32, DType.I32
+    bs = 32
+    k = [I("DefineGlobal", f32, index=0), I("DefineGlobal", f32, index=1), I("Special", i32, op=1), I("Special", i32, op=0),
+         I("Binary", i32, op=B.Mul, a0=2, a1=ssa.i32(bs)), I("Binary", i32, op=B.Add, a0=4, a1=3),
+         I("Load", f32, v0=0, a0=5), I("Unary", f32, op=U.Exp, a0=6), I("Store", f32, v0=1, a0=5, a1=7)]
+    x = synth.normal(31, (4, bs))
+    src, dst = dev.slice_from_values(x), dev.allocate_uninit(DType.F32, x.size)
+    dev.run(dev.compile(k, grid_dim=4, block_dim=bs), [src, dst])
+    dev.synchronize()
+    assert rel_err(dst.to_vec().reshape(x.shape), np.exp(x.astype(np.float64))) < 1e-6
+    dim2 = 96
+    k = [I("DefineGlobal", f32, index=0), I("DefineGlobal", f32, index=1), I("Special", i32, op=1), I("Special", i32, op=0),
+         I("Binary", i32, op=B.Mul, a0=2, a1=ssa.i32(dim2)), I("Binary", i32, op=B.Add, a0=4, a1=3)]
+    for i in range(0, dim2, bs):
+        n = len(k)
+        k += [I("Binary", i32, op=B.Add, a0=5, a1=ssa.i32(i)), I("Load", f32, v0=0, a0=n),
+              I("Unary", f32, op=U.Exp, a0=n + 1), I("Store", f32, v0=1, a0=n, a1=n + 2)]
+    x = synth.normal(32, (5, dim2))
+    src, dst = dev.slice_from_values(x), dev.allocate_uninit(DType.F32, x.size)
+    dev.run(dev.compile(k, grid_dim=5, block_dim=bs), [src, dst])
+    dev.synchronize()
+    assert rel_err(dst.to_vec().reshape(x.shape), np.exp(x.astype(np.float64))) < 1e-6
+
+
+def test_ssa_if_mod_min_and_i64(dev):
+    # If / EndIf, Mod, Min, Neg and 64-bit integers: dst[i] = i % 3 == 0 ? min(a[i], -a[i]) : a[i]  (i64)
+    i32, i64 = DType.I32, DType.I64
+    k = [I("DefineGlobal", i64, index=0), I("DefineGlobal", i64, index=1), I("Special", i32, op=0),
+         I("Load", i64, v0=0, a0=2), I("Store", i64, v0=1, a0=2, a1=3),
+         I("Binary", i32, op=B.Mod, a0=2, a1=ssa.i32(3)),
+         I("Binary", i32, op=B.Sub, a0=ssa.i32(1), a1=5),        # 1 - (i % 3): positive only where i % 3 == 0
+         I("Binary", i32, op=B.Max, a0=6, a1=ssa.i32(0)),        # condition: non-zero = taken
+         I("If", a0=7, v0=12),
+         I("Unary", i64, op=U.Neg, a0=3), I("Binary", i64, op=B.Min, a0=3, a1=9), I("Store", i64, v0=1, a0=2, a1=10),
+         I("EndIf")]
+    a = np.array([5, -7, 2**40, 9, -2**41, 1, 0, 12], np.int64)
+    src, dst = dev.slice_from_values(a), dev.allocate_uninit(DType.I64, a.size)
+    dev.run(dev.compile(k, grid_dim=1, block_dim=a.size), [src, dst])
+    dev.synchronize()
+    want = np.where(np.arange(a.size) % 3 == 0, np.minimum(a, -a), a)
+    assert np.array_equal(dst.to_vec(), want)
+
+
+def test_ssa_half_precision_and_unary_ops(dev):
+    # Sqrt / Sin / Cos / Id in f32, and 16-bit buffers copied element by element in their own dtype
+    f32, bf16, f16, i32 = DType.F32, DType.BF16, DType.F16, DType.I32
+    k = [I("DefineGlobal", bf16, index=0), I("DefineGlobal", f16, index=1), I("DefineGlobal", f32, index=2),
+         I("DefineGlobal", bf16, index=3), I("DefineGlobal", f16, index=4),
+         I("Special", i32, op=0), I("Load", f32, v0=2, a0=5),
+         I("Unary", f32, op=U.Sqrt, a0=6), I("Unary", f32, op=U.Sin, a0=6), I("Unary", f32, op=U.Cos, a0=6),
+         I("Binary", f32, op=B.Mul, a0=7, a1=8), I("Binary", f32, op=B.Add, a0=10, a1=9), I("Unary", f32, op=U.Id, a0=11),
+         I("Store", f32, v0=2, a0=5, a1=12),
+         I("Load", bf16, v0=3, a0=5), I("Store", bf16, v0=0, a0=5, a1=14),
+         I("Load", f16, v0=4, a0=5), I("Store", f16, v0=1, a0=5, a1=16)]
+    x = np.abs(synth.normal(33, (64,))) + 0.1
+    src_bf = synth.to_bf16_bits(synth.normal(34, (64,)))
+    src_h = synth.normal(35, (64,)).astype(np.float16)
+    o_bf = dev.allocate_uninit(DType.BF16, 64)
+    o_h = dev.allocate_uninit(DType.F16, 64)
+    xs = dev.slice_from_values(x)
+    dev.run(dev.compile(k, grid_dim=1, block_dim=64),
+            [o_bf, o_h, xs, dev.slice_from_values(src_bf, bf16=True), dev.slice_from_values(src_h)])
+    dev.synchronize()
+    x64 = x.astype(np.float64)
+    assert rel_err(xs.to_vec(), np.sqrt(x64) * np.sin(x64) + np.cos(x64)) < 1e-5
+    assert np.array_equal(o_bf.to_vec(), src_bf)
+    assert np.array_equal(o_h.to_vec().view(np.float16), src_h)

@@ -311,7 +311,7 @@ int32_t generate(ugb_device *dev, const ugb_ssa_instr *ins, size_t n, const std:
         const std::string elem = std::string("ugb_cast<") + ty + ", " + bty + ">(v" + std::to_string(i.v0) + "[o" + std::to_string(l) + "])";
         os << ind << "const long long o" << l << " = (long long)(" << arg_str(i.a0) << ");\n";
         if (global) {
-          os << ind << ty << " v" << l << " = " << ty << "();\n";
+          os << ind << ty << " v" << l << " = (" << ty << ")0;\n";
           os << ind << "if ((unsigned long long)o" << l << " < n" << i.v0 << ") v" << l << " = " << elem << "; else ugb_oob(ugb_status, " << l << "u);\n";
         } else {
           os << ind << ty << " v" << l << " = " << elem << ";\n";
