@@ -38,9 +38,12 @@ def logit_err(got, ref):
     (dict(hidden_size=256, num_attention_heads=4, num_key_value_heads=4, intermediate_size=320), 8, 130),
     (dict(), 1, 1),                                   # a block of one position
 ])
-def test_prefill_matches_oracle(dev, over, batch, t):
+@pytest.mark.parametrize("tc", [0, 1])
+def test_prefill_matches_oracle(dev, over, batch, t, tc):
+    """tc = 1: attention on the tcgen05 / TMEM kernel (128-query tiles), 0: on the mma.sync kernel (64-query tiles)."""
     cfg = Config(**{**TINY, **over})
     gpu, ref = make(cfg, dev, batch, 256)
+    gpu.set_option("prefill_attention_tc", tc)
     prompts = synth.tokens(7, (batch, t), cfg.vocab_size)
     gpu.prefill(prompts, all_logits=True)
     got = gpu.prefill_logits()
@@ -55,18 +58,21 @@ def test_prefill_matches_oracle(dev, over, batch, t):
     gpu.close()
 
 
-def test_chunked_prefill_and_continuation(dev):
+@pytest.mark.parametrize("tc", [0, 1])
+def test_chunked_prefill_and_continuation(dev, tc):
     """Chunks of 16 positions (prefill_rows 64 at batch 4) give the logits of one whole block, and
     prefill(t1) followed by prefill(t2) continues at cache position t1."""
     cfg = Config(**TINY)
     prompts = synth.tokens(9, (4, 100), cfg.vocab_size)
     whole, ref = make(cfg, dev, 4, 128)
+    whole.set_option("prefill_attention_tc", tc)
     whole.prefill(prompts, all_logits=True)
     base = whole.prefill_logits()
     want = ref.fwd(prompts[1:2], 0, ref.new_cache())[0]
     assert logit_err(base[1], want) < TOL
 
     chunked, _ = make(cfg, dev, 4, 128)
+    chunked.set_option("prefill_attention_tc", tc)
     chunked.set_option("prefill_rows", 64)
     chunked.prefill(prompts, all_logits=True)
     got = chunked.prefill_logits()
@@ -139,6 +145,7 @@ def test_prefill_config4_shape(dev):
     cfg = Config(hidden_size=2048, intermediate_size=5632, max_position_embeddings=2048, num_attention_heads=32,
                  num_key_value_heads=4, num_hidden_layers=2, vocab_size=32000)
     gpu, ref = make(cfg, dev, 8, 512)
+    gpu.set_option("prefill_attention_tc", 1)
     prompts = synth.tokens(13, (8, 512), cfg.vocab_size)
     gpu.prefill(prompts, all_logits=True)
     got = gpu.prefill_logits()

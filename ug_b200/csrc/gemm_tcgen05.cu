@@ -25,14 +25,13 @@
 #include <cuda_bf16.h>
 
 #include "gemm_tcgen05.cuh"
+#include "tc_ptx.cuh"
 
 namespace {
 
 constexpr int BK = 64;
 constexpr int ACC_STAGES = 2;
-constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
 
 // Tile shapes.  BM = 128 (one accumulator row per TMEM lane) for tall products;
 // BM = 64 when m <= 64 (decode: the activation tile is half the size, so the
@@ -69,99 +68,7 @@ struct Params {
   ugb_status_word *status;
 };
 
-// ----------------------------------------------------------------- PTX -----
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ unsigned long long globaltimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false when the CTA is (or becomes) aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          ugb_status_word *status, unsigned site) {
-  if (mbar_try(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer();
-  for (unsigned it = 1;; ++it) {
-    if (mbar_try(bar, parity)) return true;
-    if ((it & 255u) == 0) {
-      if (*abort_flag) return false;
-      if (globaltimer() - t0 > WAIT_LIMIT_NS) {
-        *abort_flag = 1;
-        if (atomicCAS(&status->code, 0u, (unsigned)UGB_ERR_TIMEOUT) == 0u) status->detail = site;
-        return false;
-      }
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x,
-                                            int y, int z) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// Arrives on `bar` once every tcgen05.mma issued so far by this thread is done.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
-//   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
-//   bits 32-45 stride byte offset >> 4  bits 46-47 version   bits 61-63 layout (2 = SWIZZLE_128B)
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
-  d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-// Instruction descriptor for kind::f16: D = f32, A = B = bf16, M x N tile.
-//   bits 4-5 D format (1 = f32)   bits 7-9 A format (1 = bf16)   bits 10-12 B format
-//   bit 15 A major (0 = K)        bit 16 B major (1 = MN)        bits 17-22 N >> 3   bits 24-28 M >> 4
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) |
-         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
+using namespace ugb_tc;
 
 template <int BM, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -423,6 +330,17 @@ TcState *state_of(ugb_device *dev) {
   return (TcState *)dev->gemm_state;
 }
 
+int32_t ensure_encode(ugb_device *dev, TcState *st) {
+  if (st->encode) return UGB_OK;
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+    return ugb_fail(dev, UGB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  st->encode = (EncodeTiledFn)fn;
+  return UGB_OK;
+}
+
 // rank-3 bf16 tensor map: dims {d0 (contiguous), d1, d2}, strides in elements for d1, d2.
 int32_t encode_map(ugb_device *dev, TcState *st, CUtensorMap *map, const void *base, uint64_t d0,
                    uint64_t d1, uint64_t d2, uint64_t s1, uint64_t s2, uint32_t box0, uint32_t box1) {
@@ -499,6 +417,21 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
 
 }  // namespace
 
+int32_t ugb_tc_encode_bf16(ugb_device *dev, CUtensorMap *map, const void *base, int rank, const uint64_t *dims,
+                           const uint64_t *strides_elems, const uint32_t *box) {
+  TcState *st = state_of(dev);
+  if (int32_t rc = ensure_encode(dev, st)) return rc;
+  cuuint64_t d[5], sb[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+  for (int i = 0; i + 1 < rank; ++i) sb[i] = strides_elems[i] * 2;
+  CUresult r = st->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void *>(base), d, sb, bx, es,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return ugb_fail(dev, UGB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return UGB_OK;
+}
+
 int ugb_tc_gemm_effective_splits(size_t k, int splits) {
   const int k_blocks = (int)((k + BK - 1) / BK);
   if (splits < 1) splits = 1;
@@ -521,14 +454,7 @@ int32_t ugb_tc_gemm(ugb_device *dev, const ugb_tc_gemm_args &g) {
   if (m == 0 || n == 0) return UGB_ERR_UNSUPPORTED;
 
   TcState *st = state_of(dev);
-  if (!st->encode) {
-    void *fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
-    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
-      return ugb_fail(dev, UGB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
-    st->encode = (EncodeTiledFn)fn;
-  }
+  if (int32_t rc = ensure_encode(dev, st)) return rc;
   // A shared B with densely stacked A batches is one tall GEMM.
   const long long dense_c = (long long)m * (long long)(g.epi == UGB_EPI_SILU_MUL_BF16 ? n / 2 : n);
   if (batch > 1 && g.b_batch == 0 && g.a_batch == (long long)(m * k) && (g.c_batch == 0 || g.c_batch == dense_c)) {

@@ -1,5 +1,7 @@
 // Interface of the tcgen05 / TMEM bf16 GEMM translation unit.
 #pragma once
+#include <cuda.h>
+
 #include "ugb_internal.h"
 
 // Epilogues applied to the fp32 accumulators.
@@ -35,4 +37,8 @@ int ugb_tc_gemm_effective_splits(size_t k, int splits);
 int32_t ugb_tc_gemm_bf16(ugb_device *dev, void *c, const void *a, const void *b_, size_t batch,
                          size_t m, size_t n, size_t k, long long a_batch, long long b_batch,
                          bool b_is_nk);
+// bf16 tensor map with the 128-byte swizzle: dims / box of `rank` entries (dims[0] contiguous), strides in
+// elements for dims 1 .. rank-1 (multiples of 8).
+int32_t ugb_tc_encode_bf16(ugb_device *dev, CUtensorMap *map, const void *base, int rank, const uint64_t *dims,
+                           const uint64_t *strides_elems, const uint32_t *box);
 void ugb_tc_state_free(ugb_device *dev);

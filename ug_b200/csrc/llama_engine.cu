@@ -28,6 +28,7 @@
 #include "decode_kernels.cuh"
 #include "gemm_tcgen05.cuh"
 #include "tp_kernels.cuh"
+#include "attention_tc.cuh"
 
 using namespace ugb_decode;
 
@@ -79,6 +80,7 @@ struct ugb_llama {
   size_t loaded = 0;
   // prefill workspace, allocated by the first ugb_llama_prefill: activations of one chunk of
   // pf_rows = batch * pf_chunk rows (pf_chunk positions of every sequence)
+  int pf_att_tc = 1;              // option prefill_attention_tc: 1 = tcgen05 / TMEM attention kernel, 0 = mma.sync one
   int pf_rows_max = 8192;         // option prefill_rows: upper bound on rows per chunk
   int pf_rows = 0, pf_chunk = 0;
   float *pf_x = nullptr, *pf_f32 = nullptr;            // residual stream; f32 GEMM output (qkv, o, down)
@@ -359,9 +361,14 @@ int32_t enqueue_prefill_chunk(ugb_llama *m, const int *tok, int t, int c0, int t
                    c.rope_interleaved, tc, c0);
     if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of rope_append_kernel failed: %s", cudaGetErrorString(e));
     if ((rc = ugb_after_launch(dev, "rope_append_kernel"))) return rc;
-    prefill_attention_kernel<<<dim3((tc + PF_BQ - 1) / PF_BQ, c.n_heads, B), 128, 0, st>>>(
-        m->pf_q, kc, vc, m->pf_att, tc, m->host_pos + c0, c.n_heads, c.n_kv_heads, m->t_max, scale);
-    if ((rc = ugb_after_launch(dev, "prefill_attention_kernel"))) return rc;
+    if (m->pf_att_tc) {
+      if ((rc = ugb_prefill_attention_tc(dev, m->pf_q, kc, vc, m->pf_att, B, tc, m->host_pos + c0, c.n_heads, c.n_kv_heads,
+                                         m->t_max, scale))) return rc;
+    } else {
+      prefill_attention_kernel<<<dim3((tc + PF_BQ - 1) / PF_BQ, c.n_heads, B), 128, 0, st>>>(
+          m->pf_q, kc, vc, m->pf_att, tc, m->host_pos + c0, c.n_heads, c.n_kv_heads, m->t_max, scale);
+      if ((rc = ugb_after_launch(dev, "prefill_attention_kernel"))) return rc;
+    }
     if ((rc = gemm_rows(m, rows, po, m->pf_att, w.wo, H, AW, UGB_EPI_F32, 1, 0))) return rc;
     if ((rc = launch_reduce(m, rows, m->pf_x, m->pf_xn, RED_O, po, 1, w.rms2))) return rc;
     if ((rc = gemm_rows(m, rows, m->pf_h, m->pf_xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, 0))) return rc;
@@ -606,6 +613,10 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
     UGB_REQUIRE(dev, value == 0 || (value >= 32 && value <= 220), UGB_ERR_INVALID, "option gemm_smem_kib: %d outside 32..220 (0 = no cap)", value);
     m->gemm_smem_kib = value;
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    return UGB_OK;
+  }
+  if (k == "prefill_attention_tc") {
+    m->pf_att_tc = value != 0;
     return UGB_OK;
   }
   if (k == "prefill_rows") {
