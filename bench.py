@@ -103,6 +103,9 @@ class RmsSiluWorkload:
     dtype = "f32"
     bound = "hbm"
     rows, cols = 8192, 4096
+    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload's kernel, from the ncu capture
+    # summarised in profiles/row_kernels_ncu.md (the output's tail is still in L2 when the counters stop)
+    ncu_traffic_bytes = 268_472_576 + 97_029_120
 
     def __init__(self, rank):
         from ug_b200 import synth
@@ -194,6 +197,7 @@ class SoftmaxWorkload(RmsSiluWorkload):
     name = "custom_softmax f32 [32768,4096] (config 1 row shape, 32x rows so the batch exceeds L2)"
     metric = "softmax effective GB/s (rows*cols*8 bytes / time)"
     rows, cols = 32768, 4096
+    ncu_traffic_bytes = 536_986_880 + 484_354_048      # profiles/row_kernels_ncu.md
 
     def __init__(self, rank):
         from ug_b200 import synth
@@ -281,6 +285,7 @@ class GemmWorkload:
     dtype = "bf16"
     bound = "tensor"
     bs, m, n, k = 16, 512, 4096, 4096
+    ncu_traffic_bytes = 383_233_024 + 56_642_048       # profiles/tc_gemm_config3_ncu.md (A is re-read from DRAM across waves)
 
     def __init__(self, rank):
         from ug_b200 import synth
@@ -746,6 +751,9 @@ def main():
             extra["roofline_scope"] = ("whole decode step (one CUDA graph of %d kernels): weight bytes + KV bytes "
                                        "at the mean cache depth %.0f" % (wl.launches_per_step, depth))
             extra["decode_attention_roofline"] = {
+                # 141.2 MB of DRAM traffic per launch at 2049 cached positions (profiles/decode_attention_ncu.md),
+                # scaled by the cached positions of this run: the traffic grows in proportion to them
+                "traffic": int(141_193_472 * wl.model.position / 2049 * wl.batch / 64) if not tp else None,
                 "achieved": round(att_bytes / (kern["decode_attention"] / 1e3) / 1e9, 1), "peak": peaks["hbm"],
                 "unit": "GB/s", "frac": round(att_bytes / (kern["decode_attention"] / 1e3) / 1e9 / peaks["hbm"], 4)}
         else:
@@ -770,7 +778,7 @@ def main():
             "clocks": clocks,
             "roofline": {"bound": wl.bound, "achieved": round(achieved, 1), "peak": peak,
                          "unit": runit, "frac": round(achieved / peak, 4),
-                         "traffic": None, "peak_source": peaks["source"]},
+                         "traffic": getattr(wl, "ncu_traffic_bytes", None), "peak_source": peaks["source"]},
         }
         line.update(extra)
         if hasattr(wl, "reference_cuda_gbs"):
