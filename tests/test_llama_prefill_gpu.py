@@ -152,3 +152,21 @@ def test_prefill_config4_shape(dev):
     want = ref.fwd(prompts[5:6], 0, ref.new_cache())[0]
     assert logit_err(got[5], want) < TOL
     gpu.close()
+
+
+@pytest.mark.parametrize("tc", [0, 1])
+def test_long_prefill_many_key_tiles(dev, tc):
+    """1100 positions in chunks of 256 and 300: up to 18 key tiles per query tile on the tcgen05 kernel (every
+    barrier's phase wraps many times), a ragged last tile, and chunks that start inside a key tile."""
+    cfg = Config(**{**TINY, "max_position_embeddings": 2048})
+    gpu, ref = make(cfg, dev, 2, 1152)
+    gpu.set_option("prefill_attention_tc", tc)
+    gpu.set_option("prefill_rows", 512)               # 256 positions per chunk at batch 2
+    prompts = synth.tokens(15, (2, 1100), cfg.vocab_size)
+    gpu.prefill(prompts[:, :300])                      # the second call starts at cache position 300
+    gpu.prefill(prompts[:, 300:], all_logits=True)
+    got = gpu.prefill_logits()
+    want = ref.fwd(prompts[1:2], 0, ref.new_cache())[0]
+    assert logit_err(got[1], want[300:]) < TOL
+    assert gpu.position == 1100
+    gpu.close()

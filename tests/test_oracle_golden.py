@@ -1,15 +1,20 @@
 """Pins the CPU oracle against the reference's own known-answer vectors
 (ug-core/tests/basic_tests.rs, ug-core/src/common_tests.rs) and against
 independent float64 computations.  CPU only."""
+import json
+import os
+
 import numpy as np
 
 import oracle
 from conftest import rel_err
 
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+REF = json.load(open(os.path.join(GOLDEN, "reference_vectors.json")))
+
 # ug-core/tests/basic_tests.rs:41-61 (same vector in :63-116 for the SSA forms)
-SOFTMAX_IN = np.array([[0., 1., 2., 3.], [2., 1., 2., 1.]], dtype=np.float32)
-SOFTMAX_OUT = np.array([0.032058604, 0.08714432, 0.23688284, 0.6439143,
-                        0.3655293, 0.13447072, 0.3655293, 0.13447072], dtype=np.float32)
+SOFTMAX_IN = np.array(REF["softmax_2x4"]["input"], dtype=np.float32)
+SOFTMAX_OUT = np.array(REF["softmax_2x4"]["output"], dtype=np.float32)
 
 
 def test_custom_softmax_golden_bit_exact():
@@ -129,3 +134,19 @@ def test_gemm_standin_matches_float64():
     w = rng.standard_normal((9, 33)).astype(np.float32)  # shared [n, k] weight
     ref2 = a.astype(np.float64) @ w.astype(np.float64).T
     assert np.max(np.abs(oracle.matmul(a, w, transpose_rhs=True) - ref2)) < 1e-4
+
+
+def test_oracle_reproduces_committed_fixtures():
+    """tests/golden/oracle_fixtures.npz (written by tests/golden/make_fixtures.py): the Rust-semantics operators
+    bit for bit; the emitted-C forms (gcc -ffast-math -march=native, CPU dependent) and the model to 1e-6."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_fixtures", os.path.join(GOLDEN, "make_fixtures.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    now = mod.build()
+    fix = np.load(os.path.join(GOLDEN, "oracle_fixtures.npz"))
+    assert set(fix.files) == set(now)
+    for k in ("softmax_out", "rope_out", "rope_i_out", "llama_prompt", "softmax_in_seed"):
+        assert np.array_equal(fix[k], now[k]), k
+    assert rel_err(now["rms_silu_out"], fix["rms_silu_out"]) < 1e-6
+    assert np.max(np.abs(now["llama_logits"] - fix["llama_logits"])) < 1e-5 * np.abs(fix["llama_logits"]).max()
