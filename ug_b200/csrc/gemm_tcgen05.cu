@@ -66,6 +66,7 @@ struct Params {
   long long c_split;      // output elements between split-K partials
   void *C;
   ugb_status_word *status;
+  ugb_tc_rope_epilogue rope;
 };
 
 using namespace ugb_tc;
@@ -243,6 +244,82 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const bool row_lane = BM == 128 || lane < 16;
       const int row = BM == 128 ? m0 + quad * 32 + lane : m0 + quad * 16 + lane;
       const long long out_off = (long long)sp * p.c_split + (long long)bi * p.c_batch;
+      if constexpr (BM == 128) {
+        if (p.epi == UGB_EPI_ROPE_QKV) {
+          // One head (64 columns) at a time: both halves of every rotation pair (i, i + 32) -- or the 32
+          // adjacent pairs of the interleaved form -- are columns of this thread's row.
+          const ugb_tc_rope_epilogue &R = p.rope;
+          const bool live = row < p.M;
+          const int rr = live ? row : 0;
+          const int seq = rr / R.t, pos = *R.pos_p + R.pos_off + (rr - seq * R.t);
+          const float4 *cs4 = reinterpret_cast<const float4 *>(R.cos_ + (size_t)pos * 32);
+          const float4 *sn4 = reinterpret_cast<const float4 *>(R.sin_ + (size_t)pos * 32);
+#pragma unroll 1
+          for (int hc = 0; hc < BN / 64; ++hc) {
+            const int head = (n0 >> 6) + hc;                  // warp-uniform
+            if (head * 64 >= p.N) break;
+            uint32_t v0[32], v1[32];
+            tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * Cfg<BM, BN>::ACC_STRIDE + hc * 64), v0);
+            tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * Cfg<BM, BN>::ACC_STRIDE + hc * 64 + 32), v1);
+            tmem_ld_wait();
+            if (!live) continue;
+            __nv_bfloat16 *dst;
+            if (head < R.n_heads) dst = R.q_out + ((size_t)row * R.n_heads + head) * 64;
+            else if (head < R.n_heads + R.n_kv) dst = R.kcache + (((size_t)seq * R.n_kv + (head - R.n_heads)) * R.t_max + pos) * 64;
+            else dst = R.vcache + (((size_t)seq * R.n_kv + (head - R.n_heads - R.n_kv)) * R.t_max + pos) * 64;
+            uint32_t o[32];                                   // 64 bf16
+            if (head >= R.n_heads + R.n_kv) {                 // value head: rounded as it is
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(v0[2 * e]), __uint_as_float(v0[2 * e + 1]));
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v1[2 * e]), __uint_as_float(v1[2 * e + 1]));
+                o[e] = *(uint32_t *)&a; o[16 + e] = *(uint32_t *)&b2;
+              }
+            } else if (R.interleaved) {                       // pairs (2i, 2i + 1): y0 = x0 c - x1 s, y1 = x0 s + x1 c
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4) {
+                const float4 c = __ldg(cs4 + q4), sn = __ldg(sn4 + q4);
+                const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int i = q4 * 4 + e;                   // pair index 0..31: columns 2i, 2i + 1
+                  const float x0 = __uint_as_float(i < 16 ? v0[2 * i] : v1[2 * i - 32]);
+                  const float x1 = __uint_as_float(i < 16 ? v0[2 * i + 1] : v1[2 * i - 31]);
+                  __nv_bfloat162 y = __floats2bfloat162_rn(__fsub_rn(__fmul_rn(x0, cc[e]), __fmul_rn(x1, ss[e])),
+                                                           __fadd_rn(__fmul_rn(x0, ss[e]), __fmul_rn(x1, cc[e])));
+                  o[i] = *(uint32_t *)&y;
+                }
+              }
+            } else {                                          // pairs (i, i + 32): v0 holds x1, v1 holds x2
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4) {
+                const float4 c = __ldg(cs4 + q4), sn = __ldg(sn4 + q4);
+                const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int e = 0; e < 4; e += 2) {
+                  const int i = q4 * 4 + e;
+                  const float a0 = __uint_as_float(v0[i]), a1 = __uint_as_float(v0[i + 1]);
+                  const float b0 = __uint_as_float(v1[i]), b1 = __uint_as_float(v1[i + 1]);
+                  __nv_bfloat162 lo = __floats2bfloat162_rn(__fsub_rn(__fmul_rn(a0, cc[e]), __fmul_rn(b0, ss[e])),
+                                                            __fsub_rn(__fmul_rn(a1, cc[e + 1]), __fmul_rn(b1, ss[e + 1])));
+                  __nv_bfloat162 hi = __floats2bfloat162_rn(__fadd_rn(__fmul_rn(a0, ss[e]), __fmul_rn(b0, cc[e])),
+                                                            __fadd_rn(__fmul_rn(a1, ss[e + 1]), __fmul_rn(b1, cc[e + 1])));
+                  o[i >> 1] = *(uint32_t *)&lo;
+                  o[16 + (i >> 1)] = *(uint32_t *)&hi;
+                }
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<uint4 *>(dst + q * 8) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+          }
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+          if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
+          continue;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < (BN + 31) / 32; ++c) {      // a tile width that is not a multiple of 32 ends in a partly used chunk
         uint32_t v[32];
@@ -387,6 +464,7 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   p.c_split = (long long)batch * m * out_cols;
   p.C = g.out;
   p.status = dev->status_dev;
+  p.rope = g.rope;
 
   CUtensorMap tmA, tmB;
   p.stage_tx = Cfg<BM, BN>::STAGE_BYTES;
@@ -451,6 +529,7 @@ int32_t ugb_tc_gemm(ugb_device *dev, const ugb_tc_gemm_args &g) {
   if (m > (1u << 30) || n > (1u << 30) || k > (1u << 30) || batch > 65535) return UGB_ERR_UNSUPPORTED;
   if (g.epi == UGB_EPI_SILU_MUL_BF16 && n % 16 != 0) return UGB_ERR_UNSUPPORTED;
   if (g.splits > 1 && g.epi != UGB_EPI_F32) return UGB_ERR_UNSUPPORTED;
+  if (g.epi == UGB_EPI_ROPE_QKV && (m <= 64 || batch != 1 || !g.b_is_nk || n % 64 != 0 || g.rope.t < 1)) return UGB_ERR_UNSUPPORTED;
   if (m == 0 || n == 0) return UGB_ERR_UNSUPPORTED;
 
   TcState *st = state_of(dev);

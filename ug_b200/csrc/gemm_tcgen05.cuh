@@ -1,6 +1,7 @@
 // Interface of the tcgen05 / TMEM bf16 GEMM translation unit.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 
 #include "ugb_internal.h"
 
@@ -8,7 +9,19 @@
 enum {
   UGB_EPI_BF16 = 0,           // out bf16 [b, m, n]
   UGB_EPI_F32 = 1,            // out f32 [splits, b, m, n]  (split-K partials when splits > 1)
-  UGB_EPI_SILU_MUL_BF16 = 2   // columns are (gate, up) pairs: out bf16 [b, m, n/2] = silu(gate) * up
+  UGB_EPI_SILU_MUL_BF16 = 2,  // columns are (gate, up) pairs: out bf16 [b, m, n/2] = silu(gate) * up
+  UGB_EPI_ROPE_QKV = 3        // columns are [q heads | k heads | v heads] of 64: rope + KV append (see ugb_tc_rope_epilogue)
+};
+
+// Epilogue UGB_EPI_ROPE_QKV (m > 64, b_is_nk, batch 1, no split-K): row r of the product is position
+// pos = *pos_p + pos_off + r % t of sequence r / t.  Query heads are rotated and written as bf16 to
+// q_out[r][head][64]; key heads are rotated and written to kcache[b][kvh][pos][64]; value heads are
+// written to vcache likewise -- what rope_append_kernel does with the fp32 product, without the round trip.
+struct ugb_tc_rope_epilogue {
+  const float *cos_, *sin_;       // [max_pos, 32]
+  const int *pos_p;
+  int pos_off, t, n_heads, n_kv, t_max, interleaved;
+  __nv_bfloat16 *q_out, *kcache, *vcache;
 };
 
 struct ugb_tc_gemm_args {
@@ -25,6 +38,7 @@ struct ugb_tc_gemm_args {
   bool b_static;        // no kernel on the stream writes b (weights): fetch it before waiting for the predecessor
   bool pdl;             // launch with programmatic stream serialization (see ugb_launch)
   int smem_kib = 0;     // cap on the shared memory of a CTA (ring depth follows); 0 = as deep as fits in 220 KiB
+  ugb_tc_rope_epilogue rope = {};   // UGB_EPI_ROPE_QKV only
 };
 
 // Returns UGB_ERR_UNSUPPORTED (without touching last_error) when the shape

@@ -149,8 +149,9 @@ int32_t put_vector(ugb_llama *m, const ugb_slice *w, float *dst, size_t n, const
 
 // out[rows, n] = a[rows, k] . w[n, k]^T on the tensor-core kernel (weights are the static operand).
 int32_t gemm_rows(ugb_llama *m, size_t rows, void *out, const __nv_bfloat16 *a, const __nv_bfloat16 *w, size_t n,
-                  size_t k, int epi, int splits, int bn) {
+                  size_t k, int epi, int splits, int bn, const ugb_tc_rope_epilogue *rope = nullptr) {
   ugb_tc_gemm_args g;
+  if (rope) g.rope = *rope;
   g.out = out; g.a = a; g.b = w;
   g.batch = 1; g.m = rows; g.n = n; g.k = k;
   g.a_batch = 0; g.b_batch = 0; g.b_is_nk = true;
@@ -355,12 +356,21 @@ int32_t enqueue_prefill_chunk(ugb_llama *m, const int *tok, int t, int c0, int t
     __nv_bfloat16 *kc = m->kcache + (size_t)l * m->kv_layer_stride;
     __nv_bfloat16 *vc = m->vcache + (size_t)l * m->kv_layer_stride;
     if ((rc = launch_reduce(m, rows, m->pf_x, m->pf_xn, l == 0 ? RED_NONE : RED_DOWN, pd, l == 0 ? 0 : 1, w.rms1))) return rc;
-    if ((rc = gemm_rows(m, rows, m->pf_f32, m->pf_xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, 1, 0))) return rc;
-    e = ugb_launch(rope_append_kernel, dim3(rows, (rope_items + 255) / 256), dim3(256), 0, st, pdl, m->pf_f32, 1,
-                   (size_t)0, m->cos, m->sin, m->pos, m->pf_q, kc, vc, c.n_heads, c.n_kv_heads, c.head_dim, m->t_max,
-                   c.rope_interleaved, tc, c0);
-    if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of rope_append_kernel failed: %s", cudaGetErrorString(e));
-    if ((rc = ugb_after_launch(dev, "rope_append_kernel"))) return rc;
+    if (rows > 64) {
+      // qkv projection with the rotation and the cache append in its epilogue: no fp32 round trip, no rope kernel
+      ugb_tc_rope_epilogue re;
+      re.cos_ = m->cos; re.sin_ = m->sin; re.pos_p = m->pos; re.pos_off = c0; re.t = tc;
+      re.n_heads = c.n_heads; re.n_kv = c.n_kv_heads; re.t_max = m->t_max; re.interleaved = c.rope_interleaved;
+      re.q_out = m->pf_q; re.kcache = kc; re.vcache = vc;
+      if ((rc = gemm_rows(m, rows, m->pf_f32, m->pf_xn, w.wqkv, m->qkv_dim, H, UGB_EPI_ROPE_QKV, 1, 0, &re))) return rc;
+    } else {
+      if ((rc = gemm_rows(m, rows, m->pf_f32, m->pf_xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, 1, 0))) return rc;
+      e = ugb_launch(rope_append_kernel, dim3(rows, (rope_items + 255) / 256), dim3(256), 0, st, pdl, m->pf_f32, 1,
+                     (size_t)0, m->cos, m->sin, m->pos, m->pf_q, kc, vc, c.n_heads, c.n_kv_heads, c.head_dim, m->t_max,
+                     c.rope_interleaved, tc, c0);
+      if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of rope_append_kernel failed: %s", cudaGetErrorString(e));
+      if ((rc = ugb_after_launch(dev, "rope_append_kernel"))) return rc;
+    }
     if (m->pf_att_tc) {
       if ((rc = ugb_prefill_attention_tc(dev, m->pf_q, kc, vc, m->pf_att, B, tc, m->host_pos + c0, c.n_heads, c.n_kv_heads,
                                          m->t_max, scale))) return rc;
