@@ -199,6 +199,18 @@ typedef struct {
 UGB_API int32_t ugb_compile(ugb_device *dev, const ugb_ssa_instr *instrs, size_t n_instrs,
                             uint32_t grid_dim, uint32_t block_dim, uint32_t shared_mem,
                             const char *name, ugb_func **out);
+/* ug_cuda::Device::compile_cu / compile_ptx (ug-cuda/src/runtime.rs:179-193): a
+ * kernel written by the caller, CUDA C compiled at run time with
+ * use_fast_math as the reference does, or PTX handed to the driver.  Its
+ * parameters must be device pointers only: ugb_run passes the slices' pointers
+ * in order and nothing else (no lengths, no status word), with the launch
+ * shape given here.  Bounds are the author's responsibility. */
+UGB_API int32_t ugb_compile_cu(ugb_device *dev, const char *cu_code, const char *func_name,
+                               uint32_t grid_dim, uint32_t block_dim, uint32_t shared_mem,
+                               ugb_func **out);
+UGB_API int32_t ugb_compile_ptx(ugb_device *dev, const char *ptx_code, const char *func_name,
+                                uint32_t grid_dim, uint32_t block_dim, uint32_t shared_mem,
+                                ugb_func **out);
 UGB_API int32_t ugb_func_free(ugb_func *f);
 /* The CUDA C this backend generated for the kernel (inspection, tests). */
 UGB_API const char *ugb_func_source(const ugb_func *f);

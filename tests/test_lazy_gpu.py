@@ -293,3 +293,50 @@ def test_ssa_half_precision_and_unary_ops(dev):
     assert rel_err(xs.to_vec(), np.sqrt(x64) * np.sin(x64) + np.cos(x64)) < 1e-5
     assert np.array_equal(o_bf.to_vec(), src_bf)
     assert np.array_equal(o_h.to_vec().view(np.float16), src_h)
+
+
+def test_compile_cu_and_ptx_launch3(dev):
+    """Device.compile_cu / compile_ptx and Func.launch3 of the reference's Python module: a caller-written
+    kernel over three f32 slices."""
+    n = 1000
+    cu = r"""
+extern "C" __global__ void axpy(const float* a, const float* b, float* c) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < 1000) c[i] = 2.0f * a[i] + b[i];
+}
+"""
+    f = dev.compile_cu(cu, "axpy", grid_dim=(n + 127) // 128, block_dim=128)
+    a, b = synth.normal(61, (n,)), synth.normal(62, (n,))
+    sa, sb, sc = dev.slice_from_values(a), dev.slice_from_values(b), dev.zeros(n)
+    f.launch3(sa, sb, sc)
+    dev.synchronize()
+    assert np.array_equal(sc.to_vec(), np.float32(2.0) * a + b)
+    with pytest.raises(UgError):
+        f.launch3(sa, dev.zeros(n - 1), sc)                   # length mismatch
+    with pytest.raises(UgError) as e:
+        dev.compile_cu("this is not CUDA", "axpy")
+    assert e.value.code == 8
+    with pytest.raises(UgError) as e:
+        dev.compile_cu(cu, "no_such_entry")
+    assert e.value.code == 8
+    ptx = r"""
+.version 8.7
+.target sm_100a
+.address_size 64
+.visible .entry fill7(.param .u64 p0) {
+    .reg .b32 %r<4>; .reg .b64 %rd<4>; .reg .f32 %f<2>;
+    ld.param.u64 %rd1, [p0];
+    cvta.to.global.u64 %rd2, %rd1;
+    mov.u32 %r1, %tid.x;
+    mul.wide.u32 %rd3, %r1, 4;
+    add.s64 %rd2, %rd2, %rd3;
+    mov.f32 %f1, 0f40E00000;
+    st.global.f32 [%rd2], %f1;
+    ret;
+}
+"""
+    g = dev.compile_ptx(ptx, "fill7", grid_dim=1, block_dim=64)
+    out = dev.zeros(64)
+    dev.run(g, [out])
+    dev.synchronize()
+    assert np.array_equal(out.to_vec(), np.full(64, 7.0, np.float32))

@@ -35,6 +35,7 @@ struct ugb_func {
   unsigned grid = 1, block = 1, smem = 0;
   std::vector<int32_t> arg_dtypes;
   std::string source, name;
+  bool raw = false;     // user-supplied CUDA C / PTX: pointer arguments only, no length or status parameters
 };
 
 namespace {
@@ -358,6 +359,56 @@ int32_t generate(ugb_device *dev, const ugb_ssa_instr *ins, size_t n, const std:
   return UGB_OK;
 }
 
+// NVRTC (unless `is_ptx`) -> module -> function.  `fast_math`: the reference compiles user CUDA C with
+// use_fast_math (ug-cuda/src/runtime.rs:179-186); generated kernels are compiled without it.
+int32_t compile_and_load(ugb_device *dev, const std::string &src, const std::string &unit, const std::string &entry,
+                         bool fast_math, bool is_ptx, ugb_func **out) {
+  Driver &drv = driver();
+  UGB_REQUIRE(dev, drv.error.empty(), UGB_ERR_COMPILE, "%s", drv.error.c_str());
+  UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
+  std::vector<char> image;
+  if (is_ptx) {
+    image.assign(src.begin(), src.end());
+    image.push_back('\0');
+  } else {
+    Nvrtc &nv = nvrtc();
+    UGB_REQUIRE(dev, nv.error.empty(), UGB_ERR_COMPILE, "NVRTC unavailable: %s", nv.error.c_str());
+    void *prog = nullptr;
+    if (nv.create(&prog, src.c_str(), (unit + ".cu").c_str(), 0, nullptr, nullptr) != 0)
+      return ugb_fail(dev, UGB_ERR_COMPILE, "nvrtcCreateProgram failed");
+    const char *cuda_home = getenv("CUDA_HOME");
+    const std::string inc = std::string("--include-path=") + (cuda_home ? cuda_home : "/usr/local/cuda") + "/include";
+    const char *opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", inc.c_str(), "--use_fast_math"};
+    const nvrtcResult_t cr = nv.compile(prog, fast_math ? 4 : 3, opts);
+    if (cr != 0) {
+      size_t ls = 0;
+      nv.log_size(prog, &ls);
+      std::string log(ls, '\0');
+      if (ls) nv.get_log(prog, &log[0]);
+      nv.destroy(&prog);
+      return ugb_fail(dev, UGB_ERR_COMPILE, "NVRTC failed for %s: %.700s", unit.c_str(), log.c_str());
+    }
+    size_t cs = 0;
+    nv.cubin_size(prog, &cs);
+    image.resize(cs);
+    nv.get_cubin(prog, image.data());
+    nv.destroy(&prog);
+  }
+  ugb_func *f = new ugb_func();
+  f->dev = dev;
+  f->source = src;
+  f->name = entry;
+  CUresult r = drv.module_load_data(&f->module, image.data());
+  if (r == CUDA_SUCCESS) r = drv.module_get_function(&f->fn, f->module, entry.c_str());
+  if (r != CUDA_SUCCESS) {
+    if (f->module) drv.module_unload(f->module);
+    delete f;
+    return ugb_fail(dev, UGB_ERR_COMPILE, "loading kernel %s failed with CUresult %d", entry.c_str(), (int)r);
+  }
+  *out = f;
+  return UGB_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -377,46 +428,39 @@ int32_t ugb_compile(ugb_device *dev, const ugb_ssa_instr *instrs, size_t n_instr
   int32_t rc = generate(dev, instrs, n_instrs, fname, &src, &arg_dtypes);
   if (rc) return rc;
 
-  Nvrtc &nv = nvrtc();
-  UGB_REQUIRE(dev, nv.error.empty(), UGB_ERR_COMPILE, "NVRTC unavailable: %s", nv.error.c_str());
-  Driver &drv = driver();
-  UGB_REQUIRE(dev, drv.error.empty(), UGB_ERR_COMPILE, "%s", drv.error.c_str());
-  UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
-
-  void *prog = nullptr;
-  if (nv.create(&prog, src.c_str(), (fname + ".cu").c_str(), 0, nullptr, nullptr) != 0)
-    return ugb_fail(dev, UGB_ERR_COMPILE, "nvrtcCreateProgram failed");
-  const char *cuda_home = getenv("CUDA_HOME");
-  const std::string inc = std::string("--include-path=") + (cuda_home ? cuda_home : "/usr/local/cuda") + "/include";
-  const char *opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", inc.c_str()};
-  const nvrtcResult_t cr = nv.compile(prog, 3, opts);
-  if (cr != 0) {
-    size_t ls = 0;
-    nv.log_size(prog, &ls);
-    std::string log(ls, '\0');
-    if (ls) nv.get_log(prog, &log[0]);
-    nv.destroy(&prog);
-    return ugb_fail(dev, UGB_ERR_COMPILE, "NVRTC failed for %s: %.700s", fname.c_str(), log.c_str());
-  }
-  size_t cs = 0;
-  nv.cubin_size(prog, &cs);
-  std::vector<char> cubin(cs);
-  nv.get_cubin(prog, cubin.data());
-  nv.destroy(&prog);
-
-  ugb_func *f = new ugb_func();
-  f->dev = dev;
+  ugb_func *f = nullptr;
+  rc = compile_and_load(dev, src, fname, fname, false, false, &f);
+  if (rc) return rc;
   f->grid = grid_dim; f->block = block_dim; f->smem = shared_mem;
   f->arg_dtypes = arg_dtypes;
-  f->source = src;
-  f->name = fname;
-  CUresult r = drv.module_load_data(&f->module, cubin.data());
-  if (r == CUDA_SUCCESS) r = drv.module_get_function(&f->fn, f->module, fname.c_str());
-  if (r != CUDA_SUCCESS) {
-    if (f->module) drv.module_unload(f->module);
-    delete f;
-    return ugb_fail(dev, UGB_ERR_COMPILE, "loading the compiled kernel failed with CUresult %d", (int)r);
-  }
+  *out = f;
+  return UGB_OK;
+}
+
+int32_t ugb_compile_cu(ugb_device *dev, const char *cu_code, const char *func_name, uint32_t grid_dim,
+                       uint32_t block_dim, uint32_t shared_mem, ugb_func **out) {
+  if (!dev) return UGB_ERR_INVALID;
+  UGB_REQUIRE(dev, cu_code && func_name && out, UGB_ERR_INVALID, "ugb_compile_cu: null argument");
+  *out = nullptr;
+  ugb_func *f = nullptr;
+  const int32_t rc = compile_and_load(dev, cu_code, func_name, func_name, true, false, &f);
+  if (rc) return rc;
+  f->grid = grid_dim; f->block = block_dim; f->smem = shared_mem;
+  f->raw = true;
+  *out = f;
+  return UGB_OK;
+}
+
+int32_t ugb_compile_ptx(ugb_device *dev, const char *ptx_code, const char *func_name, uint32_t grid_dim,
+                        uint32_t block_dim, uint32_t shared_mem, ugb_func **out) {
+  if (!dev) return UGB_ERR_INVALID;
+  UGB_REQUIRE(dev, ptx_code && func_name && out, UGB_ERR_INVALID, "ugb_compile_ptx: null argument");
+  *out = nullptr;
+  ugb_func *f = nullptr;
+  const int32_t rc = compile_and_load(dev, ptx_code, func_name, func_name, false, true, &f);
+  if (rc) return rc;
+  f->grid = grid_dim; f->block = block_dim; f->smem = shared_mem;
+  f->raw = true;
   *out = f;
   return UGB_OK;
 }
@@ -439,6 +483,21 @@ int32_t ugb_run(ugb_device *dev, ugb_func *f, ugb_slice *const *args, size_t n_a
   UGB_REQUIRE(dev, f != nullptr && f->dev == dev, UGB_ERR_INVALID, "ugb_run: function belongs to another device");
   // a zero launch dimension is a no-op (ug-cuda/src/runtime.rs:269-277)
   if (f->grid == 0 || f->block == 0) return UGB_OK;
+  if (f->raw) {
+    // user-supplied kernel: its parameters are the slices' device pointers in order, nothing else.  Bounds
+    // are the kernel author's business, as with Func::launch in the reference (ug-pyo3/src/lib.rs:27-50).
+    std::vector<void *> p(n_args), pp(n_args);
+    for (size_t i = 0; i < n_args; ++i) {
+      UGB_REQUIRE(dev, args[i] != nullptr && args[i]->dev == dev, UGB_ERR_INVALID, "ugb_run: argument %zu is null or on another device", i);
+      p[i] = args[i]->ptr;
+      pp[i] = &p[i];
+    }
+    UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
+    CUresult rr = driver().launch_kernel(f->fn, f->grid, 1, 1, f->block, 1, 1, f->smem, (CUstream)dev->stream, pp.data(), nullptr);
+    if (rr != CUDA_SUCCESS) return ugb_fail(dev, UGB_ERR_CUDA, "launch of %s failed with CUresult %d", f->name.c_str(), (int)rr);
+    dev->launches++;
+    return UGB_OK;
+  }
   UGB_REQUIRE(dev, n_args == f->arg_dtypes.size(), UGB_ERR_INVALID, "unsupported number of args for kernel %zu, it takes %zu",
               n_args, f->arg_dtypes.size());
   std::vector<void *> ptrs(n_args);

@@ -119,6 +119,15 @@ class Func:
     def source(self):
         return (lib.ugb_func_source(self._h) or b"").decode()
 
+    def launch3(self, s1, s2, s3):
+        """Func.launch3 of the reference's Python module (ug-pyo3/src/lib.rs:27-50): three slices of one
+        length, the last one written."""
+        if len(s1) != len(s3):
+            raise UgError(3, f"length mismatch {len(s1)} <> {len(s3)}")
+        if len(s2) != len(s3):
+            raise UgError(3, f"length mismatch {len(s2)} <> {len(s3)}")
+        self.device.run(self, [s1, s2, s3])
+
 
 class Device:
     """ug::Device (ug-core/src/lib.rs:49-73) + ug-llama's operator trait."""
@@ -169,6 +178,24 @@ class Device:
         self._check(lib.ugb_compile(self._h, arr, len(instrs), grid_dim, block_dim, shared_mem,
                                     name.encode() if name else None, C.byref(h)))
         return Func(self, h)
+
+    def compile_cu(self, cu_code, func_name, grid_dim=1, block_dim=1, shared_mem=0):
+        """ug_cuda::Device::compile_cu (runtime.rs:179-186): caller-written CUDA C, pointer parameters only."""
+        h = C.c_void_p()
+        self._check(lib.ugb_compile_cu(self._h, cu_code.encode(), func_name.encode(), grid_dim, block_dim,
+                                       shared_mem, C.byref(h)))
+        return Func(self, h)
+
+    def compile_ptx(self, ptx_code, func_name, grid_dim=1, block_dim=1, shared_mem=0):
+        """ug_cuda::Device::compile_ptx (runtime.rs:188-193)."""
+        h = C.c_void_p()
+        self._check(lib.ugb_compile_ptx(self._h, ptx_code.encode(), func_name.encode(), grid_dim, block_dim,
+                                        shared_mem, C.byref(h)))
+        return Func(self, h)
+
+    def zeros(self, length):
+        """ug_cuda::Device::zeros (runtime.rs:195-198): an f32 slice of zeros."""
+        return self.slice_from_values(np.zeros(length, np.float32))
 
     def run(self, func, args):
         """ug::Device::run: one slice per pointer argument of the kernel."""
