@@ -186,3 +186,23 @@ def test_gemm_tile_widths_agree(dev, bn):
     assert worst < TOL
     assert np.max(np.abs(gpu.logits() - base)) < 2e-3 * np.abs(base).max()
     gpu.close()
+
+
+def test_attention_front_end_variants_are_bit_identical(dev):
+    """The K / V ring filled before or after the wait on the qkv projection, by cp.async or by TMA: the same
+    numbers in the same order, so the logits and the chosen tokens are bit for bit the same."""
+    cfg = Config(**{**TINY, "num_hidden_layers": 3})
+    gpu, ref = make(cfg, dev, 16, 128)
+    prompts = synth.tokens(23, (16, 50), cfg.vocab_size)
+    results = []
+    for early, tma in ((1, 0), (0, 0), (1, 1), (0, 1)):
+        gpu.set_option("att_early", early)
+        gpu.set_option("att_tma", tma)
+        gpu.reset(0)
+        gpu.prefill(prompts)
+        gpu.decode(30)                                # crosses sub-tile and ring boundaries
+        results.append((gpu.logits(), gpu.next_tokens()))
+        dev.synchronize()
+    for lg, tk in results[1:]:
+        assert np.array_equal(lg, results[0][0]) and np.array_equal(tk, results[0][1])
+    gpu.close()

@@ -14,6 +14,7 @@
 #include <cuda_bf16.h>
 
 #include "ugb_internal.h"
+#include "tc_ptx.cuh"
 
 namespace ugb_decode {
 
@@ -225,24 +226,52 @@ struct AttRope {
   size_t part_stride;
   const float *cos_, *sin_;
   int interleaved, append;
+  int early;                     // 1: the ring may be filled before griddepcontrol.wait (see the kernel)
+  ugb_status_word *status;       // TMA variant: where a wait that gave up is reported
 };
 
-template <int NSTAGE>
+// TMA variant (TMA = true): the K / V sub-tiles arrive by cp.async.bulk.tensor through rank-3 maps over the
+// caches (dims {64, t_max, sequences x KV heads}, box {64, 16, 1}, 128-byte swizzle = the XOR pattern the
+// cp.async path applies by hand); one lane issues the two copies of a sub-tile and the warp waits on the
+// stage's mbarrier (bounded: 2^22 polls, then the status word is raised and the warp goes on).
+constexpr int att_dyn_smem(int stages, bool tma) {
+  return att_ring_bytes(stages) + (tma ? 1024 + ATT_WARPS * stages * 8 : 0);
+}
+
+template <int NSTAGE, bool TMA = false>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__restrict__ kcache,
                         __nv_bfloat16 *__restrict__ vcache, const int *__restrict__ pos_p,
                         float *__restrict__ part_o, float *__restrict__ part_ml,
                         unsigned int *__restrict__ counters, __nv_bfloat16 *__restrict__ out,
-                        int n_heads, int n_kv, int group, int t_max, float scale, AttRope rope) {
-  extern __shared__ __align__(128) uint8_t att_smem[];                     // the cp.async ring, 64 KiB
+                        int n_heads, int n_kv, int group, int t_max, float scale, AttRope rope,
+                        const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
+  extern __shared__ __align__(128) uint8_t att_smem_raw[];                 // the K / V ring
+  // the swizzle atoms of the TMA variant are 1024 bytes: align the ring by hand
+  uint8_t *att_smem = TMA ? (uint8_t *)(((uintptr_t)att_smem_raw + 1023) & ~(uintptr_t)1023) : att_smem_raw;
   uint8_t (*ring)[NSTAGE][2][ATT_SUB_BYTES] =
       reinterpret_cast<uint8_t (*)[NSTAGE][2][ATT_SUB_BYTES]>(att_smem);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(att_smem + att_ring_bytes(NSTAGE));   // [warp][stage], TMA only
   __shared__ float merge_o[ATT_WARPS][ATT_GROUP][ATT_HD];
   __shared__ float merge_ml[ATT_WARPS][ATT_GROUP][2];
   __shared__ int is_last;
 
+  if (TMA) {
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < ATT_WARPS * NSTAGE; ++i) ugb_tc::mbar_init(ugb_tc::smem_u32(&bars[i]), 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmK) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmV) : "memory");
+    }
+    __syncthreads();
+  }
+  // With rope.early the ring is filled before waiting for the preceding kernel (the qkv projection), whose
+  // output only the rotation of q and the new cache row need: the cached rows of earlier positions were
+  // written a step ago.  The caller sets it only where the position counter, too, is certainly up to date
+  // (not for the first layer of a step, which follows the previous step's argmax closely).
   ugb_pdl_trigger();
-  ugb_pdl_wait();
+  bool dep_ready = false;
+  if (rope.part == nullptr || !rope.early) { ugb_pdl_wait(); dep_ready = true; }
   const int sp = blockIdx.x, n_split = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -318,6 +347,7 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__
       *reinterpret_cast<uint2 *>(vd + i) = make_uint2(pack_bf16(x.x, x.y), pack_bf16(x.z, x.w));
     }
     __threadfence();                                     // in L2 before this warp's cp.async fetches the row
+    if (TMA) asm volatile("fence.proxy.async;" ::: "memory");   // ... or before the TMA engine reads it
     __syncwarp();
   };
   const int sub_pos = (T - 1) / ATT_SUB;                 // sub-tile of the new position
@@ -328,6 +358,15 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__
     // 16 keys x 128 B for K and for V: 4 + 4 chunks of 16 B per lane, XOR-swizzled rows
     const uint32_t ks = (uint32_t)__cvta_generic_to_shared(&ring[warp][stage][0][0]);
     const uint32_t vs = (uint32_t)__cvta_generic_to_shared(&ring[warp][stage][1][0]);
+    if (TMA) {
+      if (lane == 0) {
+        const uint32_t bar = ugb_tc::smem_u32(&bars[warp * NSTAGE + stage]);
+        ugb_tc::mbar_expect_tx(bar, 2 * ATT_SUB_BYTES);
+        ugb_tc::tma_load_3d(ks, &tmK, bar, 0, sub * ATT_SUB, b * n_kv + kvh);
+        ugb_tc::tma_load_3d(vs, &tmV, bar, 0, sub * ATT_SUB, b * n_kv + kvh);
+      }
+      return;
+    }
     const char *kg = reinterpret_cast<const char *>(kbase + (size_t)sub * ATT_SUB * ATT_HD);
     const char *vg = reinterpret_cast<const char *>(vbase + (size_t)sub * ATT_SUB * ATT_HD);
 #pragma unroll
@@ -347,6 +386,7 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__
   // prologue: fill the ring
   const int first = sub_lo + warp;
   const bool append_first = appender && sub_pos < first + (NSTAGE - 1) * ATT_WARPS;
+  if (!dep_ready && append_first) { ugb_pdl_wait(); dep_ready = true; }   // the new row comes first
   if (append_first) append_kv();
 #pragma unroll
   for (int s = 0; s < NSTAGE - 1; ++s) {
@@ -354,6 +394,7 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__
     if (sub < sub_hi) issue(sub, s);
     cp_async_commit();
   }
+  if (!dep_ready) ugb_pdl_wait();
   if (appender && !append_first) append_kv();
   if (rope.part != nullptr) {
     // ---- this lane's 16 dims of query head g, rotated -------------------------------------------
@@ -404,6 +445,7 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__
     for (int e = 0; e < 8; ++e) qa[e] = pack_bf16(y[2 * e], y[2 * e + 1]);
   }
   int stage = 0;
+  uint32_t phases = 0;                                   // TMA: parity of the next completion of every stage
   for (int sub = first; sub < sub_hi; sub += ATT_WARPS) {
     {
       const int nxt = sub + (NSTAGE - 1) * ATT_WARPS;
@@ -411,7 +453,20 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__
       if (nxt < sub_hi) issue(nxt, nstage);
       cp_async_commit();
     }
-    cp_async_wait<NSTAGE - 1>();
+    if (TMA) {
+      const uint32_t bar = ugb_tc::smem_u32(&bars[warp * NSTAGE + stage]);
+      const uint32_t par = (phases >> stage) & 1u;
+      unsigned polls = 0;
+      while (!ugb_tc::mbar_try(bar, par)) {
+        if (++polls > (1u << 22)) {                      // the copy never landed: report, do not hang
+          if (lane == 0 && atomicCAS(&rope.status->code, 0u, (unsigned)UGB_ERR_TIMEOUT) == 0u) rope.status->detail = 0x51u;
+          break;
+        }
+      }
+      phases ^= 1u << stage;
+    } else {
+      cp_async_wait<NSTAGE - 1>();
+    }
     __syncwarp();
     const uint8_t *ks = &ring[warp][stage][0][0];
     const uint32_t vs = (uint32_t)__cvta_generic_to_shared(&ring[warp][stage][1][0]);

@@ -80,6 +80,9 @@ struct ugb_llama {
   size_t loaded = 0;
   // prefill workspace, allocated by the first ugb_llama_prefill: activations of one chunk of
   // pf_rows = batch * pf_chunk rows (pf_chunk positions of every sequence)
+  int att_early = 1;              // option att_early: attention of layers >= 1 fills its K / V ring before griddepcontrol.wait
+  int att_tma = 0;                // option att_tma: decode attention fetches K / V by TMA (1) or cp.async (0)
+  std::vector<CUtensorMap> att_kmap, att_vmap;   // per layer, for the TMA variant
   int pf_att_tc = 1;              // option prefill_attention_tc: 1 = tcgen05 / TMEM attention kernel, 0 = mma.sync one
   int pf_rows_max = 8192;         // option prefill_rows: upper bound on rows per chunk
   int pf_rows = 0, pf_chunk = 0;
@@ -257,18 +260,28 @@ int32_t launch_lm_head_argmax(ugb_llama *m, bool pdl_first) {
 
 // Rope of q and k, append of the new K / V rows and attention over the cache, one kernel per layer.
 // `append` false (kernel timing): the cache is left untouched.
-int32_t launch_attention(ugb_llama *m, __nv_bfloat16 *kc, __nv_bfloat16 *vc, float scale, int n_part, bool append) {
+int32_t launch_attention(ugb_llama *m, int layer, float scale, int n_part, bool append) {
   const ugb_llama_config &c = m->lc;
+  __nv_bfloat16 *kc = m->kcache + (size_t)layer * m->kv_layer_stride;
+  __nv_bfloat16 *vc = m->vcache + (size_t)layer * m->kv_layer_stride;
   dim3 grid(m->att_splits, c.n_kv_heads, m->batch);
   cudaStream_t st = m->dev->stream;
   AttRope rope;
   rope.part = m->part; rope.n_part = n_part; rope.part_stride = (size_t)m->batch * m->qkv_dim;
   rope.cos_ = m->cos; rope.sin_ = m->sin; rope.interleaved = c.rope_interleaved; rope.append = append ? 1 : 0;
+  rope.status = m->dev->status_dev;
+  rope.early = (layer > 0 && append && m->att_early) ? 1 : 0;
+  const bool tma = m->att_tma != 0 && !m->att_kmap.empty();
+  const CUtensorMap none{};
+  const CUtensorMap &mk = tma ? m->att_kmap[layer] : none, &mv = tma ? m->att_vmap[layer] : none;
   cudaError_t e = cudaSuccess;
 #define UGB_ATT_LAUNCH(NS)                                                                                   \
-  e = ugb_launch(decode_attention_kernel_t<NS>, grid, dim3(ATT_WARPS * 32), att_ring_bytes(NS), st,           \
-                 m->pdl != 0, (const __nv_bfloat16 *)nullptr, kc, vc, (const int *)m->pos, m->att_po, m->att_pml, \
-                 m->att_cnt, m->att, c.n_heads, c.n_kv_heads, c.n_heads / c.n_kv_heads, m->t_max, scale, rope)
+  e = tma ? ugb_launch(decode_attention_kernel_t<NS, true>, grid, dim3(ATT_WARPS * 32), att_dyn_smem(NS, true), st,       \
+                       m->pdl != 0, (const __nv_bfloat16 *)nullptr, kc, vc, (const int *)m->pos, m->att_po, m->att_pml,   \
+                       m->att_cnt, m->att, c.n_heads, c.n_kv_heads, c.n_heads / c.n_kv_heads, m->t_max, scale, rope, mk, mv) \
+          : ugb_launch(decode_attention_kernel_t<NS, false>, grid, dim3(ATT_WARPS * 32), att_dyn_smem(NS, false), st,     \
+                       m->pdl != 0, (const __nv_bfloat16 *)nullptr, kc, vc, (const int *)m->pos, m->att_po, m->att_pml,   \
+                       m->att_cnt, m->att, c.n_heads, c.n_kv_heads, c.n_heads / c.n_kv_heads, m->t_max, scale, rope, mk, mv)
   switch (m->att_stages) {
     case 2: UGB_ATT_LAUNCH(2); break;
     case 4: UGB_ATT_LAUNCH(4); break;
@@ -303,7 +316,7 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
     if (!(m->skip & 2) && (rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv))) return rc;
     __nv_bfloat16 *kc = m->kcache + (size_t)l * m->kv_layer_stride;
     __nv_bfloat16 *vc = m->vcache + (size_t)l * m->kv_layer_stride;
-    if (!(m->skip & 8) && (rc = launch_attention(m, kc, vc, scale, s_qkv, true))) return rc;   // rope + append + attention
+    if (!(m->skip & 8) && (rc = launch_attention(m, l, scale, s_qkv, true))) return rc;   // rope + append + attention
     if (!(m->skip & 16) && (rc = gemm(m, po, m->att, w.wo, H, AW, UGB_EPI_F32, m->splits_o, m->bn_o))) return rc;
     if (!(m->skip & 1) && (rc = launch_reduce(m, B, m->x, m->xn, RED_O, po, s_o, w.rms2))) return rc;
     if (!(m->skip & 32) && (rc = gemm(m, m->h, m->xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, m->bn_gate_up))) return rc;
@@ -550,6 +563,26 @@ int32_t ugb_llama_create_tp(ugb_device *dev, const ugb_llama_config *cfg, int32_
     ugb_llama_destroy(m);
     return UGB_ERR_CUDA;
   }
+  if (cudaFuncSetAttribute(decode_attention_kernel_t<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, att_dyn_smem(2, true)) != cudaSuccess ||
+      cudaFuncSetAttribute(decode_attention_kernel_t<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, att_dyn_smem(3, true)) != cudaSuccess ||
+      cudaFuncSetAttribute(decode_attention_kernel_t<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, att_dyn_smem(4, true)) != cudaSuccess ||
+      cudaFuncSetAttribute(decode_attention_kernel_t<5, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, att_dyn_smem(5, true)) != cudaSuccess ||
+      cudaFuncSetAttribute(decode_attention_kernel_t<6, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, att_dyn_smem(6, true)) != cudaSuccess) {
+    ugb_fail(dev, UGB_ERR_CUDA, "cudaFuncSetAttribute(decode_attention_kernel, TMA) failed");
+    ugb_llama_destroy(m);
+    return UGB_ERR_CUDA;
+  }
+  {   // per-layer maps over the caches for the TMA variant: dims {d, position, sequence x kv head}, box 16 positions
+    const uint64_t dims[3] = {(uint64_t)c.head_dim, (uint64_t)m->t_max, (uint64_t)B * c.n_kv_heads};
+    const uint64_t strides[2] = {(uint64_t)c.head_dim, (uint64_t)m->t_max * c.head_dim};
+    const uint32_t box[3] = {(uint32_t)c.head_dim, (uint32_t)ATT_SUB, 1};
+    m->att_kmap.resize(c.layers);
+    m->att_vmap.resize(c.layers);
+    for (int l = 0; l < c.layers; ++l) {
+      TRY(ugb_tc_encode_bf16(dev, &m->att_kmap[l], m->kcache + (size_t)l * m->kv_layer_stride, 3, dims, strides, box));
+      TRY(ugb_tc_encode_bf16(dev, &m->att_vmap[l], m->vcache + (size_t)l * m->kv_layer_stride, 3, dims, strides, box));
+    }
+  }
 #undef TRY
   *out = m;
   return UGB_OK;
@@ -622,6 +655,16 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
   if (k == "gemm_smem_kib") {
     UGB_REQUIRE(dev, value == 0 || (value >= 32 && value <= 220), UGB_ERR_INVALID, "option gemm_smem_kib: %d outside 32..220 (0 = no cap)", value);
     m->gemm_smem_kib = value;
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    return UGB_OK;
+  }
+  if (k == "att_early") {
+    m->att_early = value != 0;
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    return UGB_OK;
+  }
+  if (k == "att_tma") {
+    m->att_tma = value != 0;
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
     return UGB_OK;
   }
@@ -808,9 +851,7 @@ int32_t ugb_llama_time_kernel(ugb_llama *m, int32_t which, int32_t iters, float 
       switch (which) {
         case UGB_LLAMA_K_QKV: rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv); break;
         case UGB_LLAMA_K_ATTENTION: {
-          rc = launch_attention(m, m->kcache + (size_t)l * m->kv_layer_stride,
-                                m->vcache + (size_t)l * m->kv_layer_stride, scale,
-                                ugb_tc_gemm_effective_splits(H, m->splits_qkv), false);
+          rc = launch_attention(m, l, scale, ugb_tc_gemm_effective_splits(H, m->splits_qkv), false);
           break;
         }
         case UGB_LLAMA_K_O: rc = gemm(m, m->part, m->att, w.wo, H, AW, UGB_EPI_F32, m->splits_o, m->bn_o); break;
