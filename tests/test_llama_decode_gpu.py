@@ -189,11 +189,14 @@ def test_gemm_tile_widths_agree(dev, bn):
 
 
 def test_attention_front_end_variants_are_bit_identical(dev):
-    """The K / V ring filled before or after the wait on the qkv projection, by cp.async or by TMA: the same
-    numbers in the same order, so the logits and the chosen tokens are bit for bit the same."""
-    cfg = Config(**{**TINY, "num_hidden_layers": 3})
-    gpu, ref = make(cfg, dev, 16, 128)
-    prompts = synth.tokens(23, (16, 50), cfg.vocab_size)
+    """Work moved in front of griddepcontrol.wait (the attention kernel's K / V ring, the norm kernel's
+    residual row) and the TMA fetch path change when bytes are requested, not what is computed: logits and
+    chosen tokens are bit for bit the same.  The early paths switch themselves on only for shapes whose
+    projections cannot be co-resident (the condition under which they are race-free), hence the wide model."""
+    cfg = Config(hidden_size=1536, intermediate_size=4864, max_position_embeddings=256, num_attention_heads=24,
+                 num_key_value_heads=4, num_hidden_layers=2, vocab_size=1024)
+    gpu = Model.new(cfg, synth.llama_weights(cfg, 31), dev, 64, 128)
+    prompts = synth.tokens(23, (64, 50), cfg.vocab_size)
     results = []
     for early, tma in ((1, 0), (0, 0), (1, 1), (0, 1)):
         gpu.set_option("att_early", early)

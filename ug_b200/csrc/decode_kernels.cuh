@@ -59,21 +59,32 @@ template <int VPT>
 __global__ void __launch_bounds__(256)
 reduce_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ part, int n_part,
                       size_t part_stride, const float *__restrict__ alpha,
-                      __nv_bfloat16 *__restrict__ xn, int hidden, float inv_d, float eps) {
+                      __nv_bfloat16 *__restrict__ xn, int hidden, float inv_d, float eps, int early) {
   __shared__ float sm[8];
   ugb_pdl_trigger();
-  ugb_pdl_wait();
+  // `early`: x was last written two or more kernels back (the previous residual add), so its row and the
+  // norm gains are fetched before waiting for the preceding kernel, whose partials are all that is new.
+  if (!early) ugb_pdl_wait();
   const int b = blockIdx.x;
   const int nvec = hidden >> 2;
   float4 *xr = reinterpret_cast<float4 *>(x + (size_t)b * hidden);
-  float4 v[VPT];
+  float4 v[VPT], w[VPT];
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int c = threadIdx.x + i * 256;
     v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    w[i] = v[i];
     if (c < nvec) {
       v[i] = xr[c];
+      w[i] = __ldg(reinterpret_cast<const float4 *>(alpha) + c);
+    }
+  }
+  if (early) ugb_pdl_wait();
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < nvec) {
       for (int s = 0; s < n_part; ++s) {
         const float4 p = __ldcs(reinterpret_cast<const float4 *>(part + s * part_stride + (size_t)b * hidden) + c);
         v[i].x += p.x; v[i].y += p.y; v[i].z += p.z; v[i].w += p.w;
@@ -93,9 +104,8 @@ reduce_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ part, int
   for (int i = 0; i < VPT; ++i) {
     const int c = threadIdx.x + i * 256;
     if (c < nvec) {
-      const float4 w = __ldg(reinterpret_cast<const float4 *>(alpha) + c);
-      __nv_bfloat162 lo = __floats2bfloat162_rn(v[i].x / m * w.x, v[i].y / m * w.y);
-      __nv_bfloat162 hi = __floats2bfloat162_rn(v[i].z / m * w.z, v[i].w / m * w.w);
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v[i].x / m * w[i].x, v[i].y / m * w[i].y);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(v[i].z / m * w[i].z, v[i].w / m * w[i].w);
       out[c] = make_uint2(*(uint32_t *)&lo, *(uint32_t *)&hi);
     }
   }

@@ -80,7 +80,8 @@ struct ugb_llama {
   size_t loaded = 0;
   // prefill workspace, allocated by the first ugb_llama_prefill: activations of one chunk of
   // pf_rows = batch * pf_chunk rows (pf_chunk positions of every sequence)
-  int att_early = 1;              // option att_early: attention of layers >= 1 fills its K / V ring before griddepcontrol.wait
+  int att_early = 1;              // option att_early: kernels may fetch old data before griddepcontrol.wait when that is provably safe
+  bool early_ok = false;          // ... and it is, for the current shapes and options (set by enqueue_step)
   int att_tma = 0;                // option att_tma: decode attention fetches K / V by TMA (1) or cp.async (0)
   std::vector<CUtensorMap> att_kmap, att_vmap;   // per layer, for the TMA variant
   int pf_att_tc = 1;              // option prefill_attention_tc: 1 = tcgen05 / TMEM attention kernel, 0 = mma.sync one
@@ -172,7 +173,7 @@ int32_t gemm(ugb_llama *m, void *out, const __nv_bfloat16 *a, const __nv_bfloat1
 }
 
 int32_t launch_reduce_rmsnorm_rows(ugb_llama *m, int rows, float *x, __nv_bfloat16 *xn, const float *part, int n_part,
-                                   const float *alpha) {
+                                   const float *alpha, int early = 0) {
   const int hidden = m->cfg.hidden;
   const int nvec = hidden / 4;
   const size_t stride = (size_t)rows * hidden;
@@ -181,10 +182,10 @@ int32_t launch_reduce_rmsnorm_rows(ugb_llama *m, int rows, float *x, __nv_bfloat
   cudaStream_t st = m->dev->stream;
   const bool pdl = m->pdl != 0;
   cudaError_t e;
-  if (nvec <= 256) e = ugb_launch(reduce_rmsnorm_kernel<1>, grid, dim3(256), 0, st, pdl, x, part, n_part, stride, alpha, xn, hidden, inv_d, eps);
-  else if (nvec <= 512) e = ugb_launch(reduce_rmsnorm_kernel<2>, grid, dim3(256), 0, st, pdl, x, part, n_part, stride, alpha, xn, hidden, inv_d, eps);
-  else if (nvec <= 1024) e = ugb_launch(reduce_rmsnorm_kernel<4>, grid, dim3(256), 0, st, pdl, x, part, n_part, stride, alpha, xn, hidden, inv_d, eps);
-  else e = ugb_launch(reduce_rmsnorm_kernel<8>, grid, dim3(256), 0, st, pdl, x, part, n_part, stride, alpha, xn, hidden, inv_d, eps);
+  if (nvec <= 256) e = ugb_launch(reduce_rmsnorm_kernel<1>, grid, dim3(256), 0, st, pdl, x, part, n_part, stride, alpha, xn, hidden, inv_d, eps, early);
+  else if (nvec <= 512) e = ugb_launch(reduce_rmsnorm_kernel<2>, grid, dim3(256), 0, st, pdl, x, part, n_part, stride, alpha, xn, hidden, inv_d, eps, early);
+  else if (nvec <= 1024) e = ugb_launch(reduce_rmsnorm_kernel<4>, grid, dim3(256), 0, st, pdl, x, part, n_part, stride, alpha, xn, hidden, inv_d, eps, early);
+  else e = ugb_launch(reduce_rmsnorm_kernel<8>, grid, dim3(256), 0, st, pdl, x, part, n_part, stride, alpha, xn, hidden, inv_d, eps, early);
   if (e != cudaSuccess) return ugb_fail(m->dev, UGB_ERR_CUDA, "launch of reduce_rmsnorm_kernel failed: %s", cudaGetErrorString(e));
   return ugb_after_launch(m->dev, "reduce_rmsnorm_kernel");
 }
@@ -212,8 +213,8 @@ TpPeers tp_peers(const ugb_llama *m, size_t offset) {
 // x += (sum of the partials of projection `which`), xn = rmsnorm(x) for `rows` rows.  Single rank: the
 // split-K partials in `local`; tensor parallel: every rank's partials, read in place over NVLink.
 int32_t launch_reduce(ugb_llama *m, int rows, float *x, __nv_bfloat16 *xn, int which, const float *local, int n_part,
-                      const float *alpha) {
-  if (!m->tp || which == RED_NONE || n_part == 0) return launch_reduce_rmsnorm_rows(m, rows, x, xn, local, n_part, alpha);
+                      const float *alpha, int early = 0) {
+  if (!m->tp || which == RED_NONE || n_part == 0) return launch_reduce_rmsnorm_rows(m, rows, x, xn, local, n_part, alpha, early);
   if (!m->tp_ready) return ugb_fail(m->dev, UGB_ERR_INVALID, "tensor-parallel model: peers not connected (ugb_llama_tp_connect)");
   const int hidden = m->cfg.hidden, nvec = hidden / 4;
   const size_t stride = (size_t)rows * hidden;
@@ -260,6 +261,8 @@ int32_t launch_lm_head_argmax(ugb_llama *m, bool pdl_first) {
 
 // Rope of q and k, append of the new K / V rows and attention over the cache, one kernel per layer.
 // `append` false (kernel timing): the cache is left untouched.
+bool tma_requested(const ugb_llama *m) { return m->att_tma != 0 && !m->att_kmap.empty(); }
+
 int32_t launch_attention(ugb_llama *m, int layer, float scale, int n_part, bool append) {
   const ugb_llama_config &c = m->lc;
   __nv_bfloat16 *kc = m->kcache + (size_t)layer * m->kv_layer_stride;
@@ -270,7 +273,7 @@ int32_t launch_attention(ugb_llama *m, int layer, float scale, int n_part, bool 
   rope.part = m->part; rope.n_part = n_part; rope.part_stride = (size_t)m->batch * m->qkv_dim;
   rope.cos_ = m->cos; rope.sin_ = m->sin; rope.interleaved = c.rope_interleaved; rope.append = append ? 1 : 0;
   rope.status = m->dev->status_dev;
-  rope.early = (layer > 0 && append && m->att_early) ? 1 : 0;
+  rope.early = (layer > 0 && append && m->early_ok && !tma_requested(m)) ? 1 : 0;
   const bool tma = m->att_tma != 0 && !m->att_kmap.empty();
   const CUtensorMap none{};
   const CUtensorMap &mk = tma ? m->att_kmap[layer] : none, &mv = tma ? m->att_vmap[layer] : none;
@@ -310,19 +313,33 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
   const int s_down = ugb_tc_gemm_effective_splits(c.ffn, m->splits_down);
   const float scale = powf((float)c.head_dim, -0.5f);   // model.rs:236
   float *po = o_out(m, m->part), *pd = down_out(m, m->part);
+  // Work done before griddepcontrol.wait (the attention kernel's K/V ring, the norm kernel's residual row)
+  // reads data written two or more kernels back.  That is safe when the two projections around the
+  // writer's successor cannot be resident together: each GEMM CTA takes more than half an SM's shared
+  // memory, so once all CTAs of the later GEMM have started (which is what lets the reading kernel launch)
+  // fewer than sm_count - ctas(later) CTAs of the earlier one can still be there; at least one has left,
+  // hence passed its own wait, hence everything before it -- the writer included -- has completed.
+  const int sms = dev->sm_count;
+  const auto ctas = [](size_t n, int bn, int splits) { return (int)((n + bn - 1) / bn) * splits; };
+  const int c_qkv = ctas(m->qkv_dim, m->bn_qkv, s_qkv), c_o = ctas(H, m->bn_o, s_o);
+  const int c_gu = ctas(2 * (size_t)c.ffn, m->bn_gate_up, 1), c_down = ctas(H, m->bn_down, s_down);
+  const bool big_smem = m->gemm_smem_kib == 0 || m->gemm_smem_kib >= 136;   // >= 121.5 KiB per GEMM CTA: never two on an SM
+  m->early_ok = m->att_early && m->pdl && big_smem && c_qkv <= sms && c_o <= sms && c_gu <= sms && c_down <= sms &&
+                c_qkv + c_o > sms && c_gu + c_down > sms && c_down + c_qkv > sms;
+  const int early = m->early_ok ? 1 : 0;
   for (int l = 0; l < c.layers; ++l) {
     const LayerW &w = m->layers[l];
-    if (!(m->skip & 1) && (rc = launch_reduce(m, B, m->x, m->xn, l == 0 ? RED_NONE : RED_DOWN, pd, l == 0 ? 0 : s_down, w.rms1))) return rc;
+    if (!(m->skip & 1) && (rc = launch_reduce(m, B, m->x, m->xn, l == 0 ? RED_NONE : RED_DOWN, pd, l == 0 ? 0 : s_down, w.rms1, l > 0 ? early : 0))) return rc;
     if (!(m->skip & 2) && (rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv))) return rc;
     __nv_bfloat16 *kc = m->kcache + (size_t)l * m->kv_layer_stride;
     __nv_bfloat16 *vc = m->vcache + (size_t)l * m->kv_layer_stride;
     if (!(m->skip & 8) && (rc = launch_attention(m, l, scale, s_qkv, true))) return rc;   // rope + append + attention
     if (!(m->skip & 16) && (rc = gemm(m, po, m->att, w.wo, H, AW, UGB_EPI_F32, m->splits_o, m->bn_o))) return rc;
-    if (!(m->skip & 1) && (rc = launch_reduce(m, B, m->x, m->xn, RED_O, po, s_o, w.rms2))) return rc;
+    if (!(m->skip & 1) && (rc = launch_reduce(m, B, m->x, m->xn, RED_O, po, s_o, w.rms2, early))) return rc;
     if (!(m->skip & 32) && (rc = gemm(m, m->h, m->xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, m->bn_gate_up))) return rc;
     if (!(m->skip & 64) && (rc = gemm(m, pd, m->h, w.wdown, H, c.ffn, UGB_EPI_F32, m->splits_down, m->bn_down))) return rc;
   }
-  if ((rc = launch_reduce(m, B, m->x, m->xn, RED_DOWN, pd, s_down, m->ln_f))) return rc;
+  if ((rc = launch_reduce(m, B, m->x, m->xn, RED_DOWN, pd, s_down, m->ln_f, early))) return rc;
   return launch_lm_head_argmax(m, true);
 }
 
