@@ -324,7 +324,7 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
   const int c_qkv = ctas(m->qkv_dim, m->bn_qkv, s_qkv), c_o = ctas(H, m->bn_o, s_o);
   const int c_gu = ctas(2 * (size_t)c.ffn, m->bn_gate_up, 1), c_down = ctas(H, m->bn_down, s_down);
   const bool big_smem = m->gemm_smem_kib == 0 || m->gemm_smem_kib >= 136;   // >= 121.5 KiB per GEMM CTA: never two on an SM
-  m->early_ok = m->att_early && m->pdl && big_smem && c_qkv <= sms && c_o <= sms && c_gu <= sms && c_down <= sms &&
+  m->early_ok = m->att_early && m->pdl && m->skip == 0 && big_smem && c_qkv <= sms && c_o <= sms && c_gu <= sms && c_down <= sms &&
                 c_qkv + c_o > sms && c_gu + c_down > sms && c_down + c_qkv > sms;
   const int early = m->early_ok ? 1 : 0;
   for (int l = 0; l < c.layers; ++l) {
