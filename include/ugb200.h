@@ -402,7 +402,9 @@ UGB_API int32_t ugb_llama_load_weight(ugb_llama *m, const char *name, const ugb_
  * projections) and "att_splits" (KV slices per sequence and KV head), 1..8;
  * "bn_qkv", "bn_o", "bn_gate_up", "bn_down", "bn_lm_head" (GEMM tile width:
  * 64, 80, 96, 128 or 256); "gemm_smem_kib" (shared-memory cap of a decode GEMM
- * CTA, 32..220, 0 = none); "prefill_rows" (64..65536, see ugb_llama_prefill). */
+ * CTA, 32..220, 0 = none); "att_stages" (2..6); "att_early", "att_tma",
+ * "prefill_attention_tc", "pdl" (0 / 1); "prefill_rows" (64..65536, see
+ * ugb_llama_prefill). */
 UGB_API int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value);
 /* Sets the number of cached positions (0 = empty cache); cache contents at
  * positions >= pos are ignored by later steps. */
