@@ -1,25 +1,26 @@
-// Fused Llama decode engine: the Model::fwd call sites of ug-llama
-// (ug-llama/src/model.rs:298-374) for one new token per sequence, as a fixed
-// sequence of hand-written kernels captured in a CUDA graph.
+// Fused Llama engine: the Model::fwd call sites of ug-llama (ug-llama/src/model.rs:298-374) as fixed
+// sequences of hand-written kernels.
 //
-// Per layer (model.rs:203-269), 8 launches:
+// Decode (one new token per sequence), per layer (model.rs:203-269) 7 launches, captured in a CUDA graph:
 //   reduce_rmsnorm   residual += previous down-proj partials; rms1 -> bf16
 //   tcgen05 GEMM     fused q|k|v projection, split-K fp32 partials
-//   rope_append      sum partials, rope(q), rope(k), write k/v into the KV cache
-//   decode_attention grouped-query flash-decode over the cache (+ slice merge)
+//   decode_attention sums the partials, rope(q), rope(k), writes k/v into the KV cache, then
+//                    grouped-query flash-decode over the cache (+ slice merge)
 //   tcgen05 GEMM     o_proj, split-K partials
 //   reduce_rmsnorm   residual += o_proj partials; rms2 -> bf16
 //   tcgen05 GEMM     gate|up projection (rows interleaved), epilogue silu(gate)*up -> bf16
 //   tcgen05 GEMM     down projection, split-K partials
-// then the final norm, the tied lm_head GEMM (fp32 logits) and a row argmax
-// that also advances the position.  Weights and the KV cache are bf16, the
-// residual stream and every reduction are fp32.  Batch rows are independent
-// sequences that share one position (the reference's pos[0] convention).
+// then the final norm, the tied lm_head GEMM (fp32 logits) and a row argmax that also advances the
+// position.  Prefill (a block of positions per sequence, in chunks of rows): the same chain with m = rows;
+// the qkv GEMM's epilogue rotates q / k and appends K / V, attention is the causal tcgen05 kernel of
+// attention_tc.cu.  Tensor parallel: a rank keeps its share of heads / FFN columns / vocabulary and the
+// norm kernel sums all ranks' partials over peer memory (tp_kernels.cuh).
+// Weights and the KV cache are bf16, the residual stream and every reduction are fp32.  Batch rows are
+// independent sequences that share one position (the reference's pos[0] convention).
 //
-// HBM layout per model: weights [layer]{wqkv [(h+2kv)*d, hidden], wo [hidden,
-// hidden], wgu [2*ffn, hidden] (gate row j at 2j, up row j at 2j+1), wdown
-// [hidden, ffn]}, embedding [vocab, hidden]; KV cache K and V each
-// [layer][batch][kv_head][t_max][head_dim] bf16 (t_max rounded up to 16).
+// HBM layout per model: weights [layer]{wqkv [(h+2kv)*d, hidden], wo [hidden, h*d], wgu [2*ffn, hidden]
+// (gate row j at 2j, up row j at 2j+1), wdown [hidden, ffn]}, embedding [vocab, hidden]; KV cache K and V
+// each [layer][batch][kv_head][t_max][head_dim] bf16 (t_max rounded up to 16).
 #include <cmath>
 #include <cstring>
 #include <string>

@@ -1,9 +1,12 @@
-"""Host-side mirror of ug-llama's model API over the fused decode engine.
+"""Host-side mirror of ug-llama's model API over the fused Llama engine.
 
 ``Config`` and ``Model`` follow ug-llama/src/model.rs:10-30,298-374: the same
 field names, the same safetensors weight names, ``Model.new`` / ``Model.fwd``.
-``fwd`` covers seq_len == 1 (one new token per sequence); the KV cache that the
-reference threads through ``fwd`` as ``&mut [Cache]`` lives inside the engine.
+``fwd`` takes one new token per sequence (the graph-replayed decode step) or a
+block of them (the causal prefill path); the KV cache that the reference
+threads through ``fwd`` as ``&mut [Cache]`` lives inside the engine.  Weights
+come from host arrays (``Model.new``) or from .safetensors files
+(``Model.from_safetensors``); ``tp=(rank, size)`` builds the tensor-parallel variant.
 """
 import ctypes as C
 from dataclasses import dataclass
