@@ -105,7 +105,7 @@ class RmsSiluWorkload:
     rows, cols = 8192, 4096
     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload's kernel, from the ncu capture
     # summarised in profiles/row_kernels_ncu.md (the output's tail is still in L2 when the counters stop)
-    ncu_traffic_bytes = 268_472_576 + 97_029_120
+    ncu_traffic_bytes = 268_462_080 + 96_574_464
 
     def __init__(self, rank):
         from ug_b200 import synth
