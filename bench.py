@@ -569,6 +569,8 @@ class PrefillWorkload(DecodeWorkload):
         from ug_b200.llama import Model
         self.dev = dev
         self.model = Model.new(self.cfg, self.weights, dev, self.batch, self.prefill)
+        for name, value in getattr(self, "options", {}).items():
+            self.model.set_option(name, value)
         self.tok_dev = dev.slice_from_values(self.prompts.reshape(-1))
         dev.synchronize()
 
@@ -649,6 +651,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--prefill", type=int, default=None, help="decode: cached positions before timing")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=INT",
+                    help="prefill: engine option set before the run (profiling of kernel variants)")
     ap.add_argument("--layers", type=int, default=None, help="decode: layer count (profiling of small cases)")
     ap.add_argument("--tp", action="store_true",
                     help="decode: tensor-parallel variant -- the ranks share ONE batch of 64 sequences (heads, FFN "
@@ -669,7 +673,9 @@ def main():
             return DecodeWorkload(r, prefill=args.prefill, layers=args.layers, fast_prefill=args.fast_prefill,
                                   tp=(rank, world) if args.tp else None)
         if args.workload == "prefill":
-            return PrefillWorkload(r, prefill=args.prefill, layers=args.layers)
+            wl = PrefillWorkload(r, prefill=args.prefill, layers=args.layers)
+            wl.options = dict((k, int(v)) for k, v in (o.split("=") for o in args.option))
+            return wl
         return WORKLOADS[args.workload](r)
 
     if args.impl == "reference":

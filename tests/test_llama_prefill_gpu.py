@@ -38,9 +38,10 @@ def logit_err(got, ref):
     (dict(hidden_size=256, num_attention_heads=4, num_key_value_heads=4, intermediate_size=320), 8, 130),
     (dict(), 1, 1),                                   # a block of one position
 ])
-@pytest.mark.parametrize("tc", [0, 1])
+@pytest.mark.parametrize("tc", [0, 1, 2])
 def test_prefill_matches_oracle(dev, over, batch, t, tc):
-    """tc = 1: attention on the tcgen05 / TMEM kernel (128-query tiles), 0: on the mma.sync kernel (64-query tiles)."""
+    """tc = 1: attention on the tcgen05 / TMEM kernel (128-query tiles, work items drawn from a counter), 2: the
+    same with the items dealt round-robin, 0: on the mma.sync kernel (64-query tiles)."""
     cfg = Config(**{**TINY, **over})
     gpu, ref = make(cfg, dev, batch, 256)
     gpu.set_option("prefill_attention_tc", tc)
@@ -140,21 +141,30 @@ def test_prefill_rejects_bad_arguments(dev):
     gpu.close()
 
 
-def test_prefill_config4_shape(dev):
-    """Llama-1.1B widths, 8 sequences x 512 positions (2 layers to keep the oracle in seconds)."""
+@pytest.mark.parametrize("tc", [1, 2])
+def test_prefill_config4_shape(dev, tc):
+    """Llama-1.1B widths, 8 sequences x 512 positions (2 layers to keep the oracle in seconds): 1024 attention
+    work items of 2 to 8 key tiles over 296 persistent CTAs, so every CTA runs several items back to back.
+    Both ways of handing out the items give the same bits, and a second pass over the same prompts repeats them
+    (the work counter is back at zero after each launch)."""
     cfg = Config(hidden_size=2048, intermediate_size=5632, max_position_embeddings=2048, num_attention_heads=32,
                  num_key_value_heads=4, num_hidden_layers=2, vocab_size=32000)
     gpu, ref = make(cfg, dev, 8, 512)
-    gpu.set_option("prefill_attention_tc", 1)
+    gpu.set_option("prefill_attention_tc", tc)
     prompts = synth.tokens(13, (8, 512), cfg.vocab_size)
     gpu.prefill(prompts, all_logits=True)
     got = gpu.prefill_logits()
     want = ref.fwd(prompts[5:6], 0, ref.new_cache())[0]
     assert logit_err(got[5], want) < TOL
+    for other in (3 - tc, tc):
+        gpu.set_option("prefill_attention_tc", other)
+        gpu.reset(0)
+        gpu.prefill(prompts, all_logits=True)
+        assert np.array_equal(gpu.prefill_logits(), got)
     gpu.close()
 
 
-@pytest.mark.parametrize("tc", [0, 1])
+@pytest.mark.parametrize("tc", [0, 1, 2])
 def test_long_prefill_many_key_tiles(dev, tc):
     """1100 positions in chunks of 256 and 300: up to 18 key tiles per query tile on the tcgen05 kernel (every
     barrier's phase wraps many times), a ragged last tile, and chunks that start inside a key tile."""

@@ -60,7 +60,9 @@ int32_t ugb_device_create(int32_t ordinal, ugb_device **out) {
             cudaEventCreate(&d->ev_begin) == cudaSuccess &&
             cudaEventCreate(&d->ev_end) == cudaSuccess &&
             cudaMalloc(&d->status_dev, sizeof(ugb_status_word)) == cudaSuccess &&
-            cudaMemset(d->status_dev, 0, sizeof(ugb_status_word)) == cudaSuccess;
+            cudaMemset(d->status_dev, 0, sizeof(ugb_status_word)) == cudaSuccess &&
+            cudaMalloc(&d->sched_dev, 2 * sizeof(int)) == cudaSuccess &&
+            cudaMemset(d->sched_dev, 0, 2 * sizeof(int)) == cudaSuccess;
   if (!ok) {
     e = cudaGetLastError();
     ugb_fail(nullptr, UGB_ERR_CUDA, "device set-up failed: %s", cudaGetErrorString(e));
@@ -86,6 +88,7 @@ int32_t ugb_device_destroy(ugb_device *dev) {
   cudaStreamSynchronize(dev->stream);
   ugb_gemm_state_free(dev);
   if (dev->status_dev) cudaFree(dev->status_dev);
+  if (dev->sched_dev) cudaFree(dev->sched_dev);
   if (dev->ev_begin) cudaEventDestroy(dev->ev_begin);
   if (dev->ev_end) cudaEventDestroy(dev->ev_end);
   if (dev->stream) cudaStreamDestroy(dev->stream);

@@ -2,9 +2,11 @@
 // (Attention::fwd with seq_len > 1, ug-llama/src/model.rs:231-245: repeat + q.kT + scale + causal_mask +
 // softmax + .v + head merge, without the [b, h, t, T] score tensor).
 //
-//   grid (ceil(t / 128), n_heads, batch), 192 threads, two CTAs per SM (80 KiB of shared memory and 256 TMEM
-//   columns each: while one CTA's softmax warps work, the other's products run):
-//     warp 0      TMA producer: the 128 x 64 query tile once, then 64-key K and V tiles into two-deep rings
+//   persistent grid of at most 2 x SMs CTAs over the (query tile, head, sequence) work items, 192 threads,
+//   two CTAs per SM (80 KiB of shared memory and 256 TMEM columns each: while one CTA's softmax warps work,
+//   the other's products run):
+//     warp 0      TMA producer: draws the work item, loads its 128 x 64 query tile, then 64-key K and V tiles
+//                               into two-deep rings
 //     warp 1      MMA issuer:   S = Q K^T  (tcgen05.mma M128 N64 K16 x 4, both operands K-major) into one of two
 //                               TMEM score buffers; O_j = P V (M128 N64 K16 x 4, V consumed MN-major as it lies
 //                               in the cache) into one of two TMEM output buffers
@@ -34,10 +36,11 @@ constexpr int O_COL = 128;
 static_assert(BKV == 64 && HD == 64, "one 128-byte swizzle atom per P row and per K / V row");
 
 struct Params {
-  int t, pos0, n_heads, n_kv;
+  int t, pos0, n_heads, n_kv, batch;
   float scale;
   __nv_bfloat16 *out;
   ugb_status_word *status;
+  int *sched;   // {next item, CTAs done}: both zero between launches; null = items dealt round-robin
 };
 
 // 64 consecutive TMEM columns of this thread's lane: both loads in flight, one wait
@@ -55,6 +58,34 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// One work item = one 128-query tile of one head of one sequence.  Items are numbered with the query
+// tiles in descending order (the tiles with the most key tiles first).  A CTA's first item is its block
+// index; the later ones come from a global counter (longest-first list scheduling: a CTA that drew short
+// items draws more of them), or round-robin when no counter is given.  The producer draws the item and
+// publishes it to the other roles through a four-deep ring of shared-memory slots (item_full barriers,
+// -1 = no more work).  A CTA keeps its TMEM, barriers and tensor maps across its items, and the producer
+// and MMA roles run ahead into the next item while the softmax warps finish the current one.  The K / V /
+// S / P / O rings are indexed by a tile counter `g` that runs on across items (stage g & 1, phase
+// (g >> 1) & 1), the query buffer by the item counter.  The producer cannot be more than two items ahead
+// of the softmax warps (the query buffer of item n + 1 is released by products that need the probabilities
+// of item n), so a slot is never overwritten before every role has read it.
+struct Item {
+  int q0, head, b, kvh, n_tiles;
+};
+__device__ __forceinline__ Item item_of(int idx, const Params &p, int q_tiles) {
+  Item it;
+  const int per_q = p.n_heads * p.batch;
+  const int qt = q_tiles - 1 - idx / per_q;                         // descending query tile
+  const int r = idx - (idx / per_q) * per_q;
+  it.b = r / p.n_heads;
+  it.head = r - it.b * p.n_heads;
+  it.q0 = qt * BQ;
+  it.kvh = it.head / (p.n_heads / p.n_kv);
+  const int last_q = min(it.q0 + BQ, p.t) - 1;                       // last query row of the tile
+  it.n_tiles = (p.pos0 + last_q + 1 + BKV - 1) / BKV;                // key tiles any of its rows attends
+  return it;
+}
+
 __global__ void __launch_bounds__(THREADS, 2)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                             const __grid_constant__ CUtensorMap tmV, Params p) {
@@ -63,19 +94,19 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
   uint8_t *q_s = smem, *k_s = q_s + Q_BYTES, *v_s = k_s + 2 * KV_BYTES, *p_s = v_s + 2 * KV_BYTES;
   uint64_t *bars = (uint64_t *)(p_s + 2 * P_BYTES);
   uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7;
-  uint64_t *s_full = bars + 9, *p_full = bars + 11, *o_full = bars + 13;
-  uint32_t *tmem_slot = (uint32_t *)(bars + 15);
+  uint64_t *s_full = bars + 9, *p_full = bars + 11, *o_full = bars + 13, *q_empty = bars + 15, *item_full = bars + 16;
+  uint32_t *tmem_slot = (uint32_t *)(bars + 20);
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+  volatile int *item_slot = (volatile int *)(tmem_slot + 2);       // four entries
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // query tiles in descending order: the CTAs with the most key tiles (causal) start first
-  const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * BQ, head = blockIdx.y, b = blockIdx.z;
-  const int kvh = head / (p.n_heads / p.n_kv);
-  const int last_q = min(q0 + BQ, p.t) - 1;                        // last query row of this CTA
-  const int n_tiles = (p.pos0 + last_q + 1 + BKV - 1) / BKV;       // key tiles any of its rows attends
+  const int q_tiles = (p.t + BQ - 1) / BQ;
+  const int n_items = q_tiles * p.n_heads * p.batch;
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(q_full), 1);
+    mbar_init(smem_u32(q_empty), 1);
+    for (int s = 0; s < 4; ++s) mbar_init(smem_u32(&item_full[s]), 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&k_full[s]), 1);
       mbar_init(smem_u32(&k_empty[s]), 1);
@@ -104,17 +135,40 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer --
     if (lane == 0) {
-      mbar_expect_tx(smem_u32(q_full), Q_BYTES);
-      tma_load_4d(smem_u32(q_s), &tmQ, smem_u32(q_full), 0, head, q0, b);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-        if (!mbar_wait(smem_u32(&k_empty[s]), ph ^ 1u, abort_flag, p.status, 0x41)) break;
-        mbar_expect_tx(smem_u32(&k_full[s]), KV_BYTES);
-        tma_load_3d(smem_u32(k_s + s * KV_BYTES), &tmK, smem_u32(&k_full[s]), 0, j * BKV, b * p.n_kv + kvh);
-        if (!mbar_wait(smem_u32(&v_empty[s]), ph ^ 1u, abort_flag, p.status, 0x42)) break;
-        mbar_expect_tx(smem_u32(&v_full[s]), KV_BYTES);
-        tma_load_3d(smem_u32(v_s + s * KV_BYTES), &tmV, smem_u32(&v_full[s]), 0, j * BKV, b * p.n_kv + kvh);
+      int g = 0;
+      bool alive = true;
+      int idx = blockIdx.x;
+      for (int n_it = 0; alive; ++n_it) {
+        // the query buffer is free once every S product of the previous item has retired
+        if (!mbar_wait(smem_u32(q_empty), ((uint32_t)n_it & 1u) ^ 1u, abort_flag, p.status, 0x40)) break;
+        const bool more = idx < n_items;
+        item_slot[n_it & 3] = more ? idx : -1;
+        mbar_arrive(smem_u32(&item_full[n_it & 3]));                // release: the slot is visible to the waiters
+        if (!more) break;
+        const Item it = item_of(idx, p, q_tiles);
+        mbar_expect_tx(smem_u32(q_full), Q_BYTES);
+        tma_load_4d(smem_u32(q_s), &tmQ, smem_u32(q_full), 0, it.head, it.q0, it.b);
+        // the next item is drawn now, its latency hidden behind this item's tiles
+        idx = p.sched ? (int)gridDim.x + atomicAdd(p.sched, 1) : idx + (int)gridDim.x;
+        for (int j = 0; j < it.n_tiles; ++j, ++g) {
+          const int s = g & 1;
+          const uint32_t ph = (uint32_t)(g >> 1) & 1u;
+          if (!mbar_wait(smem_u32(&k_empty[s]), ph ^ 1u, abort_flag, p.status, 0x41)) { alive = false; break; }
+          mbar_expect_tx(smem_u32(&k_full[s]), KV_BYTES);
+          tma_load_3d(smem_u32(k_s + s * KV_BYTES), &tmK, smem_u32(&k_full[s]), 0, j * BKV, it.b * p.n_kv + it.kvh);
+          if (!mbar_wait(smem_u32(&v_empty[s]), ph ^ 1u, abort_flag, p.status, 0x42)) { alive = false; break; }
+          mbar_expect_tx(smem_u32(&v_full[s]), KV_BYTES);
+          tma_load_3d(smem_u32(v_s + s * KV_BYTES), &tmV, smem_u32(&v_full[s]), 0, j * BKV, it.b * p.n_kv + it.kvh);
+        }
+      }
+      if (p.sched) {
+        // every producer passes here exactly once, after its last draw: the last one re-arms the counters
+        __threadfence();
+        if (atomicAdd(p.sched + 1, 1) == (int)gridDim.x - 1) {
+          p.sched[0] = 0;
+          p.sched[1] = 0;
+          __threadfence();
+        }
       }
     }
   } else if (warp == 1) {
@@ -122,10 +176,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(BQ, BKV, false);          // Q and K both K-major (rows of 64 dims)
       const uint32_t idesc_o = make_idesc(BQ, HD, true);            // P K-major, V MN-major ([key][dim] rows)
-      bool alive = mbar_wait(smem_u32(q_full), 0, abort_flag, p.status, 0x43);
-      auto issue_s = [&](int j) {
-        const int s = j & 1;
-        if (!mbar_wait(smem_u32(&k_full[s]), (uint32_t)(j >> 1) & 1u, abort_flag, p.status, 0x44)) { alive = false; return; }
+      bool alive = true;
+      auto issue_s = [&](int g) {
+        const int s = g & 1;
+        if (!mbar_wait(smem_u32(&k_full[s]), (uint32_t)(g >> 1) & 1u, abort_flag, p.status, 0x44)) { alive = false; return; }
         tcgen05_fence_after();
         const uint32_t qa = smem_u32(q_s), kb = smem_u32(k_s + s * KV_BYTES);
 #pragma unroll
@@ -135,9 +189,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         umma_commit(smem_u32(&k_empty[s]));                         // K stage free once the products retire
         umma_commit(smem_u32(&s_full[s]));                          // scores ready for the softmax warps
       };
-      auto issue_pv = [&](int j) {
-        const int s = j & 1;
-        const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+      auto issue_pv = [&](int g) {
+        const int s = g & 1;
+        const uint32_t ph = (uint32_t)(g >> 1) & 1u;
         if (!mbar_wait(smem_u32(&p_full[s]), ph, abort_flag, p.status, 0x45)) { alive = false; return; }
         if (!mbar_wait(smem_u32(&v_full[s]), ph, abort_flag, p.status, 0x46)) { alive = false; return; }
         tcgen05_fence_after();
@@ -153,99 +207,122 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         umma_commit(smem_u32(&v_empty[s]));
         umma_commit(smem_u32(&o_full[s]));
       };
-      if (alive && n_tiles > 0) issue_s(0);
-      if (alive && n_tiles > 1) issue_s(1);
-      for (int j = 0; j < n_tiles && alive; ++j) {
-        issue_pv(j);
-        if (alive && j + 2 < n_tiles) issue_s(j + 2);
+      int g0 = 0;
+      for (int n_it = 0; alive; ++n_it) {
+        if (!mbar_wait(smem_u32(&item_full[n_it & 3]), (uint32_t)(n_it >> 2) & 1u, abort_flag, p.status, 0x49)) break;
+        const int idx = item_slot[n_it & 3];
+        if (idx < 0) break;
+        const Item it = item_of(idx, p, q_tiles);
+        if (!mbar_wait(smem_u32(q_full), (uint32_t)n_it & 1u, abort_flag, p.status, 0x43)) break;
+        // S(0), S(1), then PV(j) followed by S(j + 2): the score buffer of tile j + 2 is the one the softmax
+        // warps released before PV(j) could be issued
+        if (alive && it.n_tiles > 0) issue_s(g0);
+        if (alive && it.n_tiles > 1) issue_s(g0 + 1);
+        if (alive && it.n_tiles <= 2) umma_commit(smem_u32(q_empty));          // no more products read Q
+        for (int j = 0; j < it.n_tiles && alive; ++j) {
+          issue_pv(g0 + j);
+          if (alive && j + 2 < it.n_tiles) {
+            issue_s(g0 + j + 2);
+            if (alive && j + 3 == it.n_tiles) umma_commit(smem_u32(q_empty));  // that was the item's last S
+          }
+        }
+        g0 += it.n_tiles;
       }
     }
   } else {
     // -------------------------------------------------------------- softmax warps --
     const int quad = warp & 3;                                      // TMEM lane quadrant this warp may read
     const int row = quad * 32 + lane;                               // query row of the tile = TMEM lane
-    const int qi = q0 + row;
-    const int reach = p.pos0 + qi;                                  // last key this query attends
     const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
     // running maximum kept in the exponent's own unit: scores are multiplied by scale * log2(e) once and the
     // probabilities are 2^(s - m), one FFMA and one ex2.approx each
     const float sc = p.scale * 1.4426950408889634f;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
-    float o[HD];
-#pragma unroll
-    for (int d = 0; d < HD; ++d) o[d] = 0.f;
     bool alive = true;
-    auto fold = [&](int j, float alpha) {                           // o = o * alpha + O_j
-      const int s = j & 1;
-      // .aligned TMEM loads follow: the whole warp leaves together or not at all
-      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&o_full[s]), (uint32_t)(j >> 1) & 1u, abort_flag, p.status, 0x47))) { alive = false; return; }
-      tcgen05_fence_after();
-      float f[HD];
-      tmem_ld64(lane_base + (uint32_t)(O_COL + s * HD), f);
+    int g0 = 0;
+    for (int n_it = 0; alive; ++n_it) {
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&item_full[n_it & 3]), (uint32_t)(n_it >> 2) & 1u, abort_flag, p.status, 0x4a))) break;
+      const int idx = item_slot[n_it & 3];
+      if (idx < 0) break;
+      const Item it = item_of(idx, p, q_tiles);
+      const int qi = it.q0 + row;
+      const int reach = p.pos0 + qi;                                // last key this query attends
+      float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+      float o[HD];
 #pragma unroll
-      for (int i = 0; i < HD; ++i) o[i] = o[i] * alpha + f[i];
-    };
-    for (int j = 0; j < n_tiles && alive; ++j) {
-      const int s = j & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_full[s]), (uint32_t)(j >> 1) & 1u, abort_flag, p.status, 0x48))) { alive = false; break; }
-      tcgen05_fence_after();
-      const int key0 = j * BKV;
-      float f[BKV];
-      tmem_ld64(lane_base + (uint32_t)(s * BKV), f);
-      // four interleaved chains for the maximum and for the sum: a single one is 64 dependent operations.
-      // The maximum is taken over the raw scores (sc > 0) and scaled once; 2^(s sc - m) is one FFMA + ex2.
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      if (key0 + BKV - 1 > reach) {                                 // the diagonal crosses this tile: causal mask
+      for (int d = 0; d < HD; ++d) o[d] = 0.f;
+      auto fold = [&](int g, float alpha) {                         // o = o * alpha + O_g
+        const int s = g & 1;
+        // .aligned TMEM loads follow: the whole warp leaves together or not at all
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&o_full[s]), (uint32_t)(g >> 1) & 1u, abort_flag, p.status, 0x47))) { alive = false; return; }
+        tcgen05_fence_after();
+        float f[HD];
+        tmem_ld64(lane_base + (uint32_t)(O_COL + s * HD), f);
 #pragma unroll
-        for (int i = 0; i < BKV; ++i)
-          if (key0 + i > reach) f[i] = -INFINITY;
+        for (int i = 0; i < HD; ++i) o[i] = o[i] * alpha + f[i];
+      };
+      for (int j = 0; j < it.n_tiles && alive; ++j) {
+        const int g = g0 + j, s = g & 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&s_full[s]), (uint32_t)(g >> 1) & 1u, abort_flag, p.status, 0x48))) { alive = false; break; }
+        tcgen05_fence_after();
+        const int key0 = j * BKV;
+        float f[BKV];
+        tmem_ld64(lane_base + (uint32_t)(s * BKV), f);
+        // four interleaved chains for the maximum and for the sum: a single one is 64 dependent operations.
+        // The maximum is taken over the raw scores (sc > 0) and scaled once; 2^(s sc - m) is one FFMA + ex2.
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (key0 + BKV - 1 > reach) {                               // the diagonal crosses this tile: causal mask
+#pragma unroll
+          for (int i = 0; i < BKV; ++i)
+            if (key0 + i > reach) f[i] = -INFINITY;
+        }
+#pragma unroll
+        for (int i = 0; i < BKV; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], f[i]);
+        const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc);   // finite: key 0 is attended by every row
+        const float alpha = ex2(m_run - m_new);
+        const float neg_m = -m_new;
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < BKV; ++i) {
+          f[i] = ex2(fmaf(f[i], sc, neg_m));
+          l4[i & 3] += f[i];
+        }
+        l_run = l_run * alpha + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
+        m_run = m_new;
+        // probabilities rounded to bf16 into the swizzled A tile of the second product
+        uint8_t *prow = p_s + s * P_BYTES + row * 128;
+#pragma unroll
+        for (int ch = 0; ch < BKV / 8; ++ch) {                      // 8 keys = 16 bytes per chunk
+          uint4 v;
+          __nv_bfloat162 t;
+          t = __floats2bfloat162_rn(f[ch * 8 + 0], f[ch * 8 + 1]); v.x = *(uint32_t *)&t;
+          t = __floats2bfloat162_rn(f[ch * 8 + 2], f[ch * 8 + 3]); v.y = *(uint32_t *)&t;
+          t = __floats2bfloat162_rn(f[ch * 8 + 4], f[ch * 8 + 5]); v.z = *(uint32_t *)&t;
+          t = __floats2bfloat162_rn(f[ch * 8 + 6], f[ch * 8 + 7]); v.w = *(uint32_t *)&t;
+          *reinterpret_cast<uint4 *>(prow + ((ch ^ (row & 7)) << 4)) = v;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P visible to the tensor core's reads
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&p_full[s]));
+        if (j > 0) fold(g - 1, alpha_prev);
+        alpha_prev = alpha;
       }
+      if (alive && it.n_tiles > 0) fold(g0 + it.n_tiles - 1, alpha_prev);
+      if (alive && qi < p.t) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16 *dst = p.out + ((size_t)it.b * p.t + qi) * ((size_t)p.n_heads * HD) + (size_t)it.head * HD;
 #pragma unroll
-      for (int i = 0; i < BKV; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], f[i]);
-      const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc);   // finite: key 0 is attended by every row
-      const float alpha = ex2(m_run - m_new);
-      const float neg_m = -m_new;
-      float l4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int i = 0; i < BKV; ++i) {
-        f[i] = ex2(fmaf(f[i], sc, neg_m));
-        l4[i & 3] += f[i];
+        for (int c = 0; c < HD / 8; ++c) {
+          uint4 v;
+          __nv_bfloat162 t;
+          t = __floats2bfloat162_rn(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv); v.x = *(uint32_t *)&t;
+          t = __floats2bfloat162_rn(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv); v.y = *(uint32_t *)&t;
+          t = __floats2bfloat162_rn(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); v.z = *(uint32_t *)&t;
+          t = __floats2bfloat162_rn(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv); v.w = *(uint32_t *)&t;
+          *reinterpret_cast<uint4 *>(dst + c * 8) = v;
+        }
       }
-      l_run = l_run * alpha + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
-      m_run = m_new;
-      // probabilities rounded to bf16 into the swizzled A tile of the second product
-      uint8_t *prow = p_s + s * P_BYTES + row * 128;
-#pragma unroll
-      for (int ch = 0; ch < BKV / 8; ++ch) {                        // 8 keys = 16 bytes per chunk
-        uint4 v;
-        __nv_bfloat162 t;
-        t = __floats2bfloat162_rn(f[ch * 8 + 0], f[ch * 8 + 1]); v.x = *(uint32_t *)&t;
-        t = __floats2bfloat162_rn(f[ch * 8 + 2], f[ch * 8 + 3]); v.y = *(uint32_t *)&t;
-        t = __floats2bfloat162_rn(f[ch * 8 + 4], f[ch * 8 + 5]); v.z = *(uint32_t *)&t;
-        t = __floats2bfloat162_rn(f[ch * 8 + 6], f[ch * 8 + 7]); v.w = *(uint32_t *)&t;
-        *reinterpret_cast<uint4 *>(prow + ((ch ^ (row & 7)) << 4)) = v;
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P visible to the tensor core's reads
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&p_full[s]));
-      if (j > 0) fold(j - 1, alpha_prev);
-      alpha_prev = alpha;
-    }
-    if (alive && n_tiles > 0) fold(n_tiles - 1, alpha_prev);
-    if (alive && qi < p.t) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16 *dst = p.out + ((size_t)b * p.t + qi) * ((size_t)p.n_heads * HD) + (size_t)head * HD;
-#pragma unroll
-      for (int c = 0; c < HD / 8; ++c) {
-        uint4 v;
-        __nv_bfloat162 t;
-        t = __floats2bfloat162_rn(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv); v.x = *(uint32_t *)&t;
-        t = __floats2bfloat162_rn(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv); v.y = *(uint32_t *)&t;
-        t = __floats2bfloat162_rn(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv); v.z = *(uint32_t *)&t;
-        t = __floats2bfloat162_rn(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv); v.w = *(uint32_t *)&t;
-        *reinterpret_cast<uint4 *>(dst + c * 8) = v;
-      }
+      g0 += it.n_tiles;
     }
   }
   tcgen05_fence_before();
@@ -260,7 +337,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
 
 int32_t ugb_prefill_attention_tc(ugb_device *dev, const __nv_bfloat16 *q, const __nv_bfloat16 *kcache,
                                  const __nv_bfloat16 *vcache, __nv_bfloat16 *out, int batch, int t, int pos0,
-                                 int n_heads, int n_kv, int t_max, float scale) {
+                                 int n_heads, int n_kv, int t_max, float scale, int dynamic) {
   if (batch == 0 || t == 0) return UGB_OK;
   static bool attr_set[64] = {};
   if (!attr_set[dev->ordinal & 63]) {
@@ -283,8 +360,12 @@ int32_t ugb_prefill_attention_tc(ugb_device *dev, const __nv_bfloat16 *q, const 
     if ((rc = ugb_tc_encode_bf16(dev, &tmV, vcache, 3, dims, strides, box))) return rc;
   }
   Params p;
-  p.t = t; p.pos0 = pos0; p.n_heads = n_heads; p.n_kv = n_kv; p.scale = scale; p.out = out; p.status = dev->status_dev;
-  dim3 grid((unsigned)((t + BQ - 1) / BQ), (unsigned)n_heads, (unsigned)batch);
+  p.t = t; p.pos0 = pos0; p.n_heads = n_heads; p.n_kv = n_kv; p.batch = batch; p.scale = scale; p.out = out;
+  p.status = dev->status_dev;
+  p.sched = dynamic ? dev->sched_dev : nullptr;
+  const long long n_items = (long long)((t + BQ - 1) / BQ) * n_heads * batch;
+  const long long slots = 2LL * dev->sm_count;                     // two CTAs per SM
+  dim3 grid((unsigned)(n_items < slots ? n_items : slots));
   prefill_attention_tc_kernel<<<grid, THREADS, SMEM_BYTES, dev->stream>>>(tmQ, tmK, tmV, p);
   return ugb_after_launch(dev, "prefill_attention_tc_kernel");
 }

@@ -85,7 +85,8 @@ struct ugb_llama {
   bool early_ok = false;          // ... and it is, for the current shapes and options (set by enqueue_step)
   int att_tma = 0;                // option att_tma: decode attention fetches K / V by TMA (1) or cp.async (0)
   std::vector<CUtensorMap> att_kmap, att_vmap;   // per layer, for the TMA variant
-  int pf_att_tc = 1;              // option prefill_attention_tc: 1 = tcgen05 / TMEM attention kernel, 0 = mma.sync one
+  int pf_att_tc = 1;              // option prefill_attention_tc: 1 = tcgen05 / TMEM attention kernel drawing its
+                                  // work items from a counter, 2 = the same dealt round-robin, 0 = mma.sync kernel
   int pf_rows_max = 8192;         // option prefill_rows: upper bound on rows per chunk
   int pf_rows = 0, pf_chunk = 0;
   float *pf_x = nullptr, *pf_f32 = nullptr;            // residual stream; f32 GEMM output (qkv, o, down)
@@ -404,7 +405,7 @@ int32_t enqueue_prefill_chunk(ugb_llama *m, const int *tok, int t, int c0, int t
     }
     if (m->pf_att_tc) {
       if ((rc = ugb_prefill_attention_tc(dev, m->pf_q, kc, vc, m->pf_att, B, tc, m->host_pos + c0, c.n_heads, c.n_kv_heads,
-                                         m->t_max, scale))) return rc;
+                                         m->t_max, scale, m->pf_att_tc == 1))) return rc;
     } else {
       prefill_attention_kernel<<<dim3((tc + PF_BQ - 1) / PF_BQ, c.n_heads, B), 128, 0, st>>>(
           m->pf_q, kc, vc, m->pf_att, tc, m->host_pos + c0, c.n_heads, c.n_kv_heads, m->t_max, scale);
@@ -687,7 +688,8 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
     return UGB_OK;
   }
   if (k == "prefill_attention_tc") {
-    m->pf_att_tc = value != 0;
+    UGB_REQUIRE(dev, value >= 0 && value <= 2, UGB_ERR_INVALID, "option prefill_attention_tc: %d outside 0..2", value);
+    m->pf_att_tc = value;
     return UGB_OK;
   }
   if (k == "prefill_rows") {

@@ -20,6 +20,7 @@ struct ugb_device {
   cudaStream_t stream = nullptr;
   cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
   ugb_status_word *status_dev = nullptr;  // device memory
+  int *sched_dev = nullptr;               // device memory: two work counters that persistent kernels leave at zero
   uint64_t launches = 0;
   int sm_count = 148;
   size_t smem_optin = 0;
