@@ -738,7 +738,8 @@ def main():
         # per-kernel share of one step, each kernel type timed alone over all layers (CUDA events); no exchange inside
         for name in wl.model.KERNELS:
             kern[name] = round(wl.model.time_kernel(name, 20), 4)
-        att_bytes = wl.kv_bytes_per_pos * wl.model.position * wl.batch
+        kdepth = wl.model.position                      # cache depth the kernels were timed at
+        att_bytes = wl.kv_bytes_per_pos * kdepth * wl.batch
     barrier()
     # under tensor parallelism every engine call is collective: all ranks run the parity check
     parity = wl.check() if (rank == 0 or tp) else None
@@ -758,8 +759,8 @@ def main():
                                        "at the mean cache depth %.0f" % (wl.launches_per_step, depth))
             extra["decode_attention_roofline"] = {
                 # 141.2 MB of DRAM traffic per launch at 2049 cached positions (profiles/decode_attention_ncu.md),
-                # scaled by the cached positions of this run: the traffic grows in proportion to them
-                "traffic": int(141_193_472 * wl.model.position / 2049 * wl.batch / 64) if not tp else None,
+                # scaled to the depth the kernel was timed at: the traffic grows in proportion to the cached positions
+                "traffic": int(141_193_472 * kdepth / 2049 * wl.batch / 64) if not tp else None,
                 "achieved": round(att_bytes / (kern["decode_attention"] / 1e3) / 1e9, 1), "peak": peaks["hbm"],
                 "unit": "GB/s", "frac": round(att_bytes / (kern["decode_attention"] / 1e3) / 1e9 / peaks["hbm"], 4)}
         else:
