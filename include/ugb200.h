@@ -333,6 +333,22 @@ UGB_API int32_t ugb_decode_attention_noalloc(ugb_device *dev, const ugb_slice *q
                                              size_t n_heads, size_t n_kv, size_t t_max,
                                              int32_t n_slices);
 
+/* Causal grouped-query attention for a block of t NEW positions per sequence:
+ * the fused form of Attention::fwd with seq_len > 1 (ug-llama/src/model.rs:231-245:
+ * repeat + q.kT + scale (head_dim^-0.5) + causal mask + softmax + .v +
+ * transpose/merge) over a preallocated bf16 KV cache, without the
+ * [b, h, t, pos0 + t] score tensor.  q bf16 [b, t, n_heads, 64] (rotation
+ * applied); k, v bf16 [b, n_kv, t_max, 64] already holding the keys / values of
+ * positions 0 .. pos0 + t - 1 (the block's own included); query i of the block
+ * attends positions 0 .. pos0 + i; out bf16 [b, t, n_heads * 64].  head_dim is
+ * 64, n_heads a multiple of n_kv, pos0 + t <= t_max, all buffers 16-byte
+ * aligned.  Cache rows between pos0 + t and the next multiple of 64 must hold
+ * finite values (they are loaded with their 64-key tile and weighted by zero).
+ * Runs on the tcgen05 / TMEM kernel; allocates nothing. */
+UGB_API int32_t ugb_causal_attention(ugb_device *dev, const ugb_slice *q, const ugb_slice *k,
+                                     const ugb_slice *v, ugb_slice *out, size_t b, size_t t,
+                                     size_t pos0, size_t n_heads, size_t n_kv, size_t t_max);
+
 /* ------------------------------------------- ug-llama Model::fwd (decode step) */
 /* The reference builds one lazy graph per token from Model::fwd
  * (ug-llama/src/model.rs:298-374) and runs ~27 launches per layer; this entry

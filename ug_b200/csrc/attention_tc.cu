@@ -369,3 +369,27 @@ int32_t ugb_prefill_attention_tc(ugb_device *dev, const __nv_bfloat16 *q, const 
   prefill_attention_tc_kernel<<<grid, THREADS, SMEM_BYTES, dev->stream>>>(tmQ, tmK, tmV, p);
   return ugb_after_launch(dev, "prefill_attention_tc_kernel");
 }
+
+extern "C" int32_t ugb_causal_attention(ugb_device *dev, const ugb_slice *q, const ugb_slice *k, const ugb_slice *v,
+                                        ugb_slice *out, size_t b, size_t t, size_t pos0, size_t n_heads,
+                                        size_t n_kv, size_t t_max) {
+  if (!dev) return UGB_ERR_INVALID;
+  UGB_REQUIRE(dev, n_kv > 0 && n_heads > 0 && n_heads % n_kv == 0, UGB_ERR_UNSUPPORTED,
+              "causal_attention: %zu query heads do not divide over %zu KV heads", n_heads, n_kv);
+  UGB_REQUIRE(dev, pos0 + t <= t_max, UGB_ERR_SHAPE, "causal_attention: positions %zu..%zu exceed the cache depth %zu",
+              pos0, pos0 + t, t_max);
+  UGB_REQUIRE(dev, b <= 65535 && n_heads <= 65535 && t_max <= (1u << 30) && b * n_kv <= (1u << 30) &&
+                       ((t + BQ - 1) / BQ) * n_heads * b <= (size_t)INT32_MAX,
+              UGB_ERR_SHAPE, "causal_attention: a dimension exceeds the kernel's index range");
+  UGB_SLICE(dev, q, UGB_BF16, b * t * n_heads * HD);
+  UGB_SLICE(dev, k, UGB_BF16, b * n_kv * t_max * HD);
+  UGB_SLICE(dev, v, UGB_BF16, b * n_kv * t_max * HD);
+  UGB_SLICE(dev, out, UGB_BF16, b * t * n_heads * HD);
+  if (b == 0 || t == 0) return UGB_OK;
+  UGB_REQUIRE(dev, (((uintptr_t)q->ptr | (uintptr_t)k->ptr | (uintptr_t)v->ptr | (uintptr_t)out->ptr) & 15) == 0,
+              UGB_ERR_UNSUPPORTED, "causal_attention: buffers must be 16-byte aligned");
+  UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
+  return ugb_prefill_attention_tc(dev, (const __nv_bfloat16 *)q->ptr, (const __nv_bfloat16 *)k->ptr,
+                                  (const __nv_bfloat16 *)v->ptr, (__nv_bfloat16 *)out->ptr, (int)b, (int)t, (int)pos0,
+                                  (int)n_heads, (int)n_kv, (int)t_max, 0.125f /* 64^-0.5, model.rs:236 */, 1);
+}

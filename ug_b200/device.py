@@ -263,6 +263,11 @@ class Device:
     def index_select(self, emb, ids, dst, n_ids, h, vocab):
         self._check(lib.ugb_index_select(self._h, emb._h, ids._h, dst._h, n_ids, h, vocab))
 
+    def causal_attention(self, q, k, v, out, b, t, pos0, n_heads, n_kv, t_max):
+        """Fused causal grouped-query attention for a block of t new positions per sequence over the
+        cache (Attention::fwd with seq_len > 1, model.rs:231-245)."""
+        self._check(lib.ugb_causal_attention(self._h, q._h, k._h, v._h, out._h, b, t, pos0, n_heads, n_kv, t_max))
+
     def decode_attention(self, q, k, v, pos, out, b, n_heads, n_kv, t_max, n_slices=2):
         """Fused grouped-query attention for one new position per sequence (model.rs:231-245)."""
         self._check(lib.ugb_decode_attention(self._h, q._h, k._h, v._h, pos._h, out._h, b, n_heads, n_kv,
