@@ -651,6 +651,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--prefill", type=int, default=None, help="decode: cached positions before timing")
+    ap.add_argument("--device-option", action="append", default=[], metavar="NAME=INT",
+                    help="device tuning switch set before the run (ugb_device_set_option), e.g. gemm_cta_pairs=1")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=INT",
                     help="prefill: engine option set before the run (profiling of kernel variants)")
     ap.add_argument("--layers", type=int, default=None, help="decode: layer count (profiling of small cases)")
@@ -688,6 +690,9 @@ def main():
 
     import ug_b200
     dev = ug_b200.Device(local_rank)
+    for o in args.device_option:
+        name, value = o.split("=")
+        dev.set_option(name, int(value))
     wl = make_workload(rank)
     e2e_steps = max(3, min(args.steps, 10 if args.workload != "decode" else 32))
     if args.workload == "decode":

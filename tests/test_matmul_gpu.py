@@ -167,3 +167,40 @@ def test_bf16_config3_full_size_sampled_rows_and_linearity(dev):
     col_ref = (a.reshape(-1, k).astype(np.float64).sum(0)) @ b.astype(np.float64)
     col_got = got.astype(np.float64).sum(0)
     assert np.max(np.abs(col_got - col_ref)) < 5e-3 * np.abs(col_ref).max() + 0.5
+
+
+# ---- CTA pairs (tcgen05 cta_group::2): 256 x 256 tiles on two SMs ---------------------------------------------
+PAIR_SHAPES = [
+    (1, 256, 256, 64, True), (1, 256, 256, 64, False),        # one tile, one k block
+    (1, 256, 256, 1024, True), (1, 256, 256, 1024, False),    # the 6-stage ring wraps (16 k blocks)
+    (1, 200, 264, 200, True), (1, 200, 264, 200, False),      # ragged m (second CTA partly empty), n, k tails
+    (1, 129, 128, 72, True),                                  # one row in the second CTA, half an n tile
+    (3, 160, 320, 136, True), (3, 160, 320, 136, False),      # per-batch rhs
+    (1, 4096, 2048, 512, True), (1, 2048, 4096, 256, False),  # more tiles than clusters (persistent loop), both tile orders
+]
+
+
+@pytest.mark.parametrize("bs,m,n,k,t", PAIR_SHAPES)
+def test_bf16_matmul_on_cta_pairs_matches_single_ctas(dev, bs, m, n, k, t):
+    """The pair kernel accumulates every output element over k in the same order as the single-CTA kernel: the
+    results agree bit for bit, and with the oracle within the bf16 tolerance."""
+    a = oracle.round_bf16(synth.normal(940 + m, (bs, m, k), 0.5))
+    b = oracle.round_bf16(synth.normal(941 + n, (bs, n, k) if t else (bs, k, n), 0.5))
+    dev.set_option("gemm_cta_pairs", 0)
+    single = gpu_matmul(dev, a, b, t, DType.BF16)
+    try:
+        dev.set_option("gemm_cta_pairs", 1)
+        pair = gpu_matmul(dev, a, b, t, DType.BF16)
+    finally:
+        dev.set_option("gemm_cta_pairs", 0)
+    ref = oracle.matmul(a, b, transpose_rhs=t)
+    err = np.abs(pair - ref) / np.maximum(np.abs(ref), 0.05 * np.abs(ref).max())
+    assert err.max() < 2e-2
+    assert np.array_equal(pair, single)
+
+
+def test_device_option_errors(dev):
+    with pytest.raises(UgError):
+        dev.set_option("gemm_cta_pairs", 2)
+    with pytest.raises(UgError):
+        dev.set_option("no_such_option", 1)

@@ -121,6 +121,16 @@ int32_t ugb_device_ordinal(const ugb_device *dev) { return dev ? dev->ordinal : 
 void *ugb_device_stream(const ugb_device *dev) { return dev ? (void *)dev->stream : nullptr; }
 uint64_t ugb_launch_count(const ugb_device *dev) { return dev ? dev->launches : 0; }
 
+int32_t ugb_device_set_option(ugb_device *dev, const char *name, int32_t value) {
+  if (!dev || !name) return UGB_ERR_INVALID;
+  if (strcmp(name, "gemm_cta_pairs") == 0) {
+    UGB_REQUIRE(dev, value == 0 || value == 1, UGB_ERR_INVALID, "option gemm_cta_pairs: %d is not 0 or 1", value);
+    dev->gemm_pair = value;
+    return UGB_OK;
+  }
+  return ugb_fail(dev, UGB_ERR_INVALID, "unknown device option %s", name);
+}
+
 int32_t ugb_alloc(ugb_device *dev, int32_t dtype, size_t len, ugb_slice **out) {
   if (!dev) return UGB_ERR_INVALID;
   UGB_REQUIRE(dev, out != nullptr, UGB_ERR_INVALID, "ugb_alloc: null out pointer");

@@ -39,9 +39,13 @@ constexpr int THREADS = 192;
 // SM; the 64 accumulator rows then sit on 16 lanes of each TMEM lane quadrant).
 // BN = 256 for compute-bound products, 64 / 128 for weight streaming.  The ring
 // takes as many stages as fit in 220 KiB (at most 12).
-template <int BM, int BN> struct Cfg {
+// PAIR: two CTAs of a cluster work on one 256 x BN tile (tcgen05 cta_group::2): each stages its own 128
+// rows of A and its own half of B's n range, so a CTA's ring stage is BM x 64 of A plus BN/2 x 64 of B.
+template <int BM, int BN, bool PAIR = false> struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int BN_CTA = PAIR ? BN / 2 : BN;           // B rows (n) this CTA stages
+  static constexpr int B_BYTES = BN_CTA * BK * 2;
+  static constexpr int TILE_M = PAIR ? 2 * BM : BM;           // rows of C per tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int FIT = (220 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = FIT > 12 ? 12 : FIT;
@@ -71,13 +75,21 @@ struct Params {
 
 using namespace ugb_tc;
 
-template <int BM, int BN>
+template <int BM, int BN, bool PAIR = false>
 __global__ void __launch_bounds__(THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+  using C_ = Cfg<BM, BN, PAIR>;
   const int STAGES = p.stages;
-  constexpr int STAGE_BYTES = Cfg<BM, BN>::STAGE_BYTES;
-  constexpr int A_BYTES = Cfg<BM, BN>::A_BYTES;
-  constexpr int TMEM_COLS = Cfg<BM, BN>::TMEM_COLS;
+  constexpr int STAGE_BYTES = C_::STAGE_BYTES;
+  constexpr int A_BYTES = C_::A_BYTES;
+  constexpr int TMEM_COLS = C_::TMEM_COLS;
+  constexpr int TILE_M = C_::TILE_M;
+  constexpr int BN_CTA = C_::BN_CTA;
+  // PAIR: CTAs 2c and 2c + 1 form cluster c; rank 0 (the leader) owns the full / accumulator-empty barriers
+  // and issues the MMAs, each CTA loads and stores its own rows.  Tiles are dealt to clusters.
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int cta0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int n_ctas = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128-byte swizzle pattern repeats every 1024 bytes
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -91,13 +103,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int tiles_per_split = tiles_per_batch * p.batch;
   const int n_tiles = tiles_per_split * p.splits;
+  // `bar`: this CTA's barrier, or for PAIR the leader's (a shared::cluster address)
+  auto load3 = [&](uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y, int z) {
+    if constexpr (PAIR) tma_load_3d_pair(dst, map, bar, x, y, z);
+    else tma_load_3d(dst, map, bar, x, y, z);
+  };
   auto issue_b = [&](uint32_t b_dst, uint32_t bar, int kb, int n0, int bz) {
+    n0 += (int)rank * BN_CTA;                                     // PAIR: this CTA's half of the n range
     if (p.b_is_nk) {
-      tma_load_3d(b_dst, &tmB, bar, kb * BK, n0, bz);            // box {64 k, BN n}
+      load3(b_dst, &tmB, bar, kb * BK, n0, bz);                   // box {64 k, BN_CTA n}
     } else {
 #pragma unroll
-      for (int c = 0; c < BN / 64; ++c)                           // BN/64 boxes {64 n, 64 k}
-        tma_load_3d(b_dst + c * (64 * BK * 2), &tmB, bar, n0 + c * 64, kb * BK, bz);
+      for (int c = 0; c < BN_CTA / 64; ++c)                       // boxes {64 n, 64 k}
+        load3(b_dst + c * (64 * BK * 2), &tmB, bar, n0 + c * 64, kb * BK, bz);
     }
   };
   if (threadIdx.x == 0) {
@@ -107,7 +125,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int s = 0; s < ACC_STAGES; ++s) {
       mbar_init(smem_u32(&acc_full[s]), 1);
-      mbar_init(smem_u32(&acc_empty[s]), 4);  // one arrival per epilogue warp
+      mbar_init(smem_u32(&acc_empty[s]), PAIR ? 8 : 4);  // one arrival per epilogue warp (of both CTAs)
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -116,7 +134,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // Preamble: the B operand of the first tile (weights in the decode step) is written by no kernel of
     // the stream, so its first stages are requested right here -- before the TMEM allocation, the CTA
     // barrier and the wait for the preceding kernel; A follows once that kernel is done.
-    if (p.b_static) {
+    if (!PAIR && p.b_static) {
       const int tile = blockIdx.x;
       const int sp = tile / tiles_per_split;
       const int ts = tile - sp * tiles_per_split;
@@ -135,12 +153,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {   // collective: one warp of each CTA of the pair
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();    // both CTAs' barriers exist before either signals the other's
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) ugb_pdl_trigger();   // the next kernel on the stream may begin its preamble
@@ -154,36 +179,39 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       // The B halves of the first `pre` stages were requested in the preamble above.
       int pre = 0;
       {
-        const int tile = blockIdx.x;
+        const int tile = cta0;
         const int sp = tile / tiles_per_split;
         const int ts = tile - sp * tiles_per_split;
         const int bi = ts / tiles_per_batch;
         const int r = ts - bi * tiles_per_batch;
-        const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * BM;
+        const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * TILE_M;
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
-        pre = p.b_static ? min(STAGES, kb1 - kb0) : 0;
+        pre = (!PAIR && p.b_static) ? min(STAGES, kb1 - kb0) : 0;
         ugb_pdl_wait();
         for (int i = 0; i < pre; ++i)
           tma_load_3d(smem_u32(smem + i * STAGE_BYTES), &tmA, smem_u32(&full[i]), (kb0 + i) * BK, m0, bi);
         stage = pre % STAGES;
         phase = pre == STAGES ? 1u : 0u;
       }
-      for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+      for (int tile = cta0; tile < n_tiles && alive; tile += n_ctas) {
         const int sp = tile / tiles_per_split;
         const int ts = tile - sp * tiles_per_split;
         const int bi = ts / tiles_per_batch;
         const int r = ts - bi * tiles_per_batch;
-        const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * BM, n0 = (p.n_fast ? r % p.tiles_n : r / p.tiles_m) * BN;
+        const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * TILE_M + (int)rank * BM;
+        const int n0 = (p.n_fast ? r % p.tiles_n : r / p.tiles_m) * BN;
         const int bz = p.b_batched ? bi : 0;
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
-        for (int kb = kb0 + (tile == (int)blockIdx.x ? pre : 0); kb < kb1; ++kb) {
+        for (int kb = kb0 + (tile == cta0 ? pre : 0); kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&empty[stage]), phase ^ 1u, abort_flag, p.status, 1)) { alive = false; break; }
-          const uint32_t bar = smem_u32(&full[stage]);
-          mbar_expect_tx(bar, (uint32_t)p.stage_tx);
+          // PAIR: the leader's barrier counts the bytes of both CTAs' loads (stage_tx is their sum); the leader
+          // alone posts the expectation -- bytes of the other CTA that land first are held against it
+          const uint32_t bar = PAIR ? mapa_u32(smem_u32(&full[stage]), 0) : smem_u32(&full[stage]);
+          if (rank == 0) mbar_expect_tx(smem_u32(&full[stage]), (uint32_t)p.stage_tx);
           const uint32_t a_dst = smem_u32(smem + stage * STAGE_BYTES);
-          tma_load_3d(a_dst, &tmA, bar, kb * BK, m0, bi);
+          load3(a_dst, &tmA, bar, kb * BK, m0, bi);
           issue_b(a_dst + A_BYTES, bar, kb, n0, bz);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -191,18 +219,26 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // -------------------------------------------------------- MMA issuer --
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc(BM, BN, !p.b_is_nk);
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc(TILE_M, BN, !p.b_is_nk);
+      auto mma = [&](uint32_t d, uint64_t a_desc, uint64_t b_desc, uint32_t acc_in) {
+        if constexpr (PAIR) umma_bf16_pair(d, a_desc, b_desc, idesc, acc_in);
+        else umma_bf16(d, a_desc, b_desc, idesc, acc_in);
+      };
+      auto commit = [&](uint32_t bar) {           // PAIR: the barrier at this offset in both CTAs
+        if constexpr (PAIR) umma_commit_pair(bar);
+        else umma_commit(bar);
+      };
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+      for (int tile = cta0; tile < n_tiles && alive; tile += n_ctas) {
         const int sp = tile / tiles_per_split;
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1u, abort_flag, p.status, 2)) break;
         tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * Cfg<BM, BN>::ACC_STRIDE);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * C_::ACC_STRIDE);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&full[stage]), phase, abort_flag, p.status, 3)) { alive = false; break; }
           tcgen05_fence_after();
@@ -217,13 +253,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // apart (SBO); a k step of 16 moves 16 rows of 128 B.
             const uint64_t b_desc = p.b_is_nk ? make_smem_desc(b_addr + j * (UMMA_K * 2), 0, 1024)
                                               : make_smem_desc(b_addr + j * (UMMA_K * 128), 64 * BK * 2, 1024);
-            umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+            mma(d_tmem, a_desc, b_desc, (kb > kb0 || j > 0) ? 1u : 0u);
           }
-          umma_commit(smem_u32(&empty[stage]));      // frees the smem stage when the MMAs retire
+          commit(smem_u32(&empty[stage]));           // frees the smem stage when the MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!alive) break;
-        umma_commit(smem_u32(&acc_full[acc]));       // accumulator complete
+        commit(smem_u32(&acc_full[acc]));            // accumulator complete
         if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
       }
     }
@@ -232,12 +268,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int quad = warp & 3;                        // TMEM lane quadrant of this warp
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    auto release_acc = [&](int a) {                   // this warp is done with accumulator stage a
+      if constexpr (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[a]), 0));
+      else mbar_arrive(smem_u32(&acc_empty[a]));
+    };
+    for (int tile = cta0; tile < n_tiles; tile += n_ctas) {
       const int sp = tile / tiles_per_split;
       const int ts = tile - sp * tiles_per_split;
       const int bi = ts / tiles_per_batch;
       const int r = ts - bi * tiles_per_batch;
-      const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * BM, n0 = (p.n_fast ? r % p.tiles_n : r / p.tiles_m) * BN;
+      const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * TILE_M + (int)rank * BM;
+      const int n0 = (p.n_fast ? r % p.tiles_n : r / p.tiles_m) * BN;
       if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, abort_flag, p.status, 4)) break;
       tcgen05_fence_after();
       // BM = 128: accumulator row = TMEM lane.  BM = 64: rows 16q..16q+15 sit on lanes 0..15 of quadrant q.
@@ -259,8 +300,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int head = (n0 >> 6) + hc;                  // warp-uniform
             if (head * 64 >= p.N) break;
             uint32_t v0[32], v1[32];
-            tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * Cfg<BM, BN>::ACC_STRIDE + hc * 64), v0);
-            tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * Cfg<BM, BN>::ACC_STRIDE + hc * 64 + 32), v1);
+            tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C_::ACC_STRIDE + hc * 64), v0);
+            tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C_::ACC_STRIDE + hc * 64 + 32), v1);
             tmem_ld_wait();
             if (!live) continue;
             __nv_bfloat16 *dst;
@@ -315,7 +356,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           tcgen05_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+          if (lane == 0) release_acc(acc);
           if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
           continue;
         }
@@ -323,7 +364,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll 1
       for (int c = 0; c < (BN + 31) / 32; ++c) {      // a tile width that is not a multiple of 32 ends in a partly used chunk
         uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * Cfg<BM, BN>::ACC_STRIDE + c * 32), v);
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C_::ACC_STRIDE + c * 32), v);
         tmem_ld_wait();
         if (row_lane && row < p.M) {
           const int col0 = n0 + c * 32;
@@ -371,7 +412,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+      if (lane == 0) release_acc(acc);
       if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
     }
   }
@@ -385,9 +426,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
   tcgen05_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // neither CTA's shared memory, barriers or TMEM go away under the other
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if constexpr (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -399,7 +444,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 
 struct TcState {
   EncodeTiledFn encode = nullptr;
-  bool attr_set[8] = {false, false, false, false, false, false, false, false};
+  bool attr_set[9] = {false, false, false, false, false, false, false, false, false};
 };
 
 TcState *state_of(ugb_device *dev) {
@@ -433,19 +478,20 @@ int32_t encode_map(ugb_device *dev, TcState *st, CUtensorMap *map, const void *b
   return UGB_OK;
 }
 
-template <int BM, int BN>
+template <int BM, int BN, bool PAIR = false>
 int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_t batch, size_t m) {
+  using C_ = Cfg<BM, BN, PAIR>;
   const size_t n = g.n, k = g.k;
-  constexpr int slot = BN == 80 ? 6 : BN == 96 ? 7 : (BN == 256 ? 2 : (BN == 128 ? 1 : 0)) + (BM == 64 ? 3 : 0);
+  constexpr int slot = PAIR ? 8 : BN == 80 ? 6 : BN == 96 ? 7 : (BN == 256 ? 2 : (BN == 128 ? 1 : 0)) + (BM == 64 ? 3 : 0);
   if (!st->attr_set[slot]) {
-    UGB_CUDA(dev, cudaFuncSetAttribute(tc_gemm_kernel<BM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       Cfg<BM, BN>::SMEM_BYTES));
+    UGB_CUDA(dev, cudaFuncSetAttribute(tc_gemm_kernel<BM, BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       C_::SMEM_BYTES));
 
     st->attr_set[slot] = true;
   }
   Params p;
   p.M = (int)m; p.N = (int)n; p.K = (int)k; p.batch = (int)batch;
-  p.tiles_m = (int)((m + BM - 1) / BM);
+  p.tiles_m = (int)((m + C_::TILE_M - 1) / C_::TILE_M);
   p.tiles_n = (int)((n + BN - 1) / BN);
   p.k_blocks = (int)((k + BK - 1) / BK);
   int splits = g.splits < 1 ? 1 : g.splits;
@@ -467,28 +513,29 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   p.rope = g.rope;
 
   CUtensorMap tmA, tmB;
-  p.stage_tx = Cfg<BM, BN>::STAGE_BYTES;
+  p.stage_tx = C_::STAGE_BYTES * (PAIR ? 2 : 1);      // PAIR: one barrier counts both CTAs' stage
   int32_t rc = encode_map(dev, st, &tmA, g.a, k, m, batch, k, batch > 1 ? (uint64_t)g.a_batch : m * k, BK, BM);
   if (rc) return rc;
   const uint64_t nb = p.b_batched ? batch : 1;
   const uint64_t bs = p.b_batched ? (uint64_t)g.b_batch : n * k;
-  if (g.b_is_nk) rc = encode_map(dev, st, &tmB, g.b, k, n, nb, k, bs, BK, BN);
+  if (g.b_is_nk) rc = encode_map(dev, st, &tmB, g.b, k, n, nb, k, bs, BK, C_::BN_CTA);
   else rc = encode_map(dev, st, &tmB, g.b, n, k, nb, n, bs, 64, BK);
   if (rc) return rc;
 
   const long long n_tiles = (long long)p.tiles_m * p.tiles_n * p.batch * p.splits;
-  const unsigned grid = (unsigned)(n_tiles < dev->sm_count ? n_tiles : dev->sm_count);
+  const long long slots = PAIR ? dev->sm_count / 2 : dev->sm_count;      // PAIR: one tile per cluster of two SMs
+  const unsigned grid = (unsigned)(n_tiles < slots ? n_tiles : slots) * (PAIR ? 2u : 1u);
   // A shallower ring (smem_kib) leaves room for a second CTA per SM: with programmatic dependent launch
   // the next kernel's CTAs then become resident, and fetch their weights, while this kernel still runs.
-  int stages = Cfg<BM, BN>::STAGES;
+  int stages = C_::STAGES;
   if (g.smem_kib > 0) {
-    const int fit = (g.smem_kib * 1024 - 1536) / Cfg<BM, BN>::STAGE_BYTES;
+    const int fit = (g.smem_kib * 1024 - 1536) / C_::STAGE_BYTES;
     stages = fit < 2 ? 2 : (fit > stages ? stages : fit);
   }
   p.stages = stages;
-  const size_t smem = (size_t)stages * Cfg<BM, BN>::STAGE_BYTES + 1536;
-  cudaError_t le = ugb_launch(tc_gemm_kernel<BM, BN>, dim3(grid), dim3(THREADS), smem, dev->stream,
-                              g.pdl, tmA, tmB, p);
+  const size_t smem = (size_t)stages * C_::STAGE_BYTES + 1536;
+  cudaError_t le = ugb_launch_cluster(tc_gemm_kernel<BM, BN, PAIR>, dim3(grid), dim3(THREADS), smem, dev->stream,
+                                      g.pdl, PAIR ? 2 : 1, tmA, tmB, p);
   if (le != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of tc_gemm_kernel failed: %s", cudaGetErrorString(le));
   return ugb_after_launch(dev, "tc_gemm_kernel");
 }
@@ -551,6 +598,9 @@ int32_t ugb_tc_gemm(ugb_device *dev, const ugb_tc_gemm_args &g) {
     return launch_tc<64, 256>(dev, st, g, batch, m);
   }
   if (bn == 80 || bn == 96) bn = 128;                                  // BM = 128 needs n % 16 == 0 tiles: keep the three sizes
+  // CTA pairs: 256 x 256 tiles over two SMs; every SM fetches half as much of B per flop
+  const bool pair = g.pair < 0 ? dev->gemm_pair != 0 : g.pair != 0;
+  if (pair && bn == 256 && m > 128 && g.splits <= 1 && dev->sm_count >= 2) return launch_tc<128, 256, true>(dev, st, g, batch, m);
   if (bn == 64) return launch_tc<128, 64>(dev, st, g, batch, m);
   if (bn == 128) return launch_tc<128, 128>(dev, st, g, batch, m);
   return launch_tc<128, 256>(dev, st, g, batch, m);

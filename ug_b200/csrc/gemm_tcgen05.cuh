@@ -38,6 +38,7 @@ struct ugb_tc_gemm_args {
   bool b_static;        // no kernel on the stream writes b (weights): fetch it before waiting for the predecessor
   bool pdl;             // launch with programmatic stream serialization (see ugb_launch)
   int smem_kib = 0;     // cap on the shared memory of a CTA (ring depth follows); 0 = as deep as fits in 220 KiB
+  int pair = -1;        // 256 x 256 tiles on pairs of CTAs (cta_group::2) where the shape allows: 1 / 0, -1 = the device's setting
   ugb_tc_rope_epilogue rope = {};   // UGB_EPI_ROPE_QKV only
 };
 

@@ -26,6 +26,7 @@ struct ugb_device {
   size_t smem_optin = 0;
   std::string last_error;
   void *gemm_state = nullptr;  // owned by the GEMM translation unit
+  int gemm_pair = 0;           // option gemm_cta_pairs: tall bf16 GEMMs on pairs of CTAs (tcgen05 cta_group::2)
 };
 
 struct ugb_slice {
@@ -124,6 +125,33 @@ inline cudaError_t ugb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+// The same with thread-block clusters of `cluster` consecutive CTAs (1 = none); grid.x a multiple of it.
+template <typename... KArgs, typename... Args>
+inline cudaError_t ugb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                      bool pdl, int cluster, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = (unsigned)cluster;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 #endif

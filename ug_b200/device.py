@@ -263,6 +263,10 @@ class Device:
     def index_select(self, emb, ids, dst, n_ids, h, vocab):
         self._check(lib.ugb_index_select(self._h, emb._h, ids._h, dst._h, n_ids, h, vocab))
 
+    def set_option(self, name, value):
+        """Tuning switch of the device handle (ugb_device_set_option), e.g. gemm_cta_pairs = 0 / 1."""
+        self._check(lib.ugb_device_set_option(self._h, name.encode(), int(value)))
+
     def causal_attention(self, q, k, v, out, b, t, pos0, n_heads, n_kv, t_max):
         """Fused causal grouped-query attention for a block of t new positions per sequence over the
         cache (Attention::fwd with seq_len > 1, model.rs:231-245)."""
