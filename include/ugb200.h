@@ -78,10 +78,10 @@ UGB_API void *ugb_device_stream(const ugb_device *dev);
 /* Number of kernels this library has launched on `dev` since creation. */
 UGB_API uint64_t ugb_launch_count(const ugb_device *dev);
 /* Tuning switches of a device handle (no counterpart in the reference).
- *   "gemm_cta_pairs"  0 / 1: bf16 GEMMs with more than 128 rows run 256 x 256
- *                     tiles on pairs of CTAs (tcgen05 cta_group::2, a cluster of
- *                     two SMs sharing the B operand) instead of 128 x 256 tiles
- *                     on single CTAs.  Same results bit for bit.
+ *   "gemm_cta_pairs"  1 (default) / 0: bf16 GEMMs with more than 128 rows run
+ *                     256 x 256 tiles on pairs of CTAs (tcgen05 cta_group::2, a
+ *                     cluster of two SMs sharing the B operand) instead of
+ *                     128 x 256 tiles on single CTAs.  Same results bit for bit.
  * Unknown names and out-of-range values are UGB_ERR_INVALID. */
 UGB_API int32_t ugb_device_set_option(ugb_device *dev, const char *name, int32_t value);
 

@@ -192,7 +192,7 @@ def test_bf16_matmul_on_cta_pairs_matches_single_ctas(dev, bs, m, n, k, t):
         dev.set_option("gemm_cta_pairs", 1)
         pair = gpu_matmul(dev, a, b, t, DType.BF16)
     finally:
-        dev.set_option("gemm_cta_pairs", 0)
+        dev.set_option("gemm_cta_pairs", 1)      # the default
     ref = oracle.matmul(a, b, transpose_rhs=t)
     err = np.abs(pair - ref) / np.maximum(np.abs(ref), 0.05 * np.abs(ref).max())
     assert err.max() < 2e-2

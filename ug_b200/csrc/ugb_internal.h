@@ -26,7 +26,7 @@ struct ugb_device {
   size_t smem_optin = 0;
   std::string last_error;
   void *gemm_state = nullptr;  // owned by the GEMM translation unit
-  int gemm_pair = 0;           // option gemm_cta_pairs: tall bf16 GEMMs on pairs of CTAs (tcgen05 cta_group::2)
+  int gemm_pair = 1;           // option gemm_cta_pairs: tall bf16 GEMMs on pairs of CTAs (tcgen05 cta_group::2)
 };
 
 struct ugb_slice {
