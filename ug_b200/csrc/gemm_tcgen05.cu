@@ -15,7 +15,12 @@
 // CTA tile 128 x 256, k slices of 64 bf16 (= one 128-byte swizzle row), a
 // 4-stage shared-memory ring (48 KiB per stage) and two 256-column TMEM
 // accumulators so that the epilogue of tile i overlaps the main loop of tile
-// i+1.  No cluster launch and no multicast: every CTA fetches its own tiles.
+// i+1.  Products with more than 128 rows run on pairs of CTAs (template flag
+// PAIR, a cluster of two): one 256 x 256 tile per pair with
+// tcgen05.mma.cta_group::2 issued by the even CTA; each CTA stages its own 128
+// rows of A and its own half of B's n range (32 KiB per stage, 6 stages) and
+// drains its own 128 accumulator rows.  No multicast loads: every CTA fetches
+// its own tiles.
 //
 // Every mbarrier wait is bounded by wall-clock time; a wait that gives up
 // raises the device status word (UGB_ERR_TIMEOUT), flags the CTA as aborted so
