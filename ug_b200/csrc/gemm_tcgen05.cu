@@ -181,7 +181,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      // The B halves of the first `pre` stages were requested in the preamble above.
+      // The B halves of the first `pre` stages were requested in the preamble above; on CTA pairs they are
+      // requested here, now that the cluster barrier has made both CTAs' barriers visible -- still before the
+      // wait for the preceding kernel.
       int pre = 0;
       {
         const int tile = cta0;
@@ -189,13 +191,22 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int ts = tile - sp * tiles_per_split;
         const int bi = ts / tiles_per_batch;
         const int r = ts - bi * tiles_per_batch;
-        const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * TILE_M;
+        const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * TILE_M + (int)rank * BM;
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
-        pre = (!PAIR && p.b_static) ? min(STAGES, kb1 - kb0) : 0;
+        pre = p.b_static ? min(STAGES, kb1 - kb0) : 0;
+        if constexpr (PAIR) {
+          const int n0 = (p.n_fast ? r % p.tiles_n : r / p.tiles_m) * BN;
+          const int bz = p.b_batched ? bi : 0;
+          for (int i = 0; i < pre; ++i) {
+            if (rank == 0) mbar_expect_tx(smem_u32(&full[i]), (uint32_t)p.stage_tx);
+            issue_b(smem_u32(smem + i * STAGE_BYTES) + A_BYTES, mapa_u32(smem_u32(&full[i]), 0), kb0 + i, n0, bz);
+          }
+        }
         ugb_pdl_wait();
         for (int i = 0; i < pre; ++i)
-          tma_load_3d(smem_u32(smem + i * STAGE_BYTES), &tmA, smem_u32(&full[i]), (kb0 + i) * BK, m0, bi);
+          load3(smem_u32(smem + i * STAGE_BYTES), &tmA, PAIR ? mapa_u32(smem_u32(&full[i]), 0) : smem_u32(&full[i]),
+                (kb0 + i) * BK, m0, bi);
         stage = pre % STAGES;
         phase = pre == STAGES ? 1u : 0u;
       }
