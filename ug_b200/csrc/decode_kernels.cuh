@@ -81,6 +81,26 @@ reduce_rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ part, int
     }
   }
   if (early) ugb_pdl_wait();
+  if (n_part == 1) {
+    // one partial (the tall, unsplit products of a prefill chunk): every load of the row is in flight before
+    // the first addition -- the general loop below issues them one round trip at a time
+    float4 q[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * 256;
+      q[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c < nvec) q[i] = __ldcs(reinterpret_cast<const float4 *>(part + (size_t)b * hidden) + c);
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * 256;
+      if (c < nvec) {
+        v[i].x += q[i].x; v[i].y += q[i].y; v[i].z += q[i].z; v[i].w += q[i].w;
+        xr[c] = v[i];
+        ss += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+      }
+    }
+  } else
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int c = threadIdx.x + i * 256;
