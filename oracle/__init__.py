@@ -21,6 +21,28 @@ _ops.ug_set_threads.restype = C.c_int
 _ops.ug_set_threads.argtypes = [C.c_int]
 
 
+# "Long-run" mode, for oracle runs of thousands of positions (a 2048-position prompt through the
+# 22-layer model) that the strict forms would spend minutes on: the GEMM stand-in becomes numpy's
+# blocked sgemm (the accumulation order of crate gemm is unpinned either way) and rms_norm computes
+# each row's sum of squares once instead of once per element (the same value, O(cols) instead of
+# O(cols^2)).  Everything else -- rope, cat, masks, softmax, silu, adds -- stays on the C restatements.
+_long_run = False
+
+
+class long_run_mode:
+    """Context manager that switches the oracle to its long-run forms (see above)."""
+
+    def __enter__(self):
+        global _long_run
+        self._prev, _long_run = _long_run, True
+        return self
+
+    def __exit__(self, *exc):
+        global _long_run
+        _long_run = self._prev
+        return False
+
+
 def set_threads(n=0):
     """Threads of the oracle's row loops and GEMM stand-in (0 = leave as is); returns the count in force."""
     return int(_ops.ug_set_threads(int(n)))
@@ -142,6 +164,9 @@ def matmul(lhs, rhs, transpose_rhs=False):
     batch step (batch skip 0).
     """
     lhs, rhs = _f32(lhs), _f32(rhs)
+    if _long_run:
+        r = np.swapaxes(rhs, -1, -2) if transpose_rhs else rhs
+        return np.matmul(lhs, r)
     squeeze = lhs.ndim == 2
     if squeeze:
         lhs = lhs[None]
@@ -197,8 +222,11 @@ def gen_rms_norm(x, alpha, eps, rows=None):
     n_cols = x.shape[-1]
     n_rows = x.size // n_cols
     lo, hi = (0, n_rows) if rows is None else rows
-    y = np.zeros_like(x)
     inv_d = np.float32(1.0) / np.float32(n_cols)
+    if _long_run and rows is None:
+        ss = np.sum(x * x, axis=-1, keepdims=True, dtype=np.float32)
+        return (x / np.sqrt(ss * inv_d + np.float32(eps)) * alpha).astype(np.float32)
+    y = np.zeros_like(x)
     _gen.ug_gen_rms_norm(_p(x), _p(alpha), _p(y), n_rows, n_cols, inv_d, np.float32(eps), lo, hi)
     return y
 

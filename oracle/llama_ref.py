@@ -96,7 +96,7 @@ class Model:
         kr = np.ascontiguousarray(repeat(k, 1, nh // nkv))[0]
         vr = np.ascontiguousarray(repeat(v, 1, nh // nkv))[0]
         att = matmul(q[0], kr, transpose_rhs=True)              # [nh, t, T]
-        att = (att * np.float32(np.float32(hd) ** np.float32(-0.5))).astype(np.float32)
+        np.multiply(att, np.float32(np.float32(hd) ** np.float32(-0.5)), out=att)   # f32 * f32, in place
         att = att[None]
         if t != 1:
             att = causal_mask(att)

@@ -1,0 +1,89 @@
+"""Config 5 at its own size against the CPU oracle of ug-llama's forward pass
+(oracle/llama_ref.py), through the C ABI: the 22-layer, 2048-wide model, 64
+sequences, prompts of 2048 seeded tokens pre-filled through ugb_llama_prefill,
+then greedy decode steps at cache depth 2048+ (129 sixteen-key sub-tiles per
+(sequence, KV head), every warp of the attention CTAs and every KV slice in use).
+
+Two checks, both on logits within 2e-2 of the row's largest |logit|:
+  * sequence 0 end to end: the oracle pre-fills the same 2048-token prompt on
+    the CPU (blocks of 256 positions, oracle.long_run_mode: numpy sgemm as the
+    GEMM stand-in and one sum of squares per rms_norm row; about a minute on 8
+    cores), then follows the GPU's greedy tokens for two steps;
+  * sequences 17 and 63 at depth: the oracle decodes from the KV cache read back
+    from the GPU (bf16 values widened to f32), which costs a second per token and
+    isolates the decode step (attention over 2049+ keys, 22 layers) from the
+    prefill that filled the cache.
+"""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from oracle import llama_ref as R
+from ug_b200 import synth
+from ug_b200.llama import Config, Model
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+DEPTH, BATCH, STEPS = 2048, 64, 2
+CACHE_SEQS = (17, 63)
+
+
+def logit_err(got, ref):
+    return float(np.max(np.abs(got - ref)) / np.max(np.abs(ref)))
+
+
+@pytest.fixture(scope="module")
+def run(dev):
+    cfg = Config.llama_1b()
+    w = synth.llama_weights(cfg)
+    gpu = Model.new(cfg, w, dev, BATCH, DEPTH + 16)
+    prompts = synth.tokens(8, (BATCH, DEPTH), cfg.vocab_size)
+    gpu.reset(0)
+    gpu.prefill(prompts)
+    out = {"cfg": cfg, "w": w, "prompts": prompts, "prefill_logits": gpu.logits(), "tokens": [gpu.next_tokens()],
+           "logits": []}
+    # the cache as the prefill left it, for the sequences the oracle continues from the GPU's cache
+    kv = {b: [] for b in CACHE_SEQS}
+    for l in range(cfg.num_hidden_layers):
+        k, v = gpu.kv_cache(l, 0), gpu.kv_cache(l, 1)
+        for b in CACHE_SEQS:
+            kv[b].append([synth.bf16_bits_to_f32(k[b:b + 1, :, :DEPTH]).copy(),
+                          synth.bf16_bits_to_f32(v[b:b + 1, :, :DEPTH]).copy()])
+    out["kv"] = kv
+    for _ in range(STEPS):
+        gpu.decode(1)
+        out["logits"].append(gpu.logits())
+        out["tokens"].append(gpu.next_tokens())
+    assert gpu.position == DEPTH + STEPS
+    dev.synchronize()
+    gpu.close()
+    oracle.set_threads(os.cpu_count())
+    out["ref"] = R.Model(R.Config(**cfg.__dict__), synth.llama_weights_f32(w))
+    return out
+
+
+def test_prefill_2048_then_greedy_steps_match_oracle(run):
+    ref, prompts = run["ref"], run["prompts"]
+    cache = ref.new_cache()
+    with oracle.long_run_mode():
+        for p0 in range(0, DEPTH, 256):
+            logits = ref.fwd(prompts[:1, p0:p0 + 256], p0, cache)
+        assert logit_err(run["prefill_logits"][0], logits[0, -1]) < TOL
+        for s in range(STEPS):
+            tok = np.array([[run["tokens"][s][0]]], np.int32)      # the GPU's greedy choice
+            want = ref.fwd(tok, DEPTH + s, cache)[0, 0]
+            assert logit_err(run["logits"][s][0], want) < TOL
+    assert cache[0][0].shape[2] == DEPTH + STEPS
+
+
+@pytest.mark.parametrize("b", CACHE_SEQS)
+def test_decode_at_depth_from_the_gpu_cache(run, b):
+    ref = run["ref"]
+    cache = [[k.copy(), v.copy()] for k, v in run["kv"][b]]
+    assert cache[0][0].shape == (1, 4, DEPTH, 64)
+    for s in range(STEPS):
+        tok = np.array([[run["tokens"][s][b]]], np.int32)
+        want = ref.fwd(tok, DEPTH + s, cache)[0, 0]
+        assert logit_err(run["logits"][s][b], want) < TOL

@@ -6,7 +6,9 @@ must never wait on an allocator), so ``ugb_decode_attention_noalloc`` works
 out of a fixed scratch array inside the library.  The array is shared by all
 calls and keeps the previous call's contents, so this test makes two calls in
 a row with different shapes and compares each with ``ugb_decode_attention``
-on the same inputs, at the 2e-2 tolerance the other attention tests use.
+on the same inputs.  Both entry points run the same kernel in the same launch
+shape, so the outputs must be equal bit for bit (and, a fortiori, within the
+2e-2 tolerance the other attention tests use).
 Collected last on purpose: a failure here stops nothing else.
 """
 import ctypes as C
@@ -47,6 +49,7 @@ def test_noalloc_matches_allocating_entry_point_twice_in_a_row(dev):
     for g, w in zip(got, want):
         assert np.all(np.isfinite(g))
         assert np.max(np.abs(g - w)) <= 2e-2 * np.abs(w).max()
+        assert np.array_equal(g, w)
 
 
 def test_noalloc_rejects_more_than_its_fixed_scratch(dev):
