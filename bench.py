@@ -6,9 +6,15 @@
 One JSON line on rank 0.  A "step" is one pass of the hot path over one batch
 of seeded synthetic input.  Timing: CUDA events on the library's own stream
 (the stream its kernels run on), W warm-up steps, K timed steps bracketed by a
-barrier and a device synchronisation, maximum over ranks.  Units (rows,
-sequences) are partitioned across ranks with no collective: every rank works
-on its own full-size batch (weak scaling).
+barrier and a device synchronisation, maximum over ranks.  The default workload
+is the Llama-1.1B-shape decode of ONE batch of 64 sequences: with N ranks every
+rank owns a contiguous range of 64 / N sequences and a full replica of the
+weights, there is no data-path collective, and the value is 64 sequences per
+step of the slowest rank (strong scaling).  At N > 1 the same line also carries
+the 64-sequences-per-GPU figure (key "weak") and the head-sharded
+tensor-parallel variant (key "tp"); at N = 1 it carries one sub-record per
+other benchmark configuration (key "configs").  Rows (softmax, rms_norm) and
+GEMM batches are partitioned the same way when chosen with --workload.
 
 ``--impl reference`` times the reference's CPU path (the oracle restatement of
 ug-core's CPU backend; the Rust sources cannot be compiled in this image) on a
@@ -103,8 +109,8 @@ class RmsSiluWorkload:
     dtype = "f32"
     bound = "hbm"
     rows, cols = 8192, 4096
-    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload's kernel, from the ncu capture
-    # summarised in profiles/row_kernels_ncu.md (the output's tail is still in L2 when the counters stop)
+    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload's kernel, from an ncu capture
+    # of this shape (the output's tail is still in L2 when the counters stop)
     ncu_traffic_bytes = 268_462_080 + 96_574_464
 
     def __init__(self, rank):
@@ -197,7 +203,7 @@ class SoftmaxWorkload(RmsSiluWorkload):
     name = "custom_softmax f32 [32768,4096] (config 1 row shape, 32x rows so the batch exceeds L2)"
     metric = "softmax effective GB/s (rows*cols*8 bytes / time)"
     rows, cols = 32768, 4096
-    ncu_traffic_bytes = 536_986_880 + 484_354_048      # profiles/row_kernels_ncu.md
+    ncu_traffic_bytes = 536_986_880 + 484_354_048      # ncu capture of this shape, read + write
 
     def __init__(self, rank):
         from ug_b200 import synth
@@ -277,6 +283,43 @@ class SoftmaxWorkload(RmsSiluWorkload):
                 "l2": "inputs larger than L2 (1.07 GB touched per step vs 126 MB L2)"}
 
 
+class SoftmaxC1Workload(SoftmaxWorkload):
+    """Config 1 at its own size: softmax f32 [1024, 4096].  One launch touches 33.5 MB, which fits the
+    126 MB L2, so a step works on the next of 16 distinct input / output buffer pairs (537 MB in all): every
+    launch finds its rows in HBM.  `resident_gbs` times the same launch on one pair, i.e. out of L2."""
+    name = "custom_softmax f32 [1024,4096] (config 1), rotated over 16 buffer pairs (537 MB) so that no launch finds its rows in L2"
+    rows, cols, pairs = 1024, 4096, 16
+    ncu_traffic_bytes = (536_986_880 + 484_354_048) // 32     # the 32768-row capture scaled by rows (traffic grows with rows)
+
+    def setup(self, dev):
+        from ug_b200 import DType, synth
+        self.dev = dev
+        self.ins = [dev.slice_from_values(self.x if i == 0 else synth.normal(7000 + i, (self.rows, self.cols), 2.0))
+                    for i in range(self.pairs)]
+        self.outs = [dev.allocate_uninit(DType.F32, self.rows * self.cols) for _ in range(self.pairs)]
+        self.xs, self.out = self.ins[0], self.outs[0]
+        self.i = 0
+
+    def step(self):
+        j = self.i % self.pairs
+        self.i += 1
+        self.dev.custom_softmax(self.ins[j], self.outs[j], self.rows, self.cols)
+
+    def resident_gbs(self, steps=200):
+        for _ in range(5):
+            self.dev.custom_softmax(self.xs, self.out, self.rows, self.cols)
+        self.dev.synchronize()
+        self.dev.timer_begin()
+        for _ in range(steps):
+            self.dev.custom_softmax(self.xs, self.out, self.rows, self.cols)
+        self.dev.timer_end()
+        return self.bytes_per_step * steps / (self.dev.timer_elapsed_ms() / 1e3) / 1e9
+
+    def config(self):
+        return {"workload": self.name, "rows_per_gpu": self.rows, "cols": self.cols,
+                "l2": "16 buffer pairs of 33.5 MB, one per step in turn (537 MB vs 126 MB L2)"}
+
+
 class GemmWorkload:
     """Config 3: A bf16 [16,512,4096] x B bf16 [4096,4096] ([k,n]), fp32 accumulate, bf16 out."""
     name = "bf16 matmul [16,512,4096] x [4096,4096] (config 3), batch partitioned across GPUs"
@@ -285,7 +328,7 @@ class GemmWorkload:
     dtype = "bf16"
     bound = "tensor"
     bs, m, n, k = 16, 512, 4096, 4096
-    ncu_traffic_bytes = 111_407_616 + 47_598_336       # profiles/tc_gemm_config3_ncu.md (each operand once; part of C still in L2)
+    ncu_traffic_bytes = 111_407_616 + 47_598_336       # ncu capture of this shape (each operand once; part of C still in L2)
 
     def __init__(self, rank):
         from ug_b200 import synth
@@ -379,32 +422,37 @@ class GemmWorkload:
 
 
 class DecodeWorkload:
-    """Config 5: Llama-1.1B shape, 64 sequences per GPU, KV cache pre-filled to 2048 positions
-    from seeded random prompts, greedy decoding; sequences partitioned across GPUs."""
-    name = ("Llama-1.1B-shape greedy decode (dim 2048, 22 layers, 32q/4kv heads, ffn 5632, vocab 32000, "
-            "bf16 weights + bf16 KV), 64 sequences per GPU, cache pre-filled to 2048 positions")
-    metric = "tokens/s, Llama-1.1B-shape decode (batch 64 per GPU, KV depth 2048+)"
+    """Config 5: Llama-1.1B shape, ONE batch of 64 sequences whose KV cache is pre-filled to 2048 positions
+    from seeded random prompts, greedy decoding.  `seqs = (lo, hi)`: this rank owns sequences lo .. hi - 1 of
+    that batch (strong scaling, no collective).  `seqs = None`: the rank owns a full batch of 64 of its own
+    (weak scaling; rank-seeded prompts).  `tp = (rank, size)`: head-sharded tensor-parallel variant, every
+    rank sees all 64 sequences."""
+    metric = "tokens/s, Llama-1.1B-shape decode (batch 64, KV depth 2048+)"
     unit = "tokens/s"
     dtype = "bf16"
     bound = "hbm"
-    batch, prefill = 64, 2048
+    total_batch, prefill = 64, 2048
     step_is_graph = True
 
-    def __init__(self, rank, prefill=None, layers=None, fast_prefill=False, tp=None):
+    def __init__(self, rank, prefill=None, layers=None, fast_prefill=False, tp=None, seqs=None):
         self.fast_prefill = fast_prefill
-        self.tp = tp                       # (rank, size): tensor-parallel variant, every rank sees the same 64 sequences
-        if tp is not None:
-            rank = 0                       # same prompts on every rank
+        self.tp = tp
+        self.seqs = seqs
         from ug_b200 import synth
-        from ug_b200.llama import Config
+        from ug_b200.llama_config import Config
         self.cfg = Config.llama_1b()
         if layers:
             self.cfg.num_hidden_layers = layers
         if prefill is not None:
             self.prefill = prefill
         self.rank = rank
-        self.weights = synth.llama_weights(self.cfg)            # replicated on every GPU
-        self.prompts = synth.tokens(8 + 1000 * rank, (self.batch, self.prefill), self.cfg.vocab_size)
+        self.weights = _weights(self.cfg)                       # replicated on every GPU
+        if tp is not None or seqs is not None:                  # one global batch, the same on every rank
+            prompts = synth.tokens(8, (self.total_batch, self.prefill), self.cfg.vocab_size)
+            self.prompts = prompts if seqs is None else np.ascontiguousarray(prompts[seqs[0]:seqs[1]])
+        else:
+            self.prompts = synth.tokens(8 + 1000 * rank, (self.total_batch, self.prefill), self.cfg.vocab_size)
+        self.batch = self.prompts.shape[0]
         c = self.cfg
         per_layer = (c.hidden_size * (c.hidden_size + 2 * c.num_key_value_heads * c.head_dim())
                      + c.hidden_size * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
@@ -414,13 +462,21 @@ class DecodeWorkload:
         self.d2h_bytes = self.batch * 4
         self.launches_per_step = 1 + 7 * c.num_hidden_layers + 3
 
+    @property
+    def name(self):
+        how = ("64 sequences per GPU" if self.seqs is None and self.tp is None else
+               "ONE batch of 64 sequences" + (", heads / FFN columns / vocabulary sharded" if self.tp is not None
+                                              else ", sequences sharded across the GPUs"))
+        return ("Llama-1.1B-shape greedy decode (dim 2048, 22 layers, 32q/4kv heads, ffn 5632, vocab 32000, "
+                "bf16 weights + bf16 KV), %s, cache pre-filled to %d positions" % (how, self.prefill))
+
     def setup(self, dev, total_steps=256, group=None):
         from ug_b200.llama import Model
         self.dev = dev
         self.t_max = self.prefill + total_steps + 16
         self.model = Model.new(self.cfg, self.weights, dev, self.batch, self.t_max, tp=self.tp, group=group)
         if self.tp is not None:
-            # per-rank bytes of a step: the rank's share of the layer weights, the whole embedding slice it
+            # per-rank bytes of a step: the rank's share of the layer weights, the embedding slice it
             # multiplies by, and its KV heads
             n = self.tp[1]
             c = self.cfg
@@ -436,6 +492,9 @@ class DecodeWorkload:
         dev.synchronize()
         self.steps_done = 0
 
+    def close(self):
+        self.model.close()
+
     def step(self):
         self.model.decode(1)
         self.steps_done += 1
@@ -444,10 +503,8 @@ class DecodeWorkload:
         return first_pos + (n_steps - 1) / 2.0 + 1
 
     def step_bytes(self, depth):
+        """Algorithmic HBM bytes of one step on this GPU: its weight replica (or share) + its sequences' KV."""
         return self.weight_bytes + self.kv_bytes_per_pos * depth * self.batch
-
-    def units(self, seconds_per_step_total, n_ranks):
-        raise NotImplementedError
 
     def setup_e2e(self):
         import ctypes as C
@@ -460,7 +517,6 @@ class DecodeWorkload:
             setattr(self, attr, p)
             self._pin.append(p)
         self.tok_slice = self.dev.allocate_uninit(DType.I32, self.batch)
-        self.out_slice = None
         self.host_in = np.ctypeslib.as_array(C.cast(self.p_in, C.POINTER(C.c_int32)), shape=(self.batch,))
         self.host_out = np.ctypeslib.as_array(C.cast(self.p_out, C.POINTER(C.c_int32)), shape=(self.batch,))
         self.host_in[:] = self.model.next_tokens()
@@ -483,8 +539,36 @@ class DecodeWorkload:
             lib.ugb_host_free(p)
 
     def check(self):
-        """Logit parity against the CPU oracle of ug-llama on the same weights: 4 teacher-forced
-        positions from an empty cache, 2 sequences (max |diff| / max |logit|)."""
+        """Logit parity at the depth the run ended at (2048 + the steps taken), against the CPU oracle of
+        ug-llama on the same weights: for the first and the last sequence of this GPU, the oracle takes the KV
+        cache as the GPU holds it (bf16 widened to f32), decodes the GPU's next greedy token through all layers
+        and its logits are compared with the GPU's next step (max |diff| / max |logit|).  The tensor-parallel
+        variant, whose ranks hold a share of the KV heads each, keeps the shallow form: 4 teacher-forced
+        positions from an empty cache."""
+        if self.tp is not None:
+            return self.check_shallow(), "4 teacher-forced positions from an empty cache, 2 sequences"
+        from ug_b200 import synth
+        ref = self._oracle()
+        c, m = self.cfg, self.model
+        depth = m.position
+        seqs = sorted({0, self.batch - 1})
+        tok = m.next_tokens()
+        caches = {b: [] for b in seqs}
+        for l in range(c.num_hidden_layers):
+            k, v = m.kv_cache(l, 0), m.kv_cache(l, 1)
+            for b in seqs:
+                caches[b].append([synth.bf16_bits_to_f32(k[b:b + 1, :, :depth]).copy(),
+                                  synth.bf16_bits_to_f32(v[b:b + 1, :, :depth]).copy()])
+        m.decode(1)
+        got = m.logits()
+        worst = 0.0
+        for b in seqs:
+            want = ref.fwd(np.array([[tok[b]]], np.int32), depth, caches[b])[0, 0]
+            worst = max(worst, float(np.max(np.abs(got[b] - want)) / np.max(np.abs(want))))
+        return worst, ("one greedy step at cache depth %d, %d sequence(s), all %d layers, oracle fed the cache "
+                       "read back from the GPU" % (depth, len(seqs), c.num_hidden_layers))
+
+    def check_shallow(self):
         ref = self._oracle()
         caches = {b: ref.new_cache() for b in (0, self.batch - 1)}
         worst = 0.0
@@ -510,7 +594,8 @@ class DecodeWorkload:
     def cpu_sample(self, budget_s):
         """ug-llama's forward on the CPU oracle: one sequence, one new token per step, against a
         cache of `prefill` positions filled with N(0,1) keys/values (the cost of a step does not
-        depend on the cached values); tokens/s of that single sequence."""
+        depend on the cached values); tokens/s of that single sequence.  One sequence because that is
+        all the reference model runs (batch 1: ug-core/src/lazy_buffer.rs:432-436, ug-llama/src/model.rs:192-193)."""
         from ug_b200 import synth
         c = self.cfg
         ref = self._oracle()
@@ -527,14 +612,34 @@ class DecodeWorkload:
             dt = time.perf_counter() - t0
             if dt > budget_s or n >= 64:
                 break
-        return n / dt, self.cpu_threads, (f"{n} greedy tokens of 1 sequence at KV depth {self.prefill}+, oracle of "
-                                          f"ug-llama's CPU path (f32, GEMM stand-in on {self.cpu_threads} threads), {dt:.1f} s")
+        return n / dt, self.cpu_threads, (f"{n} greedy tokens of 1 sequence (the reference model runs batch 1 only) at KV depth "
+                                          f"{self.prefill}+, oracle of ug-llama's CPU path (f32, GEMM stand-in on "
+                                          f"{self.cpu_threads} threads), {dt:.1f} s")
 
-    def config(self):
-        par = {} if self.tp is None else {"parallelism": f"tp{self.tp[1]}", "sequences_total": self.batch}
-        return {"workload": self.name, **par, "sequences_per_gpu": self.batch, "prefill": self.prefill,
+    def config(self, world=1):
+        if self.tp is not None:
+            par = f"tp{self.tp[1]} (heads, FFN columns and vocabulary sharded; cross-rank sums over NVLink peer memory)"
+        elif self.seqs is not None:
+            par = f"dp{world} (sequences of one batch sharded, weights replicated, no collective)"
+        else:
+            par = f"dp{world} (a batch of 64 per GPU, no collective)"
+        total = self.total_batch * (world if self.seqs is None and self.tp is None else 1)
+        return {"workload": self.name, "parallelism": par, "sequences_total": total,
+                "sequences_per_gpu": self.batch, "prefill": self.prefill,
                 "layers": self.cfg.num_hidden_layers, "fast_prefill": self.fast_prefill,
-                "l2": "inputs larger than L2 (2.07 GB weights + ~3 GB KV cache read per step vs 126 MB L2)"}
+                "l2": "inputs larger than L2 (2.07 GB weights + 47.6 MB of KV per sequence read per step vs 126 MB L2)"}
+
+
+_WEIGHTS = {}
+
+
+def _weights(cfg):
+    """Synthetic weights of a configuration, generated once per process."""
+    from ug_b200 import synth
+    key = tuple(sorted(cfg.__dict__.items()))
+    if key not in _WEIGHTS:
+        _WEIGHTS[key] = synth.llama_weights(cfg)
+    return _WEIGHTS[key]
 
 
 class PrefillWorkload(DecodeWorkload):
@@ -547,7 +652,7 @@ class PrefillWorkload(DecodeWorkload):
     dtype = "bf16"
     bound = "tensor"
     sustained_peak = True          # ~200 kernels per step, seconds of back-to-back GEMMs: sustained bf16 figure
-    batch, prefill = 8, 512
+    total_batch, prefill = 8, 512
     step_is_graph = False
 
     def __init__(self, rank, prefill=None, layers=None, fast_prefill=False):
@@ -630,15 +735,122 @@ class PrefillWorkload(DecodeWorkload):
         return done / dt, self.cpu_threads, (f"{done} prompt positions in blocks of {n} (one sequence), oracle of ug-llama's "
                                              f"CPU path (f32, GEMM stand-in on {self.cpu_threads} threads), {dt:.1f} s")
 
-    def config(self):
+    def config(self, world=1):
         return {"workload": self.name, "sequences_per_gpu": self.batch, "prompt_positions": self.prefill,
                 "layers": self.cfg.num_hidden_layers,
                 "l2": "inputs larger than L2 (2.07 GB of weights read per step vs 126 MB L2)"}
 
 
-WORKLOADS = {"rms_silu": RmsSiluWorkload, "softmax": SoftmaxWorkload, "gemm": GemmWorkload,
-             "decode": DecodeWorkload, "prefill": PrefillWorkload}
+WORKLOADS = {"rms_silu": RmsSiluWorkload, "softmax": SoftmaxWorkload, "softmax_c1": SoftmaxC1Workload,
+             "gemm": GemmWorkload, "decode": DecodeWorkload, "prefill": PrefillWorkload}
 DEFAULT_WORKLOAD = "decode"
+
+# DRAM traffic of the decode step's kernels, from ncu captures of single launches (dram__bytes_read.sum +
+# dram__bytes_write.sum): the attention kernel moved 141,193,472 B at 2049 cached positions of 64 sequences
+# (1.02x its algorithmic bytes; grows in proportion to positions x sequences), the weight-streaming
+# projections 1.01-1.03x their weight bytes.  The step's traffic is put together from these, not captured whole.
+ATT_TRAFFIC_AT_2049_X64 = 141_193_472
+GEMM_TRAFFIC_OVER_WEIGHTS = 1.02
+
+
+def _config_of(wl, world):
+    try:
+        return wl.config(world)
+    except TypeError:
+        return wl.config()
+
+
+def measure(wl, dev, group, rank, local_rank, warmup, steps, e2e_steps, clocks=True):
+    """W warm-up steps, K timed steps (CUDA events on the library's stream, barrier + synchronise on both
+    sides), then the end-to-end loop with host buffers; maxima over ranks."""
+    def barrier():
+        dev.synchronize()
+        group.barrier()
+
+    for _ in range(warmup):
+        wl.step()
+    barrier()
+    sampler = ClockSampler(local_rank) if (rank == 0 and clocks) else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.3)
+    n0 = dev.launch_count
+    first_pos = wl.model.position if isinstance(wl, DecodeWorkload) and not isinstance(wl, PrefillWorkload) else 0
+    barrier()
+    dev.timer_begin()
+    for _ in range(steps):
+        wl.step()
+    dev.timer_end()
+    ms = dev.timer_elapsed_ms()
+    barrier()
+    launches = dev.launch_count - n0
+    # end to end: host buffers in, host buffers out, copies inside the timed region
+    wl.setup_e2e()
+    for _ in range(2):
+        wl.e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        wl.e2e_step()
+    dev.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    clk = sampler.stop() if sampler else None
+    wl.teardown_e2e()
+    ms, e2e_s = group.max([ms, e2e_s])      # the slowest rank defines the step
+    return {"ms": ms, "e2e_s": e2e_s, "launches": int(launches), "first_pos": first_pos, "clocks": clk,
+            "steps": steps, "e2e_steps": e2e_steps}
+
+
+def roofline_of(wl, step_s, peaks):
+    launch_s = step_s / wl.launches_per_step
+    if wl.bound == "hbm":
+        achieved, peak, unit = wl.bytes_per_step / wl.launches_per_step / launch_s / 1e9, peaks["hbm"], "GB/s"
+    else:
+        peak = peaks["bf16_sustained"] if getattr(wl, "sustained_peak", False) else peaks["bf16"]
+        achieved, unit = wl.flops_per_step / wl.launches_per_step / launch_s / 1e12, "TFLOP/s"
+    return {"bound": wl.bound, "achieved": round(achieved, 1), "peak": peak, "unit": unit,
+            "frac": round(achieved / peak, 4), "traffic": getattr(wl, "ncu_traffic_bytes", None),
+            "peak_source": peaks["source"]}
+
+
+def parity_of(wl):
+    r = wl.check()
+    return r if isinstance(r, tuple) else (r, None)
+
+
+def config_records(dev, group, peaks):
+    """One sub-record per benchmark configuration other than the decode step (N = 1): value, roofline
+    fraction, DRAM traffic of the kernel and parity against the oracle."""
+    out = {}
+    plan = [("config1_softmax_1024x4096", SoftmaxC1Workload, 200), ("config1_row_shape_32768x4096", SoftmaxWorkload, 30),
+            ("config2_rms_norm_silu_gate", RmsSiluWorkload, 50), ("config3_gemm", GemmWorkload, 30),
+            ("config4_prefill", PrefillWorkload, 10)]
+    for key, cls, steps in plan:
+        wl = cls(0)
+        wl.setup(dev)
+        for _ in range(3):
+            wl.step()
+        dev.synchronize()
+        dev.timer_begin()
+        for _ in range(steps):
+            wl.step()
+        dev.timer_end()
+        step_s = dev.timer_elapsed_ms() / 1e3 / steps
+        err, what = parity_of(wl)
+        rec = {"workload": wl.name, "metric": wl.metric, "value": round(wl.units(step_s, 1), 2), "unit": wl.unit,
+               "ms_per_step": round(step_s * 1e3, 5), "steps": steps, "roofline": roofline_of(wl, step_s, peaks),
+               "parity_max_rel_err": err}
+        if hasattr(wl, "resident_gbs"):
+            rec["l2_resident_value"] = round(wl.resident_gbs(), 1)
+        if hasattr(wl, "reference_cuda_gbs") and cls is SoftmaxWorkload:
+            g = wl.reference_cuda_gbs()
+            rec["reference_cuda_kernel"] = None if g is None else round(g, 1)
+        out[key] = rec
+        if hasattr(wl, "close"):
+            wl.close()
+        del wl
+    return out
 
 
 def main():
@@ -650,12 +862,16 @@ def main():
     ap.add_argument("--impl", default="ug_b200", choices=["ug_b200", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="decode: leave out the extra records (configs at N = 1; weak and tp at N > 1)")
     ap.add_argument("--prefill", type=int, default=None, help="decode: cached positions before timing")
     ap.add_argument("--device-option", action="append", default=[], metavar="NAME=INT",
                     help="device tuning switch set before the run (ugb_device_set_option), e.g. gemm_cta_pairs=1")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=INT",
-                    help="prefill: engine option set before the run (profiling of kernel variants)")
+                    help="engine option set before the run (profiling of kernel variants)")
     ap.add_argument("--layers", type=int, default=None, help="decode: layer count (profiling of small cases)")
+    ap.add_argument("--weak", action="store_true",
+                    help="decode at N > 1: every rank decodes its own 64 sequences (64 N in all) instead of a share of one batch")
     ap.add_argument("--tp", action="store_true",
                     help="decode: tensor-parallel variant -- the ranks share ONE batch of 64 sequences (heads, FFN "
                          "columns and vocabulary sharded, cross-rank sums inside the engine's kernels over NVLink)")
@@ -667,16 +883,25 @@ def main():
     if args.steps is None:
         args.steps = 128 if args.workload == "decode" else 50
 
-    from ug_b200.dist import env_rank
+    from ug_b200.dist import env_rank, shard_range
     rank, local_rank, world = env_rank()
+    options = dict((k, int(v)) for k, v in (o.split("=") for o in args.option))
+
+    def make_decode(mode):
+        if mode == "tp":
+            return DecodeWorkload(rank, prefill=args.prefill, layers=args.layers, fast_prefill=args.fast_prefill,
+                                  tp=(rank, world))
+        if mode == "weak":
+            return DecodeWorkload(rank, prefill=args.prefill, layers=args.layers, fast_prefill=args.fast_prefill)
+        return DecodeWorkload(rank, prefill=args.prefill, layers=args.layers, fast_prefill=args.fast_prefill,
+                              seqs=shard_range(DecodeWorkload.total_batch, rank, world))
 
     def make_workload(r):
         if args.workload == "decode":
-            return DecodeWorkload(r, prefill=args.prefill, layers=args.layers, fast_prefill=args.fast_prefill,
-                                  tp=(rank, world) if args.tp else None)
+            return make_decode("tp" if args.tp else ("weak" if args.weak else "strong"))
         if args.workload == "prefill":
             wl = PrefillWorkload(r, prefill=args.prefill, layers=args.layers)
-            wl.options = dict((k, int(v)) for k, v in (o.split("=") for o in args.option))
+            wl.options = options
             return wl
         return WORKLOADS[args.workload](r)
 
@@ -693,104 +918,87 @@ def main():
     for o in args.device_option:
         name, value = o.split("=")
         dev.set_option(name, int(value))
-    wl = make_workload(rank)
-    e2e_steps = max(3, min(args.steps, 10 if args.workload != "decode" else 32))
-    if args.workload == "decode":
-        wl.setup(dev, total_steps=args.warmup + args.steps + e2e_steps + 8, group=group)
+    decode = args.workload == "decode"
+    e2e_steps = max(3, min(args.steps, 10 if not decode else 32))
+    total_steps = args.warmup + args.steps + e2e_steps + 16
+
+    def run_decode(mode, clocks=True):
+        wl = make_decode(mode)
+        wl.setup(dev, total_steps=total_steps, group=group)
+        for name, value in options.items():
+            wl.model.set_option(name, value)
+        return wl, measure(wl, dev, group, rank, local_rank, args.warmup, args.steps, e2e_steps, clocks)
+
+    if decode:
+        mode = "tp" if args.tp else ("weak" if args.weak else "strong")
+        wl, m = run_decode(mode)
     else:
+        mode = None
+        wl = make_workload(rank)
         wl.setup(dev)
+        m = measure(wl, dev, group, rank, local_rank, args.warmup, args.steps, e2e_steps)
 
-    def barrier():
-        dev.synchronize()
-        group.barrier()
-
-    for _ in range(args.warmup):
-        wl.step()
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.3)
-    n0 = dev.launch_count
-    first_pos = wl.model.position if args.workload == "decode" else 0
-    barrier()
-    dev.timer_begin()
-    for _ in range(args.steps):
-        wl.step()
-    dev.timer_end()
-    ms = dev.timer_elapsed_ms()
-    barrier()
-    launches = dev.launch_count - n0
-
-    # end to end: host buffers in, host buffers out, copies inside the timed region
-    wl.setup_e2e()
-    for _ in range(2):
-        wl.e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        wl.e2e_step()
-    dev.synchronize()
-    e2e_s = time.perf_counter() - t0
-    barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    wl.teardown_e2e()
-
-    ms, e2e_s = group.max([ms, e2e_s])      # the slowest rank defines the step
-    tp = bool(getattr(args, "tp", False)) and args.workload == "decode"
-    kern, att_bytes = {}, 0
-    if rank == 0 and args.workload == "decode":
+    tp = decode and mode == "tp"
+    kern, kdepth = {}, 0
+    if rank == 0 and decode:
         # per-kernel share of one step, each kernel type timed alone over all layers (CUDA events); no exchange inside
         for name in wl.model.KERNELS:
             kern[name] = round(wl.model.time_kernel(name, 20), 4)
         kdepth = wl.model.position                      # cache depth the kernels were timed at
-        att_bytes = wl.kv_bytes_per_pos * kdepth * wl.batch
-    barrier()
+    dev.synchronize()
+    group.barrier()
     # under tensor parallelism every engine call is collective: all ranks run the parity check
-    parity = wl.check() if (rank == 0 or tp) else None
+    parity, parity_what = parity_of(wl) if (rank == 0 or tp) else (None, None)
 
+    peaks = measured_peaks()
+    step_s = m["ms"] / 1e3 / args.steps
+    e2e_step_s = m["e2e_s"] / e2e_steps
+    line = None
     if rank == 0:
-        peaks = measured_peaks()
-        step_s = ms / 1e3 / args.steps
         extra = {}
-        if args.workload == "decode":
-            n_seq = wl.batch if tp else world * wl.batch      # tensor parallel: one batch shared by all ranks
-            value = n_seq / step_s
-            e2e_value = n_seq / (e2e_s / e2e_steps)
-            depth = wl.mean_depth(first_pos, args.steps)
-            achieved, peak, runit = wl.step_bytes(depth) / step_s / 1e9, peaks["hbm"], "GB/s"
+        if decode:
+            n_seq = wl.total_batch * (world if mode == "weak" else 1)
+            value, e2e_value = n_seq / step_s, n_seq / e2e_step_s
+            depth = wl.mean_depth(m["first_pos"], args.steps)
+            gpu_bytes = wl.step_bytes(depth)             # this GPU's algorithmic bytes per step (rank 0 holds the largest share)
+            achieved = gpu_bytes / step_s / 1e9
+            att_traffic = ATT_TRAFFIC_AT_2049_X64 * (depth / 2049.0) * (wl.batch / 64.0) * wl.cfg.num_hidden_layers
+            traffic = None if tp else int(att_traffic + GEMM_TRAFFIC_OVER_WEIGHTS * wl.weight_bytes)
+            roof = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm"], "unit": "GB/s",
+                    "frac": round(achieved / peaks["hbm"], 4), "traffic": traffic, "peak_source": peaks["source"],
+                    "scope": ("whole decode step on one GPU (one CUDA graph of %d kernels): that GPU's weight bytes + its "
+                              "sequences' KV bytes at the mean cache depth %.0f; traffic = the per-kernel ncu captures "
+                              "(attention at 2049 positions scaled by depth x sequences, projections 1.02 x weights)"
+                              % (m["launches"] // max(args.steps, 1), depth))}
             extra["kernels_ms_per_step"] = kern
-            extra["roofline_scope"] = ("whole decode step (one CUDA graph of %d kernels): weight bytes + KV bytes "
-                                       "at the mean cache depth %.0f" % (wl.launches_per_step, depth))
+            att_bytes = wl.kv_bytes_per_pos * kdepth * wl.batch
             extra["decode_attention_roofline"] = {
-                # 141.2 MB of DRAM traffic per launch at 2049 cached positions (profiles/decode_attention_ncu.md),
-                # scaled to the depth the kernel was timed at: the traffic grows in proportion to the cached positions
-                "traffic": int(141_193_472 * kdepth / 2049 * wl.batch / 64) if not tp else None,
+                "traffic": int(ATT_TRAFFIC_AT_2049_X64 * kdepth / 2049 * wl.batch / 64) if not tp else None,
                 "achieved": round(att_bytes / (kern["decode_attention"] / 1e3) / 1e9, 1), "peak": peaks["hbm"],
                 "unit": "GB/s", "frac": round(att_bytes / (kern["decode_attention"] / 1e3) / 1e9 / peaks["hbm"], 4)}
+            # the bandwidth bound of this split: every GPU re-reads the whole weight replica, so the step cannot
+            # be shorter than (weights + this GPU's KV) / HBM bandwidth, whatever N is
+            one_gpu = DecodeWorkload.total_batch * wl.kv_bytes_per_pos * depth + wl.weight_bytes
+            extra["bound"] = {"bytes_per_gpu_per_step": int(gpu_bytes),
+                              "step_floor_ms_at_measured_hbm": round(gpu_bytes / peaks["hbm"] / 1e6, 4),
+                              "speedup_bound_vs_1_gpu": None if tp or mode == "weak" else round(one_gpu / gpu_bytes, 3)}
         else:
             value = wl.units(step_s, world)
-            e2e_value = wl.units(e2e_s / e2e_steps, world)
-            launch_s = step_s / wl.launches_per_step
-            if wl.bound == "hbm":
-                achieved, peak, runit = wl.bytes_per_step / wl.launches_per_step / launch_s / 1e9, peaks["hbm"], "GB/s"
-            else:
-                tpeak = peaks["bf16_sustained"] if getattr(wl, "sustained_peak", False) else peaks["bf16"]
-                achieved, peak, runit = wl.flops_per_step / wl.launches_per_step / launch_s / 1e12, tpeak, "TFLOP/s"
+            e2e_value = wl.units(e2e_step_s, world)
+            roof = roofline_of(wl, step_s, peaks)
         line = {
             "metric": wl.metric, "value": round(value, 2), "unit": wl.unit, "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 5),
-            "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": wl.dtype,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(m["ms"] / args.steps, 5),
+            "higher_is_better": True, "scaling": "strong" if (decode and mode != "weak") else "weak",
+            "vs_baseline": None, "dtype": wl.dtype,
             "data": "synthetic (seeded Philox, shapes and distributions of the named config)",
-            "config": wl.config(),
+            "config": _config_of(wl, world),
             "e2e": {"value": round(e2e_value, 3), "unit": wl.unit,
                     "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes,
                     "steps": e2e_steps},
-            "gpu_launches": int(launches),
-            "clocks": clocks,
-            "roofline": {"bound": wl.bound, "achieved": round(achieved, 1), "peak": peak,
-                         "unit": runit, "frac": round(achieved / peak, 4),
-                         "traffic": getattr(wl, "ncu_traffic_bytes", None), "peak_source": peaks["source"]},
+            "gpu_launches": m["launches"],
+            "clocks": m["clocks"],
+            "roofline": roof,
         }
         line.update(extra)
         if hasattr(wl, "reference_cuda_gbs"):
@@ -798,11 +1006,44 @@ def main():
             line["reference_cuda_kernel"] = None if g is None else {
                 "value": round(g, 1), "unit": "GB/s", "what": "ug-llama/src/softmax.cu compiled as is (fast-math), "
                 "launched as ug-llama/src/cuda_ops.rs does, same buffers"}
+        if hasattr(wl, "resident_gbs"):
+            line["l2_resident_value"] = round(wl.resident_gbs(), 1)
         line["parity_max_rel_err"] = parity
+        if parity_what:
+            line["parity_what"] = parity_what
         if not args.no_cpu_baseline:
             v, cores, sample = wl.cpu_sample(args.cpu_seconds)
             line["cpu_baseline"] = {"value": round(v, 4), "unit": wl.unit, "cores": cores,
                                     "kind": "port", "sample": sample}
+            if decode:
+                line["cpu_baseline"]["sequences"] = 1
+
+    # extra records of the default run: the other configurations at N = 1, the other two splits at N > 1
+    if decode and mode == "strong" and not args.no_extras:
+        wl.close()
+        del wl
+        if world == 1:
+            if rank == 0:
+                line["configs"] = config_records(dev, group, peaks)
+        else:
+            for other in ("weak", "tp"):
+                owl, om = run_decode(other, clocks=False)
+                o_step = om["ms"] / 1e3 / args.steps
+                n_seq = owl.total_batch * (world if other == "weak" else 1)
+                if rank == 0:
+                    depth = owl.mean_depth(om["first_pos"], args.steps)
+                    b = owl.step_bytes(depth)
+                    line[other] = {"value": round(n_seq / o_step, 2), "unit": "tokens/s", "sequences_total": n_seq,
+                                   "ms_per_step": round(o_step * 1e3, 5),
+                                   "e2e_value": round(n_seq / (om["e2e_s"] / e2e_steps), 2),
+                                   "config": _config_of(owl, world),
+                                   "roofline_frac": round(b / o_step / 1e9 / peaks["hbm"], 4),
+                                   "bytes_per_gpu_per_step": int(b)}
+                owl.close()
+                del owl
+                dev.synchronize()
+                group.barrier()
+    if rank == 0:
         print(json.dumps(line), flush=True)
     group.close()
     return 0
@@ -817,17 +1058,23 @@ def reference_arm(args, wl):
         if i >= args.warmup:
             vals.append(v)
     value = float(np.mean(vals))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     line = {
         "impl": "reference", "metric": wl.metric, "value": round(value, 4), "unit": wl.unit,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": None,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+        "higher_is_better": True, "scaling": "strong" if isinstance(wl, DecodeWorkload) and not isinstance(wl, PrefillWorkload) else "weak",
+        "vs_baseline": None, "dtype": wl.dtype,
         "data": "synthetic (seeded Philox, shapes and distributions of the named config)",
-        "config": wl.config(),
+        "config": _config_of(wl, world),
         "cpu_baseline": {"value": round(value, 4), "unit": wl.unit, "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": round(value, 4), "unit": wl.unit, "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
     }
+    if isinstance(wl, DecodeWorkload) and not isinstance(wl, PrefillWorkload):
+        line["cpu_baseline"]["sequences"] = 1
+        line["note"] = ("the reference model decodes one sequence at a time (batch 1 only), so this is tokens/s of ONE "
+                        "sequence on the host cores; the GPU arm's value is over the 64 sequences of the batch")
     print(json.dumps(line), flush=True)
     return 0
 

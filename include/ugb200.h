@@ -4,7 +4,7 @@
  * int32 status as the return value (0 = success).  Nothing here throws or
  * aborts across the boundary; the text of the last failure on a device is
  * kept per device and read with ugb_last_error().  A Rust `impl ug::Device`
- * binds exactly these symbols (see INTEGRATION.md for the binding).
+ * binds exactly these symbols.
  *
  * Threading model (ug-cuda/src/runtime.rs:80-85,163-169): one stream per
  * device handle, launches are asynchronous and ordered on that stream, only
@@ -82,8 +82,25 @@ UGB_API uint64_t ugb_launch_count(const ugb_device *dev);
  *                     256 x 256 tiles on pairs of CTAs (tcgen05 cta_group::2, a
  *                     cluster of two SMs sharing the B operand) instead of
  *                     128 x 256 tiles on single CTAs.  Same results bit for bit.
+ *   "wait_limit_us"   100 .. 60000000 (default 2000000): how long a device-side
+ *                     wait on something another agent completes (an mbarrier fed
+ *                     by TMA / MMA, a peer GPU's flag, a grid-wide barrier) may
+ *                     last before the kernel gives up, raises UGB_ERR_TIMEOUT in
+ *                     the status word (read by ugb_sync) and returns.  For the
+ *                     tensor-parallel engine the limit must also cover the skew
+ *                     between the ranks' host threads (a slow first launch on
+ *                     one rank counts against the others' waits).
  * Unknown names and out-of-range values are UGB_ERR_INVALID. */
 UGB_API int32_t ugb_device_set_option(ugb_device *dev, const char *name, int32_t value);
+
+/* Self-test of the bounded waits (no counterpart in the reference, which has no
+ * device-side waits): enqueues one CTA that waits on something nobody completes
+ * -- which = 0: an mbarrier without arrivals (site code 0x99); which = 1: the
+ * flag of a tensor-parallel peer that never signals (site code 0x7001) -- with
+ * the current "wait_limit_us".  The wait gives up, the kernel returns, and the
+ * NEXT ugb_sync reports UGB_ERR_TIMEOUT with that site code in its message;
+ * after that the device handle works as before.  Nothing faults or hangs. */
+UGB_API int32_t ugb_selftest_bounded_wait(ugb_device *dev, int32_t which);
 
 /* ------------------------------------------------------------------ memory */
 
@@ -401,8 +418,11 @@ UGB_API int32_t ugb_llama_destroy(ugb_llama *m);
  * over NVLink in rank order, so the replicas stay bit-identical.  Logits are
  * vocab-parallel: ugb_llama_read returns this rank's columns
  * [vocab_offset, vocab_offset + vocab_local) and the greedy choice is made over
- * (value, id) pairs exchanged the same way.  Waits on peers are bounded (2 s,
- * then UGB_ERR_TIMEOUT at the next ugb_sync); ranks must issue the same calls.
+ * (value, id) pairs exchanged the same way.  Waits on peers are bounded (device
+ * option "wait_limit_us", then UGB_ERR_TIMEOUT at the next ugb_sync, after which
+ * ugb_llama_decode / ugb_llama_prefill of this model refuse further steps: the
+ * ranks may be out of step and the model has to be recreated); ranks must issue
+ * the same calls.
  * ugb_llama_load_weight takes whole tensors and keeps the rank's slice. */
 UGB_API int32_t ugb_llama_create_tp(ugb_device *dev, const ugb_llama_config *cfg, int32_t batch,
                                     int32_t t_max, int32_t tp_rank, int32_t tp_size, ugb_llama **out);

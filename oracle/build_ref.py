@@ -13,7 +13,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("UG_REFERENCE_DIR", "/root/reference")
+# the reference checkout: $UG_REFERENCE_DIR, else a directory named "reference" beside this repository
+REF = os.environ.get("UG_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "libugref_cuda.so")
 

@@ -60,9 +60,15 @@ int32_t ugb_device_create(int32_t ordinal, ugb_device **out) {
             cudaEventCreate(&d->ev_begin) == cudaSuccess &&
             cudaEventCreate(&d->ev_end) == cudaSuccess &&
             cudaMalloc(&d->status_dev, sizeof(ugb_status_word)) == cudaSuccess &&
-            cudaMemset(d->status_dev, 0, sizeof(ugb_status_word)) == cudaSuccess &&
-            cudaMalloc(&d->sched_dev, 2 * sizeof(int)) == cudaSuccess &&
-            cudaMemset(d->sched_dev, 0, 2 * sizeof(int)) == cudaSuccess;
+            cudaMalloc(&d->sched_dev, 2 * sizeof(int)) == cudaSuccess;
+  if (ok) {
+    // initial values go through the handle's own stream (a non-blocking stream is not ordered against the
+    // legacy stream) and are complete before the handle is handed out
+    const ugb_status_word w0 = {0u, 0u, UGB_DEFAULT_WAIT_LIMIT_US, 0u};
+    ok = cudaMemcpyAsync(d->status_dev, &w0, sizeof(w0), cudaMemcpyHostToDevice, d->stream) == cudaSuccess &&
+         cudaMemsetAsync(d->sched_dev, 0, 2 * sizeof(int), d->stream) == cudaSuccess &&
+         cudaStreamSynchronize(d->stream) == cudaSuccess;
+  }
   if (!ok) {
     e = cudaGetLastError();
     ugb_fail(nullptr, UGB_ERR_CUDA, "device set-up failed: %s", cudaGetErrorString(e));
@@ -109,7 +115,8 @@ int32_t ugb_sync(ugb_device *dev) {
   UGB_CUDA(dev, cudaMemcpyAsync(&w, dev->status_dev, sizeof(w), cudaMemcpyDeviceToHost, dev->stream));
   UGB_CUDA(dev, cudaStreamSynchronize(dev->stream));
   if (w.code != 0) {
-    cudaMemsetAsync(dev->status_dev, 0, sizeof(w), dev->stream);
+    cudaMemsetAsync(dev->status_dev, 0, 2 * sizeof(unsigned int), dev->stream);   // code and detail; the wait limit stays
+    if (w.code == (unsigned)UGB_ERR_TIMEOUT) dev->wait_timeouts++;
     return ugb_fail(dev, (int32_t)w.code, "device-side status %u (detail %u) reported by a kernel",
                     w.code, w.detail);
   }
@@ -126,6 +133,15 @@ int32_t ugb_device_set_option(ugb_device *dev, const char *name, int32_t value) 
   if (strcmp(name, "gemm_cta_pairs") == 0) {
     UGB_REQUIRE(dev, value == 0 || value == 1, UGB_ERR_INVALID, "option gemm_cta_pairs: %d is not 0 or 1", value);
     dev->gemm_pair = value;
+    return UGB_OK;
+  }
+  if (strcmp(name, "wait_limit_us") == 0) {
+    UGB_REQUIRE(dev, value >= 100 && value <= 60000000, UGB_ERR_INVALID,
+                "option wait_limit_us: %d outside 100..60000000", value);
+    UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
+    const unsigned int v = (unsigned int)value;
+    UGB_CUDA(dev, cudaMemcpyAsync(&dev->status_dev->wait_limit_us, &v, sizeof(v), cudaMemcpyHostToDevice, dev->stream));
+    UGB_CUDA(dev, cudaStreamSynchronize(dev->stream));
     return UGB_OK;
   }
   return ugb_fail(dev, UGB_ERR_INVALID, "unknown device option %s", name);
@@ -223,6 +239,7 @@ int32_t ugb_h2d_async(ugb_slice *dst, const void *src, size_t len, int32_t dtype
   int32_t rc = copy_checks(dev, dst, src, len, dtype, "htod");
   if (rc) return rc;
   if (len == 0) return UGB_OK;
+  UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
   UGB_CUDA(dev, cudaMemcpyAsync(dst->ptr, src, len * ugb_dtype_size(dtype), cudaMemcpyHostToDevice, dev->stream));
   return UGB_OK;
 }
@@ -233,6 +250,7 @@ int32_t ugb_d2h_async(const ugb_slice *src, void *dst, size_t len, int32_t dtype
   int32_t rc = copy_checks(dev, src, dst, len, dtype, "dtoh");
   if (rc) return rc;
   if (len == 0) return UGB_OK;
+  UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
   UGB_CUDA(dev, cudaMemcpyAsync(dst, src->ptr, len * ugb_dtype_size(dtype), cudaMemcpyDeviceToHost, dev->stream));
   return UGB_OK;
 }

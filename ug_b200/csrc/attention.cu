@@ -37,10 +37,12 @@ int32_t launch_attention(ugb_device *dev, const ugb_slice *q, const ugb_slice *k
     attr_set[dev->ordinal & 63] = true;
   }
   dim3 grid((unsigned)n_slices, (unsigned)n_kv, (unsigned)b);
+  AttRope front{};                       // q given, cache read only
+  front.status = dev->status_dev;        // a position outside the cache is reported there
   decode_attention_kernel<<<grid, ATT_WARPS * 32, ATT_RING_BYTES, dev->stream>>>(
       (const __nv_bfloat16 *)q->ptr, (__nv_bfloat16 *)k->ptr, (__nv_bfloat16 *)v->ptr,
       (const int *)pos->ptr, part_o, part_ml, counters, (__nv_bfloat16 *)out->ptr, (int)n_heads, (int)n_kv,
-      (int)(n_heads / n_kv), (int)t_max, 0.125f /* 64^-0.5, model.rs:236 */, AttRope{} /* q given, cache read only */, CUtensorMap{}, CUtensorMap{} /* cp.async path */);
+      (int)(n_heads / n_kv), (int)t_max, 0.125f /* 64^-0.5, model.rs:236 */, front, CUtensorMap{}, CUtensorMap{} /* cp.async path */);
   return ugb_after_launch(dev, "decode_attention_kernel");
 }
 

@@ -257,7 +257,7 @@ struct AttRope {
   const float *cos_, *sin_;
   int interleaved, append;
   int early;                     // 1: the ring may be filled before griddepcontrol.wait (see the kernel)
-  ugb_status_word *status;       // TMA variant: where a wait that gave up is reported
+  ugb_status_word *status;       // where a position outside the cache, or (TMA variant) a wait that gave up, is reported
 };
 
 // TMA variant (TMA = true): the K / V sub-tiles arrive by cp.async.bulk.tensor through rank-3 maps over the
@@ -306,6 +306,15 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int T = *pos_p + 1;
+  // The position lives on the device: a stale or oversized value would walk (and, when appending, write) past
+  // the cache, where the reference panics on a slice bound.  Nothing is touched then; the status word is raised.
+  if (T < 1 || T > t_max) {
+    if (!dep_ready) ugb_pdl_wait();
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && rope.status != nullptr &&
+        atomicCAS(&rope.status->code, 0u, (unsigned)UGB_ERR_INVALID) == 0u)
+      rope.status->detail = (unsigned)(T - 1);
+    return;
+  }
   const int n_sub = (T + ATT_SUB - 1) / ATT_SUB;
   const int sub_per_split = (n_sub + n_split - 1) / n_split;
   const int sub_lo = sp * sub_per_split;

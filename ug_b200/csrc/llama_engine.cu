@@ -52,6 +52,7 @@ struct ugb_llama {
   size_t tp_off_o = 0, tp_off_down = 0, tp_off_pairs = 0, tp_block_bytes = 0, tp_part_rows = 0;
   void *tp_peer[TP_MAX] = {};     // every rank's exchange block as mapped here (own included)
   bool tp_ready = false;
+  unsigned timeouts_at_create = 0;   // dev->wait_timeouts when the model was created (see tp_in_step)
   int qkv_dim = 0;
   std::vector<LayerW> layers;
   __nv_bfloat16 *embed = nullptr;
@@ -299,6 +300,16 @@ int32_t launch_attention(ugb_llama *m, int layer, float scale, int n_part, bool 
   return ugb_after_launch(m->dev, "decode_attention_kernel");
 }
 
+// A tensor-parallel model whose device has reported a wait that gave up since the model was created may have
+// ranks that are no longer in step (a rank that stopped waiting summed partials its peers had not finished):
+// it takes no further steps.
+int32_t tp_in_step(ugb_llama *m) {
+  if (m->tp && m->tp_size > 1 && m->dev->wait_timeouts != m->timeouts_at_create)
+    return ugb_fail(m->dev, UGB_ERR_TIMEOUT, "tensor-parallel model: a wait on a peer gave up earlier (UGB_ERR_TIMEOUT was "
+                    "reported by ugb_sync); the ranks may be out of step -- destroy and recreate the model on every rank");
+  return UGB_OK;
+}
+
 // Enqueues one decode step on the device stream; `tok` holds the input ids.
 int32_t enqueue_step(ugb_llama *m, const int *tok) {
   ugb_device *dev = m->dev;
@@ -487,6 +498,7 @@ int32_t ugb_llama_create_tp(ugb_device *dev, const ugb_llama_config *cfg, int32_
   m->tp = tp;
   m->tp_rank = tp_rank;
   m->tp_size = n_rank;
+  m->timeouts_at_create = dev->wait_timeouts;
   m->q0 = tp_rank * c.n_heads;
   m->kv0 = tp_rank * g.n_kv_heads / n_rank;
   m->vl = g.vocab / n_rank;
@@ -742,6 +754,7 @@ int32_t ugb_llama_decode(ugb_llama *m, const ugb_slice *tokens, int32_t n_steps)
   UGB_REQUIRE(dev, m->host_pos + n_steps <= m->t_max && m->host_pos + n_steps <= m->cfg.max_pos, UGB_ERR_SHAPE,
               "decode of %d steps from position %d exceeds the KV cache (%d positions)", n_steps, m->host_pos, m->t_max);
   UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
+  if (int32_t in_step = tp_in_step(m)) return in_step;
   if (tokens) {
     UGB_SLICE(dev, tokens, UGB_I32, (size_t)m->batch);
     UGB_CUDA(dev, cudaMemcpyAsync(m->next, tokens->ptr, (size_t)m->batch * 4, cudaMemcpyDeviceToDevice, dev->stream));
@@ -784,6 +797,7 @@ int32_t ugb_llama_prefill(ugb_llama *m, const ugb_slice *tokens, int32_t t, int3
   UGB_REQUIRE(dev, m->host_pos + t <= m->t_max && m->host_pos + t <= m->cfg.max_pos, UGB_ERR_SHAPE,
               "prefill of %d positions from position %d exceeds the KV cache (%d positions)", t, m->host_pos, m->t_max);
   UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
+  if (int32_t in_step = tp_in_step(m)) return in_step;
   const ugb_llama_config &c = m->cfg;
   const size_t H = c.hidden;
   int32_t rc;

@@ -8,6 +8,8 @@
 // and the rotation uses separately rounded multiplies and adds (no fused
 // multiply-add), which is what the reference's Rust arithmetic does
 // (ug-llama/src/cpu_ops.rs:73-78,112-117).
+#include <algorithm>
+
 #include "ugb_internal.h"
 
 namespace {
@@ -31,8 +33,15 @@ template <bool INTERLEAVED, bool VEC>
 __global__ void __launch_bounds__(THREADS)
 rope_kernel(const float *__restrict__ src, const float *__restrict__ cos_,
             const float *__restrict__ sin_, const int *__restrict__ pos, float *__restrict__ dst,
-            size_t bh, int t, int d) {
+            size_t bh, int t, int d, size_t table_len, ugb_status_word *status) {
   const int half = d >> 1;
+  // The position lives on the device: a stale or oversized value would index past the cos / sin tables
+  // (the reference panics on the slice bound).  Nothing is read or written then; the status word is raised.
+  if (pos[0] < 0 || ((size_t)pos[0] + (size_t)t) * half > table_len) {
+    if (blockIdx.x == 0 && threadIdx.x == 0 && atomicCAS(&status->code, 0u, (unsigned)UGB_ERR_INVALID) == 0u)
+      status->detail = (unsigned)pos[0];
+    return;
+  }
   const size_t p0 = (size_t)pos[0] * half;
   constexpr int W = VEC ? 4 : 1;  // rotation pairs per thread
   const size_t pairs_per_bh = (size_t)t * half;
@@ -200,11 +209,11 @@ int32_t rope_impl(ugb_device *dev, const ugb_slice *src, const ugb_slice *cos,
   if (vec)
     rope_kernel<INTERLEAVED, true><<<grid_for(dev, pairs / 4), THREADS, 0, dev->stream>>>(
         (const float *)src->ptr, (const float *)cos->ptr, (const float *)sin->ptr,
-        (const int *)pos->ptr, (float *)dst->ptr, b * h, (int)t, (int)d);
+        (const int *)pos->ptr, (float *)dst->ptr, b * h, (int)t, (int)d, std::min(cos->len, sin->len), dev->status_dev);
   else
     rope_kernel<INTERLEAVED, false><<<grid_for(dev, pairs), THREADS, 0, dev->stream>>>(
         (const float *)src->ptr, (const float *)cos->ptr, (const float *)sin->ptr,
-        (const int *)pos->ptr, (float *)dst->ptr, b * h, (int)t, (int)d);
+        (const int *)pos->ptr, (float *)dst->ptr, b * h, (int)t, (int)d, std::min(cos->len, sin->len), dev->status_dev);
   return ugb_after_launch(dev, "rope_kernel");
 }
 

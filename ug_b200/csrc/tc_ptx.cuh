@@ -10,7 +10,6 @@
 namespace ugb_tc {
 
 constexpr int UMMA_K = 16;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
 
 // ----------------------------------------------------------------- PTX -----
 static __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -37,7 +36,8 @@ static __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false when the CTA is (or becomes) aborted.
+// Bounded wait: at most status->wait_limit_us (device option "wait_limit_us", 2 s by default) of %globaltimer.
+// Returns false when the CTA is (or becomes) aborted.
 static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                           ugb_status_word *status, unsigned site) {
   if (mbar_try(bar, parity)) return true;
@@ -46,7 +46,7 @@ static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, 
     if (mbar_try(bar, parity)) return true;
     if ((it & 255u) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer() - t0 > WAIT_LIMIT_NS) {
+      if (globaltimer() - t0 > 1000ull * *reinterpret_cast<volatile unsigned int *>(&status->wait_limit_us)) {
         *abort_flag = 1;
         if (atomicCAS(&status->code, 0u, (unsigned)UGB_ERR_TIMEOUT) == 0u) status->detail = site;
         return false;

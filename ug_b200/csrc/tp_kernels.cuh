@@ -10,9 +10,13 @@
 // epoch into its slot of every peer's flag array (st.release.sys), (3) waits
 // until its own flag array shows that epoch for every peer (ld.acquire.sys).
 // Data is only ever *read* remotely; remote stores carry flags only.  Waits
-// are bounded (2 s of %globaltimer): on expiry the kernel raises the status
-// word, marks the exchange as failed (later waits return at once) and carries
-// on with whatever the buffers hold, so that no rank can hang another.
+// are bounded (device option "wait_limit_us", 2 s of %globaltimer by default;
+// the limit also has to cover the host-side skew between the ranks' launches):
+// on expiry the kernel raises the status word, marks the exchange as failed
+// and carries on with whatever the buffers hold, so that no rank can hang
+// another.  While the mark is set every later exchange skips its wait AND
+// raises the status word again, so no step after a failed one passes for good;
+// the engine refuses further steps once ugb_sync has reported the timeout.
 //
 // Buffer reuse needs no second barrier: a partial buffer is rewritten two
 // exchanges later, and its owner passes the exchange in between only after
@@ -66,15 +70,18 @@ __device__ __forceinline__ void tp_exchange_begin(const TpPeers &tp, ugb_status_
       st_release_sys(&tp.hdr[r]->flags[tp.rank], e);           // own slot too: uniform wait below
     }
     if (!*reinterpret_cast<volatile unsigned int *>(&mine->failed)) {
+      const unsigned long long limit = 1000ull * *reinterpret_cast<volatile unsigned int *>(&status->wait_limit_us);
       const unsigned long long t0 = tp_globaltimer();
       unsigned int it = 0;
       while ((int)(ld_acquire_sys(&mine->flags[r]) - e) < 0) {
-        if ((++it & 63u) == 0u && tp_globaltimer() - t0 > 2000000000ull) {
+        if ((++it & 63u) == 0u && tp_globaltimer() - t0 > limit) {
           mine->failed = 1u;
           if (atomicCAS(&status->code, 0u, (unsigned)UGB_ERR_TIMEOUT) == 0u) status->detail = 0x7000u + r;
           break;
         }
       }
+    } else if (r == 0 && atomicCAS(&status->code, 0u, (unsigned)UGB_ERR_TIMEOUT) == 0u) {
+      status->detail = 0x70ffu;       // an earlier exchange of this model gave up: its ranks are out of step
     }
   }
   __syncthreads();

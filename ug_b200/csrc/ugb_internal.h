@@ -11,9 +11,13 @@
 
 // Device-side status word layout (one per device handle, read at ugb_sync).
 struct ugb_status_word {
-  unsigned int code;    // 0 = ok, otherwise a ugb_status value
-  unsigned int detail;  // kernel-specific (bad index, wait site, ...)
+  unsigned int code;           // 0 = ok, otherwise a ugb_status value
+  unsigned int detail;         // kernel-specific (bad index, wait site, ...)
+  unsigned int wait_limit_us;  // how long a device-side wait (mbarrier, peer flag, grid barrier) may last before it
+                               // gives up with UGB_ERR_TIMEOUT; device option "wait_limit_us", default 2 s
+  unsigned int pad;
 };
+constexpr unsigned int UGB_DEFAULT_WAIT_LIMIT_US = 2000000u;
 
 struct ugb_device {
   int ordinal = 0;
@@ -27,6 +31,8 @@ struct ugb_device {
   std::string last_error;
   void *gemm_state = nullptr;  // owned by the GEMM translation unit
   int gemm_pair = 1;           // option gemm_cta_pairs: tall bf16 GEMMs on pairs of CTAs (tcgen05 cta_group::2)
+  unsigned wait_timeouts = 0;  // device-side waits that gave up, as seen by ugb_sync (tensor-parallel models refuse
+                               // further steps once this has moved: their ranks may be out of step)
 };
 
 struct ugb_slice {

@@ -59,7 +59,7 @@ def llama_weights(cfg, seed_base=100):
     import os
     from concurrent.futures import ThreadPoolExecutor
 
-    from .llama import weight_names, weight_shape
+    from .llama_config import weight_names, weight_shape
 
     def one(item):
         i, name = item
