@@ -30,6 +30,7 @@
 #include "gemm_tcgen05.cuh"
 #include "tp_kernels.cuh"
 #include "attention_tc.cuh"
+#include "decode_step.cuh"
 
 using namespace ugb_decode;
 
@@ -82,6 +83,12 @@ struct ugb_llama {
   size_t loaded = 0;
   // prefill workspace, allocated by the first ugb_llama_prefill: activations of one chunk of
   // pf_rows = batch * pf_chunk rows (pf_chunk positions of every sequence)
+  // persistent decode-step kernel (decode_step.cu): option step_kernel
+  int step_kernel = 0;            // 1: a decode step is one launch of decode_step_kernel + lm_head + argmax
+  bool step_ready = false;
+  int step_grid = 0;
+  ugb_step_params step{};
+  unsigned step_timeouts = 0;     // dev->wait_timeouts when the barrier words were last cleared
   int att_early = 1;              // option att_early: kernels may fetch old data before griddepcontrol.wait when that is provably safe
   bool early_ok = false;          // ... and it is, for the current shapes and options (set by enqueue_step)
   int att_tma = 0;                // option att_tma: decode attention fetches K / V by TMA (1) or cp.async (0)
@@ -300,6 +307,82 @@ int32_t launch_attention(ugb_llama *m, int layer, float scale, int n_part, bool 
   return ugb_after_launch(m->dev, "decode_attention_kernel");
 }
 
+// Everything the persistent decode-step kernel needs besides the model's own buffers: the plan (tile widths and
+// k splits for this device's SM count), tensor maps over the weights and the activation buffers, partial and
+// attention scratch sized for the plan, the barrier words.  Allocated once, freed with the model.
+bool step_kernel_applies(const ugb_llama *m) { return m->step_kernel && !m->tp && m->batch <= 64 && m->skip == 0; }
+
+int32_t ensure_step_kernel(ugb_llama *m) {
+  if (m->step_ready) return UGB_OK;
+  ugb_device *dev = m->dev;
+  const ugb_llama_config &c = m->lc;
+  ugb_step_params &p = m->step;
+  p = ugb_step_params{};
+  p.batch = m->batch; p.hidden = c.hidden; p.qkv_dim = m->qkv_dim; p.att_width = c.n_heads * c.head_dim;
+  p.ffn = c.ffn; p.layers = c.layers; p.n_heads = c.n_heads; p.n_kv = c.n_kv_heads; p.group = c.n_heads / c.n_kv_heads;
+  p.t_max = m->t_max; p.vocab = c.vocab; p.interleaved = c.rope_interleaved;
+  p.eps = c.rms_eps; p.inv_d = 1.0f / (float)c.hidden; p.scale = powf((float)c.head_dim, -0.5f);   // model.rs:236
+  m->step_grid = dev->sm_count;
+  const int most = ugb_decode_step_plan(p, m->step_grid);
+  UGB_REQUIRE(dev, c.hidden % 64 == 0 && c.ffn % 8 == 0, UGB_ERR_UNSUPPORTED, "step_kernel: hidden must be a multiple of 64");
+  int32_t rc;
+  // partials of the widest projection
+  size_t part = 0;
+  for (int i = 0; i < 4; ++i)
+    if (i != UGB_STEP_GATE_UP) part = std::max(part, (size_t)p.g[i].splits * m->batch * p.g[i].n);
+  (void)most;
+  float *partials = nullptr, *po = nullptr, *pml = nullptr;
+  unsigned *cnt = nullptr, *sync = nullptr;
+  const size_t slots = (size_t)m->batch * c.n_kv_heads + (size_t)m->step_grid;
+  if ((rc = dmalloc(m, &partials, part))) return rc;
+  if ((rc = dmalloc(m, &po, slots * ATT_GROUP * ATT_HD))) return rc;
+  if ((rc = dmalloc(m, &pml, slots * ATT_GROUP * 2))) return rc;
+  if ((rc = dmalloc(m, &cnt, (size_t)m->batch * c.n_kv_heads, true))) return rc;
+  if ((rc = dmalloc(m, &sync, 4, true))) return rc;
+  // tensor maps: per layer qkv / o / gate-up / down weights with the plan's tile width, then xn / att / h
+  std::vector<CUtensorMap> maps((size_t)c.layers * 4 + 3);
+  auto weight_map = [&](CUtensorMap *map, const __nv_bfloat16 *w, const ugb_step_gemm &g) {
+    const uint64_t dims[3] = {(uint64_t)g.k, (uint64_t)g.n, 1};
+    const uint64_t strides[2] = {(uint64_t)g.k, (uint64_t)g.n * g.k};
+    const uint32_t box[3] = {64, (uint32_t)g.bn, 1};
+    return ugb_tc_encode_bf16(dev, map, w, 3, dims, strides, box);
+  };
+  auto act_map = [&](CUtensorMap *map, const __nv_bfloat16 *a, size_t k) {
+    const uint64_t dims[3] = {(uint64_t)k, (uint64_t)m->batch, 1};
+    const uint64_t strides[2] = {(uint64_t)k, (uint64_t)m->batch * k};
+    const uint32_t box[3] = {64, 64, 1};
+    return ugb_tc_encode_bf16(dev, map, a, 3, dims, strides, box);
+  };
+  std::vector<ugb_step_layer> layers(c.layers);
+  for (int l = 0; l < c.layers; ++l) {
+    const LayerW &w = m->layers[l];
+    if ((rc = weight_map(&maps[(size_t)l * 4 + UGB_STEP_QKV], w.wqkv, p.g[UGB_STEP_QKV]))) return rc;
+    if ((rc = weight_map(&maps[(size_t)l * 4 + UGB_STEP_O], w.wo, p.g[UGB_STEP_O]))) return rc;
+    if ((rc = weight_map(&maps[(size_t)l * 4 + UGB_STEP_GATE_UP], w.wgu, p.g[UGB_STEP_GATE_UP]))) return rc;
+    if ((rc = weight_map(&maps[(size_t)l * 4 + UGB_STEP_DOWN], w.wdown, p.g[UGB_STEP_DOWN]))) return rc;
+    layers[l].rms1 = w.rms1; layers[l].rms2 = w.rms2;
+    layers[l].kcache = m->kcache + (size_t)l * m->kv_layer_stride;
+    layers[l].vcache = m->vcache + (size_t)l * m->kv_layer_stride;
+  }
+  if ((rc = act_map(&maps[(size_t)c.layers * 4 + 0], m->xn, c.hidden))) return rc;
+  if ((rc = act_map(&maps[(size_t)c.layers * 4 + 1], m->att, (size_t)c.n_heads * c.head_dim))) return rc;
+  if ((rc = act_map(&maps[(size_t)c.layers * 4 + 2], m->h, c.ffn))) return rc;
+  CUtensorMap *maps_dev = nullptr;
+  ugb_step_layer *layers_dev = nullptr;
+  if ((rc = dmalloc(m, &maps_dev, maps.size()))) return rc;
+  if ((rc = dmalloc(m, &layers_dev, layers.size()))) return rc;
+  UGB_CUDA(dev, cudaMemcpyAsync(maps_dev, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, dev->stream));
+  UGB_CUDA(dev, cudaMemcpyAsync(layers_dev, layers.data(), layers.size() * sizeof(ugb_step_layer), cudaMemcpyHostToDevice, dev->stream));
+  UGB_CUDA(dev, cudaStreamSynchronize(dev->stream));         // the host vectors go away
+  p.maps = maps_dev; p.layer = layers_dev;
+  p.embed = m->embed; p.ln_f = m->ln_f; p.cos_ = m->cos; p.sin_ = m->sin; p.pos = m->pos;
+  p.x = m->x; p.xn = m->xn; p.att = m->att; p.h = m->h; p.part = partials;
+  p.att_po = po; p.att_pml = pml; p.att_cnt = cnt; p.sync = sync; p.status = dev->status_dev;
+  m->step_timeouts = dev->wait_timeouts;
+  m->step_ready = true;
+  return UGB_OK;
+}
+
 // A tensor-parallel model whose device has reported a wait that gave up since the model was created may have
 // ranks that are no longer in step (a rank that stopped waiting summed partials its peers had not finished):
 // it takes no further steps.
@@ -318,6 +401,12 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
   const int B = m->batch, H = c.hidden, AW = c.n_heads * c.head_dim;
   int32_t rc;
   const bool pdl = m->pdl != 0;
+  if (step_kernel_applies(m) && m->step_ready) {
+    // one persistent kernel for the embedding, all layers and the final norm; then the tied lm_head and the choice
+    m->step.tok = tok;
+    if ((rc = ugb_decode_step_launch(dev, m->step, m->step_grid, pdl))) return rc;
+    return launch_lm_head_argmax(m, true);
+  }
   cudaError_t e = ugb_launch(embed_gather_kernel, dim3(B), dim3(256), 0, st, pdl, m->embed, tok, m->x, H, c.vocab, dev->status_dev, 1, 1, 0);
   if (e != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of embed_gather_kernel failed: %s", cudaGetErrorString(e));
   if ((rc = ugb_after_launch(dev, "embed_gather_kernel"))) return rc;
@@ -689,6 +778,14 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
     return UGB_OK;
   }
+  if (k == "step_kernel") {
+    UGB_REQUIRE(dev, value == 0 || value == 1, UGB_ERR_INVALID, "option step_kernel: %d is not 0 or 1", value);
+    m->step_kernel = value;
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    m->warmed = false;            // the kernel's attributes are set by its first, eager launch
+    if (value && !m->tp && m->batch <= 64) return ensure_step_kernel(m);
+    return UGB_OK;
+  }
   if (k == "att_early") {
     m->att_early = value != 0;
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
@@ -755,6 +852,11 @@ int32_t ugb_llama_decode(ugb_llama *m, const ugb_slice *tokens, int32_t n_steps)
               "decode of %d steps from position %d exceeds the KV cache (%d positions)", n_steps, m->host_pos, m->t_max);
   UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
   if (int32_t in_step = tp_in_step(m)) return in_step;
+  if (m->step_ready && m->step_timeouts != dev->wait_timeouts) {
+    // a wait gave up since the barrier words were last known good (an aborted step leaves them half counted)
+    UGB_CUDA(dev, cudaMemsetAsync(m->step.sync, 0, 4 * sizeof(unsigned), dev->stream));
+    m->step_timeouts = dev->wait_timeouts;
+  }
   if (tokens) {
     UGB_SLICE(dev, tokens, UGB_I32, (size_t)m->batch);
     UGB_CUDA(dev, cudaMemcpyAsync(m->next, tokens->ptr, (size_t)m->batch * 4, cudaMemcpyDeviceToDevice, dev->stream));
