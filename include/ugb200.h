@@ -398,7 +398,8 @@ typedef struct {
   int32_t rope_interleaved; /* rope_interleaved (0 / 1)     */
 } ugb_llama_config;
 
-enum { UGB_LLAMA_LOGITS = 0, UGB_LLAMA_NEXT_TOKENS = 1, UGB_LLAMA_HIDDEN = 2, UGB_LLAMA_PREFILL_LOGITS = 3 };
+enum { UGB_LLAMA_LOGITS = 0, UGB_LLAMA_NEXT_TOKENS = 1, UGB_LLAMA_HIDDEN = 2, UGB_LLAMA_PREFILL_LOGITS = 3,
+       UGB_LLAMA_STEP_PROFILE = 4 /* measurement aid, see option "step_profile" */ };
 
 /* Model::new + Cache::new (model.rs:183-198,298-363): allocates weights, the
  * RoPE tables (model.rs:278-295) and a KV cache for `batch` sequences of up to
@@ -447,7 +448,12 @@ UGB_API int32_t ugb_llama_load_weight(ugb_llama *m, const char *name, const ugb_
  * 64, 80, 96, 128 or 256); "gemm_smem_kib" (shared-memory cap of a decode GEMM
  * CTA, 32..220, 0 = none); "att_stages" (2..6); "att_early", "att_tma",
  * "prefill_attention_tc", "pdl" (0 / 1); "prefill_rows" (64..65536, see
- * ugb_llama_prefill). */
+ * ugb_llama_prefill); "step_kernel" (0 / 1): a decode step of up to 64
+ * sequences runs all its layers in ONE persistent kernel launch (grid-wide
+ * barriers between the phases, the weight stream running ahead of them)
+ * followed by the lm_head and the greedy choice, instead of seven launches per
+ * layer; "step_profile" (0 / 1, measurement aid): that kernel records
+ * %globaltimer at every grid barrier, read with UGB_LLAMA_STEP_PROFILE. */
 UGB_API int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value);
 /* Sets the number of cached positions (0 = empty cache); cache contents at
  * positions >= pos are ignored by later steps. */

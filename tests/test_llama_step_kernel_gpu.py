@@ -114,7 +114,7 @@ def test_step_kernel_bad_token_raises_status(dev):
     from ug_b200 import UgError
     with pytest.raises(UgError) as e:
         dev.synchronize()
-    assert e.value.code == 3
+    assert e.value.code == 1
     gpu.fwd(np.array([1, 2, 3, 4], np.int32))
     dev.synchronize()
     gpu.close()

@@ -4,7 +4,7 @@
   return and the next ugb_sync report UGB_ERR_TIMEOUT (7) with the site code; the device handle works
   afterwards.  The wait gives up by design: nothing faults, nothing hangs.
 * A device-side position that points outside the KV cache or the rope tables makes the stand-alone
-  operators skip all accesses and raise UGB_ERR_INVALID (3), where the reference panics on a slice bound.
+  operators skip all accesses and raise UGB_ERR_INVALID (1), where the reference panics on a slice bound.
 """
 import time
 
@@ -62,7 +62,7 @@ def test_decode_attention_rejects_a_position_outside_the_cache(dev, bad_pos):
     dev.decode_attention(sq, sk, sv, pos, out, b, nh, nkv, t_max, 2)
     with pytest.raises(UgError) as e:
         dev.synchronize()
-    assert e.value.code == 3
+    assert e.value.code == 1
     assert np.array_equal(out.to_vec(), sentinel)
     # the largest legal position still works
     pos_ok = dev.slice_from_values(np.array([t_max - 1], np.int32))
@@ -84,7 +84,7 @@ def test_rope_rejects_a_position_outside_the_tables(dev, interleaved):
         op(sx, sc, ss, dev.slice_from_values(np.array([bad], np.int32)), out, b, h, t, d)
         with pytest.raises(UgError) as e:
             dev.synchronize()
-        assert e.value.code == 3
+        assert e.value.code == 1
         assert np.array_equal(out.to_vec(), sentinel)
     out = dev.slice_from_values(sentinel)
     op(sx, sc, ss, dev.slice_from_values(np.array([max_pos - t], np.int32)), out, b, h, t, d)   # last legal start

@@ -673,10 +673,13 @@ __global__ void __launch_bounds__(THREADS, 1) decode_step_kernel(const __grid_co
     if (!alive && et == 0 && cta == 0 && atomicCAS(&p.status->code, 0u, (unsigned)UGB_ERR_INVALID) == 0u) p.status->detail = (unsigned)(T - 1);
     if (!alive && et == 0) s.abort_flag = 1;     // every CTA reads the same position: each one bails out by itself
     // Grid barrier: the CTA's epilogue threads meet, one of them announces the CTA and waits for all CTAs.
+    unsigned long long *prof = (p.prof != nullptr && cta % 37 == 0 && cta / 37 < 4) ? p.prof + (size_t)(cta / 37) * UGB_STEP_PROF_SLOTS : nullptr;
+    if (prof && et == 0) prof[0] = globaltimer();
     auto grid_sync = [&]() -> bool {
       epi_bar();
       ++n_sync;
       if (et == 0) {
+        if (prof && 2 * n_sync < UGB_STEP_PROF_SLOTS) prof[2 * n_sync - 1] = globaltimer();
         __threadfence();
         atomicAdd(p.sync, 1u);
         const unsigned target = base + (unsigned)n_sync * (unsigned)grid;
@@ -689,6 +692,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_step_kernel(const __grid_co
           }
         }
         st_release_cta_shared(&s.sync_count, n_sync);
+        if (prof && 2 * n_sync < UGB_STEP_PROF_SLOTS) prof[2 * n_sync] = globaltimer();
       }
       epi_bar();
       return !*reinterpret_cast<volatile int *>(&s.abort_flag);

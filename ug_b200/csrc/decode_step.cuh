@@ -39,7 +39,10 @@ struct ugb_step_params {
   unsigned int *att_cnt;                 // [batch * n_kv] completion counters, left at zero
   unsigned int *sync;                    // [0] barrier arrivals, [1] arrivals at the start of this launch, [2] abort
   ugb_status_word *status;
+  unsigned long long *prof;              // measurement aid (or null): %globaltimer of CTAs 0, 37, 74, 111 at the start,
+                                         // and at the arrival at / the completion of every grid barrier: [4][UGB_STEP_PROF_SLOTS]
 };
+constexpr int UGB_STEP_PROF_SLOTS = 512;
 
 // Chooses tile widths and k splits for `grid` CTAs; returns the largest number of partials any projection writes.
 int ugb_decode_step_plan(ugb_step_params &p, int grid);

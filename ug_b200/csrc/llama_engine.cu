@@ -786,6 +786,17 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
     if (value && !m->tp && m->batch <= 64) return ensure_step_kernel(m);
     return UGB_OK;
   }
+  if (k == "step_profile") {      // measurement aid: barrier time stamps of the persistent step kernel (UGB_LLAMA_STEP_PROFILE)
+    UGB_REQUIRE(dev, m->step_ready, UGB_ERR_INVALID, "option step_profile: set step_kernel first");
+    if (value && !m->step.prof) {
+      unsigned long long *buf = nullptr;
+      if (int32_t rc = dmalloc(m, &buf, (size_t)4 * UGB_STEP_PROF_SLOTS, true)) return rc;
+      m->step.prof = buf;
+    }
+    if (!value) m->step.prof = nullptr;
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    return UGB_OK;
+  }
   if (k == "att_early") {
     m->att_early = value != 0;
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
@@ -947,6 +958,17 @@ int32_t ugb_llama_read(ugb_llama *m, int32_t what, void *host_dst, size_t len) {
     case UGB_LLAMA_PREFILL_LOGITS:
       UGB_REQUIRE(dev, m->pf_logits && m->pf_logits_t > 0, UGB_ERR_INVALID, "no all-position logits: run ugb_llama_prefill with all_logits first");
       src = m->pf_logits; n = (size_t)m->batch * m->pf_logits_t * m->vl; break;
+    case UGB_LLAMA_STEP_PROFILE: {
+      UGB_REQUIRE(dev, m->step_ready && m->step.prof, UGB_ERR_INVALID, "no step profile: set options step_kernel and step_profile first");
+      n = (size_t)4 * UGB_STEP_PROF_SLOTS;
+      UGB_REQUIRE(dev, len == n, UGB_ERR_SHAPE, "ugb_llama_read: destination holds %zu elements, %zu expected", len, n);
+      std::vector<unsigned long long> raw(n);
+      UGB_CUDA(dev, cudaMemcpyAsync(raw.data(), m->step.prof, n * 8, cudaMemcpyDeviceToHost, dev->stream));
+      UGB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+      float *out = (float *)host_dst;                 // microseconds since CTA 0's first stamp; 0 where nothing was recorded
+      for (size_t i = 0; i < n; ++i) out[i] = raw[i] ? (float)((double)(raw[i] - raw[0]) * 1e-3) : 0.f;
+      return UGB_OK;
+    }
     default: return ugb_fail(dev, UGB_ERR_INVALID, "ugb_llama_read: unknown selector %d", what);
   }
   UGB_REQUIRE(dev, len == n, UGB_ERR_SHAPE, "ugb_llama_read: destination holds %zu elements, %zu expected", len, n);
