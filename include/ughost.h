@@ -95,6 +95,10 @@ UGB_API int32_t ugh_schedule_item_kind(const ugh_schedule *s, size_t i);
 /* the SSA of a Kernel item: policy -1 = default Opts (all dims sequential), 0 = reference grid heuristic,
  * 1 = this backend's.  Writes a NUL-terminated listing (one line per instruction) into buf. */
 UGB_API int32_t ugh_schedule_item_ssa_text(const ugh_schedule *s, size_t i, int32_t policy, char *buf, size_t buf_len);
+/* CUDA C this backend generates for a Kernel item that is a row-reduce + map or a pure map (128-bit accesses,
+ * the row in registers); an empty string when the item is not of those shapes and takes the SSA path.  The first
+ * line is a comment naming the shape, the entry point and the launch dimensions. */
+UGB_API int32_t ugh_schedule_item_fast_source(const ugh_schedule *s, size_t i, char *buf, size_t buf_len);
 UGB_API ugh_cache *ugh_cache_create(void);
 UGB_API void ugh_cache_free(ugh_cache *c);
 UGB_API size_t ugh_cache_hits(const ugh_cache *c);
@@ -103,6 +107,9 @@ UGB_API ugh_compiled *ugh_schedule_compile(const ugh_schedule *s, ugh_cache *cac
 UGB_API void ugh_compiled_free(ugh_compiled *c);
 UGB_API int32_t ugh_compiled_run(const ugh_compiled *c);
 UGB_API size_t ugh_compiled_n_funcs(const ugh_compiled *c);
+/* What function i of a compiled schedule runs on: "matmul", "custom", "ssa" (per-instruction code from the SSA),
+ * "row_vec4" / "warp_row_vec4" / "map_vec4" (generated 128-bit row / map code). */
+UGB_API int32_t ugh_compiled_func_origin(const ugh_compiled *c, size_t i, char *buf, size_t buf_len);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,77 @@
+"""Graph kernels on generated 128-bit code (host layer: ug_fast.cpp) on the B200 device: which generator each
+item of a compiled schedule ran on, and parity with ug's CPU backend (the oracle's emitted-C kernels) within
+1e-5 relative for fp32 reductions.  The unmodified graph forms of ug-llama/src/model.rs:65-109 are used."""
+import numpy as np
+import pytest
+
+import oracle
+import ug_b200
+from ug_b200 import llama_graph as G
+from ug_b200 import synth
+from ug_b200.lazy import LB, BinaryOp as B, HostDevice, Schedule
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def hd(dev):
+    return HostDevice(dev)
+
+
+def run(y):
+    s = Schedule.create_one(y)
+    c = s.compile()
+    c.run()
+    return s, c, y.data_vec()
+
+
+@pytest.mark.parametrize("rows,cols", [(8192, 4096), (33, 1024), (7, 32000), (130, 64), (3, 12), (5, 2100)])
+def test_graph_softmax_is_one_row_kernel(hd, rows, cols):
+    x = synth.normal(11, (rows, cols), 2.0)
+    s, c, got = run(G.softmax(LB.copy(x, (rows, cols), hd)))
+    # exp(x - max) feeds the sum and the division of the same row: evaluated in place, one kernel, one read, one write
+    assert s.items() == ["Kernel"]
+    expect = "warp_row_vec4" if cols <= 1024 else "row_vec4"
+    assert c.origins() == [expect]
+    check = min(rows, 48)
+    ref = oracle.custom_softmax(x[:check])
+    assert np.max(np.abs(got.reshape(rows, cols)[:check] - ref) / np.maximum(ref, 1e-30)) < 1e-5
+    assert np.allclose(got.reshape(rows, cols).sum(-1), 1.0, atol=1e-4)
+
+
+@pytest.mark.parametrize("rows,cols", [(8192, 4096), (64, 2048), (9, 576)])
+def test_graph_rms_norm_is_one_row_kernel(hd, rows, cols):
+    x, a = synth.normal(12, (rows, cols)), synth.uniform(13, (cols,), 0.5, 1.5)
+    s, c, got = run(G.rms_norm(LB.copy(x, (rows, cols), hd), LB.copy(a, (cols,), hd), 1e-5))
+    assert s.items() == ["Kernel"]
+    assert c.origins() == ["warp_row_vec4" if cols <= 1024 else "row_vec4"]
+    check = min(rows, 32)
+    ref = oracle.gen_rms_norm(x[:check], a, 1e-5)
+    assert np.max(np.abs(got.reshape(rows, cols)[:check] - ref) / np.maximum(np.abs(ref), 1e-20)) < 1e-5
+
+
+def test_maps_copies_and_unaligned_shapes(hd):
+    x, g = synth.normal(14, (64, 5632)), synth.normal(15, (64, 5632))
+    lx, lg = LB.copy(x, x.shape, hd), LB.copy(g, g.shape, hd)
+    _, c, got = run(G.silu(lx).binary(B.Mul, lg))                     # model.rs:160-168: a pure map
+    assert c.origins() == ["map_vec4"]
+    ref = oracle.gen_silu_mul(x, g)
+    assert np.max(np.abs(got.reshape(x.shape) - ref) / np.maximum(np.abs(ref), 1e-6)) < 1e-5
+    _, c, got = run(lx.binary(B.Add, lg))                              # residual add
+    assert c.origins() == ["map_vec4"]
+    assert np.array_equal(got.reshape(x.shape), oracle.gen_add(x, g))
+    # q / k / v transposing copy (model.rs:207-215) and the GQA repeat (model.rs:80-92): pure data movement, bit exact
+    q = synth.normal(16, (1, 7, 32, 64))
+    _, c, got = run(LB.copy(q, q.shape, hd).transpose(2, 1))
+    assert c.origins() == ["warp_row_vec4"]
+    assert np.array_equal(got.reshape(1, 32, 7, 64), q.transpose(0, 2, 1, 3))
+    k = synth.normal(17, (1, 4, 37, 64))
+    _, c, got = run(G.repeat(LB.copy(k, k.shape, hd), 1, 8))
+    assert c.origins() == ["warp_row_vec4"]
+    assert np.array_equal(got.reshape(1, 32, 37, 64), np.repeat(k, 8, axis=1))
+    # a row length that is not a multiple of 4 has no 128-bit form: the SSA path takes it, same result
+    y = synth.normal(18, (5, 777))
+    _, c, got = run(G.softmax(LB.copy(y, y.shape, hd)))
+    assert set(c.origins()) == {"ssa"}
+    ref = oracle.custom_softmax(y)
+    assert np.max(np.abs(got.reshape(y.shape) - ref) / np.maximum(ref, 1e-30)) < 1e-5

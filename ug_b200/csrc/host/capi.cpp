@@ -121,6 +121,12 @@ struct B200Device : Device {
                          k.launch_config.shared_mem, name ? name->c_str() : nullptr, &f->h));
     return f;
   }
+  std::shared_ptr<Func> compile_cu(const FastKernel &fk) override {
+    auto f = std::make_shared<B200Func>();
+    check(d, ugb_compile_cu(d, fk.source.c_str(), fk.func_name.c_str(), fk.launch.grid_dim, fk.launch.block_dim,
+                            fk.launch.shared_mem, &f->h));
+    return f;
+  }
   void run(Func &f, std::vector<Slice *> &args) override {
     std::vector<ugb_slice *> hs;
     for (Slice *s : args) {
@@ -319,6 +325,19 @@ int32_t ugh_schedule_item_ssa_text(const ugh_schedule *s, size_t i, int32_t poli
     std::memcpy(buf, t.c_str(), t.size() + 1);
   });
 }
+int32_t ugh_schedule_item_fast_source(const ugh_schedule *s, size_t i, char *buf, size_t buf_len) {
+  return guard([&] {
+    if (i >= s->s.items.size() || s->s.items[i].kind != ScheduleItem::Kernel) bail("item ", i, " is not a kernel");
+    op::Kernel k = optimize(s->s.items[i].kernel());
+    FastKernel fk;
+    std::string t;
+    if (fast_kernel(k, "k", fk))
+      t = "// " + fk.origin + " " + fk.func_name + " grid " + std::to_string(fk.launch.grid_dim) + " block " +
+          std::to_string(fk.launch.block_dim) + "\n" + fk.source;
+    if (t.size() + 1 > buf_len) bail("buffer too small: ", t.size() + 1, " bytes needed");
+    std::memcpy(buf, t.c_str(), t.size() + 1);
+  });
+}
 ugh_cache *ugh_cache_create(void) { return new ugh_cache(); }
 void ugh_cache_free(ugh_cache *c) { delete c; }
 size_t ugh_cache_hits(const ugh_cache *c) { return c->c.hits; }
@@ -332,5 +351,14 @@ ugh_compiled *ugh_schedule_compile(const ugh_schedule *s, ugh_cache *cache) {
 void ugh_compiled_free(ugh_compiled *c) { delete c; }
 int32_t ugh_compiled_run(const ugh_compiled *c) { return guard([&] { c->c.run(); }); }
 size_t ugh_compiled_n_funcs(const ugh_compiled *c) { return c->c.funcs.size(); }
+int32_t ugh_compiled_func_origin(const ugh_compiled *c, size_t i, char *buf, size_t buf_len) {
+  return guard([&] {
+    if (i >= c->c.funcs.size()) bail("no function ", i);
+    const CompiledFunc &f = c->c.funcs[i];
+    const std::string t = f.kind == CompiledFunc::MatMul ? "matmul" : f.kind == CompiledFunc::Custom ? "custom" : (f.func ? f.func->origin : "?");
+    if (t.size() + 1 > buf_len) bail("buffer too small");
+    std::memcpy(buf, t.c_str(), t.size() + 1);
+  });
+}
 
 }  // extern "C"

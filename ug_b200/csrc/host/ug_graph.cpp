@@ -2,6 +2,8 @@
 // ug-core/src/schedule.rs.
 #include "ug_graph.hpp"
 
+#include <unordered_set>
+
 #include <algorithm>
 
 namespace ug {
@@ -261,7 +263,44 @@ void id_cnts(const LazyBuffer &b, std::unordered_map<size_t, size_t> &cnts) {
   }
 }
 
+bool fusable(const Op &o) {
+  return o.kind == Op::Unary || o.kind == Op::Binary || o.kind == Op::Reduce || o.kind == Op::Layout || o.kind == Op::Const;
+}
+
 struct Context {  // schedule.rs:308-475
+  // This backend's addition to the cut rule of schedule.rs:429-435 (a node with several users gets a kernel of
+  // its own): when ALL users of such a node end up inside one and the same fused kernel, materialising it would
+  // only buy an HBM round trip -- `exp(x - max)` of model.rs:98-100 feeds the sum and the division of the same
+  // softmax row -- so the node is evaluated in place (twice, from registers) and the row is read and written once.
+  bool fuse_private = false;
+  std::unordered_set<size_t> inlined;
+  // number of edges into every node reached from `b` without crossing a cut
+  void region_edges(const LazyBuffer &b, bool root, std::unordered_map<size_t, size_t> &seen, std::unordered_set<size_t> &multi) const {
+    if (b.realized()) return;
+    if (!root) {
+      size_t &c = seen[b->id];
+      c += 1;
+      if (c > 1) return;
+      auto it = cnts.find(b->id);
+      if (it != cnts.end() && it->second > 1 && !inlined.count(b->id)) { multi.insert(b->id); return; }   // a cut (so far)
+    }
+    const Op &o = b->op;
+    if (!fusable(o)) return;
+    if (o.a0) region_edges(o.a0, false, seen, multi);
+    if (o.kind == Op::Binary && o.a1) region_edges(o.a1, false, seen, multi);
+  }
+  void find_private(const LazyBuffer &root) {
+    if (!fuse_private || root.realized() || !fusable(root->op)) return;
+    for (int round = 0; round < 8; ++round) {
+      std::unordered_map<size_t, size_t> seen;
+      std::unordered_set<size_t> multi;
+      region_edges(root, true, seen, multi);
+      bool changed = false;
+      for (size_t id : multi)
+        if (seen[id] == cnts[id] && inlined.size() < 64) { inlined.insert(id); changed = true; }
+      if (!changed) break;
+    }
+  }
   std::vector<ScheduleItem> items;
   std::map<ArgId, LazyBuffer> per_arg_id;
   std::unordered_map<size_t, op::AstP> ast_cache;
@@ -292,7 +331,10 @@ struct Context {  // schedule.rs:308-475
     items.push_back(std::move(si));
     return dst_id;
   }
-  ArgId push_schedule_item(const LazyBuffer &b) { return push_kernel(b, walk(b), nullptr); }
+  ArgId push_schedule_item(const LazyBuffer &b) {
+    find_private(b);
+    return push_kernel(b, walk(b), nullptr);
+  }
 
   op::AstP load_of(ArgId id, const LazyBuffer &b) { return op::load(id, Layout::from_shape(b->shape), b->dtype); }
 
@@ -372,7 +414,7 @@ struct Context {  // schedule.rs:308-475
     }
     // a subtree with more than one user gets a kernel of its own (schedule.rs:429-435)
     auto c = cnts.find(b->id);
-    if (c != cnts.end() && c->second > 1) {
+    if (c != cnts.end() && c->second > 1 && !inlined.count(b->id)) {
       ArgId dst = push_kernel(b, ast, nullptr);
       ast = load_of(dst, b);
     }
@@ -385,6 +427,7 @@ struct Context {  // schedule.rs:308-475
 Schedule Schedule::create(const std::vector<LazyBuffer> &buffers) {
   if (buffers.empty()) bail("no buffers provided");
   Context ctx;
+  ctx.fuse_private = buffers[0]->device->launch_policy() == LaunchPolicy::B200;
   for (auto &b : buffers) id_cnts(b, ctx.cnts);
   for (auto &b : buffers) ctx.push_schedule_item(b);
   Schedule s;
@@ -492,6 +535,19 @@ CompiledSchedule Schedule::compile_with_cache(CompilationCache &cache) const {
         if (it != cache.op_cache.end()) { cf.func = it->second; cache.hits++; break; }
         const std::string name = kernel.ops.empty() ? std::string() : kernel.ops[0].name();
         kernel = optimize(std::move(kernel));
+        if (device->launch_policy() == LaunchPolicy::B200) {
+          // row-reduce + map and pure-map kernels run on generated 128-bit code; everything else on the SSA path
+          FastKernel fk;
+          if (fast_kernel(kernel, name.empty() ? "k" : name, fk)) {
+            cf.func = device->compile_cu(fk);
+            if (cf.func) {
+              cf.func->origin = fk.origin;
+              cache.op_cache.emplace(std::move(norm), cf.func);
+              cache.misses++;
+              break;
+            }
+          }
+        }
         Opts opts;
         switch (device->launch_policy()) {
           case LaunchPolicy::Sequential: break;

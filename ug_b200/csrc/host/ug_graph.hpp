@@ -18,6 +18,14 @@ struct Slice {
 
 struct Func {
   virtual ~Func() = default;
+  std::string origin = "ssa";   // which generator produced the code: "ssa" (per-instruction code of the SSA path) or one
+                                // of the vectorised shapes of fast_kernel() ("row_vec4", "warp_row_vec4", "map_vec4")
+};
+
+// A kernel as CUDA C source with its launch shape (see fast_kernel in ug_fast.cpp).
+struct FastKernel {
+  std::string source, func_name, origin;
+  LaunchConfig launch;
 };
 
 // How Schedule::compile picks the launch shape of a fused kernel.
@@ -37,6 +45,9 @@ struct Device {
   virtual void matmul(Slice &dst, const Slice &lhs, const Slice &rhs, size_t b, size_t m, size_t n, size_t k,
                       const Layout &lhs_l, const Layout &rhs_l) = 0;
   virtual bool use_grid() const = 0;
+  // Compiles caller-generated CUDA C whose parameters are the kernel's arguments (device pointers) in order;
+  // a device without run-time compilation of source returns null and the SSA path is taken.
+  virtual std::shared_ptr<Func> compile_cu(const FastKernel &) { return nullptr; }
   virtual LaunchPolicy launch_policy() const { return use_grid() ? LaunchPolicy::ReferenceGrid : LaunchPolicy::Sequential; }
 };
 
@@ -171,6 +182,9 @@ struct Schedule {
   CompiledSchedule compile() const { CompilationCache c; return compile_with_cache(c); }
   CompiledSchedule compile_with_cache(CompilationCache &cache) const;  // schedule.rs:115-207
 };
+
+// Vectorised CUDA C for row-reduce + map and pure-map kernels (ug_fast.cpp); false = not one of those shapes.
+bool fast_kernel(const op::Kernel &optimized, const std::string &name, FastKernel &out);
 
 // Launch shapes: the reference's heuristic and this backend's.
 Opts reference_opts(const op::Kernel &optimized);

@@ -391,6 +391,15 @@ class CompiledSchedule:
     def __len__(self):
         return host.ugh_compiled_n_funcs(self._h)
 
+    def origins(self):
+        """Per function: "matmul", "custom", "ssa", or the generated vectorised shape it runs on."""
+        out = []
+        for i in range(len(self)):
+            buf = C.create_string_buffer(64)
+            _chk(host.ugh_compiled_func_origin(self._h, i, buf, len(buf)))
+            out.append(buf.value.decode())
+        return out
+
 
 class Schedule:
     """ug::Schedule (ug-core/src/schedule.rs:62-207)."""
@@ -420,6 +429,12 @@ class Schedule:
         """SSA listing of kernel item ``i``: policy -1 default Opts, 0 reference grid, 1 this backend's."""
         buf = C.create_string_buffer(1 << 20)
         _chk(host.ugh_schedule_item_ssa_text(self._h, i, policy, buf, len(buf)))
+        return buf.value.decode()
+
+    def fast_source(self, i):
+        """CUDA C generated for kernel item ``i`` when it is a row or map kernel ("" otherwise)."""
+        buf = C.create_string_buffer(1 << 20)
+        _chk(host.ugh_schedule_item_fast_source(self._h, i, buf, len(buf)))
         return buf.value.decode()
 
     def compile(self, cache=None):
