@@ -75,3 +75,41 @@ def test_maps_copies_and_unaligned_shapes(hd):
     assert set(c.origins()) == {"ssa"}
     ref = oracle.custom_softmax(y)
     assert np.max(np.abs(got.reshape(y.shape) - ref) / np.maximum(ref, 1e-30)) < 1e-5
+
+
+def test_index_select_ssa_runs_on_the_gather_operator(hd):
+    emb = synth.normal(19, (50, 64))
+    ids = np.array([[3, 49, 0, 7, 7]], np.int32)
+    y = G.index_select(LB.copy(emb, emb.shape, hd), LB.copy(ids, ids.shape, hd))
+    s = Schedule.create_one(y)
+    c = s.compile()
+    assert s.items() == ["Ssa"] and c.origins() == ["index_select"]
+    c.run()
+    assert np.array_equal(y.data_vec().reshape(1, 5, 64), emb[ids[0]][None])
+
+
+def test_no_item_of_an_unmodified_llama_step_is_left_on_per_instruction_code(hd):
+    """Every fused kernel of ug-llama's decode step (ug-llama/src/model.rs:203-269, SURVEY's 14 generated kernels
+    per layer) is a row, map or copy kernel of the generator; logits agree with the CPU oracle."""
+    from oracle import llama_ref as R
+    from ug_b200.llama import Config
+    cfg = Config(hidden_size=256, intermediate_size=512, max_position_embeddings=64, num_attention_heads=4,
+                 num_key_value_heads=2, num_hidden_layers=2, vocab_size=96)
+    w = synth.llama_weights_f32(synth.llama_weights(cfg))
+    ref = R.Model(R.Config(**cfg.__dict__), w, custom_softmax_op=False)
+    model = G.Model(cfg, w, hd, custom_softmax_op=False)
+    toks = synth.tokens(6, (1, 9), cfg.vocab_size)
+    cache, rcache = model.new_cache(), ref.new_cache()
+    seen = set()
+    for lo, hi in ((0, 8), (8, 9)):
+        t = LB.copy(toks[:, lo:hi], (1, hi - lo), hd)
+        pos = LB.copy(np.array([[lo]], np.int32), (1, 1), hd)
+        out = model.fwd(t, pos, cache)
+        c = Schedule.create_one(out).compile()
+        seen |= set(c.origins())
+        c.run()
+        got = out.data_vec().reshape(1, hi - lo, cfg.vocab_size)
+        want = ref.fwd(toks[:, lo:hi], lo, rcache)
+        assert np.max(np.abs(got - want)) < 1e-4 * np.abs(want).max()
+    assert "ssa" not in seen
+    assert {"matmul", "custom", "index_select"} <= seen and seen & {"row_vec4", "warp_row_vec4"} and "map_vec4" in seen

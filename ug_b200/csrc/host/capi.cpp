@@ -29,7 +29,8 @@ struct B200Slice : Slice {
   ugb_device *dev = nullptr;
 };
 struct B200Func : Func {
-  ugb_func *h = nullptr;
+  ugb_func *h = nullptr;       // a compiled kernel, or null for an operator of the library:
+  size_t gather_ids = 0, gather_h = 0;   // ugb_index_select over (table, ids, dst)
   ~B200Func() override { if (h) ugb_func_free(h); }
 };
 void check(ugb_device *d, int32_t rc) {
@@ -123,6 +124,7 @@ struct B200Device : Device {
   }
   std::shared_ptr<Func> compile_cu(const FastKernel &fk) override {
     auto f = std::make_shared<B200Func>();
+    if (fk.origin == "index_select") { f->gather_ids = fk.n_ids; f->gather_h = fk.h; return f; }
     check(d, ugb_compile_cu(d, fk.source.c_str(), fk.func_name.c_str(), fk.launch.grid_dim, fk.launch.block_dim,
                             fk.launch.shared_mem, &f->h));
     return f;
@@ -134,7 +136,13 @@ struct B200Device : Device {
       if (!b) bail("run: slice of another device");
       hs.push_back(b->h);
     }
-    check(d, ugb_run(d, static_cast<B200Func &>(f).h, hs.data(), hs.size()));
+    auto &bf = static_cast<B200Func &>(f);
+    if (!bf.h) {   // the library's row gather: bad ids raise the status word instead of reading out of bounds
+      if (hs.size() != 3 || bf.gather_h == 0) bail("index_select takes (table, ids, dst)");
+      check(d, ugb_index_select(d, hs[0], hs[1], hs[2], bf.gather_ids, bf.gather_h, ugb_slice_len(hs[0]) / bf.gather_h));
+      return;
+    }
+    check(d, ugb_run(d, bf.h, hs.data(), hs.size()));
   }
   void matmul(Slice &dst, const Slice &lhs, const Slice &rhs, size_t b, size_t m, size_t n, size_t k, const Layout &ll,
               const Layout &rl) override {

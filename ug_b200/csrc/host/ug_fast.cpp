@@ -378,4 +378,34 @@ bool fast_kernel(const op::Kernel &k, const std::string &name, FastKernel &out) 
   }
 }
 
+// ug-llama/src/model.rs:32-63 as instructions: globals src (f32), ids (i32), dst (f32); for r in 0..n: the id is
+// loaded (with an f32 tag, as the reference writes it), multiplied by h; for c in 0..h: dst[r * h + c] = src[id * h + c].
+bool fast_ssa_kernel(const ssa::Kernel &k, FastKernel &out) {
+  using ssa::K;
+  const auto &in = k.instrs;
+  if (in.size() != 14 || k.args.size() != 3) return false;
+  const K kinds[14] = {K::DefineGlobal, K::DefineGlobal, K::DefineGlobal, K::Range, K::Load, K::Binary, K::Binary,
+                       K::Range, K::Binary, K::Binary, K::Load, K::Store, K::EndRange, K::EndRange};
+  for (int i = 0; i < 14; ++i) if (in[i].kind != kinds[i]) return false;
+  auto is_i32 = [](const ssa::A &a, long &v) { if (a.is_var || a.cst.dtype != DType::I32) return false; v = a.cst.i32; return true; };
+  auto is_var = [](const ssa::A &a, size_t v) { return a.is_var && a.var == v; };
+  long lo1, n, lo2, h, h5, h6;
+  if (in[0].dtype != DType::F32 || in[1].dtype != DType::I32 || in[2].dtype != DType::F32) return false;
+  if (!is_i32(in[3].a0, lo1) || !is_i32(in[3].a1, n) || lo1 != 0 || in[3].index != 1) return false;
+  if (in[4].v0 != 1 || !is_var(in[4].a0, 3)) return false;                                   // ids[r]
+  if (in[5].bop != BinaryOp::Mul || !is_var(in[5].a0, 4) || !is_i32(in[5].a1, h5)) return false;
+  if (in[6].bop != BinaryOp::Mul || !is_var(in[6].a0, 3) || !is_i32(in[6].a1, h6)) return false;
+  if (!is_i32(in[7].a0, lo2) || !is_i32(in[7].a1, h) || lo2 != 0 || in[7].index != 1 || h5 != h || h6 != h) return false;
+  if (in[8].bop != BinaryOp::Add || !is_var(in[8].a0, 5) || !is_var(in[8].a1, 7)) return false;
+  if (in[9].bop != BinaryOp::Add || !is_var(in[9].a0, 6) || !is_var(in[9].a1, 7)) return false;
+  if (in[10].v0 != 0 || !is_var(in[10].a0, 8) || in[10].dtype != DType::F32) return false;   // src[id * h + c]
+  if (in[11].v0 != 2 || !is_var(in[11].a0, 9) || !is_var(in[11].a1, 10)) return false;       // dst[r * h + c]
+  if (n <= 0 || h <= 0) return false;
+  out = FastKernel{};
+  out.origin = "index_select";
+  out.n_ids = (size_t)n;
+  out.h = (size_t)h;
+  return true;
+}
+
 }  // namespace ug

@@ -516,7 +516,12 @@ CompiledSchedule Schedule::compile_with_cache(CompilationCache &cache) const {
         auto it = cache.ssa_cache.find(item.ssa_kernel.instrs);
         if (it != cache.ssa_cache.end()) { cf.func = it->second; cache.hits++; }
         else {
-          cf.func = device->compile(item.ssa_kernel, nullptr);
+          FastKernel fk;
+          if (device->launch_policy() == LaunchPolicy::B200 && fast_ssa_kernel(item.ssa_kernel, fk)) {
+            cf.func = device->compile_cu(fk);
+            if (cf.func) cf.func->origin = fk.origin;
+          }
+          if (!cf.func) cf.func = device->compile(item.ssa_kernel, nullptr);
           cache.ssa_cache[item.ssa_kernel.instrs] = cf.func;
           cache.misses++;
         }

@@ -26,6 +26,9 @@ struct Func {
 struct FastKernel {
   std::string source, func_name, origin;
   LaunchConfig launch;
+  // origin "index_select": no source; the device runs its row-gather operator on (table, ids, dst) with
+  // n_ids rows of h elements (the table's row count comes from the slice at run time)
+  size_t n_ids = 0, h = 0;
 };
 
 // How Schedule::compile picks the launch shape of a fused kernel.
@@ -185,6 +188,9 @@ struct Schedule {
 
 // Vectorised CUDA C for row-reduce + map and pure-map kernels (ug_fast.cpp); false = not one of those shapes.
 bool fast_kernel(const op::Kernel &optimized, const std::string &name, FastKernel &out);
+// Hand-built SSA the model feeds through LB::ssa that has a dedicated kernel: ug-llama's index_select
+// (ug-llama/src/model.rs:32-63, two nested loops run by a single thread in the reference).
+bool fast_ssa_kernel(const ssa::Kernel &k, FastKernel &out);
 
 // Launch shapes: the reference's heuristic and this backend's.
 Opts reference_opts(const op::Kernel &optimized);
