@@ -235,6 +235,20 @@ UGB_API int32_t ugb_compile_cu(ugb_device *dev, const char *cu_code, const char 
 UGB_API int32_t ugb_compile_ptx(ugb_device *dev, const char *ptx_code, const char *func_name,
                                 uint32_t grid_dim, uint32_t block_dim, uint32_t shared_mem,
                                 ugb_func **out);
+/* The shape-polymorphic compile cache of the host layer (ug-core/src/cache.rs:8-101 keys on shapes, so every
+ * kernel whose shape follows the KV length is recompiled each token, ug-llama/src/main.rs:140-149) works on the
+ * CUDA C this library generates from SSA: ugb_ssa_source returns that text for an entry-point name of the
+ * caller's choice without compiling it (the kernel's parameters are its pointers, one length per pointer, the
+ * status word), together with the dtypes of the pointer arguments; ugb_compile_generated compiles a text of that
+ * form whose parameter list ends in n_dyn extra `const long long` values; ugb_run_dyn launches a function with a
+ * grid size and those values chosen per call (n_dyn == 0 and the compiled grid make it ugb_run). */
+UGB_API int32_t ugb_ssa_source(ugb_device *dev, const ugb_ssa_instr *instrs, size_t n_instrs, const char *entry_name,
+                               char *buf, size_t buf_len, int32_t *arg_dtypes, size_t max_args, size_t *n_args);
+UGB_API int32_t ugb_compile_generated(ugb_device *dev, const char *cu_code, const char *entry_name,
+                                      const int32_t *arg_dtypes, size_t n_args, int32_t n_dyn, uint32_t grid_dim,
+                                      uint32_t block_dim, uint32_t shared_mem, ugb_func **out);
+UGB_API int32_t ugb_run_dyn(ugb_device *dev, ugb_func *f, ugb_slice *const *args, size_t n_args, uint32_t grid_dim,
+                            const int64_t *dyn, size_t n_dyn);
 UGB_API int32_t ugb_func_free(ugb_func *f);
 /* The CUDA C this backend generated for the kernel (inspection, tests). */
 UGB_API const char *ugb_func_source(const ugb_func *f);

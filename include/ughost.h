@@ -103,6 +103,10 @@ UGB_API ugh_cache *ugh_cache_create(void);
 UGB_API void ugh_cache_free(ugh_cache *c);
 UGB_API size_t ugh_cache_hits(const ugh_cache *c);
 UGB_API size_t ugh_cache_misses(const ugh_cache *c);
+/* Hits served by a shape-generic function (a kernel seen before at another size; part of ugh_cache_hits), and the
+ * switch for that reuse (default on; off = the reference's per-shape behaviour, ug-core/src/cache.rs:8-12). */
+UGB_API size_t ugh_cache_poly_hits(const ugh_cache *c);
+UGB_API void ugh_cache_set_polymorphic(ugh_cache *c, int32_t on);
 UGB_API ugh_compiled *ugh_schedule_compile(const ugh_schedule *s, ugh_cache *cache_or_null);
 UGB_API void ugh_compiled_free(ugh_compiled *c);
 UGB_API int32_t ugh_compiled_run(const ugh_compiled *c);

@@ -56,8 +56,15 @@ def test_row_and_map_kernels_are_generated_and_compile(hd):
     compiles(wide)
 
 
-def test_shapes_without_a_128_bit_form_are_declined(hd):
+def test_rows_without_a_128_bit_form_and_shapes_that_are_declined(hd):
     y = LB.copy(synth.normal(5, (5, 777)), (5, 777), hd)
-    assert sources(G.softmax(y)) == ["", ""]
+    soft = sources(G.softmax(y))                                        # 777 % 4 != 0: one element per access
+    assert len(soft) == 2 and all(s.startswith("// row_scalar") and "float4" not in s.split("extern")[1] for s in soft)
+    compiles(soft[0])
+    # the head merge of model.rs:243 ([.., heads, 64] -> [.., heads * 64]): the column splits into (col / 64, col % 64)
+    a = LB.copy(synth.normal(7, (1, 4, 8, 64)), (1, 4, 8, 64), hd)
+    (merge,) = sources(a.transpose(2, 1).merge_dims(-2))
+    assert merge.startswith("// warp_row_vec4") and "/ 64L" in merge and "% 64L" in merge
+    compiles(merge)
     x = LB.copy(synth.normal(6, (8, 64)), (8, 64), hd)
-    assert sources(x.reduce(0, 0)) == [""]                              # a reduction over the leading dim
+    assert sources(x.reduce(0, 0)) == [""]                              # a reduction over the leading dim: SSA path

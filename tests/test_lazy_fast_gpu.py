@@ -69,12 +69,22 @@ def test_maps_copies_and_unaligned_shapes(hd):
     _, c, got = run(G.repeat(LB.copy(k, k.shape, hd), 1, 8))
     assert c.origins() == ["warp_row_vec4"]
     assert np.array_equal(got.reshape(1, 32, 37, 64), np.repeat(k, 8, axis=1))
-    # a row length that is not a multiple of 4 has no 128-bit form: the SSA path takes it, same result
-    y = synth.normal(18, (5, 777))
-    _, c, got = run(G.softmax(LB.copy(y, y.shape, hd)))
-    assert set(c.origins()) == {"ssa"}
-    ref = oracle.custom_softmax(y)
-    assert np.max(np.abs(got.reshape(y.shape) - ref) / np.maximum(ref, 1e-30)) < 1e-5
+    # a row length that is not a multiple of 4 has no 128-bit form: the same kernel with one element per access
+    for shape, origin in (((5, 777), "row_scalar"), ((6, 9), "warp_row_scalar")):
+        y = synth.normal(18, shape)
+        _, c, got = run(G.softmax(LB.copy(y, y.shape, hd)))
+        assert c.origins() == [origin]
+        ref = oracle.custom_softmax(y)
+        assert np.max(np.abs(got.reshape(y.shape) - ref) / np.maximum(ref, 1e-30)) < 1e-5
+    # the head merge of model.rs:243: transpose(2, 1) then merge_dims -- the column index splits into (head, dim)
+    a = synth.normal(20, (1, 4, 8, 64))
+    _, c, got = run(LB.copy(a, a.shape, hd).transpose(2, 1).merge_dims(-2))
+    assert c.origins() == ["warp_row_vec4"]
+    assert np.array_equal(got.reshape(1, 8, 256), a.transpose(0, 2, 1, 3).reshape(1, 8, 256))
+    # a reduction over a leading dim is none of the generated shapes: per-instruction code from the SSA
+    z = synth.normal(22, (8, 64))
+    _, c, got = run(LB.copy(z, z.shape, hd).reduce(0, 0))
+    assert c.origins() == ["ssa"]
 
 
 def test_index_select_ssa_runs_on_the_gather_operator(hd):
@@ -111,5 +121,52 @@ def test_no_item_of_an_unmodified_llama_step_is_left_on_per_instruction_code(hd)
         got = out.data_vec().reshape(1, hi - lo, cfg.vocab_size)
         want = ref.fwd(toks[:, lo:hi], lo, rcache)
         assert np.max(np.abs(got - want)) < 1e-4 * np.abs(want).max()
-    assert "ssa" not in seen
+    assert "ssa" not in seen, seen
     assert {"matmul", "custom", "index_select"} <= seen and seen & {"row_vec4", "warp_row_vec4"} and "map_vec4" in seen
+
+
+def test_decode_loop_stops_compiling_once_the_kv_dependent_kernels_are_generic(hd):
+    """ug-llama's step loop (ug-llama/src/main.rs:127-169: build the graph, compile_with_cache, run) over 32 tokens.
+    The reference's cache keys on shapes (ug-core/src/cache.rs:8-12), so the kernels whose shape follows the KV
+    length miss on every token.  Here each of them is compiled as it is on the first sighting, as a function of
+    the size on the second, and never again: no miss from the third decode step on, same logits as with
+    per-shape kernels, and both agree with the CPU oracle."""
+    from oracle import llama_ref as R
+    from ug_b200.lazy import CompilationCache
+    from ug_b200.llama import Config
+    cfg = Config(hidden_size=256, intermediate_size=512, max_position_embeddings=64, num_attention_heads=4,
+                 num_key_value_heads=2, num_hidden_layers=2, vocab_size=96)
+    w = synth.llama_weights_f32(synth.llama_weights(cfg))
+    ref = R.Model(R.Config(**cfg.__dict__), w, custom_softmax_op=False)
+    toks = synth.tokens(21, (1, 40), cfg.vocab_size)
+
+    def loop(polymorphic, n_steps):
+        model = G.Model(cfg, w, hd, custom_softmax_op=False)
+        cache, kv = CompilationCache(), model.new_cache()
+        cache.set_polymorphic(polymorphic)
+        misses, logits = [], []
+        # a prompt of 8 positions, then one token per step
+        spans = [(0, 8)] + [(8 + i, 9 + i) for i in range(n_steps)]
+        for lo, hi in spans:
+            t = LB.copy(toks[:, lo:hi], (1, hi - lo), hd)
+            pos = LB.copy(np.array([[lo]], np.int32), (1, 1), hd)
+            out = model.fwd(t, pos, kv)
+            before = cache.misses
+            Schedule.create_one(out).compile(cache).run()
+            misses.append(cache.misses - before)
+            logits.append(out.data_vec().reshape(hi - lo, cfg.vocab_size)[-1])
+        return misses, logits, cache
+
+    misses, logits, cache = loop(True, 32)
+    assert misses[1] > 0 and misses[2] > 0           # first decode step: as it is; second: the generic functions
+    assert misses[3:] == [0] * 30, misses
+    assert cache.poly_hits > 0
+    ref_misses, ref_logits, _ = loop(False, 8)
+    assert all(m > 0 for m in ref_misses[1:])        # per-shape kernels: every token compiles
+    for a, b in zip(logits[:9], ref_logits):
+        assert np.max(np.abs(a - b)) < 1e-5 * np.abs(b).max()
+    rcache, worst = ref.new_cache(), 0.0
+    for (lo, hi), got in zip([(0, 8)] + [(8 + i, 9 + i) for i in range(32)], logits):
+        want = ref.fwd(toks[:, lo:hi], lo, rcache)[0, -1]
+        worst = max(worst, float(np.max(np.abs(got - want)) / np.abs(want).max()))
+    assert worst < 1e-4

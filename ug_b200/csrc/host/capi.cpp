@@ -31,6 +31,7 @@ struct B200Slice : Slice {
 struct B200Func : Func {
   ugb_func *h = nullptr;       // a compiled kernel, or null for an operator of the library:
   size_t gather_ids = 0, gather_h = 0;   // ugb_index_select over (table, ids, dst)
+  bool empty = false;                    // a store of zero elements: nothing to launch
   ~B200Func() override { if (h) ugb_func_free(h); }
 };
 void check(ugb_device *d, int32_t rc) {
@@ -125,9 +126,40 @@ struct B200Device : Device {
   std::shared_ptr<Func> compile_cu(const FastKernel &fk) override {
     auto f = std::make_shared<B200Func>();
     if (fk.origin == "index_select") { f->gather_ids = fk.n_ids; f->gather_h = fk.h; return f; }
+    if (fk.origin == "empty") { f->empty = true; return f; }
     check(d, ugb_compile_cu(d, fk.source.c_str(), fk.func_name.c_str(), fk.launch.grid_dim, fk.launch.block_dim,
                             fk.launch.shared_mem, &f->h));
     return f;
+  }
+  bool ssa_source(const ssa::Kernel &k, const std::string &entry, GeneratedSource &out) override {
+    std::vector<ugb_ssa_instr> ins;
+    ins.reserve(k.instrs.size());
+    for (auto &i : k.instrs) ins.push_back(to_c(i));
+    std::vector<char> buf(1 << 18);
+    int32_t dts[32];
+    size_t n_args = 0;
+    if (ugb_ssa_source(d, ins.data(), ins.size(), entry.c_str(), buf.data(), buf.size(), dts, 32, &n_args) != 0) return false;
+    out.text = buf.data();
+    out.arg_dtypes.clear();
+    for (size_t i = 0; i < n_args; ++i) out.arg_dtypes.push_back((DType)dts[i]);
+    return true;
+  }
+  std::shared_ptr<Func> compile_generated(const GeneratedSource &g, const std::string &entry, int n_dyn, const LaunchConfig &lc) override {
+    std::vector<int32_t> dts;
+    for (DType t : g.arg_dtypes) dts.push_back((int32_t)t);
+    auto f = std::make_shared<B200Func>();
+    check(d, ugb_compile_generated(d, g.text.c_str(), entry.c_str(), dts.data(), dts.size(), n_dyn, lc.grid_dim, lc.block_dim,
+                                   lc.shared_mem, &f->h));
+    return f;
+  }
+  void run_dyn(Func &f, std::vector<Slice *> &args, uint32_t grid, const std::vector<int64_t> &dyn) override {
+    std::vector<ugb_slice *> hs;
+    for (Slice *s : args) {
+      auto *b = dynamic_cast<B200Slice *>(s);
+      if (!b) bail("run: slice of another device");
+      hs.push_back(b->h);
+    }
+    check(d, ugb_run_dyn(d, static_cast<B200Func &>(f).h, hs.data(), hs.size(), grid, dyn.data(), dyn.size()));
   }
   void run(Func &f, std::vector<Slice *> &args) override {
     std::vector<ugb_slice *> hs;
@@ -137,6 +169,7 @@ struct B200Device : Device {
       hs.push_back(b->h);
     }
     auto &bf = static_cast<B200Func &>(f);
+    if (bf.empty) return;
     if (!bf.h) {   // the library's row gather: bad ids raise the status word instead of reading out of bounds
       if (hs.size() != 3 || bf.gather_h == 0) bail("index_select takes (table, ids, dst)");
       check(d, ugb_index_select(d, hs[0], hs[1], hs[2], bf.gather_ids, bf.gather_h, ugb_slice_len(hs[0]) / bf.gather_h));
@@ -339,7 +372,7 @@ int32_t ugh_schedule_item_fast_source(const ugh_schedule *s, size_t i, char *buf
     op::Kernel k = optimize(s->s.items[i].kernel());
     FastKernel fk;
     std::string t;
-    if (fast_kernel(k, "k", fk))
+    if (fast_kernel(k, "k", fk) && !fk.source.empty())
       t = "// " + fk.origin + " " + fk.func_name + " grid " + std::to_string(fk.launch.grid_dim) + " block " +
           std::to_string(fk.launch.block_dim) + "\n" + fk.source;
     if (t.size() + 1 > buf_len) bail("buffer too small: ", t.size() + 1, " bytes needed");
@@ -350,6 +383,8 @@ ugh_cache *ugh_cache_create(void) { return new ugh_cache(); }
 void ugh_cache_free(ugh_cache *c) { delete c; }
 size_t ugh_cache_hits(const ugh_cache *c) { return c->c.hits; }
 size_t ugh_cache_misses(const ugh_cache *c) { return c->c.misses; }
+size_t ugh_cache_poly_hits(const ugh_cache *c) { return c->c.poly_hits; }
+void ugh_cache_set_polymorphic(ugh_cache *c, int32_t on) { c->c.polymorphic = on != 0; }
 ugh_compiled *ugh_schedule_compile(const ugh_schedule *s, ugh_cache *cache) {
   return guard_ptr([&] {
     if (cache) return new ugh_compiled{s->s.compile_with_cache(cache->c)};

@@ -6,6 +6,7 @@
 //                      one 128-bit read per operand element and one 128-bit write per result element;
 //   * map kernels   -- a 1-D store of a pure map (silu(gate) * up, residual add, ...): 4096 elements per
 //                      CTA, 128-bit accesses.
+// Rows whose length or bases rule 128-bit accesses out get the same kernels with one element per access (coalesced).
 // This replaces, for these shapes, the per-instruction scalar code the SSA path generates
 // (ug-cuda/src/code_gen.rs:68-186 in the reference: one 4-byte access per statement) and the launch shapes
 // of ug-core/src/schedule.rs:162-188.  Anything the analysis below does not understand (non-affine
@@ -27,14 +28,18 @@ namespace ug {
 
 namespace {
 
-// One index (or address) as a function of the store's loop indexes: cc * column + row part + off, where the
-// row part is any integer expression of the leading indexes i0, i1, ... (kept as C text) that is known to be a
-// multiple of `rm` (0: there is no row part).
+// One index (or address) as a function of the store's loop indexes:
+//   column part + row part + off
+// The column part is cc * col, or -- after a merge_dims of the store's last dim, e.g. the head merge
+// [.., heads, 64] -> [.., heads * 64] of model.rs:243 -- ch * (col / cd) + cl * (col % cd).  The row part is any
+// integer expression of the leading indexes i0, i1, ... (kept as C text) known to be a multiple of `rm`.
 struct Affine {
   long cc = 0;
+  long cd = 0, ch = 0, cl = 0;   // cd != 0: split column
   std::string re;
   long rm = 0;
   long off = 0;
+  bool col_free() const { return cc == 0 && (cd == 0 || (ch == 0 && cl == 0)); }
 };
 using Idx = std::vector<Affine>;
 
@@ -44,8 +49,12 @@ long gcd_l(long a, long b) { a = a < 0 ? -a : a; b = b < 0 ? -b : b; while (b) {
 Affine aff_const(long c) { Affine a; a.off = c; return a; }
 Affine aff_add(const Affine &x, const Affine &y) {
   Affine a;
-  a.cc = x.cc + y.cc;
   a.off = x.off + y.off;
+  if (x.cd == 0 && y.cd == 0) a.cc = x.cc + y.cc;
+  else if (x.cd != 0 && y.cd != 0 && x.cd == y.cd) { a.cd = x.cd; a.ch = x.ch + y.ch; a.cl = x.cl + y.cl; }
+  else if (x.cd != 0 && y.cd == 0 && y.cc == 0) { a.cd = x.cd; a.ch = x.ch; a.cl = x.cl; }
+  else if (y.cd != 0 && x.cd == 0 && x.cc == 0) { a.cd = y.cd; a.ch = y.ch; a.cl = y.cl; }
+  else throw NotApplicable{};
   if (x.re.empty()) { a.re = y.re; a.rm = y.rm; }
   else if (y.re.empty()) { a.re = x.re; a.rm = x.rm; }
   else { a.re = "(" + x.re + " + " + y.re + ")"; a.rm = gcd_l(x.rm, y.rm); }
@@ -53,23 +62,30 @@ Affine aff_add(const Affine &x, const Affine &y) {
 }
 Affine aff_scale(const Affine &x, long s) {
   Affine a = x;
-  a.cc *= s;
+  a.cc *= s; a.ch *= s; a.cl *= s;
   a.off *= s;
-  if (s == 0) { a.re.clear(); a.rm = 0; }
+  if (s == 0) { a.re.clear(); a.rm = 0; a.cd = 0; }
   else if (!a.re.empty() && s != 1) { a.re = "(" + a.re + " * " + std::to_string(s) + "L)"; a.rm *= s; }
   return a;
 }
-// idx / n and idx % n: only for indexes that do not move with the column
+// idx / n and idx % n
 Affine aff_divmod(const Affine &x, long n, bool mod) {
-  if (x.cc != 0) throw NotApplicable{};
   Affine a;
-  if (x.re.empty()) { a.off = mod ? x.off % n : x.off / n; return a; }
-  a.re = "((" + x.re + " + " + std::to_string(x.off) + "L) " + (mod ? "% " : "/ ") + std::to_string(n) + "L)";
-  a.rm = 1;
-  return a;
+  if (x.col_free()) {
+    if (x.re.empty()) { a.off = mod ? x.off % n : x.off / n; return a; }
+    a.re = "((" + x.re + " + " + std::to_string(x.off) + "L) " + (mod ? "% " : "/ ") + std::to_string(n) + "L)";
+    a.rm = 1;
+    return a;
+  }
+  if (x.cd == 0 && x.cc == 1 && x.re.empty() && x.off == 0) {   // the column itself
+    a.cd = n;
+    (mod ? a.cl : a.ch) = 1;
+    return a;
+  }
+  throw NotApplicable{};
 }
 
-// lower_op.rs:131-200 on these indexes; merge_dims (idx / n, idx % n) only where the index does not move with the column
+// lower_op.rs:131-200 on these indexes
 Idx layout_op(const Idx &in, const op::LayoutOp &op, const Shape &shape, const Shape &arg_shape) {
   Idx idxs = in;
   using L = op::LayoutOp;
@@ -140,29 +156,39 @@ struct Gen {
   const op::Kernel &k;
   size_t n = 0;              // rank of the store
   size_t cols = 0;
-  bool chunked = false;      // 1-D map cut into chunks (the affine "row" coefficient is the chunk length)
+  int W = 4;                 // elements per access: 4 (128-bit) or 1
+  bool chunked = false;      // 1-D map cut into chunks (the element index is row * chunk + column)
   std::vector<LoadSite> loads;
   std::vector<Pass> passes;
 
-  explicit Gen(const op::Kernel &k_) : k(k_) {}
+  Gen(const op::Kernel &k_, int w) : k(k_), W(w) {}
 
   size_t arg_pos(ArgId id) const {
     for (size_t i = 0; i < k.args.size(); ++i) if (k.args[i].id == id) return i;
     throw NotApplicable{};
   }
   size_t load_site(size_t arg, const Affine &addr) {
-    for (size_t i = 0; i < loads.size(); ++i)
-      if (loads[i].arg == arg && loads[i].addr.cc == addr.cc && loads[i].addr.re == addr.re && loads[i].addr.off == addr.off) return i;
+    for (size_t i = 0; i < loads.size(); ++i) {
+      const Affine &o = loads[i].addr;
+      if (loads[i].arg == arg && o.cc == addr.cc && o.cd == addr.cd && o.ch == addr.ch && o.cl == addr.cl && o.re == addr.re && o.off == addr.off) return i;
+    }
     LoadSite s;
     s.arg = arg;
     s.addr = addr;
-    const bool aligned = addr.off % 4 == 0 && (addr.re.empty() || addr.rm % 4 == 0);
-    if (addr.cc == 1 && aligned) s.kind = LoadSite::Vec;
-    else if (addr.cc == 0) s.kind = LoadSite::Scalar;
-    else s.kind = LoadSite::Gather;
+    const bool aligned = W == 1 || (addr.off % 4 == 0 && (addr.re.empty() || addr.rm % 4 == 0));
+    if (addr.col_free()) s.kind = LoadSite::Scalar;
+    else if (addr.cd == 0) s.kind = (addr.cc == 1 && aligned) ? LoadSite::Vec : LoadSite::Gather;
+    else s.kind = (addr.cl == 1 && aligned && (W == 1 || (addr.cd % 4 == 0 && addr.ch % 4 == 0))) ? LoadSite::Vec : LoadSite::Gather;
     if (chunked && s.kind == LoadSite::Gather) throw NotApplicable{};
+    if (chunked && addr.cd != 0) throw NotApplicable{};
     loads.push_back(s);
     return loads.size() - 1;
+  }
+  // element offset of column `col` (a C expression) from the load's row base
+  static std::string col_offset(const Affine &a, const std::string &col) {
+    if (a.cd == 0) return std::to_string(a.cc) + "L * (" + col + ")";
+    return "(" + std::to_string(a.ch) + "L * ((" + col + ") / " + std::to_string(a.cd) + "L) + " + std::to_string(a.cl) + "L * ((" + col + ") % " +
+           std::to_string(a.cd) + "L))";
   }
 
   // C expression of `a` at element J (register index) / column COL of the current row
@@ -181,9 +207,7 @@ struct Gen {
         switch (loads[s].kind) {
           case LoadSite::Vec: return "L" + std::to_string(s) + "[J]";
           case LoadSite::Scalar: return "S" + std::to_string(s);
-          case LoadSite::Gather:
-            return "__ldg(a" + std::to_string(loads[s].arg) + " + B" + std::to_string(s) + " + " +
-                   std::to_string(loads[s].addr.cc) + "L * COL)";
+          case LoadSite::Gather: return "__ldg(a" + std::to_string(loads[s].arg) + " + B" + std::to_string(s) + " + " + col_offset(loads[s].addr, "COL") + ")";
         }
         throw NotApplicable{};
       }
@@ -229,7 +253,7 @@ struct Gen {
         inner[dim] = aff_const(0);
         inner[dim].cc = 1;
         for (size_t d = 0; d < inner.size(); ++d)
-          if (d != dim && inner[d].cc != 0) throw NotApplicable{};
+          if (d != dim && !inner[d].col_free()) throw NotApplicable{};
         Pass p;
         p.node = a.get();
         p.rop = a->rop;
@@ -250,32 +274,26 @@ __device__ __forceinline__ float ugf_fold2(float a, float b) { return fminf(a, b
   for (int o_ = (W) / 2; o_ > 0; o_ >>= 1) v = FOLD(v, __shfl_xor_sync(0xffffffffu, v, o_));
 )";
 
-}  // namespace
-
-// Returns true and fills `out` when `k` (already through optimize()) is one of the shapes above.
-bool fast_kernel(const op::Kernel &k, const std::string &name, FastKernel &out) {
+bool generate(const op::Kernel &k, const std::string &name, int W, FastKernel &out) {
   try {
-    if (k.ops.size() != 1) return false;
     const op::Store &st = k.ops[0];
     const Layout &dl = st.layout;
-    if (st.value->dtype != DType::F32 || dl.rank() == 0 || dl.num_elements() == 0) return false;
-    if (!dl.c_contiguous() || dl.offset % 4 != 0) return false;
-    if (dl.num_elements() >= (1ull << 31)) return false;
-    Gen g(k);
+    Gen g(k, W);
     g.n = dl.rank();
     const size_t total = dl.num_elements();
-    constexpr size_t CHUNK = 4096;
+    const size_t CHUNK = 1024 * (size_t)W;
     size_t rows;
     if (dl.rank() == 1) {
       g.chunked = true;
       g.cols = CHUNK;
       rows = (total + CHUNK - 1) / CHUNK;
-      if (total % 4 != 0) return false;
+      if (total % W != 0) return false;
     } else {
       g.cols = dl.shape.back();
       rows = total / g.cols;
-      if (g.cols % 4 != 0) return false;
+      if (g.cols % W != 0) return false;
     }
+    if (W == 4 && dl.offset % 4 != 0) return false;
     Idx idx;
     for (size_t d = 0; d < g.n; ++d) {
       Affine a;
@@ -285,20 +303,21 @@ bool fast_kernel(const op::Kernel &k, const std::string &name, FastKernel &out) 
     }
     const std::string value = g.emit(st.value, idx);
     const size_t dst_arg = g.arg_pos(st.dst);
-    const size_t c4 = g.cols / 4;
+    const size_t cw = g.cols / W;          // accesses per row
     // lanes per row: part of a warp for short rows (several rows per warp), a whole CTA of 256 .. 1024 threads otherwise
-    const bool warp_mode = !g.chunked && c4 <= 256;
+    const bool warp_mode = !g.chunked && cw <= 256;
     int threads = 256;
-    if (warp_mode) threads = c4 <= 8 ? 8 : (c4 <= 16 ? 16 : 32);
-    else if (!g.chunked) while (threads < 1024 && (c4 + threads - 1) / threads > 8) threads *= 2;
+    if (warp_mode) threads = cw <= 8 ? 8 : (cw <= 16 ? 16 : 32);
+    else if (!g.chunked) while (threads < 1024 && (cw + threads - 1) / threads > 8) threads *= 2;
     const int block = warp_mode ? 256 : threads;
-    const size_t vpt = (c4 + threads - 1) / threads;
+    const size_t vpt = (cw + threads - 1) / threads;
     size_t cached = 0;
-    for (auto &l : g.loads) if (l.kind == LoadSite::Vec) cached += vpt * 4;
+    for (auto &l : g.loads) if (l.kind == LoadSite::Vec) cached += vpt * W;
     if (vpt > 8 || cached > 96) return false;
     for (auto &l : g.loads)      // a store into one of its own operands needs the element-wise order of the SSA path
       if (l.arg == dst_arg) return false;
 
+    const std::string ws = std::to_string(W);
     std::string s = PRELUDE;
     char buf[512];
     const std::string fn = "ugf_" + std::string(g.chunked ? "map" : (warp_mode ? "wrow" : "row")) + "_" + name;
@@ -310,7 +329,7 @@ bool fast_kernel(const op::Kernel &k, const std::string &name, FastKernel &out) 
       s += std::string(i ? ", " : "") + (i == dst_arg ? "float *__restrict__ a" : "const float *__restrict__ a") + std::to_string(i);
     }
     s += ") {\n";
-    snprintf(buf, sizeof buf, "  constexpr int T = %d, VPT = %zu, C4 = %zu;\n  constexpr long ROWS = %zuL, TOTAL = %zuL;\n", threads, vpt, c4, rows, total);
+    snprintf(buf, sizeof buf, "  constexpr int T = %d, VPT = %zu, W = %d, CW = %zu;\n  const long ROWS = %zuL, TOTAL = %zuL;\n", threads, vpt, W, cw, rows, total);
     s += buf;
     if (warp_mode) s += "  const int tid = threadIdx.x % T;\n  const long row = (long)blockIdx.x * (256 / T) + threadIdx.x / T;\n  const bool live_row = row < ROWS;\n";
     else s += "  const int tid = threadIdx.x;\n  const long row = blockIdx.x;\n  const bool live_row = true;\n  __shared__ float ugf_sm[2][T / 32];\n";
@@ -332,24 +351,30 @@ bool fast_kernel(const op::Kernel &k, const std::string &name, FastKernel &out) 
       }
       return e;
     };
-    const std::string live4 = g.chunked ? "(row * C4 + c4_ < TOTAL / 4)" : "(live_row && c4_ < C4)";
+    const std::string live = g.chunked ? "(row * CW + c_ < TOTAL / W)" : "(live_row && c_ < CW)";
+    const std::string vty = W == 4 ? "float4" : "float";
     for (size_t i = 0; i < g.loads.size(); ++i) {
       const LoadSite &l = g.loads[i];
       const std::string id = std::to_string(i), arg = "a" + std::to_string(l.arg);
       s += "  const long B" + id + " = " + base_expr(l.addr) + ";\n";
       if (l.kind == LoadSite::Scalar) s += "  const float S" + id + " = live_row ? __ldg(" + arg + " + B" + id + ") : 0.f;\n";
       if (l.kind == LoadSite::Vec) {
-        s += "  float L" + id + "[VPT * 4];\n#pragma unroll\n  for (int v_ = 0; v_ < VPT; ++v_) {\n    const int c4_ = tid + v_ * T;\n"
-             "    float4 t_ = make_float4(0.f, 0.f, 0.f, 0.f);\n    if " + live4 + " t_ = " + (l.addr.re.empty() && !g.chunked ? "__ldg" : "__ldcs") + "(reinterpret_cast<const float4 *>(" + arg + " + B" + id + ") + c4_);\n"
-             "    L" + id + "[4 * v_] = t_.x; L" + id + "[4 * v_ + 1] = t_.y; L" + id + "[4 * v_ + 2] = t_.z; L" + id + "[4 * v_ + 3] = t_.w;\n  }\n";
+        const std::string ld = (l.addr.re.empty() && !g.chunked) ? "__ldg" : "__ldcs";    // shared by all rows: keep it cached
+        const std::string at = arg + " + B" + id + " + " + Gen::col_offset(l.addr, ws + "L * c_");
+        s += "  float L" + id + "[VPT * W];\n#pragma unroll\n  for (int v_ = 0; v_ < VPT; ++v_) {\n    const int c_ = tid + v_ * T;\n";
+        if (W == 4)
+          s += "    float4 t_ = make_float4(0.f, 0.f, 0.f, 0.f);\n    if " + live + " t_ = " + ld + "(reinterpret_cast<const float4 *>(" + at + "));\n"
+               "    L" + id + "[4 * v_] = t_.x; L" + id + "[4 * v_ + 1] = t_.y; L" + id + "[4 * v_ + 2] = t_.z; L" + id + "[4 * v_ + 3] = t_.w;\n  }\n";
+        else
+          s += "    L" + id + "[v_] = " + live + " ? " + ld + "(" + at + ") : 0.f;\n  }\n";
       }
     }
     for (size_t i = 0; i < g.passes.size(); ++i) {
       const Pass &p = g.passes[i];
       const std::string id = std::to_string(i), fold = "ugf_fold" + std::to_string((int)p.rop);
       const std::string init = p.rop == ReduceOp::Sum ? "0.f" : (p.rop == ReduceOp::Max ? "__int_as_float(0xff800000)" : "__int_as_float(0x7f800000)");
-      s += "  float R" + id + ";\n  {\n    float acc_ = " + init + ";\n#pragma unroll\n    for (int v_ = 0; v_ < VPT; ++v_) {\n      const int c4_ = tid + v_ * T;\n      if (live_row && c4_ < C4) {\n#pragma unroll\n"
-           "        for (int e_ = 0; e_ < 4; ++e_) {\n          const int J = 4 * v_ + e_; const long COL = 4L * c4_ + e_; (void)J; (void)COL;\n"
+      s += "  float R" + id + ";\n  {\n    float acc_ = " + init + ";\n#pragma unroll\n    for (int v_ = 0; v_ < VPT; ++v_) {\n      const int c_ = tid + v_ * T;\n      if (live_row && c_ < CW) {\n#pragma unroll\n"
+           "        for (int e_ = 0; e_ < W; ++e_) {\n          const int J = W * v_ + e_; const long COL = (long)W * c_ + e_; (void)J; (void)COL;\n"
            "          acc_ = " + fold + "(acc_, " + p.body + ");\n        }\n      }\n    }\n    UGF_WARP_RED(" + fold + ", acc_, T < 32 ? T : 32)\n";
       if (!warp_mode) {
         const std::string b = std::to_string(i & 1);
@@ -361,9 +386,11 @@ bool fast_kernel(const op::Kernel &k, const std::string &name, FastKernel &out) 
     {
       const std::string dst = "a" + std::to_string(dst_arg);
       snprintf(buf, sizeof buf, "%zuL + row * %zuL", dl.offset, g.cols);
-      s += "  float *out_ = " + dst + " + " + buf + ";\n#pragma unroll\n  for (int v_ = 0; v_ < VPT; ++v_) {\n    const int c4_ = tid + v_ * T;\n    if " + live4 + " {\n      float o_[4];\n#pragma unroll\n"
-           "      for (int e_ = 0; e_ < 4; ++e_) {\n        const int J = 4 * v_ + e_; const long COL = 4L * c4_ + e_; (void)J; (void)COL;\n        o_[e_] = " + value + ";\n      }\n"
-           "      __stcs(reinterpret_cast<float4 *>(out_) + c4_, make_float4(o_[0], o_[1], o_[2], o_[3]));\n    }\n  }\n}\n";
+      s += "  float *out_ = " + dst + " + " + buf + ";\n#pragma unroll\n  for (int v_ = 0; v_ < VPT; ++v_) {\n    const int c_ = tid + v_ * T;\n    if " + live + " {\n      float o_[W];\n#pragma unroll\n"
+           "      for (int e_ = 0; e_ < W; ++e_) {\n        const int J = W * v_ + e_; const long COL = (long)W * c_ + e_; (void)J; (void)COL;\n        o_[e_] = " + value + ";\n      }\n";
+      if (W == 4) s += "      __stcs(reinterpret_cast<float4 *>(out_) + c_, make_float4(o_[0], o_[1], o_[2], o_[3]));\n";
+      else s += "      __stcs(out_ + c_, o_[0]);\n";
+      s += "    }\n  }\n}\n";
     }
     out.source = std::move(s);
     out.func_name = fname;
@@ -371,11 +398,31 @@ bool fast_kernel(const op::Kernel &k, const std::string &name, FastKernel &out) 
     out.launch.grid_dim = (uint32_t)((rows + rows_per_cta - 1) / rows_per_cta);
     out.launch.block_dim = (uint32_t)block;
     out.launch.shared_mem = 0;
-    out.origin = g.chunked ? "map_vec4" : (warp_mode ? "warp_row_vec4" : "row_vec4");
+    const std::string w = W == 4 ? "vec4" : "scalar";
+    out.origin = (g.chunked ? "map_" : (warp_mode ? "warp_row_" : "row_")) + w;
     return true;
   } catch (const NotApplicable &) {
     return false;
   }
+}
+
+}  // namespace
+
+// Returns true and fills `out` when `k` (already through optimize()) is one of the shapes above: 128-bit accesses
+// where the row length and every base allow them, otherwise the same kernel with one element per access.  A store of
+// zero elements (the empty KV cache of model.rs:192-193) needs no code at all: origin "empty".
+bool fast_kernel(const op::Kernel &k, const std::string &name, FastKernel &out) {
+  if (k.ops.size() != 1) return false;
+  const op::Store &st = k.ops[0];
+  const Layout &dl = st.layout;
+  if (dl.rank() >= 1 && dl.num_elements() == 0) {
+    out = FastKernel{};
+    out.origin = "empty";
+    return true;
+  }
+  if (st.value->dtype != DType::F32 || dl.rank() == 0) return false;
+  if (!dl.c_contiguous() || dl.num_elements() >= (1ull << 31)) return false;
+  return generate(k, name, 4, out) || generate(k, name, 1, out);
 }
 
 // ug-llama/src/model.rs:32-63 as instructions: globals src (f32), ids (i32), dst (f32); for r in 0..n: the id is

@@ -540,6 +540,53 @@ CompiledSchedule Schedule::compile_with_cache(CompilationCache &cache) const {
         if (it != cache.op_cache.end()) { cf.func = it->second; cache.hits++; break; }
         const std::string name = kernel.ops.empty() ? std::string() : kernel.ops[0].name();
         kernel = optimize(std::move(kernel));
+        if (device->launch_policy() == LaunchPolicy::B200 && cache.polymorphic) {
+          // the same kernel at another size (see ug_poly.cpp): reuse, or build, the function that takes the size at run time
+          const ssa::Kernel poly_k = lower(kernel, b200_opts(kernel));
+          GeneratedSource gs;
+          if (device->ssa_source(poly_k, "ug_poly_kernel", gs)) {
+            std::vector<PolyToken> toks = poly_tokenize(gs.text);
+            const uint32_t grid = poly_k.launch_config.grid_dim;
+            PolyEntry &pe = cache.poly[poly_skeleton(toks) + "|" + std::to_string(poly_k.launch_config.block_dim) + "|" +
+                                       std::to_string(poly_k.launch_config.shared_mem)];
+            long long t = 0;
+            bool served = false;
+            for (const PolyGeneric &g : pe.generics)
+              if (poly_match(g, toks, grid, t)) {
+                cf.func = g.func; cf.dyn = true; cf.dyn_grid = grid; cf.dyn_t = t;
+                cache.hits++; cache.poly_hits++;
+                served = true;
+                break;
+              }
+            if (served) break;
+            if (!pe.failed && pe.have_pending && pe.generics.size() < 8) {
+              std::string generic;
+              PolyGeneric g;
+              bool ok = poly_generalize(pe, toks, grid, g, generic);
+              const std::string sig = "ugb_status_word* ugb_status) {";
+              const size_t at = ok ? generic.find(sig) : std::string::npos;
+              ok = ok && at != std::string::npos;
+              if (ok) {
+                generic.replace(at, sig.size(), "ugb_status_word* ugb_status, const long long ugp_t) {");
+                GeneratedSource g2{generic, gs.arg_dtypes};
+                try { g.func = device->compile_generated(g2, "ug_poly_kernel", 1, poly_k.launch_config); }
+                catch (const Error &) { g.func = nullptr; }   // a literal the compiler needs as a constant: per-shape kernels
+                ok = (bool)g.func;
+              }
+              if (ok) {
+                g.func->origin = "ssa_generic";
+                cf.func = g.func; cf.dyn = true; cf.dyn_grid = grid; cf.dyn_t = 1;
+                pe.generics.push_back(std::move(g));
+                pe.pending.clear();
+                pe.have_pending = false;
+                cache.misses++;
+                break;
+              }
+              pe.failed = true;
+            }
+            if (!pe.have_pending) { pe.pending = std::move(toks); pe.pending_grid = grid; pe.have_pending = true; }
+          }
+        }
         if (device->launch_policy() == LaunchPolicy::B200) {
           // row-reduce + map and pure-map kernels run on generated 128-bit code; everything else on the SSA path
           FastKernel fk;
@@ -577,7 +624,8 @@ void CompiledSchedule::run() const {
       case CompiledFunc::Kernel: {
         std::vector<Slice *> bs;
         for (auto &[id, lb] : f.args) { lb.maybe_allocate_uninit(); bs.push_back(lb->data->slice.get()); }
-        device->run(*f.func, bs);
+        if (f.dyn) device->run_dyn(*f.func, bs, f.dyn_grid, {f.dyn_t});
+        else device->run(*f.func, bs);
         break;
       }
       case CompiledFunc::MatMul: {  // schedule.rs:256-288: operand layouts come from the shapes, padded with leading 1s

@@ -31,6 +31,12 @@ struct FastKernel {
   size_t n_ids = 0, h = 0;
 };
 
+// CUDA C generated from an SSA kernel, with the dtypes of its pointer arguments.
+struct GeneratedSource {
+  std::string text;
+  std::vector<DType> arg_dtypes;
+};
+
 // How Schedule::compile picks the launch shape of a fused kernel.
 enum class LaunchPolicy {
   Sequential,     // use_grid() == false: default Opts, every dim a sequential loop (the CPU backend)
@@ -51,6 +57,13 @@ struct Device {
   // Compiles caller-generated CUDA C whose parameters are the kernel's arguments (device pointers) in order;
   // a device without run-time compilation of source returns null and the SSA path is taken.
   virtual std::shared_ptr<Func> compile_cu(const FastKernel &) { return nullptr; }
+  // The pieces the shape-polymorphic cache (ug_poly.cpp) needs from a backend that generates source from SSA:
+  // the text for an entry name, compilation of a text of that form with `n_dyn` trailing value parameters, and a
+  // launch with the grid and those values chosen per call.  A backend without them keeps the per-shape cache.
+  virtual bool ssa_source(const ssa::Kernel &, const std::string & /*entry*/, GeneratedSource &) { return false; }
+  virtual std::shared_ptr<Func> compile_generated(const GeneratedSource &, const std::string & /*entry*/, int /*n_dyn*/,
+                                                  const LaunchConfig &) { return nullptr; }
+  virtual void run_dyn(Func &, std::vector<Slice *> &, uint32_t /*grid*/, const std::vector<int64_t> &) { bail("run_dyn: not supported by this device"); }
   virtual LaunchPolicy launch_policy() const { return use_grid() ? LaunchPolicy::ReferenceGrid : LaunchPolicy::Sequential; }
 };
 
@@ -153,10 +166,37 @@ struct ScheduleItem {  // schedule.rs:42-60
   op::Kernel kernel() const;  // schedule.rs:23-39
 };
 
+// ---- shape-polymorphic reuse (ug_poly.cpp) ----
+struct PolyToken {
+  std::string ws, text;       // white space before the token, the token
+  bool is_int = false;        // a decimal integer literal
+  long long value = 0;
+};
+struct PolySlot { size_t token; long long a, b; };   // literal number `token` of the template is b + a * t
+struct PolyGeneric {                  // one generic function: template tokens, the literals that move, the grid
+  std::shared_ptr<Func> func;
+  std::vector<PolyToken> tmpl;
+  std::vector<PolySlot> slots;
+  long long grid_a = 0, grid_b = 0;
+};
+struct PolyEntry {                    // everything known about one token skeleton
+  bool failed = false, have_pending = false;
+  std::vector<PolyToken> pending;     // a sighting that no generic function covers yet
+  uint32_t pending_grid = 0;
+  std::vector<PolyGeneric> generics;  // several when the same text moves along more than one line of sizes
+};
+std::vector<PolyToken> poly_tokenize(const std::string &text);
+std::string poly_skeleton(const std::vector<PolyToken> &toks);
+bool poly_generalize(const PolyEntry &e, const std::vector<PolyToken> &second, uint32_t second_grid, PolyGeneric &out,
+                     std::string &generic_text);
+bool poly_match(const PolyGeneric &e, const std::vector<PolyToken> &toks, uint32_t grid, long long &t);
+
 struct CompilationCache {  // cache.rs:73-101
   std::map<NormalizedKernel, std::shared_ptr<Func>> op_cache;
   std::map<std::vector<ssa::Instr>, std::shared_ptr<Func>> ssa_cache;
-  size_t hits = 0, misses = 0;
+  std::map<std::string, PolyEntry> poly;   // by token skeleton of the generated text (+ block size)
+  bool polymorphic = true;                 // B200 launch policy only
+  size_t hits = 0, misses = 0, poly_hits = 0;
 };
 
 struct CompiledFunc {  // schedule.rs:209-227
@@ -167,6 +207,9 @@ struct CompiledFunc {  // schedule.rs:209-227
   size_t b = 0, m = 0, n = 0, k = 0;
   bool transpose = false;
   CustomF f;
+  bool dyn = false;         // func is a shape-generic kernel: launched with this grid and this value of t
+  uint32_t dyn_grid = 0;
+  int64_t dyn_t = 0;
 };
 
 struct CompiledSchedule {

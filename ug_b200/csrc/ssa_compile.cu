@@ -22,6 +22,7 @@
 #include <cctype>
 #include <cstdlib>
 #include <mutex>
+#include <cstring>
 #include <sstream>
 #include <string>
 #include <vector>
@@ -36,6 +37,7 @@ struct ugb_func {
   std::vector<int32_t> arg_dtypes;
   std::string source, name;
   bool raw = false;     // user-supplied CUDA C / PTX: pointer arguments only, no length or status parameters
+  int n_dyn = 0;        // trailing `long long` value parameters that ugb_run_dyn supplies
 };
 
 namespace {
@@ -478,22 +480,25 @@ int32_t ugb_func_free(ugb_func *f) {
 
 const char *ugb_func_source(const ugb_func *f) { return f ? f->source.c_str() : nullptr; }
 
-int32_t ugb_run(ugb_device *dev, ugb_func *f, ugb_slice *const *args, size_t n_args) {
-  if (!dev) return UGB_ERR_INVALID;
+static int32_t run_impl(ugb_device *dev, ugb_func *f, ugb_slice *const *args, size_t n_args, unsigned grid,
+                        const long long *dyn, size_t n_dyn) {
   UGB_REQUIRE(dev, f != nullptr && f->dev == dev, UGB_ERR_INVALID, "ugb_run: function belongs to another device");
+  UGB_REQUIRE(dev, (size_t)f->n_dyn == n_dyn, UGB_ERR_INVALID, "kernel %s takes %d run-time values, %zu given", f->name.c_str(), f->n_dyn, n_dyn);
   // a zero launch dimension is a no-op (ug-cuda/src/runtime.rs:269-277)
-  if (f->grid == 0 || f->block == 0) return UGB_OK;
+  if (grid == 0 || f->block == 0) return UGB_OK;
+  std::vector<long long> dv(dyn, dyn + n_dyn);
   if (f->raw) {
     // user-supplied kernel: its parameters are the slices' device pointers in order, nothing else.  Bounds
     // are the kernel author's business, as with Func::launch in the reference (ug-pyo3/src/lib.rs:27-50).
-    std::vector<void *> p(n_args), pp(n_args);
+    std::vector<void *> p(n_args), pp;
     for (size_t i = 0; i < n_args; ++i) {
       UGB_REQUIRE(dev, args[i] != nullptr && args[i]->dev == dev, UGB_ERR_INVALID, "ugb_run: argument %zu is null or on another device", i);
       p[i] = args[i]->ptr;
-      pp[i] = &p[i];
     }
+    for (size_t i = 0; i < n_args; ++i) pp.push_back(&p[i]);
+    for (size_t i = 0; i < n_dyn; ++i) pp.push_back(&dv[i]);
     UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
-    CUresult rr = driver().launch_kernel(f->fn, f->grid, 1, 1, f->block, 1, 1, f->smem, (CUstream)dev->stream, pp.data(), nullptr);
+    CUresult rr = driver().launch_kernel(f->fn, grid, 1, 1, f->block, 1, 1, f->smem, (CUstream)dev->stream, pp.data(), nullptr);
     if (rr != CUDA_SUCCESS) return ugb_fail(dev, UGB_ERR_CUDA, "launch of %s failed with CUresult %d", f->name.c_str(), (int)rr);
     dev->launches++;
     return UGB_OK;
@@ -515,10 +520,60 @@ int32_t ugb_run(ugb_device *dev, ugb_func *f, ugb_slice *const *args, size_t n_a
   for (size_t i = 0; i < n_args; ++i) params.push_back(&lens[i]);
   void *status = dev->status_dev;
   params.push_back(&status);
+  for (size_t i = 0; i < n_dyn; ++i) params.push_back(&dv[i]);
   UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
-  CUresult r = driver().launch_kernel(f->fn, f->grid, 1, 1, f->block, 1, 1, f->smem, (CUstream)dev->stream, params.data(), nullptr);
+  CUresult r = driver().launch_kernel(f->fn, grid, 1, 1, f->block, 1, 1, f->smem, (CUstream)dev->stream, params.data(), nullptr);
   if (r != CUDA_SUCCESS) return ugb_fail(dev, UGB_ERR_CUDA, "launch of %s failed with CUresult %d", f->name.c_str(), (int)r);
   dev->launches++;
+  return UGB_OK;
+}
+
+int32_t ugb_run(ugb_device *dev, ugb_func *f, ugb_slice *const *args, size_t n_args) {
+  if (!dev) return UGB_ERR_INVALID;
+  UGB_REQUIRE(dev, f != nullptr, UGB_ERR_INVALID, "ugb_run: null function");
+  return run_impl(dev, f, args, n_args, f->grid, nullptr, 0);
+}
+
+int32_t ugb_run_dyn(ugb_device *dev, ugb_func *f, ugb_slice *const *args, size_t n_args, uint32_t grid_dim,
+                    const int64_t *dyn, size_t n_dyn) {
+  if (!dev) return UGB_ERR_INVALID;
+  UGB_REQUIRE(dev, f != nullptr && (dyn != nullptr || n_dyn == 0) && n_dyn <= 8, UGB_ERR_INVALID, "ugb_run_dyn: bad argument");
+  long long v[8];
+  for (size_t i = 0; i < n_dyn; ++i) v[i] = (long long)dyn[i];
+  return run_impl(dev, f, args, n_args, grid_dim, v, n_dyn);
+}
+
+int32_t ugb_ssa_source(ugb_device *dev, const ugb_ssa_instr *instrs, size_t n_instrs, const char *entry_name, char *buf,
+                       size_t buf_len, int32_t *arg_dtypes, size_t max_args, size_t *n_args) {
+  if (!dev) return UGB_ERR_INVALID;
+  UGB_REQUIRE(dev, entry_name && buf && arg_dtypes && n_args && (instrs || n_instrs == 0), UGB_ERR_INVALID, "ugb_ssa_source: null argument");
+  std::string src;
+  std::vector<int32_t> dts;
+  int32_t rc = generate(dev, instrs, n_instrs, entry_name, &src, &dts);
+  if (rc) return rc;
+  UGB_REQUIRE(dev, src.size() + 1 <= buf_len && dts.size() <= max_args, UGB_ERR_SHAPE, "ugb_ssa_source: %zu bytes and %zu arguments needed",
+              src.size() + 1, dts.size());
+  memcpy(buf, src.c_str(), src.size() + 1);
+  for (size_t i = 0; i < dts.size(); ++i) arg_dtypes[i] = dts[i];
+  *n_args = dts.size();
+  return UGB_OK;
+}
+
+int32_t ugb_compile_generated(ugb_device *dev, const char *cu_code, const char *entry_name, const int32_t *arg_dtypes,
+                              size_t n_args, int32_t n_dyn, uint32_t grid_dim, uint32_t block_dim, uint32_t shared_mem,
+                              ugb_func **out) {
+  if (!dev) return UGB_ERR_INVALID;
+  UGB_REQUIRE(dev, cu_code && entry_name && out && (arg_dtypes || n_args == 0) && n_dyn >= 0 && n_dyn <= 8, UGB_ERR_INVALID,
+              "ugb_compile_generated: bad argument");
+  *out = nullptr;
+  UGB_REQUIRE(dev, block_dim <= 1024, UGB_ERR_INVALID, "ugb_compile_generated: block_dim %u exceeds 1024", block_dim);
+  ugb_func *f = nullptr;
+  const int32_t rc = compile_and_load(dev, cu_code, entry_name, entry_name, false, false, &f);
+  if (rc) return rc;
+  f->grid = grid_dim; f->block = block_dim; f->smem = shared_mem;
+  f->arg_dtypes.assign(arg_dtypes, arg_dtypes + n_args);
+  f->n_dyn = n_dyn;
+  *out = f;
   return UGB_OK;
 }
 

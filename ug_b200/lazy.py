@@ -375,6 +375,14 @@ class CompilationCache:
     def misses(self):
         return host.ugh_cache_misses(self._h)
 
+    @property
+    def poly_hits(self):
+        """Hits served by a shape-generic kernel (the same kernel seen before at another size)."""
+        return host.ugh_cache_poly_hits(self._h)
+
+    def set_polymorphic(self, on):
+        host.ugh_cache_set_polymorphic(self._h, int(bool(on)))
+
 
 class CompiledSchedule:
     def __init__(self, h, buffers):
