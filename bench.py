@@ -320,6 +320,51 @@ class SoftmaxC1Workload(SoftmaxWorkload):
                 "l2": "16 buffer pairs of 33.5 MB, one per step in turn (537 MB vs 126 MB L2)"}
 
 
+class GraphRowWorkload:
+    """The UNMODIFIED graph forms of ug-llama (softmax, model.rs:94-101; rms_norm, model.rs:65-78) on f32
+    [8192, 4096] through the lazy graph -> schedule -> compile -> run path of the host layer: what the drop-in
+    backend makes of ug-core's own op graph (the reference lowers the same graphs to scalar code, two kernels
+    for softmax)."""
+    unit = "GB/s"
+    dtype = "f32"
+    bound = "hbm"
+    rows, cols = 8192, 4096
+    ncu_traffic_bytes = None
+
+    def __init__(self, which):
+        from ug_b200 import synth
+        self.which = which
+        self.name = f"graph {which} f32 [8192,4096] through LazyBuffer / Schedule (unmodified ug-llama graph form)"
+        self.metric = f"effective HBM GB/s, graph-form {which} (rows*cols*8 bytes / time)"
+        self.x = synth.normal(31, (self.rows, self.cols), 2.0 if which == "softmax" else 1.0)
+        self.w = synth.uniform(32, (self.cols,), 0.5, 1.5)
+        self.bytes_per_step = 2 * self.rows * self.cols * 4
+        self.launches_per_step = 1
+
+    def setup(self, dev):
+        from ug_b200 import llama_graph as G
+        from ug_b200.lazy import LB, HostDevice, Schedule
+        self.dev = dev
+        self.hd = HostDevice(dev)
+        lx = LB.copy(self.x, (self.rows, self.cols), self.hd)
+        self.y = G.softmax(lx) if self.which == "softmax" else G.rms_norm(lx, LB.copy(self.w, (self.cols,), self.hd), 1e-5)
+        self.sched = Schedule.create_one(self.y)
+        self.compiled = self.sched.compile()
+        self.launches_per_step = len(self.compiled)
+
+    def step(self):
+        self.compiled.run()
+
+    def units(self, step_seconds, n_ranks):
+        return n_ranks * self.bytes_per_step / step_seconds / 1e9
+
+    def check(self):
+        import oracle
+        got = self.y.data_vec().reshape(self.rows, self.cols)[:32]
+        ref = oracle.custom_softmax(self.x[:32]) if self.which == "softmax" else oracle.gen_rms_norm(self.x[:32], self.w, 1e-5)
+        return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1e-30)))
+
+
 class GemmWorkload:
     """Config 3: A bf16 [16,512,4096] x B bf16 [4096,4096] ([k,n]), fp32 accumulate, bf16 out."""
     name = "bf16 matmul [16,512,4096] x [4096,4096] (config 3), batch partitioned across GPUs"
@@ -825,7 +870,9 @@ def config_records(dev, group, peaks):
     out = {}
     plan = [("config1_softmax_1024x4096", SoftmaxC1Workload, 200), ("config1_row_shape_32768x4096", SoftmaxWorkload, 30),
             ("config2_rms_norm_silu_gate", RmsSiluWorkload, 50), ("config3_gemm", GemmWorkload, 30),
-            ("config4_prefill", PrefillWorkload, 10)]
+            ("config4_prefill", PrefillWorkload, 10),
+            ("graph_softmax_8192x4096", lambda r: GraphRowWorkload("softmax"), 30),
+            ("graph_rms_norm_8192x4096", lambda r: GraphRowWorkload("rms_norm"), 30)]
     for key, cls, steps in plan:
         wl = cls(0)
         wl.setup(dev)
@@ -843,6 +890,8 @@ def config_records(dev, group, peaks):
                "parity_max_rel_err": err}
         if hasattr(wl, "resident_gbs"):
             rec["l2_resident_value"] = round(wl.resident_gbs(), 1)
+        if isinstance(wl, GraphRowWorkload):
+            rec["kernels"] = wl.compiled.origins()
         if hasattr(wl, "reference_cuda_gbs") and cls is SoftmaxWorkload:
             g = wl.reference_cuda_gbs()
             rec["reference_cuda_kernel"] = None if g is None else round(g, 1)
