@@ -36,6 +36,8 @@ def gpu_matmul(dev, a, b, transpose_rhs, dtype):
     if dtype == DType.BF16:
         sa, sb = dev.slice_from_values(synth.to_bf16_bits(a), bf16=True), \
             dev.slice_from_values(synth.to_bf16_bits(b), bf16=True)
+    elif dtype == DType.F16:
+        sa, sb = dev.slice_from_values(a.astype(np.float16)), dev.slice_from_values(b.astype(np.float16))
     else:
         sa, sb = dev.slice_from_values(a), dev.slice_from_values(b)
     dst = dev.allocate_uninit(dtype, bs * m * n)
@@ -48,7 +50,7 @@ def gpu_matmul(dev, a, b, transpose_rhs, dtype):
     out = dst.to_vec()
     if dtype == DType.BF16:
         out = synth.bf16_bits_to_f32(out)
-    return out.reshape(bs, m, n)
+    return out.astype(np.float32).reshape(bs, m, n)
 
 
 def test_mm_reference_fixture(dev):
@@ -131,6 +133,45 @@ def test_bf16_tensor_core_matmul(dev, bs, m, n, k, t):
     assert err.max() < 2e-2
     # and the mean error must look like bf16 rounding of an exact f32 sum, not like a dropped k block
     assert np.abs(got - oracle.round_bf16(ref)).mean() < 2e-3 * np.abs(ref).mean()
+
+
+@pytest.mark.parametrize("bs,m,n,k,t", TC_SHAPES)
+def test_f16_tensor_core_matmul(dev, bs, m, n, k, t):
+    """IEEE f16 operands on the same tcgen05 kernel (the instruction's format field is the only difference;
+    the reference sends f16 to cublasGemmStridedBatchedEx like bf16, ug-cuda/src/gemm.rs:130-232)."""
+    a = synth.normal(950 + m, (bs, m, k), 0.5).astype(np.float16).astype(np.float32)
+    b = synth.normal(951 + n, (bs, n, k) if t else (bs, k, n), 0.5).astype(np.float16).astype(np.float32)
+    got = gpu_matmul(dev, a, b, t, DType.F16)
+    ref = oracle.matmul(a, b, transpose_rhs=t)
+    err = np.abs(got - ref) / np.maximum(np.abs(ref), 0.05 * np.abs(ref).max())
+    assert err.max() < 4e-3                       # f16 keeps 11 significant bits: 8x tighter than bf16's 2e-2
+    assert np.abs(got - ref.astype(np.float16).astype(np.float32)).mean() < 3e-4 * np.abs(ref).mean()
+
+
+# ---- f32 on the FP32 pipe: the skinny (decode) kernel and the 128 x 128 register-blocked kernel ----------------
+@pytest.mark.parametrize("bs,m,n,k,t", [
+    (1, 1, 2048, 2048, True), (1, 3, 5632, 2048, True), (2, 16, 264, 512, True), (1, 8, 32000, 256, True),   # skinny
+    (1, 130, 200, 72, True), (1, 130, 200, 72, False), (2, 256, 384, 128, True), (1, 512, 2048, 2048, True),  # tiles
+    (1, 127, 129, 67, False), (1, 17, 1031, 259, True)])                                                      # no 128-bit form
+def test_f32_matmul_kernels(dev, bs, m, n, k, t):
+    a = synth.normal(960 + m, (bs, m, k))
+    b = synth.normal(961 + n, (bs, n, k) if t else (bs, k, n))
+    got = gpu_matmul(dev, a, b, t, DType.F32)
+    ref = oracle.matmul(a, b, transpose_rhs=t) if m * n * k < 5e8 else np.matmul(a, np.swapaxes(b, -1, -2) if t else b)
+    assert np.max(np.abs(got - ref)) / np.sqrt(k) < 1e-5     # fp32 products and sums, another order than the oracle
+
+
+def test_f32_transposed_lhs(dev):
+    """lhs stored [k, m] (its transpose is what the product reads): gemm.rs:18-43 accepts it."""
+    bs, m, n, k = 1, 96, 136, 64
+    a = synth.normal(970, (bs, m, k))
+    b = synth.normal(971, (bs, k, n))
+    at = np.ascontiguousarray(a.transpose(0, 2, 1))            # [k, m] in memory
+    sa, sb = dev.slice_from_values(at), dev.slice_from_values(b)
+    dst = dev.allocate_uninit(DType.F32, bs * m * n)
+    dev.matmul(dst, sa, sb, (bs, m, n, k), transposed(contiguous(at.shape)), contiguous(b.shape))
+    dev.synchronize()
+    assert np.max(np.abs(dst.to_vec().reshape(bs, m, n) - oracle.matmul(a, b))) / np.sqrt(k) < 1e-5
 
 
 def test_bf16_shared_weight_batch_is_flattened(dev):

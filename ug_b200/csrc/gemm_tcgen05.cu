@@ -28,6 +28,7 @@
 // returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "gemm_tcgen05.cuh"
 #include "tc_ptx.cuh"
@@ -71,6 +72,7 @@ struct Params {
   int n_fast;             // tile order: 1 = n-tiles vary fastest (a wave re-reads B, the smaller operand)
   int b_static;           // 1: no kernel on the stream writes B (weights): it may be fetched before ugb_pdl_wait
   int stages;             // depth of the shared-memory ring in use (2 .. Cfg::STAGES)
+  int f16;                // operands and 16-bit output are IEEE f16 (0: bf16)
   long long c_batch;      // output elements between batch steps
   long long c_split;      // output elements between split-K partials
   void *C;
@@ -236,7 +238,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else if (warp == 1) {
     // -------------------------------------------------------- MMA issuer --
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = make_idesc(TILE_M, BN, !p.b_is_nk);
+      const uint32_t idesc = make_idesc(TILE_M, BN, !p.b_is_nk, p.f16 != 0);
       auto mma = [&](uint32_t d, uint64_t a_desc, uint64_t b_desc, uint32_t acc_in) {
         if constexpr (PAIR) umma_bf16_pair(d, a_desc, b_desc, idesc, acc_in);
         else umma_bf16(d, a_desc, b_desc, idesc, acc_in);
@@ -390,11 +392,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int q = 0; q < 4; ++q) {
               if (c * 32 + q * 8 < BN && col0 + q * 8 < p.N) {   // BN % 8 == N % 8 == 0: a chunk of 8 is all in or all out
                 uint4 o;
-                __nv_bfloat162 t;
-                t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])); o.x = *(uint32_t *)&t;
-                t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])); o.y = *(uint32_t *)&t;
-                t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])); o.z = *(uint32_t *)&t;
-                t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7])); o.w = *(uint32_t *)&t;
+                if (p.f16) {
+                  __half2 t;
+                  t = __floats2half2_rn(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])); o.x = *(uint32_t *)&t;
+                  t = __floats2half2_rn(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])); o.y = *(uint32_t *)&t;
+                  t = __floats2half2_rn(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])); o.z = *(uint32_t *)&t;
+                  t = __floats2half2_rn(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7])); o.w = *(uint32_t *)&t;
+                } else {
+                  __nv_bfloat162 t;
+                  t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])); o.x = *(uint32_t *)&t;
+                  t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])); o.y = *(uint32_t *)&t;
+                  t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])); o.z = *(uint32_t *)&t;
+                  t = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7])); o.w = *(uint32_t *)&t;
+                }
                 *reinterpret_cast<uint4 *>(crow + q * 8) = o;
               }
             }
@@ -481,12 +491,12 @@ int32_t ensure_encode(ugb_device *dev, TcState *st) {
 
 // rank-3 bf16 tensor map: dims {d0 (contiguous), d1, d2}, strides in elements for d1, d2.
 int32_t encode_map(ugb_device *dev, TcState *st, CUtensorMap *map, const void *base, uint64_t d0,
-                   uint64_t d1, uint64_t d2, uint64_t s1, uint64_t s2, uint32_t box0, uint32_t box1) {
+                   uint64_t d1, uint64_t d2, uint64_t s1, uint64_t s2, uint32_t box0, uint32_t box1, bool f16 = false) {
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {s1 * 2, s2 * 2};
   cuuint32_t box[3] = {box0, box1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = st->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides,
+  CUresult r = st->encode(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides,
                           box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
@@ -518,6 +528,7 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   p.b_is_nk = g.b_is_nk ? 1 : 0;
   p.epi = g.epi;
   p.b_static = g.b_static ? 1 : 0;
+  p.f16 = g.f16 ? 1 : 0;
   // Consecutive tiles run in the same wave.  The operand that is walked completely by every wave is read
   // from L2 again and again, so it should be the smaller one: B (n x k) when n <= m, otherwise A.
   p.n_fast = n <= m ? 1 : 0;
@@ -530,12 +541,12 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
 
   CUtensorMap tmA, tmB;
   p.stage_tx = C_::STAGE_BYTES * (PAIR ? 2 : 1);      // PAIR: one barrier counts both CTAs' stage
-  int32_t rc = encode_map(dev, st, &tmA, g.a, k, m, batch, k, batch > 1 ? (uint64_t)g.a_batch : m * k, BK, BM);
+  int32_t rc = encode_map(dev, st, &tmA, g.a, k, m, batch, k, batch > 1 ? (uint64_t)g.a_batch : m * k, BK, BM, g.f16);
   if (rc) return rc;
   const uint64_t nb = p.b_batched ? batch : 1;
   const uint64_t bs = p.b_batched ? (uint64_t)g.b_batch : n * k;
-  if (g.b_is_nk) rc = encode_map(dev, st, &tmB, g.b, k, n, nb, k, bs, BK, C_::BN_CTA);
-  else rc = encode_map(dev, st, &tmB, g.b, n, k, nb, n, bs, 64, BK);
+  if (g.b_is_nk) rc = encode_map(dev, st, &tmB, g.b, k, n, nb, k, bs, BK, C_::BN_CTA, g.f16);
+  else rc = encode_map(dev, st, &tmB, g.b, n, k, nb, n, bs, 64, BK, g.f16);
   if (rc) return rc;
 
   const long long n_tiles = (long long)p.tiles_m * p.tiles_n * p.batch * p.splits;
@@ -592,6 +603,7 @@ int32_t ugb_tc_gemm(ugb_device *dev, const ugb_tc_gemm_args &g) {
   if (m > (1u << 30) || n > (1u << 30) || k > (1u << 30) || batch > 65535) return UGB_ERR_UNSUPPORTED;
   if (g.epi == UGB_EPI_SILU_MUL_BF16 && n % 16 != 0) return UGB_ERR_UNSUPPORTED;
   if (g.splits > 1 && g.epi != UGB_EPI_F32) return UGB_ERR_UNSUPPORTED;
+  if (g.f16 && g.epi != UGB_EPI_BF16 && g.epi != UGB_EPI_F32) return UGB_ERR_UNSUPPORTED;   // the fused epilogues write bf16
   if (g.epi == UGB_EPI_ROPE_QKV && (m <= 64 || batch != 1 || !g.b_is_nk || n % 64 != 0 || g.rope.t < 1)) return UGB_ERR_UNSUPPORTED;
   if (m == 0 || n == 0) return UGB_ERR_UNSUPPORTED;
 
@@ -623,8 +635,9 @@ int32_t ugb_tc_gemm(ugb_device *dev, const ugb_tc_gemm_args &g) {
 }
 
 int32_t ugb_tc_gemm_bf16(ugb_device *dev, void *c, const void *a, const void *b_, size_t batch, size_t m,
-                         size_t n, size_t k, long long a_batch, long long b_batch, bool b_is_nk) {
+                         size_t n, size_t k, long long a_batch, long long b_batch, bool b_is_nk, bool f16) {
   ugb_tc_gemm_args g;
+  g.f16 = f16;
   g.out = c; g.a = a; g.b = b_;
   g.batch = batch; g.m = m; g.n = n; g.k = k;
   g.a_batch = a_batch; g.b_batch = b_batch; g.b_is_nk = b_is_nk;

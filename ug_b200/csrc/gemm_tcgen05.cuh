@@ -7,7 +7,7 @@
 
 // Epilogues applied to the fp32 accumulators.
 enum {
-  UGB_EPI_BF16 = 0,           // out bf16 [b, m, n]
+  UGB_EPI_BF16 = 0,           // out [b, m, n] in the operands' 16-bit type (bf16, or f16 with args.f16)
   UGB_EPI_F32 = 1,            // out f32 [splits, b, m, n]  (split-K partials when splits > 1)
   UGB_EPI_SILU_MUL_BF16 = 2,  // columns are (gate, up) pairs: out bf16 [b, m, n/2] = silu(gate) * up
   UGB_EPI_ROPE_QKV = 3        // columns are [q heads | k heads | v heads] of 64: rope + KV append (see ugb_tc_rope_epilogue)
@@ -38,6 +38,7 @@ struct ugb_tc_gemm_args {
   bool b_static;        // no kernel on the stream writes b (weights): fetch it before waiting for the predecessor
   bool pdl;             // launch with programmatic stream serialization (see ugb_launch)
   int smem_kib = 0;     // cap on the shared memory of a CTA (ring depth follows); 0 = as deep as fits in 220 KiB
+  bool f16 = false;     // operands (and the UGB_EPI_BF16 output) are IEEE f16 instead of bf16: same instruction, other format field
   int pair = -1;        // 256 x 256 tiles on pairs of CTAs (cta_group::2) where the shape allows: 1 / 0, -1 = the device's setting
   ugb_tc_rope_epilogue rope = {};   // UGB_EPI_ROPE_QKV only
 };
@@ -48,10 +49,10 @@ struct ugb_tc_gemm_args {
 int32_t ugb_tc_gemm(ugb_device *dev, const ugb_tc_gemm_args &args);
 // Number of partials ugb_tc_gemm writes for a requested split factor.
 int ugb_tc_gemm_effective_splits(size_t k, int splits);
-// C[b, m, n] bf16 = A . B with the default epilogue.
+// C[b, m, n] = A . B with the default epilogue, all three bf16 (f16 = false) or IEEE f16.
 int32_t ugb_tc_gemm_bf16(ugb_device *dev, void *c, const void *a, const void *b_, size_t batch,
                          size_t m, size_t n, size_t k, long long a_batch, long long b_batch,
-                         bool b_is_nk);
+                         bool b_is_nk, bool f16 = false);
 // bf16 tensor map with the 128-byte swizzle: dims / box of `rank` entries (dims[0] contiguous), strides in
 // elements for dims 1 .. rank-1 (multiples of 8).
 int32_t ugb_tc_encode_bf16(ugb_device *dev, CUtensorMap *map, const void *base, int rank, const uint64_t *dims,

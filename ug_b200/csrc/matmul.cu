@@ -6,8 +6,10 @@
 // layout rules pick between
 //   * the tcgen05 / TMEM tensor-core kernel (bf16 operands, fp32 accumulate),
 //     declared in gemm_tcgen05.cuh, and
-//   * a strided SIMT kernel with fp32 accumulation that covers every dtype
-//     and every accepted layout (f32 model paths, tiny or odd shapes).
+//   * for f32 (the dtype ug-llama casts every weight to, model.rs:118,140,313) two FP32-pipe kernels: a
+//     warp-per-column streaming kernel for the skinny products of a decode step and a 128 x 128 register-blocked
+//     FFMA kernel for the rest, and
+//   * a strided SIMT kernel with fp32 accumulation for bf16 / f16 shapes the tensor-core kernel does not take.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -122,6 +124,171 @@ simt_gemm_kernel(T *__restrict__ C, const T *__restrict__ A, const T *__restrict
   }
 }
 
+// ---- fp32 on the FP32 pipe (the reference's default for f32 is CUBLAS_COMPUTE_32F, gemm.rs:87-128: no reduced
+// precision), two shapes -------------------------------------------------------------------------------------
+// (1) Skinny products, m <= 16 rows against a [n, k] operand with k contiguous (Linear::fwd = matmul_t with a
+// weight, model.rs:147-149, for the one new token of a decode step): HBM-bound on the weight.  One warp per output
+// column: the lanes stream the column's k values with 128-bit loads, every value is used for all m rows, the
+// partial dot products are summed by warp shuffles.
+template <int MR>
+__global__ void __launch_bounds__(256)
+f32_skinny_kernel(float *__restrict__ C, const float *__restrict__ A, const float *__restrict__ B, int m, int n, int k,
+                  long long a_b, long long b_b) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = blockIdx.x * 8 + warp;
+  if (col >= n) return;
+  const int batch = blockIdx.y;
+  const float4 *w = reinterpret_cast<const float4 *>(B + (long long)batch * b_b + (long long)col * k);
+  const float *a = A + (long long)batch * a_b;
+  float acc[MR];
+#pragma unroll
+  for (int r = 0; r < MR; ++r) acc[r] = 0.f;
+  const int k4 = k >> 2;
+#pragma unroll 4
+  for (int c = lane; c < k4; c += 32) {
+    const float4 wv = __ldcs(w + c);                 // streamed once
+#pragma unroll
+    for (int r = 0; r < MR; ++r) {
+      if (r < m) {
+        const float4 x = __ldg(reinterpret_cast<const float4 *>(a + (long long)r * k) + c);
+        acc[r] = fmaf(x.x, wv.x, fmaf(x.y, wv.y, fmaf(x.z, wv.z, fmaf(x.w, wv.w, acc[r]))));
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < MR; ++r) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+    if (lane == 0 && r < m) C[(long long)batch * m * n + (long long)r * n + col] = acc[r];
+  }
+}
+
+// (2) Everything else in f32: 128 x 128 output tile per CTA, k slices of 8, 256 threads with 8 x 8 outputs each in
+// registers (64 FFMA per 16 shared-memory values read), global loads one slice ahead of the arithmetic, 128-bit
+// global and shared accesses where the layout allows (VEC), zero fill at the m / n / k tails.
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+f32_tile_kernel(float *__restrict__ C, const float *__restrict__ A, const float *__restrict__ B, int m, int n, int k,
+                long long a_rs, long long a_cs, long long a_b, long long b_rs, long long b_cs, long long b_b) {
+  constexpr int BM = 128, BN = 128, BK = 8;
+  __shared__ __align__(16) float As[2][BK][BM + 4];
+  __shared__ __align__(16) float Bs[2][BK][BN + 4];
+  const int batch = blockIdx.z, t = threadIdx.x;
+  const float *Ab = A + (long long)batch * a_b;
+  const float *Bb = B + (long long)batch * b_b;
+  float *Cb = C + (long long)batch * m * n;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  // one 4-element piece of each tile per thread: along the operand's contiguous direction
+  const bool a_kc = a_cs == 1, b_nc = b_cs == 1;       // A: k contiguous?  B: n contiguous?
+  const int a_i = a_kc ? t >> 1 : (t & 31) * 4, a_p = a_kc ? (t & 1) * 4 : t >> 5;
+  const int b_j = b_nc ? (t & 31) * 4 : t >> 1, b_p = b_nc ? t >> 5 : (t & 1) * 4;
+  float ra[4], rb[4];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int gi = m0 + a_i + (a_kc ? 0 : e), gp = k0 + a_p + (a_kc ? e : 0);
+      ra[e] = (gi < m && gp < k) ? __ldg(Ab + gi * a_rs + gp * a_cs) : 0.f;
+      const int gj = n0 + b_j + (b_nc ? e : 0), gq = k0 + b_p + (b_nc ? 0 : e);
+      rb[e] = (gj < n && gq < k) ? __ldg(Bb + gq * b_rs + gj * b_cs) : 0.f;
+    }
+  };
+  auto fetch_vec = [&](int k0) {       // whole pieces inside the matrix, 16-byte aligned (checked by the host)
+    const int gi = m0 + a_i, gp = k0 + a_p;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (gi < m && gp < k) v = __ldg(reinterpret_cast<const float4 *>(Ab + gi * a_rs + gp * a_cs));
+    ra[0] = v.x; ra[1] = v.y; ra[2] = v.z; ra[3] = v.w;
+    const int gj = n0 + b_j, gq = k0 + b_p;
+    v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (gj < n && gq < k) v = __ldg(reinterpret_cast<const float4 *>(Bb + gq * b_rs + gj * b_cs));
+    rb[0] = v.x; rb[1] = v.y; rb[2] = v.z; rb[3] = v.w;
+  };
+  auto stage = [&](int buf) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      As[buf][a_p + (a_kc ? e : 0)][a_i + (a_kc ? 0 : e)] = ra[e];
+      Bs[buf][b_p + (b_nc ? 0 : e)][b_j + (b_nc ? e : 0)] = rb[e];
+    }
+  };
+  const int tx = t & 15, ty = t >> 4;
+  float acc[8][8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u)
+#pragma unroll
+    for (int v = 0; v < 8; ++v) acc[u][v] = 0.f;
+  if (VEC) fetch_vec(0); else fetch(0);
+  stage(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < k; k0 += BK) {
+    const bool more = k0 + BK < k;
+    if (more) { if (VEC) fetch_vec(k0 + BK); else fetch(k0 + BK); }
+#pragma unroll
+    for (int p = 0; p < BK; ++p) {
+      // rows ty*4 .. +3 and 64 + ty*4 .. +3, columns tx*4 .. +3 and 64 + tx*4 .. +3: conflict-free 128-bit reads
+      const float4 a0 = *reinterpret_cast<const float4 *>(&As[buf][p][ty * 4]);
+      const float4 a1 = *reinterpret_cast<const float4 *>(&As[buf][p][64 + ty * 4]);
+      const float4 b0 = *reinterpret_cast<const float4 *>(&Bs[buf][p][tx * 4]);
+      const float4 b1 = *reinterpret_cast<const float4 *>(&Bs[buf][p][64 + tx * 4]);
+      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int v = 0; v < 8; ++v) acc[u][v] = fmaf(a[u], b[v], acc[u][v]);
+    }
+    if (more) {
+      stage(buf ^ 1);
+      __syncthreads();
+      buf ^= 1;
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const int gi = m0 + (u < 4 ? ty * 4 + u : 64 + ty * 4 + (u - 4));
+    if (gi >= m) continue;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int gj = n0 + h * 64 + tx * 4;
+      float *crow = Cb + (long long)gi * n + gj;
+      if (VEC && gj + 3 < n) {
+        *reinterpret_cast<float4 *>(crow) = make_float4(acc[u][4 * h], acc[u][4 * h + 1], acc[u][4 * h + 2], acc[u][4 * h + 3]);
+      } else {
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+          if (gj + v < n) crow[v] = acc[u][4 * h + v];
+      }
+    }
+  }
+}
+
+inline bool al16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+int32_t launch_f32(ugb_device *dev, float *dst, const float *lhs, const float *rhs, size_t b, size_t m, size_t n, size_t k,
+                   const MatLayout &L, const MatLayout &R) {
+  if (k == 0) {
+    UGB_CUDA(dev, cudaMemsetAsync(dst, 0, b * m * n * sizeof(float), dev->stream));
+    return UGB_OK;
+  }
+  UGB_REQUIRE(dev, b <= 65535, UGB_ERR_UNSUPPORTED, "matmul: batch too large");
+  const bool bases = al16(dst) && al16(lhs) && al16(rhs) && L.batch % 4 == 0 && R.batch % 4 == 0;
+  if (m <= 16 && !L.transposed && R.transposed && k % 4 == 0 && bases) {
+    const dim3 grid((unsigned)((n + 7) / 8), (unsigned)b);
+#define UGB_SKINNY(MR) f32_skinny_kernel<MR><<<grid, 256, 0, dev->stream>>>(dst, lhs, rhs, (int)m, (int)n, (int)k, L.batch, R.batch)
+    if (m <= 1) UGB_SKINNY(1); else if (m <= 2) UGB_SKINNY(2); else if (m <= 4) UGB_SKINNY(4); else if (m <= 8) UGB_SKINNY(8); else UGB_SKINNY(16);
+#undef UGB_SKINNY
+    return ugb_after_launch(dev, "f32_skinny_kernel");
+  }
+  const dim3 grid((unsigned)((n + 127) / 128), (unsigned)((m + 127) / 128), (unsigned)b);
+  UGB_REQUIRE(dev, grid.y <= 65535, UGB_ERR_UNSUPPORTED, "matmul: m too large for the f32 kernel");
+  // 128-bit pieces: the contiguous extent and the leading stride of each operand in whole float4s
+  const size_t a_c = L.transposed ? m : k, a_ld = (size_t)(L.transposed ? L.cs : L.rs);
+  const size_t b_c = R.transposed ? k : n, b_ld = (size_t)(R.transposed ? R.cs : R.rs);
+  const bool vec = bases && a_c % 4 == 0 && a_ld % 4 == 0 && b_c % 4 == 0 && b_ld % 4 == 0 && n % 4 == 0;
+  if (vec) f32_tile_kernel<true><<<grid, 256, 0, dev->stream>>>(dst, lhs, rhs, (int)m, (int)n, (int)k, L.rs, L.cs, L.batch, R.rs, R.cs, R.batch);
+  else f32_tile_kernel<false><<<grid, 256, 0, dev->stream>>>(dst, lhs, rhs, (int)m, (int)n, (int)k, L.rs, L.cs, L.batch, R.rs, R.cs, R.batch);
+  return ugb_after_launch(dev, "f32_tile_kernel");
+}
+
 template <typename T>
 int32_t launch_simt(ugb_device *dev, void *dst, const void *lhs, const void *rhs, size_t b, size_t m,
                     size_t n, size_t k, const MatLayout &L, const MatLayout &R) {
@@ -178,14 +345,15 @@ int32_t ugb_matmul(ugb_device *dev, ugb_slice *dst, const ugb_slice *lhs, const 
   const char *rp = (const char *)rhs->ptr + rhs_off * es;
 
   // Tiny products do not fill a 128-row tensor-core tile; the strided kernel handles them.
-  if (dt == UGB_BF16 && !L.transposed && m >= 16 && m * n >= 128 * 64) {
-    // tensor-core path: A [m,k] row-major, B either [n,k] row-major ("TN",
-    // matmul_t with a weight) or [k,n] row-major ("NN").
-    int32_t trc = ugb_tc_gemm_bf16(dev, dst->ptr, lp, rp, b, m, n, k, L.batch, R.batch, R.transposed);
+  if ((dt == UGB_BF16 || dt == UGB_F16) && !L.transposed && m >= 16 && m * n >= 128 * 64) {
+    // tensor-core path (bf16 and f16 are the same tcgen05.mma.kind::f16 instruction with another format field, as
+    // both go to cublasGemmStridedBatchedEx in the reference, gemm.rs:130-232): A [m,k] row-major, B either
+    // [n,k] row-major ("TN", matmul_t with a weight) or [k,n] row-major ("NN").
+    int32_t trc = ugb_tc_gemm_bf16(dev, dst->ptr, lp, rp, b, m, n, k, L.batch, R.batch, R.transposed, dt == UGB_F16);
     if (trc != UGB_ERR_UNSUPPORTED) return trc;
   }
   switch (dt) {
-    case UGB_F32: return launch_simt<float>(dev, dst->ptr, lp, rp, b, m, n, k, L, R);
+    case UGB_F32: return launch_f32(dev, (float *)dst->ptr, (const float *)lp, (const float *)rp, b, m, n, k, L, R);
     case UGB_BF16: return launch_simt<__nv_bfloat16>(dev, dst->ptr, lp, rp, b, m, n, k, L, R);
     default: return launch_simt<__half>(dev, dst->ptr, lp, rp, b, m, n, k, L, R);
   }

@@ -146,11 +146,11 @@ static __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_
   d |= (uint64_t)2 << 61;
   return d;
 }
-// Instruction descriptor for kind::f16: D = f32, A = B = bf16, M x N tile.
-//   bits 4-5 D format (1 = f32)   bits 7-9 A format (1 = bf16)   bits 10-12 B format
+// Instruction descriptor for kind::f16: D = f32, A and B both bf16 (or both f16), M x N tile.
+//   bits 4-5 D format (1 = f32)   bits 7-9 A format (0 = f16, 1 = bf16)   bits 10-12 B format
 //   bit 15 A major (0 = K)        bit 16 B major (1 = MN)        bits 17-22 N >> 3   bits 24-28 M >> 4
-static __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+static __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn_major, bool f16 = false) {
+  return (1u << 4) | ((f16 ? 0u : 1u) << 7) | ((f16 ? 0u : 1u) << 10) | ((b_mn_major ? 1u : 0u) << 16) |
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
