@@ -130,48 +130,37 @@ simt_gemm_kernel(T *__restrict__ C, const T *__restrict__ A, const T *__restrict
 // weight, model.rs:147-149, for the one new token of a decode step): HBM-bound on the weight.  One warp per output
 // column: the lanes stream the column's k values with 128-bit loads, every value is used for all m rows, the
 // partial dot products are summed by warp shuffles.
-template <int MR, int CPW>
+template <int MR>
 __global__ void __launch_bounds__(256)
 f32_skinny_kernel(float *__restrict__ C, const float *__restrict__ A, const float *__restrict__ B, int m, int n, int k,
                   long long a_b, long long b_b) {
-  // a warp owns CPW consecutive output columns: every activation value it loads is used for CPW weights
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int col0 = (blockIdx.x * 8 + warp) * CPW;
-  if (col0 >= n) return;
+  const int col = blockIdx.x * 8 + warp;
+  if (col >= n) return;
   const int batch = blockIdx.y;
-  const float *wb = B + (long long)batch * b_b;
+  const float4 *w = reinterpret_cast<const float4 *>(B + (long long)batch * b_b + (long long)col * k);
   const float *a = A + (long long)batch * a_b;
-  float acc[MR][CPW];
+  float acc[MR];
 #pragma unroll
-  for (int r = 0; r < MR; ++r)
-#pragma unroll
-    for (int j = 0; j < CPW; ++j) acc[r][j] = 0.f;
+  for (int r = 0; r < MR; ++r) acc[r] = 0.f;
   const int k4 = k >> 2;
-#pragma unroll 2
+#pragma unroll 4
   for (int c = lane; c < k4; c += 32) {
-    float4 wv[CPW];
-#pragma unroll
-    for (int j = 0; j < CPW; ++j)                      // streamed once; columns past n repeat the last one (never stored)
-      wv[j] = __ldcs(reinterpret_cast<const float4 *>(wb + (long long)min(col0 + j, n - 1) * k) + c);
+    const float4 wv = __ldcs(w + c);                 // streamed once
 #pragma unroll
     for (int r = 0; r < MR; ++r) {
       if (r < m) {
         const float4 x = __ldg(reinterpret_cast<const float4 *>(a + (long long)r * k) + c);
-#pragma unroll
-        for (int j = 0; j < CPW; ++j)
-          acc[r][j] = fmaf(x.x, wv[j].x, fmaf(x.y, wv[j].y, fmaf(x.z, wv[j].z, fmaf(x.w, wv[j].w, acc[r][j]))));
+        acc[r] = fmaf(x.x, wv.x, fmaf(x.y, wv.y, fmaf(x.z, wv.z, fmaf(x.w, wv.w, acc[r]))));
       }
     }
   }
 #pragma unroll
-  for (int r = 0; r < MR; ++r)
+  for (int r = 0; r < MR; ++r) {
 #pragma unroll
-    for (int j = 0; j < CPW; ++j) {
-      float v = acc[r][j];
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane == 0 && r < m && col0 + j < n) C[(long long)batch * m * n + (long long)r * n + col0 + j] = v;
-    }
+    for (int o = 16; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+    if (lane == 0 && r < m) C[(long long)batch * m * n + (long long)r * n + col] = acc[r];
+  }
 }
 
 // (2) Everything else in f32: 128 x 128 output tile per CTA, k slices of 8, 256 threads with 8 x 8 outputs each in
@@ -283,9 +272,9 @@ int32_t launch_f32(ugb_device *dev, float *dst, const float *lhs, const float *r
   UGB_REQUIRE(dev, b <= 65535, UGB_ERR_UNSUPPORTED, "matmul: batch too large");
   const bool bases = al16(dst) && al16(lhs) && al16(rhs) && L.batch % 4 == 0 && R.batch % 4 == 0;
   if (m <= 16 && !L.transposed && R.transposed && k % 4 == 0 && bases) {
-#define UGB_SKINNY(MR, CPW) f32_skinny_kernel<MR, CPW><<<dim3((unsigned)((n + 8 * CPW - 1) / (8 * CPW)), (unsigned)b), 256, 0, dev->stream>>>( \
-    dst, lhs, rhs, (int)m, (int)n, (int)k, L.batch, R.batch)
-    if (m <= 1) UGB_SKINNY(1, 1); else if (m <= 2) UGB_SKINNY(2, 2); else if (m <= 4) UGB_SKINNY(4, 4); else if (m <= 8) UGB_SKINNY(8, 4); else UGB_SKINNY(16, 2);
+    const dim3 grid((unsigned)((n + 7) / 8), (unsigned)b);
+#define UGB_SKINNY(MR) f32_skinny_kernel<MR><<<grid, 256, 0, dev->stream>>>(dst, lhs, rhs, (int)m, (int)n, (int)k, L.batch, R.batch)
+    if (m <= 1) UGB_SKINNY(1); else if (m <= 2) UGB_SKINNY(2); else if (m <= 4) UGB_SKINNY(4); else if (m <= 8) UGB_SKINNY(8); else UGB_SKINNY(16);
 #undef UGB_SKINNY
     return ugb_after_launch(dev, "f32_skinny_kernel");
   }
