@@ -9,11 +9,11 @@
 // layers in order, limited only by its shared-memory ring, so the weights of the next projection arrive
 // while the current phase computes and while the barrier is pending.
 //
-// CTA = 256 threads:
+// CTA = 384 threads:
 //   warp 0      weight producer: cp.async.bulk.tensor (TMA) of [bn x 64] weight tiles into a ring of 16 KiB stages
 //   warp 1      MMA issuer: tcgen05.mma (M = 64, N = bn, K = 16) into two TMEM accumulator stages; owns TMEM
 //   warp 2      activation producer: TMA of [64 rows x 64] activation tiles, after the barrier that completes them
-//   warps 4..7  everything else: GEMM epilogues (tcgen05.ld -> fp32 split-K partials / silu(gate) * up),
+//   warps 4..11 everything else: GEMM epilogues (tcgen05.ld -> fp32 split-K partials / silu(gate) * up),
 //               residual add + RMSNorm rows, rope + KV append + grouped-query flash-decode attention, and the
 //               grid barriers
 // Phases of a layer (a grid barrier after each):
@@ -50,28 +50,30 @@ using ugb_decode::pack_bf16;
 using ugb_decode::warp_sum;
 
 constexpr int BK = 64;
-constexpr int NB = 8;                       // weight ring stages
-constexpr int NA = 8;                       // activation ring stages
+constexpr int NB = 7;                       // weight ring stages
+constexpr int NA = 12;                      // activation ring stages
 constexpr int B_STAGE = 16384;              // up to 128 weight rows x 64 k bf16
 constexpr int A_STAGE = 8192;               // 64 activation rows x 64 k bf16
 constexpr int ACC_STRIDE = 128;             // TMEM columns between the two accumulator stages
 constexpr int TMEM_COLS = 256;
-constexpr int THREADS = 256;
-constexpr int EPI_WARP0 = 4;                // warps 4..7: TMEM lane quadrants 0..3
-constexpr int EPI_THREADS = 128;
-constexpr int ATT_ST = 4;                   // 16-key sub-tiles in flight per warp (4 warps x 4 x 4 KiB = the activation ring)
+constexpr int THREADS = 384;
+constexpr int EPI_WARP0 = 4;                // warps 4..11: TMEM lane quadrant = warp & 3
+constexpr int EPI_WARPS = 8;
+constexpr int EPI_THREADS = EPI_WARPS * 32;
+constexpr int ATT_ST = 3;                   // 16-key sub-tiles per warp in the ring (8 warps x 3 x 4 KiB = the activation ring)
+constexpr int ATT_PF = 4;                   // L2 prefetch distance, in sub-tiles of the same warp
 constexpr int ATT_SUB = 16, ATT_HD = 64, ATT_GROUP = 8;
 constexpr int ATT_SUB_BYTES = ATT_SUB * ATT_HD * 2;
 constexpr int MAX_PART = 9;                 // split-K partials a row phase sums at most
 constexpr int SYNCS_PER_LAYER = 7;
 
-static_assert(NA * A_STAGE == 4 * ATT_ST * 2 * ATT_SUB_BYTES, "the attention ring aliases the activation ring");
+static_assert(NA * A_STAGE == EPI_WARPS * ATT_ST * 2 * ATT_SUB_BYTES, "the attention ring aliases the activation ring");
 
 struct Smem {
   uint8_t b_ring[NB][B_STAGE];
   uint8_t a_ring[NA][A_STAGE];              // during the attention phase: [warp][stage][K | V][2 KiB]
-  float merge_o[4][ATT_GROUP][ATT_HD];
-  float merge_ml[4][ATT_GROUP][2];
+  float merge_o[EPI_WARPS][ATT_GROUP][ATT_HD];
+  float merge_ml[EPI_WARPS][ATT_GROUP][2];
   float red[8];
   uint64_t full_b[NB], empty_b[NB], full_a[NA], empty_a[NA], acc_full[2], acc_empty[2];
   uint32_t tmem_slot;
@@ -93,7 +95,10 @@ __device__ __forceinline__ int ld_acquire_cta_shared(const int *p) {
 __device__ __forceinline__ void st_release_cta_shared(int *p, int v) {
   asm volatile("st.release.cta.shared.s32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
 }
-__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
 
 // What every bounded wait of this kernel shares: the CTA's abort flag, the grid's abort word, the status word.
 struct Waiter {
@@ -113,11 +118,13 @@ struct Waiter {
   __device__ __forceinline__ unsigned long long limit_ns() const {
     return 1000ull * *reinterpret_cast<volatile unsigned int *>(&status->wait_limit_us);
   }
+  int backoff_ns = 0;
   __device__ __forceinline__ bool mbar(uint32_t bar, uint32_t parity, unsigned site) const {
     if (mbar_try(bar, parity)) return true;
     const unsigned long long t0 = globaltimer();
     for (unsigned it = 1;; ++it) {
       if (mbar_try(bar, parity)) return true;
+      if (backoff_ns) __nanosleep(backoff_ns);
       if ((it & 255u) == 0) {
         if (aborted()) return false;
         if (globaltimer() - t0 > limit_ns()) { give_up(site); return false; }
@@ -138,7 +145,7 @@ __device__ __forceinline__ Item item_of(const ugb_step_gemm &g, int item) {
 
 // ---------------------------------------------------------------------------------------------------------
 // rows phase: x[r] (+)= sum of partials (or the embedding row), xn[r] = bf16(x / sqrt(mean(x^2) + eps) * gain)
-// (Layer::fwd's residual add + RmsNorm::fwd, model.rs:65-78,259-269).  128 threads per row.
+// (Layer::fwd's residual add + RmsNorm::fwd, model.rs:65-78,259-269).  256 threads per row.
 __device__ void rows_phase(const ugb_step_params &p, Smem &s, int et, int cta, int grid, const float *part, int n_part,
                            size_t part_stride, const float *__restrict__ gain, bool from_embed) {
   const int H = p.hidden, nvec = H >> 2;
@@ -154,8 +161,52 @@ __device__ void rows_phase(const ugb_step_params &p, Smem &s, int et, int cta, i
       er = reinterpret_cast<const uint2 *>(p.embed + (size_t)id * H);
     }
     float ss = 0.f;
-    // one float4 of the row: the embedding value, or x plus the partials (all loads of a float4 issued together)
-    auto fetch = [&](int c) {
+    // The row's first 1024 float4 (all of them when hidden <= 4096) are fetched with every load -- x and all partials
+    // -- in flight before the first addition, and stay in registers for the second pass.
+    constexpr int KEEP = 4;
+    float4 keep[KEEP];
+    if (from_embed) {
+#pragma unroll
+      for (int i = 0; i < KEEP; ++i) {
+        const int c = et + i * EPI_THREADS;
+        keep[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < nvec) {
+          const uint2 e = __ldg(er + c);
+          const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&e.x));
+          const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&e.y));
+          keep[i] = make_float4(lo.x, lo.y, hi.x, hi.y);
+        }
+      }
+    } else {
+      float4 q[2][MAX_PART];
+#pragma unroll
+      for (int h = 0; h < KEEP; h += 2) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int c = et + (h + i) * EPI_THREADS;
+          keep[h + i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (c < nvec) keep[h + i] = __ldcg(xr + c);
+#pragma unroll
+          for (int sp = 0; sp < MAX_PART; ++sp)
+            q[i][sp] = (c < nvec && sp < n_part) ? __ldcg(reinterpret_cast<const float4 *>(part + sp * part_stride + (size_t)r * H) + c)
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+          for (int sp = 0; sp < MAX_PART; ++sp)
+            if (sp < n_part) { keep[h + i].x += q[i][sp].x; keep[h + i].y += q[i][sp].y; keep[h + i].z += q[i][sp].z; keep[h + i].w += q[i][sp].w; }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) {
+      const int c = et + i * EPI_THREADS;
+      if (c < nvec) {
+        if (from_embed || n_part > 0) xr[c] = keep[i];
+        ss += (keep[i].x * keep[i].x + keep[i].y * keep[i].y) + (keep[i].z * keep[i].z + keep[i].w * keep[i].w);
+      }
+    }
+    for (int c = et + KEEP * EPI_THREADS; c < nvec; c += EPI_THREADS) {      // hidden > 4096: the rest of the row, one float4 at a time
       float4 v;
       if (from_embed) {
         const uint2 e = __ldg(er + c);
@@ -164,31 +215,19 @@ __device__ void rows_phase(const ugb_step_params &p, Smem &s, int et, int cta, i
         v = make_float4(lo.x, lo.y, hi.x, hi.y);
       } else {
         v = __ldcg(xr + c);
-        float4 q[MAX_PART];
-#pragma unroll
-        for (int sp = 0; sp < MAX_PART; ++sp)
-          q[sp] = sp < n_part ? __ldcg(reinterpret_cast<const float4 *>(part + sp * part_stride + (size_t)r * H) + c)
-                              : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int sp = 0; sp < MAX_PART; ++sp)
-          if (sp < n_part) { v.x += q[sp].x; v.y += q[sp].y; v.z += q[sp].z; v.w += q[sp].w; }
+        for (int sp = 0; sp < n_part; ++sp) {
+          const float4 qv = __ldcg(reinterpret_cast<const float4 *>(part + sp * part_stride + (size_t)r * H) + c);
+          v.x += qv.x; v.y += qv.y; v.z += qv.z; v.w += qv.w;
+        }
       }
       if (from_embed || n_part > 0) xr[c] = v;
       ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
-      return v;
-    };
-    float4 keep[4];                          // the row's first 512 float4 stay in registers (all of them when hidden <= 2048)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c = et + i * EPI_THREADS;
-      keep[i] = c < nvec ? fetch(c) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    for (int c = et + 4 * EPI_THREADS; c < nvec; c += EPI_THREADS) fetch(c);
     ss = warp_sum(ss);
     epi_bar();                               // s.red is free again (previous row)
     if ((et & 31) == 0) s.red[et >> 5] = ss;
     epi_bar();
-    const float tot = (s.red[0] + s.red[1]) + (s.red[2] + s.red[3]);
+    const float tot = ((s.red[0] + s.red[1]) + (s.red[2] + s.red[3])) + ((s.red[4] + s.red[5]) + (s.red[6] + s.red[7]));
     const float m = sqrtf(tot * p.inv_d + p.eps);
     uint2 *out = reinterpret_cast<uint2 *>(p.xn + (size_t)r * H);
     auto emit = [&](int c, const float4 &v) {
@@ -196,17 +235,17 @@ __device__ void rows_phase(const ugb_step_params &p, Smem &s, int et, int cta, i
       out[c] = make_uint2(pack_bf16(v.x / m * gw.x, v.y / m * gw.y), pack_bf16(v.z / m * gw.z, v.w / m * gw.w));
     };
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < KEEP; ++i) {
       const int c = et + i * EPI_THREADS;
       if (c < nvec) emit(c, keep[i]);
     }
-    for (int c = et + 4 * EPI_THREADS; c < nvec; c += EPI_THREADS) emit(c, xr[c]);
+    for (int c = et + KEEP * EPI_THREADS; c < nvec; c += EPI_THREADS) emit(c, xr[c]);
   }
 }
 
 // ---------------------------------------------------------------------------------------------------------
 // GEMM epilogue of one phase: drains this CTA's accumulators.  64 accumulator rows: rows 16q .. 16q + 15 sit on
-// lanes 0 .. 15 of TMEM lane quadrant q (= epilogue warp q).
+// lanes 0 .. 15 of TMEM lane quadrant q; warps q and q + 4 share quadrant q and take alternate 32-column chunks.
 __device__ bool gemm_epilogue(const ugb_step_params &p, Smem &s, const Waiter &w, const ugb_step_gemm &g, int phase,
                               uint32_t tmem_base, int ew, int lane, int cta, int grid, int &acc, uint32_t &acc_phase) {
   for (int item = cta; item < g.items; item += grid) {
@@ -214,11 +253,12 @@ __device__ bool gemm_epilogue(const ugb_step_params &p, Smem &s, const Waiter &w
     const int sp = item / g.tiles, n0 = it.tile * g.bn;
     if (!w.mbar(smem_u32(&s.acc_full[acc]), acc_phase, 0x104u)) return false;
     tcgen05_fence_after();
-    const int row = ew * 16 + lane;
+    const int quad = ew & 3;
+    const int row = quad * 16 + lane;
     const bool live = lane < 16 && row < p.batch;
-    for (int c = 0; c * 32 < g.bn; ++c) {
+    for (int c = ew >> 2; c * 32 < g.bn; c += 2) {
       uint32_t v[32];
-      tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * ACC_STRIDE + c * 32), v);
+      tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * ACC_STRIDE + c * 32), v);
       tmem_ld_wait();
       if (!live) continue;
       const int col0 = n0 + c * 32;
@@ -255,8 +295,9 @@ __device__ bool gemm_epilogue(const ugb_step_params &p, Smem &s, const Waiter &w
 
 // ---------------------------------------------------------------------------------------------------------
 // attention phase (model.rs:203-245 between the projections, for one query position per sequence): the CTA's
-// share [f_lo, f_hi) of the flattened (pair, 16-key sub-tile) list; warp w of the four takes sub-tiles
-// f_lo + w, f_lo + w + 4, ...  with a private cp.async ring and a private online-softmax state.
+// share [f_lo, f_hi) of the flattened (pair, 16-key sub-tile) list; warp w of the eight takes sub-tiles
+// f_lo + w, f_lo + w + 8, ...  with a private cp.async ring (plus L2 prefetches further ahead) and a private
+// online-softmax state.
 __device__ void attention_phase(const ugb_step_params &p, Smem &s, int layer, int T, int ew, int lane, int et, int cta,
                                 int grid) {
   const int n_kv = p.n_kv, n_heads = p.n_heads, group = p.group, t_max = p.t_max;
@@ -266,7 +307,24 @@ __device__ void attention_phase(const ugb_step_params &p, Smem &s, int layer, in
   const long long f_lo = (long long)cta * per, f_hi = min(S, f_lo + per);
   if (f_lo >= f_hi) return;                                   // CTA-uniform: nothing dealt to this CTA
   __nv_bfloat16 *kcache = p.layer[layer].kcache, *vcache = p.layer[layer].vcache;
-  uint8_t (*ring)[ATT_ST][2][ATT_SUB_BYTES] = reinterpret_cast<uint8_t (*)[ATT_ST][2][ATT_SUB_BYTES]>(&s.a_ring[0][0]);
+  if (p.tune & 8) {   // measurement aid: read this CTA's share of K and V with plain 128-bit loads, nothing else
+    float sink = 0.f;
+    for (int which = 0; which < 2; ++which) {
+      const int pair0 = (int)(f_lo / n_sub), sub0 = (int)(f_lo - (long long)pair0 * n_sub);
+      const uint4 *src = reinterpret_cast<const uint4 *>((which ? vcache : kcache) + ((size_t)pair0 * t_max + (size_t)sub0 * ATT_SUB) * ATT_HD);
+      const long long n16 = (f_hi - f_lo) * (ATT_SUB_BYTES / 16);     // (ignores the gaps between pairs: a bandwidth probe)
+      for (long long i = et; i < n16; i += 8 * EPI_THREADS) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = i + u * EPI_THREADS < n16 ? __ldcs(src + i + u * EPI_THREADS) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) sink += __uint_as_float(v[u].x ^ v[u].w);
+      }
+    }
+    if (sink == 123.456f) p.att_pml[0] = sink;
+    return;
+  }
+  uint8_t (*ring)[ATT_ST][2][ATT_SUB_BYTES] = reinterpret_cast<uint8_t (*)[ATT_ST][2][ATT_SUB_BYTES]>(&s.a_ring[0][0]);   // [warp][stage][K | V]
   const int g = lane >> 2, t = lane & 3;
   const int half = ATT_HD / 2, pos = T - 1, sub_pos = pos / ATT_SUB;
   const int n_part = p.g[UGB_STEP_QKV].splits;
@@ -325,6 +383,14 @@ __device__ void attention_phase(const ugb_step_params &p, Smem &s, int layer, in
   auto issue = [&](long long f, int stage) {
     const int pair = (int)(f / n_sub), sub = (int)(f - (long long)pair * n_sub);
     if (sub == sub_pos) append_kv(pair);
+    {   // the sub-tile this warp will fetch ATT_PF iterations from now: on its way from HBM to L2 already
+      const long long fp = f + (long long)ATT_PF * EPI_WARPS;
+      if (fp < f_hi && lane < 2 && !(p.tune & 2)) {
+        const int pp = (int)(fp / n_sub), sp2 = (int)(fp - (long long)pp * n_sub);
+        const __nv_bfloat16 *base = lane == 0 ? kcache : vcache;
+        l2_prefetch(base + ((size_t)pp * t_max + (size_t)sp2 * ATT_SUB) * ATT_HD, ATT_SUB_BYTES);
+      }
+    }
     const uint32_t ks = smem_u32(&ring[ew][stage][0][0]), vs = smem_u32(&ring[ew][stage][1][0]);
     const char *kg = reinterpret_cast<const char *>(kcache + ((size_t)pair * t_max + (size_t)sub * ATT_SUB) * ATT_HD);
     const char *vg = reinterpret_cast<const char *>(vcache + ((size_t)pair * t_max + (size_t)sub * ATT_SUB) * ATT_HD);
@@ -413,10 +479,10 @@ __device__ void attention_phase(const ugb_step_params &p, Smem &s, int layer, in
       const int h = idx / ATT_HD, dd = idx - h * ATT_HD;
       float mm = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) mm = fmaxf(mm, s.merge_ml[w][h][0]);
+      for (int w = 0; w < EPI_WARPS; ++w) mm = fmaxf(mm, s.merge_ml[w][h][0]);
       float acc = 0.f, ll = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
+      for (int w = 0; w < EPI_WARPS; ++w) {
         const float f = s.merge_ml[w][h][0] == -INFINITY ? 0.f : __expf(s.merge_ml[w][h][0] - mm);
         acc += s.merge_o[w][h][dd] * f;
         ll += s.merge_ml[w][h][1] * f;
@@ -463,13 +529,13 @@ __device__ void attention_phase(const ugb_step_params &p, Smem &s, int layer, in
   const int last_pair = (int)((f_hi - 1) / n_sub);
 #pragma unroll
   for (int st = 0; st < ATT_ST - 1; ++st) {
-    const long long f = f_lo + ew + 4 * st;
+    const long long f = f_lo + ew + EPI_WARPS * st;
     if (f < f_hi) issue(f, st);
     cp_async_commit();
   }
   begin_pair(cur_pair);
   int stage = 0;
-  for (long long f = f_lo + ew;; f += 4) {
+  for (long long f = f_lo + ew;; f += EPI_WARPS) {
     bool done = false;
     while (f >= f_hi || (int)(f / n_sub) > cur_pair) {         // this warp is through with cur_pair
       end_pair(cur_pair);
@@ -478,13 +544,14 @@ __device__ void attention_phase(const ugb_step_params &p, Smem &s, int layer, in
     }
     if (done) break;
     {
-      const long long nxt = f + (ATT_ST - 1) * 4;
+      const long long nxt = f + (ATT_ST - 1) * EPI_WARPS;
       if (nxt < f_hi) issue(nxt, (stage + ATT_ST - 1) % ATT_ST);
       cp_async_commit();
     }
     cp_async_wait<ATT_ST - 1>();
     __syncwarp();
     const int sub = (int)(f - (long long)cur_pair * n_sub);
+    if (p.tune & 1) { __syncwarp(); stage = (stage + 1) % ATT_ST; continue; }
     const uint8_t *ks = &ring[ew][stage][0][0];
     const uint32_t vs = smem_u32(&ring[ew][stage][1][0]);
     float s_acc[2][4];
@@ -544,14 +611,14 @@ __global__ void __launch_bounds__(THREADS, 1) decode_step_kernel(const __grid_co
   Smem &s = *reinterpret_cast<Smem *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x, grid = gridDim.x;
-  const Waiter w{&s.abort_flag, p.sync + 2, p.status};
+  const Waiter w{&s.abort_flag, p.sync + 2, p.status, (p.tune & 4) ? 200 : 0};
   const int L = p.layers;
   const CUtensorMap *act_maps = p.maps + (size_t)L * 4;        // xn, att, h
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NB; ++i) { mbar_init(smem_u32(&s.full_b[i]), 1); mbar_init(smem_u32(&s.empty_b[i]), 1); }
     for (int i = 0; i < NA; ++i) { mbar_init(smem_u32(&s.full_a[i]), 1); mbar_init(smem_u32(&s.empty_a[i]), 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&s.acc_full[i]), 1); mbar_init(smem_u32(&s.acc_empty[i]), 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&s.acc_full[i]), 1); mbar_init(smem_u32(&s.acc_empty[i]), EPI_WARPS); }
     s.abort_flag = 0;
     s.sync_count = 0;
     s.is_last = 0;
@@ -640,6 +707,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_step_kernel(const __grid_co
             const unsigned long long t0 = globaltimer();
             unsigned itn = 0;
             while (ld_acquire_cta_shared(&s.sync_count) < need) {
+              if (p.tune & 4) __nanosleep(200);
               if ((++itn & 63u) == 0) {
                 if (w.aborted()) { alive = false; break; }
                 if (globaltimer() - t0 > w.limit_ns()) { w.give_up(0x106u); alive = false; break; }
@@ -663,7 +731,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_step_kernel(const __grid_co
     }
   } else if (warp >= EPI_WARP0) {
     // --------------------------------------------- epilogues, row phases, attention, barriers --
-    const int ew = warp - EPI_WARP0, et = threadIdx.x - EPI_WARP0 * 32;
+    const int ew = warp - EPI_WARP0, et = threadIdx.x - EPI_WARP0 * 32;   // 0..7, 0..255
     ugb_pdl_wait();                                            // position, tokens and the barrier words are the predecessor's
     const unsigned base = *reinterpret_cast<volatile unsigned *>(p.sync + 1);
     const int T = *p.pos + 1;

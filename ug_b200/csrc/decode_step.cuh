@@ -39,6 +39,8 @@ struct ugb_step_params {
   unsigned int *att_cnt;                 // [batch * n_kv] completion counters, left at zero
   unsigned int *sync;                    // [0] barrier arrivals, [1] arrivals at the start of this launch, [2] abort
   ugb_status_word *status;
+  int tune;                              // measurement aid: bit 0 leaves the attention arithmetic out (results are garbage),
+                                         // bit 1 leaves the L2 prefetches out
   unsigned long long *prof;              // measurement aid (or null): %globaltimer of CTAs 0, 37, 74, 111 at the start,
                                          // and at the arrival at / the completion of every grid barrier: [4][UGB_STEP_PROF_SLOTS]
 };

@@ -786,6 +786,11 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
     if (value && !m->tp && m->batch <= 64) return ensure_step_kernel(m);
     return UGB_OK;
   }
+  if (k == "step_tune") {         // measurement aid of the persistent step kernel; non-zero values give wrong results
+    m->step.tune = value;
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    return UGB_OK;
+  }
   if (k == "step_profile") {      // measurement aid: barrier time stamps of the persistent step kernel (UGB_LLAMA_STEP_PROFILE)
     UGB_REQUIRE(dev, m->step_ready, UGB_ERR_INVALID, "option step_profile: set step_kernel first");
     if (value && !m->step.prof) {
