@@ -330,6 +330,7 @@ class GraphRowWorkload:
     bound = "hbm"
     rows, cols = 8192, 4096
     ncu_traffic_bytes = None
+    kernel_only = True
 
     def __init__(self, which):
         from ug_b200 import synth
@@ -363,6 +364,62 @@ class GraphRowWorkload:
         got = self.y.data_vec().reshape(self.rows, self.cols)[:32]
         ref = oracle.custom_softmax(self.x[:32]) if self.which == "softmax" else oracle.gen_rms_norm(self.x[:32], self.w, 1e-5)
         return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1e-30)))
+
+    def config(self):
+        return {"workload": self.name, "rows_per_gpu": self.rows, "cols": self.cols,
+                "l2": "inputs larger than L2 (268 MB touched per step vs 126 MB L2)"}
+
+
+class F32MatmulWorkload:
+    """f32 matmul_t on the FP32 pipe (the dtype ug-llama casts every weight to, model.rs:118,140,313): the
+    128 x 128 register-blocked kernel on 4096^3 ("gemm_f32", FP32-pipe bound) or the warp-per-column kernel on one
+    activation row against the [32000, 2048] embedding ("gemv_f32", HBM bound on the weight)."""
+    dtype = "f32"
+    kernel_only = True
+    ncu_traffic_bytes = None
+    FP32_PEAK_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12       # SMs x FP32 lanes x 2 flop x max SM clock
+
+    def __init__(self, which):
+        from ug_b200 import synth
+        self.which = which
+        self.m, self.n, self.k = (4096, 4096, 4096) if which == "gemm_f32" else (1, 32000, 2048)
+        self.name = f"f32 matmul_t [{self.m},{self.k}] x [{self.n},{self.k}]^T on the FP32 pipe"
+        self.a = synth.normal(41, (1, self.m, self.k), 0.5)
+        self.b = synth.normal(42, (1, self.n, self.k), 0.5)
+        self.flops_per_step = 2 * self.m * self.n * self.k
+        self.bytes_per_step = 4 * (self.n * self.k + self.m * self.k + self.m * self.n)
+        self.launches_per_step = 1
+        self.bound = "fp32" if which == "gemm_f32" else "hbm"
+        self.unit = "TFLOP/s" if which == "gemm_f32" else "GB/s"
+        self.metric = "f32 GEMM TFLOP/s (FP32 pipe, fp32 products and sums)" if which == "gemm_f32" else \
+            "effective HBM GB/s of the f32 weight stream (decode-shaped matmul_t)"
+
+    def setup(self, dev):
+        from ug_b200 import DType
+        self.dev = dev
+        self.sa, self.sb = dev.slice_from_values(self.a), dev.slice_from_values(self.b)
+        self.dst = dev.allocate_uninit(DType.F32, self.m * self.n)
+        m, n, k = self.m, self.n, self.k
+        self.args = (self.dst, self.sa, self.sb, (1, m, n, k), ([1, m, k], [m * k, k, 1], 0), ([1, k, n], [n * k, 1, k], 0))
+
+    def step(self):
+        self.dev.matmul(*self.args)
+
+    def units(self, step_seconds, n_ranks):
+        if self.which == "gemm_f32":
+            return n_ranks * self.flops_per_step / step_seconds / 1e12
+        return n_ranks * self.bytes_per_step / step_seconds / 1e9
+
+    def check(self):
+        import oracle
+        rows = slice(0, min(self.m, 8))
+        got = self.dst.to_vec().reshape(self.m, self.n)[rows]
+        ref = oracle.matmul(self.a[0, rows], self.b[0], transpose_rhs=True)
+        return float(np.max(np.abs(got - ref)) / (np.sqrt(self.k) * 0.25))
+
+    def config(self):
+        return {"workload": self.name, "m": self.m, "n": self.n, "k": self.k,
+                "l2": "operands of 64 MB or more per launch" if self.which == "gemm_f32" else "262 MB weight read per launch vs 126 MB L2"}
 
 
 class GemmWorkload:
@@ -787,7 +844,9 @@ class PrefillWorkload(DecodeWorkload):
 
 
 WORKLOADS = {"rms_silu": RmsSiluWorkload, "softmax": SoftmaxWorkload, "softmax_c1": SoftmaxC1Workload,
-             "gemm": GemmWorkload, "decode": DecodeWorkload, "prefill": PrefillWorkload}
+             "gemm": GemmWorkload, "decode": DecodeWorkload, "prefill": PrefillWorkload,
+             "graph_softmax": lambda r: GraphRowWorkload("softmax"), "graph_rms_norm": lambda r: GraphRowWorkload("rms_norm"),
+             "gemm_f32": lambda r: F32MatmulWorkload("gemm_f32"), "gemv_f32": lambda r: F32MatmulWorkload("gemv_f32")}
 DEFAULT_WORKLOAD = "decode"
 
 # DRAM traffic of the decode step's kernels, from ncu captures of single launches (dram__bytes_read.sum +
@@ -851,6 +910,11 @@ def roofline_of(wl, step_s, peaks):
     launch_s = step_s / wl.launches_per_step
     if wl.bound == "hbm":
         achieved, peak, unit = wl.bytes_per_step / wl.launches_per_step / launch_s / 1e9, peaks["hbm"], "GB/s"
+    elif wl.bound == "fp32":
+        r = {"bound": "fp32", "achieved": round(wl.flops_per_step / launch_s / 1e12, 2), "peak": round(wl.FP32_PEAK_TFLOPS, 1),
+             "unit": "TFLOP/s", "traffic": None, "peak_source": "nominal: SMs x 128 FP32 lanes x 2 x max SM clock"}
+        r["frac"] = round(r["achieved"] / r["peak"], 4)
+        return r
     else:
         peak = peaks["bf16_sustained"] if getattr(wl, "sustained_peak", False) else peaks["bf16"]
         achieved, unit = wl.flops_per_step / wl.launches_per_step / launch_s / 1e12, "TFLOP/s"
@@ -872,7 +936,9 @@ def config_records(dev, group, peaks):
             ("config2_rms_norm_silu_gate", RmsSiluWorkload, 50), ("config3_gemm", GemmWorkload, 30),
             ("config4_prefill", PrefillWorkload, 10),
             ("graph_softmax_8192x4096", lambda r: GraphRowWorkload("softmax"), 30),
-            ("graph_rms_norm_8192x4096", lambda r: GraphRowWorkload("rms_norm"), 30)]
+            ("graph_rms_norm_8192x4096", lambda r: GraphRowWorkload("rms_norm"), 30),
+            ("f32_gemm_4096", lambda r: F32MatmulWorkload("gemm_f32"), 10),
+            ("f32_decode_matmul_1x32000x2048", lambda r: F32MatmulWorkload("gemv_f32"), 50)]
     for key, cls, steps in plan:
         wl = cls(0)
         wl.setup(dev)
@@ -985,6 +1051,27 @@ def main():
         mode = None
         wl = make_workload(rank)
         wl.setup(dev)
+        if getattr(wl, "kernel_only", False):
+            # secondary records (no end-to-end leg, no CPU arm): device-timed value, roofline, parity
+            for _ in range(args.warmup):
+                wl.step()
+            dev.synchronize()
+            dev.timer_begin()
+            for _ in range(args.steps):
+                wl.step()
+            dev.timer_end()
+            step_s = dev.timer_elapsed_ms() / 1e3 / args.steps
+            err, _ = parity_of(wl)
+            if rank == 0:
+                rec = {"metric": wl.metric, "value": round(wl.units(step_s, 1), 2), "unit": wl.unit, "n_gpus": 1,
+                       "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(step_s * 1e3, 5), "dtype": wl.dtype,
+                       "config": _config_of(wl, 1), "roofline": roofline_of(wl, step_s, measured_peaks()),
+                       "parity_max_rel_err": err, "gpu_launches": int(dev.launch_count)}
+                if hasattr(wl, "compiled"):
+                    rec["kernels"] = wl.compiled.origins()
+                print(json.dumps(rec), flush=True)
+            group.close()
+            return 0
         m = measure(wl, dev, group, rank, local_rank, args.warmup, args.steps, e2e_steps)
 
     tp = decode and mode == "tp"

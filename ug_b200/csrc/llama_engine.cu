@@ -630,6 +630,13 @@ int32_t ugb_llama_create_tp(ugb_device *dev, const ugb_llama_config *cfg, int32_
   TRY(dmalloc(m, &m->tok, B, true));
   TRY(dmalloc(m, &m->next, B, true));
   TRY(dmalloc(m, &m->pos, 1, true));
+  {
+    // A (sequence, KV head) pair is one attention CTA per KV slice; with few sequences (a rank's share of a batch that
+    // is split over several GPUs) the cache is cut into slices so that about 256 CTAs stream it, as at batch 64
+    const int pairs = batch * c.n_kv_heads;
+    int splits = (256 + pairs - 1) / pairs;
+    m->att_splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
+  }
   if (tp) {
     // exchange block: header | o_proj partials | down_proj partials | argmax pairs.  Partial buffers hold
     // up to 8 split-K partials of a decode step or one partial of a prefill chunk, whichever is larger.
