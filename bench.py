@@ -1081,6 +1081,24 @@ def main():
         for name in wl.model.KERNELS:
             kern[name] = round(wl.model.time_kernel(name, 20), 4)
         kdepth = wl.model.position                      # cache depth the kernels were timed at
+    step_phases = None
+    if rank == 0 and decode and options.get("step_kernel") and options.get("step_profile"):
+        # the persistent step kernel's own clock: per layer, mean microseconds CTA 0 spends working in each phase and
+        # waiting at the grid barrier that ends it (%globaltimer stamps of the last step)
+        import ctypes as C
+        from ug_b200._lib import lib
+        buf = np.zeros(4 * 512, np.float32)
+        dev._check(lib.ugb_llama_read(wl.model._h, 4, buf.ctypes.data, buf.size))
+        t = buf.reshape(4, 512)[0]
+        n_sync = 7 * wl.cfg.num_hidden_layers
+        arrive, done = t[1:1 + 2 * n_sync:2], t[2:2 + 2 * n_sync:2]
+        start = np.concatenate([[t[0]], done[:-1]])
+        names = ["rows1", "qkv", "attention", "o", "rows2", "gate_up", "down"]
+        work = (arrive - start).reshape(-1, 7)[1:].mean(0)
+        wait = (done - arrive).reshape(-1, 7)[1:].mean(0)
+        step_phases = {"work_us": {n: round(float(v), 2) for n, v in zip(names, work)},
+                       "barrier_wait_us": {n: round(float(v), 2) for n, v in zip(names, wait)},
+                       "kernel_us": round(float(done[-1] - t[0]), 1)}
     dev.synchronize()
     group.barrier()
     # under tensor parallelism every engine call is collective: all ranks run the parity check
@@ -1137,6 +1155,8 @@ def main():
             "roofline": roof,
         }
         line.update(extra)
+        if step_phases:
+            line["step_kernel_phases"] = step_phases
         if hasattr(wl, "reference_cuda_gbs"):
             g = wl.reference_cuda_gbs()
             line["reference_cuda_kernel"] = None if g is None else {
