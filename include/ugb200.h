@@ -217,7 +217,13 @@ typedef struct {
 
 /* ug::Device::compile (lib.rs:56; ug-cuda/src/runtime.rs:247-264) with the
  * kernel's LaunchConfig (lang.rs:34-45).  The kernel's pointer arguments are
- * its DefineGlobal instructions in index order.  Errors in the IR or in the
+ * its DefineGlobal instructions in index order.  Loads and stores of global AND
+ * of DefineLocal (shared-memory) buffers are checked against the buffer's length
+ * and raise the status word (UGB_ERR_INVALID at the next ugb_sync) instead of
+ * touching memory outside it.  Barrier and ReduceLocal are block-wide: they must
+ * be reached by every thread of the block (not under an If, nor inside a Range
+ * whose bounds depend on the thread index); anything else is undefined, as for
+ * __syncthreads.  Errors in the IR or in the
  * run-time compilation are UGB_ERR_COMPILE with the compiler log in the
  * message. */
 UGB_API int32_t ugb_compile(ugb_device *dev, const ugb_ssa_instr *instrs, size_t n_instrs,

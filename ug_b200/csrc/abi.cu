@@ -75,12 +75,21 @@ int32_t ugb_device_create(int32_t ordinal, ugb_device **out) {
     delete d;
     return UGB_ERR_CUDA;
   }
-  // Keep freed blocks in the stream-ordered pool instead of returning them to
-  // the driver at every synchronisation: decode allocates per step.
-  cudaMemPool_t pool;
-  if (cudaDeviceGetDefaultMemPool(&pool, ordinal) == cudaSuccess) {
-    uint64_t thresh = UINT64_MAX;
-    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thresh);
+  // A pool of the handle's own, which keeps freed blocks instead of returning them to the driver at every
+  // synchronisation (decode allocates per step); the default pool that other users of the process share is not touched.
+  {
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = ordinal;
+    if (cudaMemPoolCreate(&d->pool, &props) == cudaSuccess) {
+      uint64_t thresh = UINT64_MAX;
+      cudaMemPoolSetAttribute(d->pool, cudaMemPoolAttrReleaseThreshold, &thresh);
+    } else {
+      d->pool = nullptr;            // fall back to the default pool with its default behaviour
+      cudaGetLastError();
+    }
   }
   *out = d;
   return UGB_OK;
@@ -93,6 +102,7 @@ int32_t ugb_device_destroy(ugb_device *dev) {
   cudaSetDevice(dev->ordinal);
   cudaStreamSynchronize(dev->stream);
   ugb_gemm_state_free(dev);
+  if (dev->pool) { cudaMemPoolDestroy(dev->pool); dev->pool = nullptr; }
   if (dev->status_dev) cudaFree(dev->status_dev);
   if (dev->sched_dev) cudaFree(dev->sched_dev);
   if (dev->ev_begin) cudaEventDestroy(dev->ev_begin);
@@ -155,7 +165,7 @@ int32_t ugb_alloc(ugb_device *dev, int32_t dtype, size_t len, ugb_slice **out) {
   UGB_REQUIRE(dev, es != 0, UGB_ERR_INVALID, "ugb_alloc: unknown dtype %d", dtype);
   UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
   void *p = nullptr;
-  if (len > 0) UGB_CUDA(dev, cudaMallocAsync(&p, len * es, dev->stream));
+  if (len > 0) UGB_CUDA(dev, ugb_malloc_async(dev, &p, len * es));
   ugb_slice *s = new ugb_slice();
   s->dev = dev;
   s->ptr = p;

@@ -109,7 +109,7 @@ int32_t ugb_decode_attention(ugb_device *dev, const ugb_slice *q, const ugb_slic
   const size_t ml_bytes = slots * ATT_GROUP * 2 * sizeof(float);
   const size_t cnt_bytes = b * n_kv * sizeof(unsigned int);
   char *scratch = nullptr;
-  UGB_CUDA(dev, cudaMallocAsync((void **)&scratch, o_bytes + ml_bytes + cnt_bytes, dev->stream));
+  UGB_CUDA(dev, ugb_malloc_async(dev, (void **)&scratch, o_bytes + ml_bytes + cnt_bytes));
   unsigned int *counters = (unsigned int *)(scratch + o_bytes + ml_bytes);
   cudaError_t e = cudaMemsetAsync(counters, 0, cnt_bytes, dev->stream);
   if (e == cudaSuccess)

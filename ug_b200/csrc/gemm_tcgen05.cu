@@ -568,6 +568,13 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   }
   p.stages = stages;
   const size_t smem = (size_t)stages * C_::STAGE_BYTES + 1536;
+  if (g.query_grid || g.query_ctas_per_sm) {
+    int occ = 0;
+    UGB_CUDA(dev, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, tc_gemm_kernel<BM, BN, PAIR>, THREADS, smem));
+    if (g.query_grid) *g.query_grid = (int)grid;
+    if (g.query_ctas_per_sm) *g.query_ctas_per_sm = occ;
+    return UGB_OK;
+  }
   cudaError_t le = ugb_launch_cluster(tc_gemm_kernel<BM, BN, PAIR>, dim3(grid), dim3(THREADS), smem, dev->stream,
                                       g.pdl, PAIR ? 2 : 1, tmA, tmB, p);
   if (le != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of tc_gemm_kernel failed: %s", cudaGetErrorString(le));

@@ -41,6 +41,9 @@ struct ugb_tc_gemm_args {
   bool f16 = false;     // operands (and the UGB_EPI_BF16 output) are IEEE f16 instead of bf16: same instruction, other format field
   int pair = -1;        // 256 x 256 tiles on pairs of CTAs (cta_group::2) where the shape allows: 1 / 0, -1 = the device's setting
   ugb_tc_rope_epilogue rope = {};   // UGB_EPI_ROPE_QKV only
+  // Query instead of launch: when set, ugb_tc_gemm launches nothing and reports the grid it would launch and how many
+  // CTAs of that kernel (with its dynamic shared memory) the hardware keeps resident per SM.
+  int *query_grid = nullptr, *query_ctas_per_sm = nullptr;
 };
 
 // Returns UGB_ERR_UNSUPPORTED (without touching last_error) when the shape

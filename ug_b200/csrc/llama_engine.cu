@@ -163,8 +163,11 @@ int32_t put_vector(ugb_llama *m, const ugb_slice *w, float *dst, size_t n, const
 
 // out[rows, n] = a[rows, k] . w[n, k]^T on the tensor-core kernel (weights are the static operand).
 int32_t gemm_rows(ugb_llama *m, size_t rows, void *out, const __nv_bfloat16 *a, const __nv_bfloat16 *w, size_t n,
-                  size_t k, int epi, int splits, int bn, const ugb_tc_rope_epilogue *rope = nullptr) {
+                  size_t k, int epi, int splits, int bn, const ugb_tc_rope_epilogue *rope = nullptr, int *query_grid = nullptr,
+                  int *query_occ = nullptr) {
   ugb_tc_gemm_args g;
+  g.query_grid = query_grid;
+  g.query_ctas_per_sm = query_occ;
   if (rope) g.rope = *rope;
   g.out = out; g.a = a; g.b = w;
   g.batch = 1; g.m = rows; g.n = n; g.k = k;
@@ -417,31 +420,40 @@ int32_t enqueue_step(ugb_llama *m, const int *tok) {
   float *po = o_out(m, m->part), *pd = down_out(m, m->part);
   // Work done before griddepcontrol.wait (the attention kernel's K/V ring, the norm kernel's residual row)
   // reads data written two or more kernels back.  That is safe when the two projections around the
-  // writer's successor cannot be resident together: each GEMM CTA takes more than half an SM's shared
-  // memory, so once all CTAs of the later GEMM have started (which is what lets the reading kernel launch)
-  // fewer than sm_count - ctas(later) CTAs of the earlier one can still be there; at least one has left,
-  // hence passed its own wait, hence everything before it -- the writer included -- has completed.
+  // writer's successor cannot be resident together: if at most ONE CTA of each projection fits on an SM and
+  // neither grid exceeds the SM count, then once all CTAs of the later GEMM have started (which is what lets
+  // the reading kernel launch) fewer than sm_count - ctas(later) CTAs of the earlier one can still be there;
+  // with ctas(earlier) + ctas(later) > sm_count at least one has left, hence passed its own wait, hence
+  // everything before it -- the writer included -- has completed.  Both facts are taken from the launches
+  // themselves (the grid each projection gets, the residency the occupancy calculator gives its kernel with
+  // its shared memory), not from the tuning options, so a retune that breaks the argument switches this off.
   const int sms = dev->sm_count;
-  const auto ctas = [](size_t n, int bn, int splits) { return (int)((n + bn - 1) / bn) * splits; };
-  const int c_qkv = ctas(m->qkv_dim, m->bn_qkv, s_qkv), c_o = ctas(H, m->bn_o, s_o);
-  const int c_gu = ctas(2 * (size_t)c.ffn, m->bn_gate_up, 1), c_down = ctas(H, m->bn_down, s_down);
-  const bool big_smem = m->gemm_smem_kib == 0 || m->gemm_smem_kib >= 136;   // >= 121.5 KiB per GEMM CTA: never two on an SM
-  m->early_ok = m->att_early && m->pdl && m->skip == 0 && big_smem && c_qkv <= sms && c_o <= sms && c_gu <= sms && c_down <= sms &&
-                c_qkv + c_o > sms && c_gu + c_down > sms && c_down + c_qkv > sms;
-  const int early = m->early_ok ? 1 : 0;
+  int c_qkv = 0, c_o = 0, c_gu = 0, c_down = 0, o_qkv = 0, o_o = 0, o_gu = 0, o_down = 0;
+  bool early = m->att_early && m->pdl && m->skip == 0;
+  if (early) {
+    const LayerW &w0 = m->layers[0];
+    if (gemm_rows(m, B, m->part, m->xn, w0.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv, nullptr, &c_qkv, &o_qkv) ||
+        gemm_rows(m, B, po, m->att, w0.wo, H, AW, UGB_EPI_F32, m->splits_o, m->bn_o, nullptr, &c_o, &o_o) ||
+        gemm_rows(m, B, m->h, m->xn, w0.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, m->bn_gate_up, nullptr, &c_gu, &o_gu) ||
+        gemm_rows(m, B, pd, m->h, w0.wdown, H, c.ffn, UGB_EPI_F32, m->splits_down, m->bn_down, nullptr, &c_down, &o_down))
+      early = false;
+  }
+  m->early_ok = early && o_qkv == 1 && o_o == 1 && o_gu == 1 && o_down == 1 && c_qkv <= sms && c_o <= sms && c_gu <= sms &&
+                c_down <= sms && c_qkv + c_o > sms && c_gu + c_down > sms && c_down + c_qkv > sms;
+  const int early_i = m->early_ok ? 1 : 0;
   for (int l = 0; l < c.layers; ++l) {
     const LayerW &w = m->layers[l];
-    if (!(m->skip & 1) && (rc = launch_reduce(m, B, m->x, m->xn, l == 0 ? RED_NONE : RED_DOWN, pd, l == 0 ? 0 : s_down, w.rms1, l > 0 ? early : 0))) return rc;
+    if (!(m->skip & 1) && (rc = launch_reduce(m, B, m->x, m->xn, l == 0 ? RED_NONE : RED_DOWN, pd, l == 0 ? 0 : s_down, w.rms1, l > 0 ? early_i : 0))) return rc;
     if (!(m->skip & 2) && (rc = gemm(m, m->part, m->xn, w.wqkv, m->qkv_dim, H, UGB_EPI_F32, m->splits_qkv, m->bn_qkv))) return rc;
     __nv_bfloat16 *kc = m->kcache + (size_t)l * m->kv_layer_stride;
     __nv_bfloat16 *vc = m->vcache + (size_t)l * m->kv_layer_stride;
     if (!(m->skip & 8) && (rc = launch_attention(m, l, scale, s_qkv, true))) return rc;   // rope + append + attention
     if (!(m->skip & 16) && (rc = gemm(m, po, m->att, w.wo, H, AW, UGB_EPI_F32, m->splits_o, m->bn_o))) return rc;
-    if (!(m->skip & 1) && (rc = launch_reduce(m, B, m->x, m->xn, RED_O, po, s_o, w.rms2, early))) return rc;
+    if (!(m->skip & 1) && (rc = launch_reduce(m, B, m->x, m->xn, RED_O, po, s_o, w.rms2, early_i))) return rc;
     if (!(m->skip & 32) && (rc = gemm(m, m->h, m->xn, w.wgu, 2 * (size_t)c.ffn, H, UGB_EPI_SILU_MUL_BF16, 1, m->bn_gate_up))) return rc;
     if (!(m->skip & 64) && (rc = gemm(m, pd, m->h, w.wdown, H, c.ffn, UGB_EPI_F32, m->splits_down, m->bn_down))) return rc;
   }
-  if ((rc = launch_reduce(m, B, m->x, m->xn, RED_DOWN, pd, s_down, m->ln_f, early))) return rc;
+  if ((rc = launch_reduce(m, B, m->x, m->xn, RED_DOWN, pd, s_down, m->ln_f, early_i))) return rc;
   return launch_lm_head_argmax(m, true);
 }
 

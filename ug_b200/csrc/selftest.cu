@@ -45,7 +45,7 @@ extern "C" int32_t ugb_selftest_bounded_wait(ugb_device *dev, int32_t which) {
   UGB_REQUIRE(dev, which == 0 || which == 1, UGB_ERR_INVALID, "ugb_selftest_bounded_wait: which = %d is not 0 or 1", which);
   UGB_CUDA(dev, cudaSetDevice(dev->ordinal));
   TpHeader *hdrs = nullptr;
-  UGB_CUDA(dev, cudaMallocAsync((void **)&hdrs, 2 * sizeof(TpHeader), dev->stream));
+  UGB_CUDA(dev, ugb_malloc_async(dev, (void **)&hdrs, 2 * sizeof(TpHeader)));
   cudaError_t e = cudaMemsetAsync(hdrs, 0, 2 * sizeof(TpHeader), dev->stream);
   int32_t rc = UGB_OK;
   if (e != cudaSuccess) {

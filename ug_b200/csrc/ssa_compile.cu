@@ -313,12 +313,11 @@ int32_t generate(ugb_device *dev, const ugb_ssa_instr *ins, size_t n, const std:
         // a load may name another dtype than the buffer's (ug-llama/src/model.rs:49 reads i32 ids as f32): convert
         const std::string elem = std::string("ugb_cast<") + ty + ", " + bty + ">(v" + std::to_string(i.v0) + "[o" + std::to_string(l) + "])";
         os << ind << "const long long o" << l << " = (long long)(" << arg_str(i.a0) << ");\n";
-        if (global) {
-          os << ind << ty << " v" << l << " = (" << ty << ")0;\n";
-          os << ind << "if ((unsigned long long)o" << l << " < n" << i.v0 << ") v" << l << " = " << elem << "; else ugb_oob(ugb_status, " << l << "u);\n";
-        } else {
-          os << ind << ty << " v" << l << " = " << elem << ";\n";
-        }
+        // every access is checked against the buffer's length -- the slice length for an argument, the declared size for
+        // shared memory -- and raises the status word instead of touching memory outside it
+        os << ind << ty << " v" << l << " = (" << ty << ")0;\n";
+        if (global) os << ind << "if ((unsigned long long)o" << l << " < n" << i.v0 << ") v" << l << " = " << elem << "; else ugb_oob(ugb_status, " << l << "u);\n";
+        else os << ind << "if ((unsigned long long)o" << l << " < " << ins[i.v0].index << "ull) v" << l << " = " << elem << "; else ugb_oob(ugb_status, " << l << "u);\n";
         vtype[l] = i.dtype;
         break;
       }
@@ -333,7 +332,7 @@ int32_t generate(ugb_device *dev, const ugb_ssa_instr *ins, size_t n, const std:
         const std::string val = std::string("ugb_cast<") + bty + ", " + sty + ">(" + arg_str(i.a1) + ")";
         os << ind << "{ const long long o = (long long)(" << arg_str(i.a0) << "); ";
         if (global) os << "if ((unsigned long long)o < n" << i.v0 << ") v" << i.v0 << "[o] = " << val << "; else ugb_oob(ugb_status, " << l << "u); }\n";
-        else os << "v" << i.v0 << "[o] = " << val << "; }\n";
+        else os << "if ((unsigned long long)o < " << ins[i.v0].index << "ull) v" << i.v0 << "[o] = " << val << "; else ugb_oob(ugb_status, " << l << "u); }\n";
         break;
       }
       case UGB_SSA_ASSIGN:

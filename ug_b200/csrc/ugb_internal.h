@@ -31,6 +31,7 @@ struct ugb_device {
   std::string last_error;
   void *gemm_state = nullptr;  // owned by the GEMM translation unit
   int gemm_pair = 1;           // option gemm_cta_pairs: tall bf16 GEMMs on pairs of CTAs (tcgen05 cta_group::2)
+  cudaMemPool_t pool = nullptr;  // this handle's own stream-ordered pool (the process-wide default pool is left alone)
   unsigned wait_timeouts = 0;  // device-side waits that gave up, as seen by ugb_sync (tensor-parallel models refuse
                                // further steps once this has moved: their ranks may be out of step)
 };
@@ -66,6 +67,11 @@ static inline const char *ugb_dtype_name(int32_t dt) {
     case UGB_I64: return "I64";
     default: return "?";
   }
+}
+
+// Stream-ordered allocation from the handle's own pool.
+static inline cudaError_t ugb_malloc_async(ugb_device *dev, void **p, size_t bytes) {
+  return dev->pool ? cudaMallocFromPoolAsync(p, bytes, dev->pool, dev->stream) : cudaMallocAsync(p, bytes, dev->stream);
 }
 
 // Records a formatted message on the device handle and returns `code`.
