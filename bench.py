@@ -370,6 +370,116 @@ class GraphRowWorkload:
                 "l2": "inputs larger than L2 (268 MB touched per step vs 126 MB L2)"}
 
 
+class GraphDecodeWorkload:
+    """ug-llama's own generation loop (ug-llama/src/main.rs:127-169: build the graph of one forward pass, schedule,
+    compile_with_cache, run, read the logits, pick the next token) for ONE sequence of the 1.1B shape in f32, exactly
+    as the reference runs it, on this backend: the drop-in path a user of ug-core gets without touching the model.
+    A step is one generated token, timed on the host around the whole loop body (the graph is rebuilt per token,
+    as in the reference); the phases are reported beside it the way main.rs -v prints them."""
+    unit = "tokens/s"
+    dtype = "f32"
+    bound = "hbm"
+    kernel_only = True
+    ncu_traffic_bytes = None
+    prompt_len = 16
+    name = ("ug-llama generation loop through LazyBuffer / Schedule / compile_with_cache (unmodified graph, f32 weights), "
+            "Llama-1.1B shape, 1 sequence, 16-token prompt")
+    metric = "tokens/s, one sequence, graph rebuilt / scheduled / compiled / run per token (host time included)"
+
+    def __init__(self, rank=0):
+        from ug_b200 import synth
+        from ug_b200.llama import Config
+        self.cfg = Config.llama_1b()
+        self.w = synth.llama_weights_f32(_weights(self.cfg))
+        self.prompt = synth.tokens(21, (1, self.prompt_len), self.cfg.vocab_size)
+        # every f32 matrix once per token (the embedding table is read whole as the output projection)
+        self.bytes_per_step = sum(v.nbytes for k, v in self.w.items() if v.ndim == 2)
+        self.launches_per_step = 1
+
+    def setup(self, dev):
+        from ug_b200 import llama_graph as G
+        from ug_b200.lazy import CompilationCache, HostDevice
+        self.dev = dev
+        self.hd = HostDevice(dev)
+        self.model = G.Model(self.cfg, self.w, self.hd, custom_softmax_op=False)
+        self.cache, self.kv = CompilationCache(), self.model.new_cache()
+        self.pos, self.phases, self.trace = 0, [], []
+        self._forward(self.prompt)
+
+    def _forward(self, ids):
+        from ug_b200.lazy import LB, Schedule
+        n = ids.shape[1]
+        t = [time.perf_counter()]
+        out = self.model.fwd(LB.copy(ids, (1, n), self.hd), LB.copy(np.array([[self.pos]], np.int32), (1, 1), self.hd),
+                             self.kv)
+        t.append(time.perf_counter())
+        sched = Schedule.create_one(out)
+        t.append(time.perf_counter())
+        misses = self.cache.misses
+        compiled = sched.compile(self.cache)
+        t.append(time.perf_counter())
+        compiled.run()
+        self.dev.synchronize()
+        t.append(time.perf_counter())
+        logits = out.data_vec().reshape(n, self.cfg.vocab_size)[-1]
+        self.tok = int(np.argmax(logits))
+        t.append(time.perf_counter())
+        self.trace.append((ids.copy(), self.pos, logits))
+        self.pos += n
+        self.compiled = compiled
+        self.launches_per_step = len(compiled)
+        self.phases.append([1e3 * (b - a) for a, b in zip(t, t[1:])] + [self.cache.misses - misses])
+
+    def step(self):
+        self._forward(np.array([[self.tok]], np.int32))
+
+    def units(self, step_seconds, n_ranks):
+        return n_ranks / step_seconds
+
+    def check(self):
+        """The prompt's last logits and the first two generated tokens' logits against the CPU oracle."""
+        import oracle
+        from oracle import llama_ref as R
+        oracle.set_threads(os.cpu_count())
+        ref = R.Model(R.Config(**self.cfg.__dict__), self.w, custom_softmax_op=False)
+        cache, worst = ref.new_cache(), 0.0
+        for ids, pos, got in self.trace[:3]:
+            want = ref.fwd(ids, pos, cache)[0, -1]
+            worst = max(worst, float(np.max(np.abs(got - want)) / np.max(np.abs(want))))
+        return worst
+
+    def record(self, dev, warmup, steps, peaks):
+        for _ in range(max(warmup, 4)):          # the KV-dependent kernels become size-generic on their second sighting
+            self.step()
+        self.phases = []
+        dev.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            self.step()
+        step_s = (time.perf_counter() - t0) / steps
+        ph = np.array(self.phases, np.float64)
+        origins = {}
+        for o in self.compiled.origins():
+            origins[o] = origins.get(o, 0) + 1
+        rec = {"workload": self.name, "metric": self.metric, "value": round(1.0 / step_s, 2), "unit": self.unit,
+               "ms_per_step": round(step_s * 1e3, 3), "ms_per_step_median": round(float(np.median(ph[:, :5].sum(axis=1))), 3),
+               "steps": steps, "dtype": self.dtype,
+               "phases_ms": dict(zip(["build_graph", "schedule", "compile_with_cache", "run", "read_logits"],
+                                     [round(float(x), 3) for x in np.median(ph[:, :5], axis=0)])),
+               "compile_misses_in_timed_steps": int(ph[:, 5].sum()), "poly_hits_total": int(self.cache.poly_hits),
+               "launches_per_step": self.launches_per_step, "kernels": origins,
+               "cached_positions": [self.pos - steps, self.pos],
+               "roofline": {"bound": "hbm", "achieved": round(self.bytes_per_step / step_s / 1e9, 1), "peak": peaks["hbm"],
+                            "unit": "GB/s", "frac": round(self.bytes_per_step / step_s / 1e9 / peaks["hbm"], 4),
+                            "traffic": None, "peak_source": peaks["source"],
+                            "note": "f32 weight bytes per token / whole loop-body time; the loop is host- and launch-bound"},
+               "parity_max_rel_err": self.check()}
+        return rec
+
+    def config(self):
+        return {"workload": self.name, "sequences": 1, "prompt": self.prompt_len}
+
+
 class F32MatmulWorkload:
     """f32 matmul_t on the FP32 pipe (the dtype ug-llama casts every weight to, model.rs:118,140,313): the
     128 x 128 register-blocked kernel on 4096^3 ("gemm_f32", FP32-pipe bound) or the warp-per-column kernel on one
@@ -846,7 +956,8 @@ class PrefillWorkload(DecodeWorkload):
 WORKLOADS = {"rms_silu": RmsSiluWorkload, "softmax": SoftmaxWorkload, "softmax_c1": SoftmaxC1Workload,
              "gemm": GemmWorkload, "decode": DecodeWorkload, "prefill": PrefillWorkload,
              "graph_softmax": lambda r: GraphRowWorkload("softmax"), "graph_rms_norm": lambda r: GraphRowWorkload("rms_norm"),
-             "gemm_f32": lambda r: F32MatmulWorkload("gemm_f32"), "gemv_f32": lambda r: F32MatmulWorkload("gemv_f32")}
+             "gemm_f32": lambda r: F32MatmulWorkload("gemm_f32"), "gemv_f32": lambda r: F32MatmulWorkload("gemv_f32"),
+             "graph_decode": GraphDecodeWorkload}
 DEFAULT_WORKLOAD = "decode"
 
 # DRAM traffic of the decode step's kernels, from ncu captures of single launches (dram__bytes_read.sum +
@@ -938,10 +1049,15 @@ def config_records(dev, group, peaks):
             ("graph_softmax_8192x4096", lambda r: GraphRowWorkload("softmax"), 30),
             ("graph_rms_norm_8192x4096", lambda r: GraphRowWorkload("rms_norm"), 30),
             ("f32_gemm_4096", lambda r: F32MatmulWorkload("gemm_f32"), 10),
-            ("f32_decode_matmul_1x32000x2048", lambda r: F32MatmulWorkload("gemv_f32"), 50)]
+            ("f32_decode_matmul_1x32000x2048", lambda r: F32MatmulWorkload("gemv_f32"), 50),
+            ("graph_decode_llama_1b_f32", GraphDecodeWorkload, 32)]
     for key, cls, steps in plan:
         wl = cls(0)
         wl.setup(dev)
+        if hasattr(wl, "record"):
+            out[key] = wl.record(dev, 4, steps, peaks)
+            del wl
+            continue
         for _ in range(3):
             wl.step()
         dev.synchronize()
@@ -1051,6 +1167,14 @@ def main():
         mode = None
         wl = make_workload(rank)
         wl.setup(dev)
+        if hasattr(wl, "record"):
+            rec = wl.record(dev, args.warmup, args.steps, measured_peaks())
+            rec.update({"n_gpus": 1, "warmup": max(args.warmup, 4), "config": _config_of(wl, 1),
+                        "gpu_launches": int(dev.launch_count)})
+            if rank == 0:
+                print(json.dumps(rec), flush=True)
+            group.close()
+            return 0
         if getattr(wl, "kernel_only", False):
             # secondary records (no end-to-end leg, no CPU arm): device-timed value, roofline, parity
             for _ in range(args.warmup):

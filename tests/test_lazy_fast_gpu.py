@@ -125,6 +125,23 @@ def test_no_item_of_an_unmodified_llama_step_is_left_on_per_instruction_code(hd)
     assert {"matmul", "custom", "index_select"} <= seen and seen & {"row_vec4", "warp_row_vec4"} and "map_vec4" in seen
 
 
+def test_generic_kernel_takes_its_grid_per_launch(hd):
+    """A one-dimensional map over [3, T] runs on ceil(3 T / 256) blocks, which is not affine in T (1 block up to
+    T = 85, 2 from 86 on).  The grid is not part of what a later sighting has to match: the function generalised
+    from T = 84 and 85 serves 86 and 87 with their own grids and no further compilation."""
+    from ug_b200.lazy import CompilationCache
+    cache, misses = CompilationCache(), []
+    for t in (84, 85, 86, 87, 200):
+        x = synth.normal(40 + t, (3, t))
+        lx = LB.copy(x, (3, t), hd)
+        y = lx.binary(B.Mul, lx).binary(B.Add, lx)
+        before = cache.misses
+        Schedule.create_one(y).compile(cache).run()
+        misses.append(cache.misses - before)
+        assert np.allclose(y.data_vec().reshape(3, t), x * x + x, rtol=1e-6, atol=1e-7)
+    assert misses == [1, 1, 0, 0, 0] and cache.poly_hits == 3
+
+
 def test_decode_loop_stops_compiling_once_the_kv_dependent_kernels_are_generic(hd):
     """ug-llama's step loop (ug-llama/src/main.rs:127-169: build the graph, compile_with_cache, run) over 32 tokens.
     The reference's cache keys on shapes (ug-core/src/cache.rs:8-12), so the kernels whose shape follows the KV

@@ -545,14 +545,19 @@ CompiledSchedule Schedule::compile_with_cache(CompilationCache &cache) const {
           const ssa::Kernel poly_k = lower(kernel, b200_opts(kernel));
           GeneratedSource gs;
           if (device->ssa_source(poly_k, "ug_poly_kernel", gs)) {
-            std::vector<PolyToken> toks = poly_tokenize(gs.text);
+            PolyText txt = poly_scan(gs.text);
             const uint32_t grid = poly_k.launch_config.grid_dim;
-            PolyEntry &pe = cache.poly[poly_skeleton(toks) + "|" + std::to_string(poly_k.launch_config.block_dim) + "|" +
-                                       std::to_string(poly_k.launch_config.shared_mem)];
+            // the map key: the skeleton followed by the launch shape (no marks in the suffix; text_len says where it starts)
+            std::string &key = txt.skeleton;
+            key += '|'; key += std::to_string(poly_k.launch_config.block_dim);
+            key += '|'; key += std::to_string(poly_k.launch_config.shared_mem);
+            auto pit = cache.poly.find(key);
+            if (pit == cache.poly.end()) pit = cache.poly.emplace(key, PolyEntry{}).first;
+            PolyEntry &pe = pit->second;
             long long t = 0;
             bool served = false;
             for (const PolyGeneric &g : pe.generics)
-              if (poly_match(g, toks, grid, t)) {
+              if (poly_match(g, txt.ints, t)) {
                 cf.func = g.func; cf.dyn = true; cf.dyn_grid = grid; cf.dyn_t = t;
                 cache.hits++; cache.poly_hits++;
                 served = true;
@@ -562,7 +567,7 @@ CompiledSchedule Schedule::compile_with_cache(CompilationCache &cache) const {
             if (!pe.failed && pe.have_pending && pe.generics.size() < 8) {
               std::string generic;
               PolyGeneric g;
-              bool ok = poly_generalize(pe, toks, grid, g, generic);
+              bool ok = poly_generalize(pe, txt, g, generic);
               const std::string sig = "ugb_status_word* ugb_status) {";
               const size_t at = ok ? generic.find(sig) : std::string::npos;
               ok = ok && at != std::string::npos;
@@ -584,7 +589,7 @@ CompiledSchedule Schedule::compile_with_cache(CompilationCache &cache) const {
               }
               pe.failed = true;
             }
-            if (!pe.have_pending) { pe.pending = std::move(toks); pe.pending_grid = grid; pe.have_pending = true; }
+            if (!pe.have_pending) { pe.pending = std::move(txt.ints); pe.have_pending = true; }
           }
         }
         if (device->launch_policy() == LaunchPolicy::B200) {

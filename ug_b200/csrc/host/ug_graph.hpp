@@ -167,34 +167,31 @@ struct ScheduleItem {  // schedule.rs:42-60
 };
 
 // ---- shape-polymorphic reuse (ug_poly.cpp) ----
-struct PolyToken {
-  std::string ws, text;       // white space before the token, the token
-  bool is_int = false;        // a decimal integer literal
-  long long value = 0;
+// A generated text split into what stays and what moves: `skeleton` is the text with every decimal integer
+// literal's digits replaced by POLY_MARK, `ints` the literal values in order of appearance.
+constexpr char POLY_MARK = '\x01';
+struct PolyText {
+  std::string skeleton;
+  size_t text_len = 0;                // skeleton[0, text_len) is the program text; a caller may append a key suffix
+  std::vector<long long> ints;
 };
-struct PolySlot { size_t token; long long a, b; };   // literal number `token` of the template is b + a * t
-struct PolyGeneric {                  // one generic function: template tokens, the literals that move, the grid
+struct PolyGeneric {                  // one generic function: literal number i of the text is b[i] + a[i] * t
   std::shared_ptr<Func> func;
-  std::vector<PolyToken> tmpl;
-  std::vector<PolySlot> slots;
-  long long grid_a = 0, grid_b = 0;
+  std::vector<long long> a, b;
 };
-struct PolyEntry {                    // everything known about one token skeleton
+struct PolyEntry {                    // everything known about one skeleton
   bool failed = false, have_pending = false;
-  std::vector<PolyToken> pending;     // a sighting that no generic function covers yet
-  uint32_t pending_grid = 0;
+  std::vector<long long> pending;     // the literals of a sighting that no generic function covers yet
   std::vector<PolyGeneric> generics;  // several when the same text moves along more than one line of sizes
 };
-std::vector<PolyToken> poly_tokenize(const std::string &text);
-std::string poly_skeleton(const std::vector<PolyToken> &toks);
-bool poly_generalize(const PolyEntry &e, const std::vector<PolyToken> &second, uint32_t second_grid, PolyGeneric &out,
-                     std::string &generic_text);
-bool poly_match(const PolyGeneric &e, const std::vector<PolyToken> &toks, uint32_t grid, long long &t);
+PolyText poly_scan(const std::string &text);
+bool poly_generalize(const PolyEntry &e, const PolyText &second, PolyGeneric &out, std::string &generic_text);
+bool poly_match(const PolyGeneric &e, const std::vector<long long> &ints, long long &t);
 
 struct CompilationCache {  // cache.rs:73-101
   std::map<NormalizedKernel, std::shared_ptr<Func>> op_cache;
   std::map<std::vector<ssa::Instr>, std::shared_ptr<Func>> ssa_cache;
-  std::map<std::string, PolyEntry> poly;   // by token skeleton of the generated text (+ block size)
+  std::unordered_map<std::string, PolyEntry> poly;   // by skeleton of the generated text (+ block size, shared memory)
   bool polymorphic = true;                 // B200 launch policy only
   size_t hits = 0, misses = 0, poly_hits = 0;
 };
