@@ -1106,6 +1106,9 @@ def main():
     ap.add_argument("--tp", action="store_true",
                     help="decode: tensor-parallel variant -- the ranks share ONE batch of 64 sequences (heads, FFN "
                          "columns and vocabulary sharded, cross-rank sums inside the engine's kernels over NVLink)")
+    ap.add_argument("--sequences", type=int, default=None,
+                    help="decode, profiling aid: this GPU decodes the first N sequences of the batch only (the share of "
+                         "one GPU of a 64 / N-GPU run, on one GPU)")
     ap.add_argument("--fast-prefill", action="store_true",
                     help="decode, profiling aid: place the cache at --prefill positions without running the "
                          "prompts (the cache then holds zeros); not a valid benchmark configuration")
@@ -1125,7 +1128,7 @@ def main():
         if mode == "weak":
             return DecodeWorkload(rank, prefill=args.prefill, layers=args.layers, fast_prefill=args.fast_prefill)
         return DecodeWorkload(rank, prefill=args.prefill, layers=args.layers, fast_prefill=args.fast_prefill,
-                              seqs=shard_range(DecodeWorkload.total_batch, rank, world))
+                              seqs=(0, args.sequences) if args.sequences else shard_range(DecodeWorkload.total_batch, rank, world))
 
     def make_workload(r):
         if args.workload == "decode":
@@ -1235,7 +1238,7 @@ def main():
     if rank == 0:
         extra = {}
         if decode:
-            n_seq = wl.total_batch * (world if mode == "weak" else 1)
+            n_seq = args.sequences if args.sequences else wl.total_batch * (world if mode == "weak" else 1)
             value, e2e_value = n_seq / step_s, n_seq / e2e_step_s
             depth = wl.mean_depth(m["first_pos"], args.steps)
             gpu_bytes = wl.step_bytes(depth)             # this GPU's algorithmic bytes per step (rank 0 holds the largest share)

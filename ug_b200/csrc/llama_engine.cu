@@ -69,7 +69,7 @@ struct ugb_llama {
   int *tok = nullptr, *next = nullptr, *pos = nullptr;
   int host_pos = 0;
   // tuning
-  int splits_qkv = 3, splits_o = 4, splits_down = 8, att_splits = 1, att_stages = 3;
+  int splits_qkv = 3, splits_o = 4, splits_down = 8, att_splits = 1, att_stages = 5;
   int pdl = 1;                    // programmatic dependent launch between the kernels of a step
   int gemm_smem_kib = 144;        // shared-memory cap of the decode GEMM CTAs (0 = deepest ring); measured best
   int skip = 0;                   // measurement aid: bit mask of kernel types left out of the step
@@ -302,8 +302,9 @@ int32_t launch_attention(ugb_llama *m, int layer, float scale, int n_part, bool 
     case 2: UGB_ATT_LAUNCH(2); break;
     case 4: UGB_ATT_LAUNCH(4); break;
     case 5: UGB_ATT_LAUNCH(5); break;
+    case 3: UGB_ATT_LAUNCH(3); break;
     case 6: UGB_ATT_LAUNCH(6); break;
-    default: UGB_ATT_LAUNCH(3); break;
+    default: UGB_ATT_LAUNCH(5); break;
   }
 #undef UGB_ATT_LAUNCH
   if (e != cudaSuccess) return ugb_fail(m->dev, UGB_ERR_CUDA, "launch of decode_attention_kernel failed: %s", cudaGetErrorString(e));
@@ -644,10 +645,15 @@ int32_t ugb_llama_create_tp(ugb_device *dev, const ugb_llama_config *cfg, int32_
   TRY(dmalloc(m, &m->pos, 1, true));
   {
     // A (sequence, KV head) pair is one attention CTA per KV slice; with few sequences (a rank's share of a batch that
-    // is split over several GPUs) the cache is cut into slices so that about 256 CTAs stream it, as at batch 64
+    // is split over several GPUs) the cache is cut into slices so that up to about 256 CTAs stream it, as at batch 64.
+    // Measured at 2048+ positions (step time in ms, slices 1 / 2 / 4 / 8): 32 sequences 1.47 / 1.35 / 1.45 / -,
+    // 16 sequences - / 1.29 / 1.21 / 1.42, 8 sequences - / 1.29 / 1.17 / 1.19: more than 4 slices cost more in
+    // start-up and merging than they gain.  The ring holds 5 sub-tiles per warp (80 KiB per CTA, two CTAs per SM):
+    // step time at 64 sequences with 3 / 4 / 5 / 6 of them 1.535 / 1.529 / 1.521 / 1.531 ms; 8 of them for a
+    // grid of one CTA per SM (8 sequences) 1.166 against 1.140 ms with 5.
     const int pairs = batch * c.n_kv_heads;
     int splits = (256 + pairs - 1) / pairs;
-    m->att_splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
+    m->att_splits = splits < 1 ? 1 : (splits > 4 ? 4 : splits);
   }
   if (tp) {
     // exchange block: header | o_proj partials | down_proj partials | argmax pairs.  Partial buffers hold
@@ -669,12 +675,11 @@ int32_t ugb_llama_create_tp(ugb_device *dev, const ugb_llama_config *cfg, int32_
     m->tp_peer[tp_rank] = blk;
     m->tp_ready = n_rank == 1;
     if (n_rank > 1) {
-      // a rank's projections are 1 / n_rank of the work: fewer split-K partials to fetch from the peers, and
-      // the KV range cut in slices so that the rank's fewer (sequence, KV head) pairs still fill the SMs
+      // a rank's projections are 1 / n_rank of the work: fewer split-K partials to fetch from the peers (the KV
+      // slices above already follow the rank's own number of (sequence, KV head) pairs)
       m->splits_qkv = 7;
       m->splits_o = 2;
       m->splits_down = 2;
-      m->att_splits = n_rank < 8 ? n_rank : 8;
     }
   }
   // rope tables, model.rs:278-295: theta_i = 1 / theta^(i/d) in f32 on the host
