@@ -78,6 +78,12 @@ def test_long_context_crosses_tiles_and_slices(dev):
         gpu.fwd(prompts[:, 299])
         # slices change the running max, hence the bf16 rounding of the probabilities: not bit-equal
         assert np.max(np.abs(gpu.logits() - base)) < 5e-3 * np.abs(base).max()
+    base = gpu.logits()
+    for stages in (2, 3, 4, 6):         # the ring depth only changes when a sub-tile is requested: same bits
+        gpu.set_option("att_stages", stages)
+        gpu.reset(299)
+        gpu.fwd(prompts[:, 299])
+        assert np.array_equal(gpu.logits(), base)
     gpu.close()
 
 
