@@ -370,6 +370,109 @@ class GraphRowWorkload:
                 "l2": "inputs larger than L2 (268 MB touched per step vs 126 MB L2)"}
 
 
+class LlamaOpsWorkload:
+    """The operators of ug_llama::Device and the small map kernels, each alone at HBM size (f32): rope and rope_i
+    (ug-llama/src/cpu_ops.rs:58-127) on [32, 32, 512, 64], cat (cpu_ops.rs:129-167) of two [8192, 4096] along the
+    last axis, causal_mask (cpu_ops.rs:33-56) on [32, 1024, 1024], index_select (model.rs:32-63) of 16384 rows of a
+    [32000, 2048] table, add and silu(gate) * up on 2^25 elements.  One value per operator: algorithmic bytes
+    (every input element read once, every output element written once) / time; parity bit-exact or 1e-6."""
+    unit = "GB/s"
+    dtype = "f32"
+    bound = "hbm"
+    kernel_only = True
+    ncu_traffic_bytes = None
+    name = "rope, rope_i, cat, causal_mask, index_select, add, silu_mul f32, each alone on 134-402 MB per launch"
+    metric = "effective HBM GB/s per operator (algorithmic bytes / time)"
+
+    def __init__(self, rank=0):
+        self.launches_per_step = 1
+
+    def setup(self, dev):
+        from ug_b200 import DType, synth
+        self.dev = dev
+        A = lambda n: dev.allocate_uninit(DType.F32, n)
+        b, h, t, d = 32, 32, 512, 64
+        n = b * h * t * d                                   # 2^25 elements = 134 MB
+        self.x = synth.normal(41, (n,))
+        self.y = synth.normal(42, (n,))
+        xs, ys, out = dev.slice_from_values(self.x), dev.slice_from_values(self.y), A(n)
+        pos_max = 1024
+        ang = np.outer(np.arange(pos_max, dtype=np.float32), (1.0 / 10000.0 ** (np.arange(0, d, 2, dtype=np.float32) / d)))
+        self.cos, self.sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+        cs, sn = dev.slice_from_values(self.cos), dev.slice_from_values(self.sin)
+        self.pos = np.array([7], np.int32)
+        ps = dev.slice_from_values(self.pos)
+        vocab, hid, n_ids = 32000, 2048, 16384
+        self.emb = synth.normal(43, (vocab, hid))
+        self.ids = synth.tokens(44, (n_ids,), vocab)
+        es, ids = dev.slice_from_values(self.emb), dev.slice_from_values(self.ids)
+        self.out = out
+        self.shape = (b, h, t, d)
+        self.ops = {
+            "rope": (lambda: dev.rope(xs, cs, sn, ps, out, b, h, t, d), 8 * n),
+            "rope_i": (lambda: dev.rope_i(xs, cs, sn, ps, out, b, h, t, d), 8 * n),
+            "cat": (lambda: dev.cat(xs, ys, self.big, 8192, 4096, 4096), 16 * n),
+            "causal_mask": (lambda: dev.causal_mask(xs, out, 32, 1024, 1024), 8 * n),
+            "index_select": (lambda: dev.index_select(es, ids, out, n_ids, hid, vocab), 8 * n_ids * hid),
+            "add": (lambda: dev.add(xs, ys, out, n), 12 * n),
+            "silu_mul": (lambda: dev.silu_mul(xs, ys, out, n), 12 * n),
+        }
+        self.big = A(2 * n)                                  # cat output: [8192, 8192]
+        self._keep = (xs, ys, cs, sn, ps, es, ids)
+
+    def step(self):
+        for f, _ in self.ops.values():
+            f()
+
+    def _check(self, name):
+        import oracle
+        b, h, t, d = self.shape
+        n = b * h * t * d
+        if name in ("rope", "rope_i"):
+            got = self.out.to_vec().reshape(b, h, t, d)[:1, :2]
+            fn = oracle.rope if name == "rope" else oracle.rope_i
+            return float(np.max(np.abs(got - fn(self.x.reshape(b, h, t, d)[:1, :2], self.cos, self.sin, self.pos))))
+        if name == "cat":
+            got = self.big.to_vec().reshape(8192, 8192)[:16]
+            want = oracle.cat(self.x.reshape(8192, 4096)[:16], self.y.reshape(8192, 4096)[:16], 1)
+            return float(np.max(np.abs(got - want)))
+        if name == "causal_mask":
+            got = self.out.to_vec().reshape(1, 32, 1024, 1024)[:, :1]
+            want = oracle.causal_mask(self.x.reshape(1, 32, 1024, 1024)[:, :1])
+            return 0.0 if np.array_equal(got, want) else 1.0
+        if name == "index_select":
+            got = self.out.to_vec().reshape(-1, 2048)[:64]
+            return float(np.max(np.abs(got - oracle.index_select(self.emb, self.ids[:64]))))
+        if name == "add":
+            return float(np.max(np.abs(self.out.to_vec()[:65536] - oracle.gen_add(self.x[:65536], self.y[:65536]))))
+        got, want = self.out.to_vec()[:65536], oracle.gen_silu_mul(self.x[:65536], self.y[:65536])
+        return float(np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-30)))
+
+    def record(self, dev, warmup, steps, peaks):
+        ops = {}
+        for name, (f, nbytes) in self.ops.items():
+            for _ in range(max(warmup, 3)):
+                f()
+            dev.synchronize()
+            dev.timer_begin()
+            for _ in range(steps):
+                f()
+            dev.timer_end()
+            sec = dev.timer_elapsed_ms() / 1e3 / steps
+            ops[name] = {"value": round(nbytes / sec / 1e9, 1), "frac": round(nbytes / sec / 1e9 / peaks["hbm"], 4),
+                         "us_per_launch": round(sec * 1e6, 2), "bytes_per_launch": nbytes,
+                         "parity_max_err": self._check(name)}
+        worst = min(ops, key=lambda k: ops[k]["frac"])
+        return {"workload": self.name, "metric": self.metric, "unit": self.unit, "dtype": self.dtype, "steps": steps,
+                "value": ops[worst]["value"], "value_of": worst, "operators": ops,
+                "roofline": {"bound": "hbm", "achieved": ops[worst]["value"], "peak": peaks["hbm"], "unit": "GB/s",
+                             "frac": ops[worst]["frac"], "traffic": None, "peak_source": peaks["source"],
+                             "note": "the slowest of the operators; inputs larger than L2"}}
+
+    def config(self):
+        return {"workload": self.name}
+
+
 class GraphDecodeWorkload:
     """ug-llama's own generation loop (ug-llama/src/main.rs:127-169: build the graph of one forward pass, schedule,
     compile_with_cache, run, read the logits, pick the next token) for ONE sequence of the 1.1B shape in f32, exactly
@@ -957,7 +1060,7 @@ WORKLOADS = {"rms_silu": RmsSiluWorkload, "softmax": SoftmaxWorkload, "softmax_c
              "gemm": GemmWorkload, "decode": DecodeWorkload, "prefill": PrefillWorkload,
              "graph_softmax": lambda r: GraphRowWorkload("softmax"), "graph_rms_norm": lambda r: GraphRowWorkload("rms_norm"),
              "gemm_f32": lambda r: F32MatmulWorkload("gemm_f32"), "gemv_f32": lambda r: F32MatmulWorkload("gemv_f32"),
-             "graph_decode": GraphDecodeWorkload}
+             "graph_decode": GraphDecodeWorkload, "llama_ops": LlamaOpsWorkload}
 DEFAULT_WORKLOAD = "decode"
 
 # DRAM traffic of the decode step's kernels, from ncu captures of single launches (dram__bytes_read.sum +
@@ -1050,6 +1153,7 @@ def config_records(dev, group, peaks):
             ("graph_rms_norm_8192x4096", lambda r: GraphRowWorkload("rms_norm"), 30),
             ("f32_gemm_4096", lambda r: F32MatmulWorkload("gemm_f32"), 10),
             ("f32_decode_matmul_1x32000x2048", lambda r: F32MatmulWorkload("gemv_f32"), 50),
+            ("llama_operators_f32", LlamaOpsWorkload, 20),
             ("graph_decode_llama_1b_f32", GraphDecodeWorkload, 32)]
     for key, cls, steps in plan:
         wl = cls(0)
