@@ -78,6 +78,19 @@ def test_long_context_crosses_tiles_and_slices(dev):
         gpu.fwd(prompts[:, 299])
         # slices change the running max, hence the bf16 rounding of the probabilities: not bit-equal
         assert np.max(np.abs(gpu.logits() - base)) < 5e-3 * np.abs(base).max()
+    for splits in (2, 3, 4, 8):         # slices combined inside a cluster or through scratch: the same sums, same bits
+        gpu.set_option("att_splits", splits)
+        both = []
+        for cluster in (1, 0):
+            gpu.set_option("att_cluster", cluster)
+            gpu.reset(299)
+            gpu.fwd(prompts[:, 299])
+            both.append(gpu.logits())
+        assert np.array_equal(both[0], both[1])
+    gpu.set_option("att_cluster", 1)
+    gpu.set_option("att_splits", 2)
+    gpu.reset(299)
+    gpu.fwd(prompts[:, 299])
     base = gpu.logits()
     for stages in (2, 3, 4, 6):         # the ring depth only changes when a sub-tile is requested: same bits
         gpu.set_option("att_stages", stages)

@@ -218,6 +218,11 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {      // addr: a shared::cluster address (mapa)
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
   return *(uint32_t *)&t;
@@ -259,6 +264,9 @@ struct AttRope {
   const float *cos_, *sin_;
   int interleaved, append;
   int early;                     // 1: the ring may be filled before griddepcontrol.wait (see the kernel)
+  int cluster;                   // 1: the launch groups the KV slices of a (sequence, KV head) pair into one thread-block
+                                 // cluster (cluster dims = (n_split, 1, 1)): the slices are combined through
+                                 // distributed shared memory instead of scratch, fence, counter and a last CTA
   ugb_status_word *status;       // where a position outside the cache, or (TMA variant) a wait that gave up, is reported
 };
 
@@ -286,6 +294,7 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__
   uint64_t *bars = reinterpret_cast<uint64_t *>(att_smem + att_ring_bytes(NSTAGE));   // [warp][stage], TMA only
   __shared__ float merge_o[ATT_WARPS][ATT_GROUP][ATT_HD];
   __shared__ float merge_ml[ATT_WARPS][ATT_GROUP][2];
+  __shared__ float cl_o[ATT_GROUP][ATT_HD], cl_ml[ATT_GROUP][2];   // this CTA's slice result, read by the cluster's rank 0
   __shared__ int is_last;
 
   if (TMA) {
@@ -592,10 +601,50 @@ decode_attention_kernel_t(const __nv_bfloat16 *__restrict__ q, __nv_bfloat16 *__
       if (h < group) out[((size_t)b * n_heads + kvh * group + h) * ATT_HD + dd] = __float2bfloat16_rn(acc / ll);
       continue;
     }
+    if (rope.cluster) {
+      cl_o[h][dd] = acc;
+      if (dd == 0) { cl_ml[h][0] = mm; cl_ml[h][1] = ll; }
+      continue;
+    }
     part_o[(slot * ATT_GROUP + h) * ATT_HD + dd] = acc;
     if (dd == 0) { part_ml[(slot * ATT_GROUP + h) * 2] = mm; part_ml[(slot * ATT_GROUP + h) * 2 + 1] = ll; }
   }
   if (n_split == 1) return;
+  if (rope.cluster) {
+    // ---- the slices of this (b, kvh) are the CTAs of one cluster (rank = slice): rank 0 combines them in slice
+    // order, the same sums as the scratch path below, reading the peers' shared memory -------------------------
+    ugb_tc::cluster_sync_all();                     // every slice's result is in its CTA's shared memory
+    if (sp == 0) {
+      for (int idx = threadIdx.x; idx < group * ATT_HD; idx += blockDim.x) {
+        const int h = idx / ATT_HD, dd = idx - h * ATT_HD;
+        const uint32_t a_ml = ugb_tc::smem_u32(&cl_ml[h][0]), a_o = ugb_tc::smem_u32(&cl_o[h][dd]);
+        float ms[8], ls[8], os[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          const bool on = s < n_split;
+          const uint32_t r = (uint32_t)(on ? s : 0);
+          ms[s] = on ? ld_cluster_f32(ugb_tc::mapa_u32(a_ml, r)) : -INFINITY;
+          ls[s] = on ? ld_cluster_f32(ugb_tc::mapa_u32(a_ml + 4, r)) : 0.f;
+          os[s] = on ? ld_cluster_f32(ugb_tc::mapa_u32(a_o, r)) : 0.f;
+        }
+        float mm = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) mm = fmaxf(mm, ms[s]);
+        float acc = 0.f, ll = 0.f;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          if (s < n_split) {
+            const float f = ms[s] == -INFINITY ? 0.f : __expf(ms[s] - mm);
+            acc += os[s] * f;
+            ll += ls[s] * f;
+          }
+        }
+        out[((size_t)b * n_heads + kvh * group + h) * ATT_HD + dd] = __float2bfloat16_rn(acc / ll);
+      }
+    }
+    ugb_tc::cluster_sync_all();                     // no CTA leaves while rank 0 may still read its shared memory
+    return;
+  }
   // ---- last CTA of this (b, kvh) combines the slices ------------------------
   __threadfence();
   __syncthreads();

@@ -91,6 +91,8 @@ struct ugb_llama {
   unsigned step_timeouts = 0;     // dev->wait_timeouts when the barrier words were last cleared
   int att_early = 1;              // option att_early: kernels may fetch old data before griddepcontrol.wait when that is provably safe
   bool early_ok = false;          // ... and it is, for the current shapes and options (set by enqueue_step)
+  int att_cluster = 1;            // option att_cluster: the KV slices of a (sequence, KV head) pair run as one cluster and
+                                  // are combined through distributed shared memory
   int att_tma = 0;                // option att_tma: decode attention fetches K / V by TMA (1) or cp.async (0)
   std::vector<CUtensorMap> att_kmap, att_vmap;   // per layer, for the TMA variant
   int pf_att_tc = 1;              // option prefill_attention_tc: 1 = tcgen05 / TMEM attention kernel drawing its
@@ -287,16 +289,18 @@ int32_t launch_attention(ugb_llama *m, int layer, float scale, int n_part, bool 
   rope.cos_ = m->cos; rope.sin_ = m->sin; rope.interleaved = c.rope_interleaved; rope.append = append ? 1 : 0;
   rope.status = m->dev->status_dev;
   rope.early = (layer > 0 && append && m->early_ok && !tma_requested(m)) ? 1 : 0;
+  const int cluster = (m->att_cluster && m->att_splits > 1) ? m->att_splits : 1;
+  rope.cluster = cluster > 1 ? 1 : 0;
   const bool tma = m->att_tma != 0 && !m->att_kmap.empty();
   const CUtensorMap none{};
   const CUtensorMap &mk = tma ? m->att_kmap[layer] : none, &mv = tma ? m->att_vmap[layer] : none;
   cudaError_t e = cudaSuccess;
 #define UGB_ATT_LAUNCH(NS)                                                                                   \
-  e = tma ? ugb_launch(decode_attention_kernel_t<NS, true>, grid, dim3(ATT_WARPS * 32), att_dyn_smem(NS, true), st,       \
-                       m->pdl != 0, (const __nv_bfloat16 *)nullptr, kc, vc, (const int *)m->pos, m->att_po, m->att_pml,   \
+  e = tma ? ugb_launch_cluster(decode_attention_kernel_t<NS, true>, grid, dim3(ATT_WARPS * 32), att_dyn_smem(NS, true), st,       \
+                       m->pdl != 0, cluster, (const __nv_bfloat16 *)nullptr, kc, vc, (const int *)m->pos, m->att_po, m->att_pml,   \
                        m->att_cnt, m->att, c.n_heads, c.n_kv_heads, c.n_heads / c.n_kv_heads, m->t_max, scale, rope, mk, mv) \
-          : ugb_launch(decode_attention_kernel_t<NS, false>, grid, dim3(ATT_WARPS * 32), att_dyn_smem(NS, false), st,     \
-                       m->pdl != 0, (const __nv_bfloat16 *)nullptr, kc, vc, (const int *)m->pos, m->att_po, m->att_pml,   \
+          : ugb_launch_cluster(decode_attention_kernel_t<NS, false>, grid, dim3(ATT_WARPS * 32), att_dyn_smem(NS, false), st,     \
+                       m->pdl != 0, cluster, (const __nv_bfloat16 *)nullptr, kc, vc, (const int *)m->pos, m->att_po, m->att_pml,   \
                        m->att_cnt, m->att, c.n_heads, c.n_kv_heads, c.n_heads / c.n_kv_heads, m->t_max, scale, rope, mk, mv)
   switch (m->att_stages) {
     case 2: UGB_ATT_LAUNCH(2); break;
@@ -828,6 +832,11 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
   }
   if (k == "att_early") {
     m->att_early = value != 0;
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    return UGB_OK;
+  }
+  if (k == "att_cluster") {
+    m->att_cluster = value != 0;
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
     return UGB_OK;
   }
