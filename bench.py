@@ -465,6 +465,7 @@ class LlamaOpsWorkload:
         worst = min(ops, key=lambda k: ops[k]["frac"])
         return {"workload": self.name, "metric": self.metric, "unit": self.unit, "dtype": self.dtype, "steps": steps,
                 "value": ops[worst]["value"], "value_of": worst, "operators": ops,
+                "parity_max_rel_err": max(o["parity_max_err"] for o in ops.values()),
                 "roofline": {"bound": "hbm", "achieved": ops[worst]["value"], "peak": peaks["hbm"], "unit": "GB/s",
                              "frac": ops[worst]["frac"], "traffic": None, "peak_source": peaks["source"],
                              "note": "the slowest of the operators; inputs larger than L2"}}

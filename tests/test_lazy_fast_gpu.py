@@ -99,7 +99,7 @@ def test_index_select_ssa_runs_on_the_gather_operator(hd):
 
 
 def test_no_item_of_an_unmodified_llama_step_is_left_on_per_instruction_code(hd):
-    """Every fused kernel of ug-llama's decode step (ug-llama/src/model.rs:203-269, SURVEY's 14 generated kernels
+    """Every fused kernel of ug-llama's decode step (ug-llama/src/model.rs:203-269: 14 generated kernels
     per layer) is a row, map or copy kernel of the generator; logits agree with the CPU oracle."""
     from oracle import llama_ref as R
     from ug_b200.llama import Config
