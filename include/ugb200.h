@@ -468,6 +468,7 @@ UGB_API int32_t ugb_llama_load_weight(ugb_llama *m, const char *name, const ugb_
  * 64, 80, 96, 128 or 256); "gemm_smem_kib" (shared-memory cap of a decode GEMM
  * CTA, 32..220, 0 = none); "att_stages" (2..6); "att_early", "att_tma",
  * "att_cluster" (the KV slices of a pair run as one thread-block cluster),
+ * "gate_up_pair" (decode gate|up on pairs of CTAs that split k),
  * "prefill_attention_tc", "pdl" (0 / 1); "prefill_rows" (64..65536, see
  * ugb_llama_prefill); "step_kernel" (0 / 1): a decode step of up to 64
  * sequences runs all its layers in ONE persistent kernel launch (grid-wide

@@ -131,6 +131,26 @@ def test_full_width_two_layers_greedy(dev):
     gpu.close()
 
 
+def test_gate_up_on_cta_pairs_or_single_ctas(dev):
+    """The gate|up projection of a decode step runs its k halves on a pair of CTAs (a cluster) that exchange their
+    sums through shared memory, or on one CTA per tile: two summation orders of the same products, both within
+    tolerance of the oracle, at a width whose last tile is partly outside (ffn 5632: 11264 = 70 x 160 + 64) and at
+    a small one."""
+    for over, batch in (({"hidden_size": 2048, "intermediate_size": 5632, "num_attention_heads": 32, "num_key_value_heads": 4,
+                          "num_hidden_layers": 1, "vocab_size": 512, "max_position_embeddings": 128}, 64), ({}, 5)):
+        cfg = Config(**{**TINY, **over})
+        gpu, ref = make(cfg, dev, batch, 32)
+        prompts = synth.tokens(12, (batch, 6), cfg.vocab_size)
+        logits = []
+        for pair in (1, 0):
+            gpu.set_option("gate_up_pair", pair)
+            worst, _ = run_teacher_forced(gpu, ref, prompts, check_seqs=[0, batch - 1])
+            assert worst < TOL
+            logits.append(gpu.logits())
+        assert np.max(np.abs(logits[0] - logits[1])) < 2e-3 * np.abs(logits[1]).max()
+        gpu.close()
+
+
 def test_multi_step_graph_replay_equals_single_steps(dev):
     cfg = Config(**TINY)
     gpu, _ = make(cfg, dev, 16, 64)

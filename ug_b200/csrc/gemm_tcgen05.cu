@@ -73,6 +73,8 @@ struct Params {
   int b_static;           // 1: no kernel on the stream writes B (weights): it may be fetched before ugb_pdl_wait
   int stages;             // depth of the shared-memory ring in use (2 .. Cfg::STAGES)
   int f16;                // operands and 16-bit output are IEEE f16 (0: bf16)
+  int pair_k;             // 1: CTAs 2c and 2c + 1 are a cluster and take the two k halves of tile c (BM = 64,
+                          // UGB_EPI_SILU_MUL_BF16): rank 1 hands its sums to rank 0 through shared memory
   long long c_batch;      // output elements between batch steps
   long long c_split;      // output elements between split-K partials
   void *C;
@@ -107,9 +109,16 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  bool pair_ready = false;           // pair_k: this epilogue thread saw its accumulator complete
+  int pair_m0 = 0, pair_n0 = 0;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int tiles_per_split = tiles_per_batch * p.batch;
   const int n_tiles = tiles_per_split * p.splits;
+  // tile number -> (k split, tile inside the split); with pair_k the two k halves of a tile are neighbours
+  auto split_of = [&](int tile, int &sp, int &ts) {
+    if (p.pair_k) { sp = tile & 1; ts = tile >> 1; }
+    else { sp = tile / tiles_per_split; ts = tile - sp * tiles_per_split; }
+  };
   // `bar`: this CTA's barrier, or for PAIR the leader's (a shared::cluster address)
   auto load3 = [&](uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y, int z) {
     if constexpr (PAIR) tma_load_3d_pair(dst, map, bar, x, y, z);
@@ -143,8 +152,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // barrier and the wait for the preceding kernel; A follows once that kernel is done.
     if (!PAIR && p.b_static) {
       const int tile = blockIdx.x;
-      const int sp = tile / tiles_per_split;
-      const int ts = tile - sp * tiles_per_split;
+      int sp, ts;
+      split_of(tile, sp, ts);
       const int bi = ts / tiles_per_batch;
       const int r = ts - bi * tiles_per_batch;
       const int n0 = (p.n_fast ? r % p.tiles_n : r / p.tiles_m) * BN;
@@ -189,8 +198,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int pre = 0;
       {
         const int tile = cta0;
-        const int sp = tile / tiles_per_split;
-        const int ts = tile - sp * tiles_per_split;
+        int sp, ts;
+        split_of(tile, sp, ts);
         const int bi = ts / tiles_per_batch;
         const int r = ts - bi * tiles_per_batch;
         const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * TILE_M + (int)rank * BM;
@@ -213,8 +222,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         phase = pre == STAGES ? 1u : 0u;
       }
       for (int tile = cta0; tile < n_tiles && alive; tile += n_ctas) {
-        const int sp = tile / tiles_per_split;
-        const int ts = tile - sp * tiles_per_split;
+        int sp, ts;
+        split_of(tile, sp, ts);
         const int bi = ts / tiles_per_batch;
         const int r = ts - bi * tiles_per_batch;
         const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * TILE_M + (int)rank * BM;
@@ -251,7 +260,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t phase = 0, acc_phase = 0;
       bool alive = true;
       for (int tile = cta0; tile < n_tiles && alive; tile += n_ctas) {
-        const int sp = tile / tiles_per_split;
+        int sp, ts_unused;
+        split_of(tile, sp, ts_unused);
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1u, abort_flag, p.status, 2)) break;
@@ -291,8 +301,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       else mbar_arrive(smem_u32(&acc_empty[a]));
     };
     for (int tile = cta0; tile < n_tiles; tile += n_ctas) {
-      const int sp = tile / tiles_per_split;
-      const int ts = tile - sp * tiles_per_split;
+      int sp, ts;
+      split_of(tile, sp, ts);
       const int bi = ts / tiles_per_batch;
       const int r = ts - bi * tiles_per_batch;
       const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * TILE_M + (int)rank * BM;
@@ -303,6 +313,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const bool row_lane = BM == 128 || lane < 16;
       const int row = BM == 128 ? m0 + quad * 32 + lane : m0 + quad * 16 + lane;
       const long long out_off = (long long)sp * p.c_split + (long long)bi * p.c_batch;
+      if constexpr (BM == 64 && !PAIR) {
+        if (p.pair_k) {
+          // both k halves keep their sums in TMEM; they meet after the role branches (below)
+          pair_ready = true;
+          pair_m0 = m0; pair_n0 = n0;
+          break;
+        }
+      }
       if constexpr (BM == 128) {
         if (p.epi == UGB_EPI_ROPE_QKV) {
           // One head (64 columns) at a time: both halves of every rotation pair (i, i + 32) -- or the 32
@@ -450,6 +468,81 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   }
 
+  // ---------------------------------------- pair_k: the two k halves meet --
+  // Each half finishes one half of the tile's columns (groups of 16 = 8 (gate, up) pairs: half h owns the groups
+  // g with g / (groups / 2) == h).  First barrier: both accumulators are complete, so both rings are idle.  Then
+  // each half writes its sums of the OTHER half's groups, row-major f32 [64][BN], into the start of the other's
+  // ring (remote stores, which unlike remote loads are not waited for one by one).  Second barrier: the sums
+  // have arrived; each half adds its own and applies the epilogue to its groups.
+  if constexpr (BM == 64 && !PAIR && BN % 32 == 0) {
+    if (p.pair_k) {
+      constexpr int GROUPS = BN / 16;
+      const int half = (int)(blockIdx.x & 1);
+      const int quad = warp & 3;
+      const bool row_lane = lane < 16;
+      const bool work = warp >= 2 && pair_ready && !*abort_flag;
+      auto mine = [&](int g) { return (g >= GROUPS / 2 ? 1 : 0) == half; };
+      __syncwarp();
+      cluster_sync_all();
+      if (work) {
+        const uint32_t park = mapa_u32(smem_u32(smem), (uint32_t)(half ^ 1)) + (uint32_t)((quad * 16 + (lane & 15)) * BN * 4);
+        tcgen05_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (mine(2 * c) && mine(2 * c + 1)) continue;       // warp-uniform: nothing of this chunk goes to the peer
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
+          tmem_ld_wait();
+          if (row_lane) {                       // lanes 16..31 of a BM = 64 warp hold no rows
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              if (!mine(2 * c + q / 4))
+                asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};"
+                             ::"r"(park + (uint32_t)((c * 32 + q * 4) * 4)), "r"(v[q * 4]), "r"(v[q * 4 + 1]), "r"(v[q * 4 + 2]), "r"(v[q * 4 + 3])
+                             : "memory");
+          }
+        }
+        tcgen05_fence_before();
+      }
+      __syncwarp();
+      cluster_sync_all();
+      if (work) {
+        const int row = pair_m0 + quad * 16 + lane;
+        const float *park = reinterpret_cast<const float *>(smem) + (size_t)(quad * 16 + (lane & 15)) * BN;
+        tcgen05_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          if (!mine(2 * c) && !mine(2 * c + 1)) continue;
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
+          tmem_ld_wait();
+          if (row_lane && row < p.M) {
+            const int col0 = pair_n0 + c * 32;
+            // out [M, N/2] bf16 = silu(gate) * up over the summed (gate, up) column pairs
+            __nv_bfloat16 *crow = (__nv_bfloat16 *)p.C + (long long)row * (p.N / 2) + col0 / 2;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              if (mine(2 * c + q) && col0 + q * 16 < p.N) {
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float4 w = *reinterpret_cast<const float4 *>(park + c * 32 + q * 16 + e * 4);
+                  const float g0 = __uint_as_float(v[q * 16 + e * 4 + 0]) + w.x, u0 = __uint_as_float(v[q * 16 + e * 4 + 1]) + w.y;
+                  const float g1 = __uint_as_float(v[q * 16 + e * 4 + 2]) + w.z, u1 = __uint_as_float(v[q * 16 + e * 4 + 3]) + w.w;
+                  __nv_bfloat162 t = __floats2bfloat162_rn(__fdividef(g0, __expf(-g0) + 1.0f) * u0,
+                                                           __fdividef(g1, __expf(-g1) + 1.0f) * u1);
+                  o[e] = *(uint32_t *)&t;
+                }
+                *reinterpret_cast<uint4 *>(crow + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
+            }
+          }
+        }
+        tcgen05_fence_before();
+      }
+    }
+  }
+
   // ------------------------------------------------------------- teardown --
   __syncwarp();
   if (*abort_flag) {
@@ -477,7 +570,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 
 struct TcState {
   EncodeTiledFn encode = nullptr;
-  bool attr_set[9] = {false, false, false, false, false, false, false, false, false};
+  bool attr_set[10] = {false, false, false, false, false, false, false, false, false, false};
 };
 
 TcState *state_of(ugb_device *dev) {
@@ -515,7 +608,7 @@ template <int BM, int BN, bool PAIR = false>
 int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_t batch, size_t m) {
   using C_ = Cfg<BM, BN, PAIR>;
   const size_t n = g.n, k = g.k;
-  constexpr int slot = PAIR ? 8 : BN == 80 ? 6 : BN == 96 ? 7 : (BN == 256 ? 2 : (BN == 128 ? 1 : 0)) + (BM == 64 ? 3 : 0);
+  constexpr int slot = PAIR ? 8 : BN == 160 ? 9 : BN == 80 ? 6 : BN == 96 ? 7 : (BN == 256 ? 2 : (BN == 128 ? 1 : 0)) + (BM == 64 ? 3 : 0);
   if (!st->attr_set[slot]) {
     UGB_CUDA(dev, cudaFuncSetAttribute(tc_gemm_kernel<BM, BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        C_::SMEM_BYTES));
@@ -536,6 +629,16 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   p.epi = g.epi;
   p.b_static = g.b_static ? 1 : 0;
   p.f16 = g.f16 ? 1 : 0;
+  p.pair_k = 0;
+  if (g.pair_k) {
+    // two CTAs (a cluster) per tile, each over half of k
+    if (!(BM == 64 && !PAIR && BN % 32 == 0) || g.epi != UGB_EPI_SILU_MUL_BF16 || batch != 1 || p.k_blocks < 2 ||
+        2 * (long long)p.tiles_m * p.tiles_n > dev->sm_count)
+      return UGB_ERR_UNSUPPORTED;
+    p.pair_k = 1;
+    p.kb_per_split = (p.k_blocks + 1) / 2;
+    p.splits = 2;
+  }
   // Consecutive tiles run in the same wave.  The operand that is walked completely by every wave is read
   // from L2 again and again, so it should be the smaller one: B (n x k) when n <= m, otherwise A.
   p.n_fast = n <= m ? 1 : 0;
@@ -576,7 +679,7 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
     return UGB_OK;
   }
   cudaError_t le = ugb_launch_cluster(tc_gemm_kernel<BM, BN, PAIR>, dim3(grid), dim3(THREADS), smem, dev->stream,
-                                      g.pdl, PAIR ? 2 : 1, tmA, tmB, p);
+                                      g.pdl, (PAIR || p.pair_k) ? 2 : 1, tmA, tmB, p);
   if (le != cudaSuccess) return ugb_fail(dev, UGB_ERR_CUDA, "launch of tc_gemm_kernel failed: %s", cudaGetErrorString(le));
   return ugb_after_launch(dev, "tc_gemm_kernel");
 }
@@ -637,6 +740,7 @@ int32_t ugb_tc_gemm(ugb_device *dev, const ugb_tc_gemm_args &g) {
     if (bn == 80) return launch_tc<64, 80>(dev, st, g, batch, m);      // widths that split n into close to one
     if (bn == 96) return launch_tc<64, 96>(dev, st, g, batch, m);      // tile per SM where 64 / 128 do not
     if (bn == 128) return launch_tc<64, 128>(dev, st, g, batch, m);
+    if (bn == 160) return launch_tc<64, 160>(dev, st, g, batch, m);
     return launch_tc<64, 256>(dev, st, g, batch, m);
   }
   if (bn == 80 || bn == 96) bn = 128;                                  // BM = 128 needs n % 16 == 0 tiles: keep the three sizes

@@ -34,11 +34,14 @@ struct ugb_tc_gemm_args {
   bool b_is_nk;
   int epi;              // UGB_EPI_*
   int splits;           // split-K factor (only with UGB_EPI_F32); the kernel may use fewer
-  int bn;               // tile width: 64, 128, 256 (80, 96 too when m <= 64 and b_is_nk), or 0 = choose from m
+  int bn;               // tile width: 64, 128, 256 (80, 96, 160 too when m <= 64 and b_is_nk), or 0 = choose from m
   bool b_static;        // no kernel on the stream writes b (weights): fetch it before waiting for the predecessor
   bool pdl;             // launch with programmatic stream serialization (see ugb_launch)
   int smem_kib = 0;     // cap on the shared memory of a CTA (ring depth follows); 0 = as deep as fits in 220 KiB
   bool f16 = false;     // operands (and the UGB_EPI_BF16 output) are IEEE f16 instead of bf16: same instruction, other format field
+  bool pair_k = false;  // m <= 64, UGB_EPI_SILU_MUL_BF16: two CTAs (a thread-block cluster) per tile, each over half of k; the
+                        // second hands its sums to the first through distributed shared memory.  UGB_ERR_UNSUPPORTED when
+                        // twice the tiles exceed the SMs
   int pair = -1;        // 256 x 256 tiles on pairs of CTAs (cta_group::2) where the shape allows: 1 / 0, -1 = the device's setting
   ugb_tc_rope_epilogue rope = {};   // UGB_EPI_ROPE_QKV only
   // Query instead of launch: when set, ugb_tc_gemm launches nothing and reports the grid it would launch and how many

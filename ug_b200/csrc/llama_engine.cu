@@ -69,11 +69,11 @@ struct ugb_llama {
   int *tok = nullptr, *next = nullptr, *pos = nullptr;
   int host_pos = 0;
   // tuning
-  int splits_qkv = 3, splits_o = 4, splits_down = 8, att_splits = 1, att_stages = 5;
+  int splits_qkv = 5, splits_o = 8, splits_down = 8, att_splits = 1, att_stages = 5;
   int pdl = 1;                    // programmatic dependent launch between the kernels of a step
   int gemm_smem_kib = 144;        // shared-memory cap of the decode GEMM CTAs (0 = deepest ring); measured best
   int skip = 0;                   // measurement aid: bit mask of kernel types left out of the step
-  int bn_qkv = 64, bn_o = 64, bn_gate_up = 128, bn_down = 128, bn_lm_head = 256;   // GEMM tile widths
+  int bn_qkv = 128, bn_o = 128, bn_gate_up = 128, bn_down = 128, bn_lm_head = 256;   // GEMM tile widths
   size_t part_elems = 0;
   // graph of one step that reads `next` as its input tokens
   cudaGraphExec_t graph = nullptr;
@@ -91,6 +91,7 @@ struct ugb_llama {
   unsigned step_timeouts = 0;     // dev->wait_timeouts when the barrier words were last cleared
   int att_early = 1;              // option att_early: kernels may fetch old data before griddepcontrol.wait when that is provably safe
   bool early_ok = false;          // ... and it is, for the current shapes and options (set by enqueue_step)
+  int gate_up_pair = 1;           // option gate_up_pair: decode gate|up on pairs of CTAs that split k (see gemm_rows)
   int att_cluster = 1;            // option att_cluster: the KV slices of a (sequence, KV head) pair run as one cluster and
                                   // are combined through distributed shared memory
   int att_tma = 0;                // option att_tma: decode attention fetches K / V by TMA (1) or cp.async (0)
@@ -176,6 +177,16 @@ int32_t gemm_rows(ugb_llama *m, size_t rows, void *out, const __nv_bfloat16 *a, 
   g.a_batch = 0; g.b_batch = 0; g.b_is_nk = true;
   g.epi = epi; g.splits = splits; g.bn = bn; g.b_static = true; g.pdl = m->pdl != 0;
   g.smem_kib = rows <= 64 ? m->gemm_smem_kib : 0;
+  if (epi == UGB_EPI_SILU_MUL_BF16 && rows <= 64 && m->gate_up_pair && !(m->tp && m->tp_size > 1) && (n + 159) / 160 * 2 <= (size_t)m->dev->sm_count) {
+    // gate|up of a decode step: 160-wide tiles, the two k halves of a tile on a pair of CTAs (the k loop of a CTA,
+    // not the weight stream, is what bounds the narrow-tile kernel)
+    g.bn = 160;
+    g.pair_k = true;
+    const int32_t rc2 = ugb_tc_gemm(m->dev, g);
+    if (rc2 != UGB_ERR_UNSUPPORTED) return rc2;
+    g.bn = bn;
+    g.pair_k = false;
+  }
   int32_t rc = ugb_tc_gemm(m->dev, g);
   if (rc == UGB_ERR_UNSUPPORTED)
     return ugb_fail(m->dev, rc, "GEMM m=%zu n=%zu k=%zu does not meet the tensor-core kernel's shape rules", rows, n, k);
@@ -684,6 +695,8 @@ int32_t ugb_llama_create_tp(ugb_device *dev, const ugb_llama_config *cfg, int32_
       m->splits_qkv = 7;
       m->splits_o = 2;
       m->splits_down = 2;
+      m->bn_qkv = 64;
+      m->bn_o = 64;
     }
   }
   // rope tables, model.rs:278-295: theta_i = 1 / theta^(i/d) in f32 on the host
@@ -833,6 +846,12 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
   if (k == "att_early") {
     m->att_early = value != 0;
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    return UGB_OK;
+  }
+  if (k == "gate_up_pair") {
+    m->gate_up_pair = value != 0;
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    m->warmed = false;
     return UGB_OK;
   }
   if (k == "att_cluster") {
