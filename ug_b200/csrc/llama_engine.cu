@@ -177,7 +177,7 @@ int32_t gemm_rows(ugb_llama *m, size_t rows, void *out, const __nv_bfloat16 *a, 
   g.a_batch = 0; g.b_batch = 0; g.b_is_nk = true;
   g.epi = epi; g.splits = splits; g.bn = bn; g.b_static = true; g.pdl = m->pdl != 0;
   g.smem_kib = rows <= 64 ? m->gemm_smem_kib : 0;
-  if (epi == UGB_EPI_SILU_MUL_BF16 && rows <= 64 && m->gate_up_pair && !(m->tp && m->tp_size > 1) && (n + 159) / 160 * 2 <= (size_t)m->dev->sm_count) {
+  if (epi == UGB_EPI_SILU_MUL_BF16 && rows <= 64 && m->gate_up_pair && (n + 159) / 160 * 2 <= (size_t)m->dev->sm_count) {
     // gate|up of a decode step: 160-wide tiles, the two k halves of a tile on a pair of CTAs (the k loop of a CTA,
     // not the weight stream, is what bounds the narrow-tile kernel)
     g.bn = 160;
