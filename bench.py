@@ -1307,6 +1307,22 @@ def main():
         m = measure(wl, dev, group, rank, local_rank, args.warmup, args.steps, e2e_steps)
 
     tp = decode and mode == "tp"
+    gemm_timeline = None
+    if rank == 0 and decode and options.get("gemm_profile"):
+        # CTA 0 of each decode projection on its own clock (%globaltimer), microseconds after the projection's wait
+        # for the preceding kernel returned: the last launches of the timed loop (qkv / o / gate|up / down of the
+        # last layer, lm_head); taken before the per-kernel timing below overwrites the stamps
+        from ug_b200._lib import lib
+        buf = np.zeros(5 * 64, np.float32)
+        dev._check(lib.ugb_llama_read(wl.model._h, 5, buf.ctypes.data, buf.size))
+        gemm_timeline = {}
+        for name, t in zip(["qkv", "o", "gate_up", "down", "lm_head"], buf.reshape(5, 64)):
+            kb = [round(float(x), 2) for x in t[8:] if x != 0]
+            gemm_timeline[name] = {
+                "cta_start": round(float(t[0]), 2), "wait_returned": 0.0, "k_blocks_complete_at": kb,
+                "ns_per_k_block": round(1e3 * (kb[-1] - kb[0]) / (len(kb) - 1), 1) if len(kb) > 1 else None,
+                "last_mma_issued": round(float(t[2]), 2), "accumulator_seen": round(float(t[3]), 2),
+                "epilogue_done": round(float(t[4]), 2), "tmem_released": round(float(t[5]), 2)}
     kern, kdepth = {}, 0
     if rank == 0 and decode:
         # per-kernel share of one step, each kernel type timed alone over all layers (CUDA events); no exchange inside
@@ -1389,6 +1405,8 @@ def main():
         line.update(extra)
         if step_phases:
             line["step_kernel_phases"] = step_phases
+        if gemm_timeline:
+            line["gemm_timeline_us"] = gemm_timeline
         if hasattr(wl, "reference_cuda_gbs"):
             g = wl.reference_cuda_gbs()
             line["reference_cuda_kernel"] = None if g is None else {

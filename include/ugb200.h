@@ -419,7 +419,8 @@ typedef struct {
 } ugb_llama_config;
 
 enum { UGB_LLAMA_LOGITS = 0, UGB_LLAMA_NEXT_TOKENS = 1, UGB_LLAMA_HIDDEN = 2, UGB_LLAMA_PREFILL_LOGITS = 3,
-       UGB_LLAMA_STEP_PROFILE = 4 /* measurement aid, see option "step_profile" */ };
+       UGB_LLAMA_STEP_PROFILE = 4 /* measurement aid, see option "step_profile" */,
+       UGB_LLAMA_GEMM_PROFILE = 5 /* measurement aid, see option "gemm_profile" */ };
 
 /* Model::new + Cache::new (model.rs:183-198,298-363): allocates weights, the
  * RoPE tables (model.rs:278-295) and a KV cache for `batch` sequences of up to
@@ -475,7 +476,14 @@ UGB_API int32_t ugb_llama_load_weight(ugb_llama *m, const char *name, const ugb_
  * barriers between the phases, the weight stream running ahead of them)
  * followed by the lm_head and the greedy choice, instead of seven launches per
  * layer; "step_profile" (0 / 1, measurement aid): that kernel records
- * %globaltimer at every grid barrier, read with UGB_LLAMA_STEP_PROFILE. */
+ * %globaltimer at every grid barrier, read with UGB_LLAMA_STEP_PROFILE;
+ * "gemm_profile" (0 / 1, measurement aid): CTA 0 of every decode projection
+ * records %globaltimer at its start, when the wait for the preceding kernel
+ * returns, at its last MMA, when the epilogue sees the accumulator, when the
+ * epilogue is done, at its end (values 0..5 of a projection) and at every k
+ * block of its main loop (values 8..); UGB_LLAMA_GEMM_PROFILE reads 5 x 64
+ * floats (qkv, o, gate|up, down, lm_head of the last launches), microseconds
+ * after the projection's own wait returned, 0 = not recorded. */
 UGB_API int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value);
 /* Sets the number of cached positions (0 = empty cache); cache contents at
  * positions >= pos are ignored by later steps. */

@@ -73,6 +73,7 @@ struct Params {
   int b_static;           // 1: no kernel on the stream writes B (weights): it may be fetched before ugb_pdl_wait
   int stages;             // depth of the shared-memory ring in use (2 .. Cfg::STAGES)
   int f16;                // operands and 16-bit output are IEEE f16 (0: bf16)
+  unsigned long long *prof;   // measurement aid (or null): %globaltimer stamps of CTA 0, see UGB_TC_PROF_* in the header
   int pair_k;             // 1: CTAs 2c and 2c + 1 are a cluster and take the two k halves of tile c (BM = 64,
                           // UGB_EPI_SILU_MUL_BF16): rank 1 hands its sums to rank 0 through shared memory
   long long c_batch;      // output elements between batch steps
@@ -83,6 +84,12 @@ struct Params {
 };
 
 using namespace ugb_tc;
+
+// Measurement aid: CTA 0 of a launch with p.prof set records when it passed the points UGB_TC_PROF_* name.
+#define UGB_TC_STAMP(i)                                                      \
+  do {                                                                       \
+    if (p.prof != nullptr && blockIdx.x == 0 && (i) < UGB_TC_PROF_SLOTS) p.prof[(i)] = globaltimer(); \
+  } while (0)
 
 template <int BM, int BN, bool PAIR = false>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -109,6 +116,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) UGB_TC_STAMP(UGB_TC_PROF_START);
   bool pair_ready = false;           // pair_k: this epilogue thread saw its accumulator complete
   int pair_m0 = 0, pair_n0 = 0;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
@@ -215,6 +223,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
         ugb_pdl_wait();
+        UGB_TC_STAMP(UGB_TC_PROF_DEP);
         for (int i = 0; i < pre; ++i)
           load3(smem_u32(smem + i * STAGE_BYTES), &tmA, PAIR ? mapa_u32(smem_u32(&full[i]), 0) : smem_u32(&full[i]),
                 (kb0 + i) * BK, m0, bi);
@@ -269,6 +278,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * C_::ACC_STRIDE);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&full[stage]), phase, abort_flag, p.status, 3)) { alive = false; break; }
+          if (tile == cta0) UGB_TC_STAMP(UGB_TC_PROF_KBLOCK0 + (kb - kb0));
           tcgen05_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
@@ -288,6 +298,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         if (!alive) break;
         commit(smem_u32(&acc_full[acc]));            // accumulator complete
+        if (tile == cta0) UGB_TC_STAMP(UGB_TC_PROF_LAST_MMA);
         if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1u; }
       }
     }
@@ -308,6 +319,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int m0 = (p.n_fast ? r / p.tiles_n : r % p.tiles_m) * TILE_M + (int)rank * BM;
       const int n0 = (p.n_fast ? r % p.tiles_n : r / p.tiles_m) * BN;
       if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, abort_flag, p.status, 4)) break;
+      if (warp == 2 && lane == 0 && tile == cta0) UGB_TC_STAMP(UGB_TC_PROF_ACC_SEEN);
       tcgen05_fence_after();
       // BM = 128: accumulator row = TMEM lane.  BM = 64: rows 16q..16q+15 sit on lanes 0..15 of quadrant q.
       const bool row_lane = BM == 128 || lane < 16;
@@ -544,6 +556,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 
   // ------------------------------------------------------------- teardown --
+  if (warp == 2 && lane == 0) UGB_TC_STAMP(UGB_TC_PROF_EPILOGUE_DONE);
   __syncwarp();
   if (*abort_flag) {
     // give copies and MMAs in flight time to land before shared memory and TMEM go away
@@ -559,6 +572,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     else
       asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if (lane == 0) UGB_TC_STAMP(UGB_TC_PROF_END);
   }
 }
 
@@ -629,6 +643,7 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   p.epi = g.epi;
   p.b_static = g.b_static ? 1 : 0;
   p.f16 = g.f16 ? 1 : 0;
+  p.prof = g.prof;
   p.pair_k = 0;
   if (g.pair_k) {
     // two CTAs (a cluster) per tile, each over half of k

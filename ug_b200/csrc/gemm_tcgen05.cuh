@@ -24,6 +24,13 @@ struct ugb_tc_rope_epilogue {
   __nv_bfloat16 *q_out, *kcache, *vcache;
 };
 
+// Measurement aid: with ugb_tc_gemm_args::prof set (device memory, UGB_TC_PROF_SLOTS values, zeroed by the caller),
+// CTA 0 records %globaltimer when it starts, when the wait for the preceding kernel returns, when its MMA thread
+// finds every k block of its first tile complete in shared memory, when it has issued the last MMA, when the
+// epilogue sees the accumulator, when the epilogue (and, with pair_k, the exchange) is done, and after the TMEM release.
+enum { UGB_TC_PROF_START = 0, UGB_TC_PROF_DEP = 1, UGB_TC_PROF_LAST_MMA = 2, UGB_TC_PROF_ACC_SEEN = 3,
+       UGB_TC_PROF_EPILOGUE_DONE = 4, UGB_TC_PROF_END = 5, UGB_TC_PROF_KBLOCK0 = 8, UGB_TC_PROF_SLOTS = 64 };
+
 struct ugb_tc_gemm_args {
   void *out;
   const void *a;        // bf16 [b, m, k] row-major
@@ -42,6 +49,7 @@ struct ugb_tc_gemm_args {
   bool pair_k = false;  // m <= 64, UGB_EPI_SILU_MUL_BF16: two CTAs (a thread-block cluster) per tile, each over half of k; the
                         // second hands its sums to the first through distributed shared memory.  UGB_ERR_UNSUPPORTED when
                         // twice the tiles exceed the SMs
+  unsigned long long *prof = nullptr;   // measurement aid, see UGB_TC_PROF_*
   int pair = -1;        // 256 x 256 tiles on pairs of CTAs (cta_group::2) where the shape allows: 1 / 0, -1 = the device's setting
   ugb_tc_rope_epilogue rope = {};   // UGB_EPI_ROPE_QKV only
   // Query instead of launch: when set, ugb_tc_gemm launches nothing and reports the grid it would launch and how many

@@ -91,6 +91,7 @@ struct ugb_llama {
   unsigned step_timeouts = 0;     // dev->wait_timeouts when the barrier words were last cleared
   int att_early = 1;              // option att_early: kernels may fetch old data before griddepcontrol.wait when that is provably safe
   bool early_ok = false;          // ... and it is, for the current shapes and options (set by enqueue_step)
+  unsigned long long *gemm_prof = nullptr;   // option gemm_profile: [5 projections][UGB_TC_PROF_SLOTS] stamps of the decode GEMMs
   int gate_up_pair = 1;           // option gate_up_pair: decode gate|up on pairs of CTAs that split k (see gemm_rows)
   int att_cluster = 1;            // option att_cluster: the KV slices of a (sequence, KV head) pair run as one cluster and
                                   // are combined through distributed shared memory
@@ -177,6 +178,10 @@ int32_t gemm_rows(ugb_llama *m, size_t rows, void *out, const __nv_bfloat16 *a, 
   g.a_batch = 0; g.b_batch = 0; g.b_is_nk = true;
   g.epi = epi; g.splits = splits; g.bn = bn; g.b_static = true; g.pdl = m->pdl != 0;
   g.smem_kib = rows <= 64 ? m->gemm_smem_kib : 0;
+  if (m->gemm_prof && rows <= 64) {     // qkv, o, gate|up, down, lm_head
+    const int kind = epi == UGB_EPI_SILU_MUL_BF16 ? 2 : n == (size_t)m->qkv_dim ? 0 : n == (size_t)m->vl ? 4 : k == (size_t)m->lc.ffn ? 3 : 1;
+    g.prof = m->gemm_prof + (size_t)kind * UGB_TC_PROF_SLOTS;
+  }
   if (epi == UGB_EPI_SILU_MUL_BF16 && rows <= 64 && m->gate_up_pair && (n + 159) / 160 * 2 <= (size_t)m->dev->sm_count) {
     // gate|up of a decode step: 160-wide tiles, the two k halves of a tile on a pair of CTAs (the k loop of a CTA,
     // not the weight stream, is what bounds the narrow-tile kernel)
@@ -848,6 +853,16 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
     return UGB_OK;
   }
+  if (k == "gemm_profile") {      // measurement aid: time stamps inside the decode projections (UGB_LLAMA_GEMM_PROFILE)
+    if (value && !m->gemm_prof) {
+      unsigned long long *buf = nullptr;
+      if (int32_t rc = dmalloc(m, &buf, (size_t)5 * UGB_TC_PROF_SLOTS, true)) return rc;
+      m->gemm_prof = buf;
+    }
+    if (!value) m->gemm_prof = nullptr;
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    return UGB_OK;
+  }
   if (k == "gate_up_pair") {
     m->gate_up_pair = value != 0;
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
@@ -1024,6 +1039,20 @@ int32_t ugb_llama_read(ugb_llama *m, int32_t what, void *host_dst, size_t len) {
       UGB_CUDA(dev, cudaStreamSynchronize(dev->stream));
       float *out = (float *)host_dst;                 // microseconds since CTA 0's first stamp; 0 where nothing was recorded
       for (size_t i = 0; i < n; ++i) out[i] = raw[i] ? (float)((double)(raw[i] - raw[0]) * 1e-3) : 0.f;
+      return UGB_OK;
+    }
+    case UGB_LLAMA_GEMM_PROFILE: {
+      UGB_REQUIRE(dev, m->gemm_prof, UGB_ERR_INVALID, "no projection profile: set option gemm_profile first");
+      n = (size_t)5 * UGB_TC_PROF_SLOTS;
+      UGB_REQUIRE(dev, len == n, UGB_ERR_SHAPE, "ugb_llama_read: destination holds %zu elements, %zu expected", len, n);
+      std::vector<unsigned long long> raw(n);
+      UGB_CUDA(dev, cudaMemcpyAsync(raw.data(), m->gemm_prof, n * 8, cudaMemcpyDeviceToHost, dev->stream));
+      UGB_CUDA(dev, cudaStreamSynchronize(dev->stream));
+      float *out = (float *)host_dst;   // microseconds after the projection's own dependency wait returned; 0 where nothing was recorded
+      for (size_t i = 0; i < n; ++i) {
+        const unsigned long long dep = raw[i / UGB_TC_PROF_SLOTS * UGB_TC_PROF_SLOTS + UGB_TC_PROF_DEP];
+        out[i] = raw[i] ? (float)(((double)raw[i] - (double)dep) * 1e-3) : 0.f;
+      }
       return UGB_OK;
     }
     default: return ugb_fail(dev, UGB_ERR_INVALID, "ugb_llama_read: unknown selector %d", what);
