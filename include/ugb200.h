@@ -466,7 +466,7 @@ UGB_API int32_t ugb_llama_load_weight(ugb_llama *m, const char *name, const ugb_
 /* Tuning knobs: "splits_qkv", "splits_o", "splits_down" (split-K factors of the
  * projections) and "att_splits" (KV slices per sequence and KV head), 1..8;
  * "bn_qkv", "bn_o", "bn_gate_up", "bn_down", "bn_lm_head" (GEMM tile width:
- * 64, 80, 96, 128 or 256); "gemm_smem_kib" (shared-memory cap of a decode GEMM
+ * 64, 80, 96, 128, 160 or 256); "gemm_smem_kib" (shared-memory cap of a decode GEMM
  * CTA, 32..220, 0 = none); "att_stages" (2..6); "att_early", "att_tma",
  * "att_cluster" (the KV slices of a pair run as one thread-block cluster),
  * "gate_up_pair" (decode gate|up on pairs of CTAs that split k),

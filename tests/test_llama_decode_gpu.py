@@ -151,6 +151,31 @@ def test_gate_up_on_cta_pairs_or_single_ctas(dev):
         gpu.close()
 
 
+def test_projection_timeline_is_recorded_and_ordered(dev):
+    """Option gemm_profile: CTA 0 of each decode projection stamps its own clock; the stamps of a projection are
+    in program order and every k block of its main loop has one."""
+    import ctypes as C
+    from ug_b200._lib import lib
+    cfg = Config(**TINY)
+    gpu, _ = make(cfg, dev, 16, 64)
+    gpu.set_option("gemm_profile", 1)
+    gpu.reset(0)
+    gpu.fwd(synth.tokens(10, (16,), cfg.vocab_size))
+    gpu.decode(2)
+    buf = np.zeros(5 * 64, np.float32)
+    dev._check(lib.ugb_llama_read(gpu._h, 5, buf.ctypes.data, buf.size))
+    for t in buf.reshape(5, 64):
+        start, dep, last_mma, acc_seen, epi, end = t[:6]
+        kb = t[8:][t[8:] != 0]
+        assert dep == 0 and start <= 0 and len(kb) >= 1
+        assert 0 < kb[0] <= kb[-1] <= last_mma <= acc_seen <= epi <= end
+        assert np.all(np.diff(kb) >= 0)
+    gpu.set_option("gemm_profile", 0)
+    with pytest.raises(UgError):
+        dev._check(lib.ugb_llama_read(gpu._h, 5, buf.ctypes.data, buf.size))
+    gpu.close()
+
+
 def test_multi_step_graph_replay_equals_single_steps(dev):
     cfg = Config(**TINY)
     gpu, _ = make(cfg, dev, 16, 64)

@@ -891,8 +891,8 @@ int32_t ugb_llama_set_option(ugb_llama *m, const char *key, int32_t value) {
     return UGB_OK;
   }
   if (k.compare(0, 3, "bn_") == 0) {
-    UGB_REQUIRE(dev, value == 64 || value == 80 || value == 96 || value == 128 || value == 256, UGB_ERR_INVALID,
-                "option %s: tile width must be 64, 80, 96, 128 or 256", key);
+    UGB_REQUIRE(dev, value == 64 || value == 80 || value == 96 || value == 128 || value == 160 || value == 256, UGB_ERR_INVALID,
+                "option %s: tile width must be 64, 80, 96, 128, 160 or 256", key);
     if (k == "bn_qkv") m->bn_qkv = value;
     else if (k == "bn_o") m->bn_o = value;
     else if (k == "bn_gate_up") m->bn_gate_up = value;
