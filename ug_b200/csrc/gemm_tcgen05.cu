@@ -59,6 +59,9 @@ template <int BM, int BN, bool PAIR = false> struct Cfg {
   static constexpr int ACC_STRIDE = BN <= 64 ? 64 : (BN <= 128 ? 128 : 256);
   static constexpr int TMEM_COLS = ACC_STAGES * ACC_STRIDE;   // 512, 256 or 128 (powers of two)
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
+  // pair_k (two CTAs split k and exchange sums): f32 [64][BN / 2] behind the barriers, where it fits
+  static constexpr int PARK_BYTES = 64 * (BN / 2) * 4;
+  static constexpr bool PAIR_K_OK = BM == 64 && !PAIR && BN % 32 == 0 && SMEM_BYTES + PARK_BYTES <= 227 * 1024;
 };
 
 struct Params {
@@ -327,7 +330,33 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const long long out_off = (long long)sp * p.c_split + (long long)bi * p.c_batch;
       if constexpr (BM == 64 && !PAIR) {
         if (p.pair_k) {
-          // both k halves keep their sums in TMEM; they meet after the role branches (below)
+          // This half's sums of the columns the OTHER half finishes go straight into the other CTA's parking area
+          // (f32 [64][BN / 2] behind the barriers: nothing else ever touches it, so no barrier is needed first);
+          // remote stores are not waited for one by one the way remote loads are.  Its own columns stay in TMEM.
+          if constexpr (BN % 32 == 0) {
+            constexpr int GROUPS = BN / 16;
+            const int half = sp;
+            auto mine = [&](int g) { return (g >= GROUPS / 2 ? 1 : 0) == half; };
+            const uint32_t park = mapa_u32(smem_u32(smem + STAGES * STAGE_BYTES + 512), (uint32_t)(half ^ 1)) +
+                                  (uint32_t)((quad * 16 + (lane & 15)) * (BN / 2) * 4);
+            const int col_base = (half ^ 1) * (BN / 2);            // first column of the peer's half
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+              if (mine(2 * c) && mine(2 * c + 1)) continue;         // warp-uniform: nothing of this chunk goes to the peer
+              uint32_t v[32];
+              tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * C_::ACC_STRIDE + c * 32), v);
+              tmem_ld_wait();
+              if (row_lane) {                                       // lanes 16..31 of a BM = 64 warp hold no rows
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                  if (!mine(2 * c + q / 4))
+                    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(park + (uint32_t)((c * 32 + q * 4 - col_base) * 4)), "r"(v[q * 4]), "r"(v[q * 4 + 1]),
+                                   "r"(v[q * 4 + 2]), "r"(v[q * 4 + 3])
+                                 : "memory");
+              }
+            }
+          }
           pair_ready = true;
           pair_m0 = m0; pair_n0 = n0;
           break;
@@ -482,10 +511,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   // ---------------------------------------- pair_k: the two k halves meet --
   // Each half finishes one half of the tile's columns (groups of 16 = 8 (gate, up) pairs: half h owns the groups
-  // g with g / (groups / 2) == h).  First barrier: both accumulators are complete, so both rings are idle.  Then
-  // each half writes its sums of the OTHER half's groups, row-major f32 [64][BN], into the start of the other's
-  // ring (remote stores, which unlike remote loads are not waited for one by one).  Second barrier: the sums
-  // have arrived; each half adds its own and applies the epilogue to its groups.
+  // g with g / (groups / 2) == h).  The epilogue warps have already sent the other half's columns over (above);
+  // after one cluster barrier the peer's sums are in this CTA's parking area, and each half adds its own and
+  // applies the epilogue to its groups.
   if constexpr (BM == 64 && !PAIR && BN % 32 == 0) {
     if (p.pair_k) {
       constexpr int GROUPS = BN / 16;
@@ -497,30 +525,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       __syncwarp();
       cluster_sync_all();
       if (work) {
-        const uint32_t park = mapa_u32(smem_u32(smem), (uint32_t)(half ^ 1)) + (uint32_t)((quad * 16 + (lane & 15)) * BN * 4);
-        tcgen05_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          if (mine(2 * c) && mine(2 * c + 1)) continue;       // warp-uniform: nothing of this chunk goes to the peer
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
-          tmem_ld_wait();
-          if (row_lane) {                       // lanes 16..31 of a BM = 64 warp hold no rows
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              if (!mine(2 * c + q / 4))
-                asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};"
-                             ::"r"(park + (uint32_t)((c * 32 + q * 4) * 4)), "r"(v[q * 4]), "r"(v[q * 4 + 1]), "r"(v[q * 4 + 2]), "r"(v[q * 4 + 3])
-                             : "memory");
-          }
-        }
-        tcgen05_fence_before();
-      }
-      __syncwarp();
-      cluster_sync_all();
-      if (work) {
         const int row = pair_m0 + quad * 16 + lane;
-        const float *park = reinterpret_cast<const float *>(smem) + (size_t)(quad * 16 + (lane & 15)) * BN;
+        const float *park = reinterpret_cast<const float *>(smem + STAGES * STAGE_BYTES + 512) +
+                            (size_t)(quad * 16 + (lane & 15)) * (BN / 2) - half * (BN / 2);   // indexed by tile column
         tcgen05_fence_after();
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -625,7 +632,7 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   constexpr int slot = PAIR ? 8 : BN == 160 ? 9 : BN == 80 ? 6 : BN == 96 ? 7 : (BN == 256 ? 2 : (BN == 128 ? 1 : 0)) + (BM == 64 ? 3 : 0);
   if (!st->attr_set[slot]) {
     UGB_CUDA(dev, cudaFuncSetAttribute(tc_gemm_kernel<BM, BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       C_::SMEM_BYTES));
+                                       C_::SMEM_BYTES + (C_::PAIR_K_OK ? C_::PARK_BYTES : 0)));
 
     st->attr_set[slot] = true;
   }
@@ -647,7 +654,7 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
   p.pair_k = 0;
   if (g.pair_k) {
     // two CTAs (a cluster) per tile, each over half of k
-    if (!(BM == 64 && !PAIR && BN % 32 == 0) || g.epi != UGB_EPI_SILU_MUL_BF16 || batch != 1 || p.k_blocks < 2 ||
+    if (!C_::PAIR_K_OK || g.epi != UGB_EPI_SILU_MUL_BF16 || batch != 1 || p.k_blocks < 2 ||
         2 * (long long)p.tiles_m * p.tiles_n > dev->sm_count)
       return UGB_ERR_UNSUPPORTED;
     p.pair_k = 1;
@@ -685,7 +692,8 @@ int32_t launch_tc(ugb_device *dev, TcState *st, const ugb_tc_gemm_args &g, size_
     stages = fit < 2 ? 2 : (fit > stages ? stages : fit);
   }
   p.stages = stages;
-  const size_t smem = (size_t)stages * C_::STAGE_BYTES + 1536;
+  // pair_k: behind the barriers, the parking area the other k half writes its sums into (f32 [64][BN / 2])
+  const size_t smem = (size_t)stages * C_::STAGE_BYTES + 1536 + (p.pair_k ? (size_t)C_::PARK_BYTES : 0);
   if (g.query_grid || g.query_ctas_per_sm) {
     int occ = 0;
     UGB_CUDA(dev, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, tc_gemm_kernel<BM, BN, PAIR>, THREADS, smem));
