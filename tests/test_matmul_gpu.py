@@ -152,7 +152,8 @@ def test_f16_tensor_core_matmul(dev, bs, m, n, k, t):
 @pytest.mark.parametrize("bs,m,n,k,t", [
     (1, 1, 2048, 2048, True), (1, 3, 5632, 2048, True), (2, 16, 264, 512, True), (1, 8, 32000, 256, True),   # skinny
     (1, 130, 200, 72, True), (1, 130, 200, 72, False), (2, 256, 384, 128, True), (1, 512, 2048, 2048, True),  # tiles
-    (1, 127, 129, 67, False), (1, 17, 1031, 259, True)])                                                      # no 128-bit form
+    (1, 127, 129, 67, False), (1, 17, 1031, 259, True),                                                       # no 128-bit form
+    (32, 1, 64, 1029, False), (3, 5, 132, 37, False), (2, 8, 4, 1, False), (1, 2, 260, 2049, False)])        # skinny, n contiguous
 def test_f32_matmul_kernels(dev, bs, m, n, k, t):
     a = synth.normal(960 + m, (bs, m, k))
     b = synth.normal(961 + n, (bs, n, k) if t else (bs, k, n))

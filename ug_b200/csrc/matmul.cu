@@ -163,6 +163,53 @@ f32_skinny_kernel(float *__restrict__ C, const float *__restrict__ A, const floa
   }
 }
 
+// (1b) Skinny products against a [k, n] operand with n contiguous (Attention::fwd's probabilities x values for the
+// one new token, model.rs:243: [1, T] x [T, 64] per head): one CTA per (128-column chunk, batch step); its warps (32 for
+// m <= 2, fewer for more rows) split k, a lane keeps 4 adjacent columns, so every k row of the chunk is one coalesced 512-byte read per warp and
+// is used for all m rows; the partial sums meet in shared memory.  (The 128 x 128 tile kernel below needs 199 us
+// for 32 heads x [1, 1024] x [1024, 64].)
+template <int MR>
+__global__ void __launch_bounds__(MR <= 2 ? 1024 : (MR <= 4 ? 512 : 256))
+f32_skinny_n_kernel(float *__restrict__ C, const float *__restrict__ A, const float *__restrict__ B, int m, int n, int k,
+                    long long a_rs, long long a_b, long long b_rs, long long b_b) {
+  constexpr int WARPS = MR <= 2 ? 32 : (MR <= 4 ? 16 : 8);       // 32 KiB of partial sums at most
+  __shared__ __align__(16) float red[WARPS][MR][128];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int batch = blockIdx.y, col = blockIdx.x * 128 + lane * 4;
+  const float *a = A + (long long)batch * a_b;
+  const float *bp = B + (long long)batch * b_b + col;
+  float acc[MR][4];
+#pragma unroll
+  for (int r = 0; r < MR; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+  if (col < n) {                                       // n % 4 == 0: a lane's 4 columns are all in or all out
+#pragma unroll 8
+    for (int kk = warp; kk < k; kk += WARPS) {
+      const float4 bv = __ldcs(reinterpret_cast<const float4 *>(bp + (long long)kk * b_rs));
+#pragma unroll
+      for (int r = 0; r < MR; ++r) {
+        if (r < m) {
+          const float x = __ldg(a + (long long)r * a_rs + kk);
+          acc[r][0] = fmaf(x, bv.x, acc[r][0]); acc[r][1] = fmaf(x, bv.y, acc[r][1]);
+          acc[r][2] = fmaf(x, bv.z, acc[r][2]); acc[r][3] = fmaf(x, bv.w, acc[r][3]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < MR; ++r)
+    *reinterpret_cast<float4 *>(&red[warp][r][lane * 4]) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+  __syncthreads();
+  for (int i = threadIdx.x; i < MR * 128; i += WARPS * 32) {
+    const int r = i >> 7, c = i & 127, gc = blockIdx.x * 128 + c;
+    if (r < m && gc < n) {
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) sum += red[w][r][c];
+      C[(long long)batch * m * n + (long long)r * n + gc] = sum;
+    }
+  }
+}
+
 // (2) Everything else in f32: 128 x 128 output tile per CTA, k slices of 8, 256 threads with 8 x 8 outputs each in
 // registers (64 FFMA per 16 shared-memory values read), global loads one slice ahead of the arithmetic, 128-bit
 // global and shared accesses where the layout allows (VEC), zero fill at the m / n / k tails.
@@ -277,6 +324,15 @@ int32_t launch_f32(ugb_device *dev, float *dst, const float *lhs, const float *r
     if (m <= 1) UGB_SKINNY(1); else if (m <= 2) UGB_SKINNY(2); else if (m <= 4) UGB_SKINNY(4); else if (m <= 8) UGB_SKINNY(8); else UGB_SKINNY(16);
 #undef UGB_SKINNY
     return ugb_after_launch(dev, "f32_skinny_kernel");
+  }
+  // only the right operand is read in 128-bit pieces: the left rows may start anywhere (their length is the KV length)
+  if (m <= 8 && !L.transposed && !R.transposed && (L.cs == 1 || k == 1) && (R.cs == 1 || n == 1) && n % 4 == 0 &&
+      R.rs % 4 == 0 && R.batch % 4 == 0 && al16(rhs)) {
+    const dim3 grid((unsigned)((n + 127) / 128), (unsigned)b);
+#define UGB_SKINNY_N(MR) f32_skinny_n_kernel<MR><<<grid, (MR) <= 2 ? 1024 : ((MR) <= 4 ? 512 : 256), 0, dev->stream>>>(dst, lhs, rhs, (int)m, (int)n, (int)k, L.rs, L.batch, R.rs, R.batch)
+    if (m <= 1) UGB_SKINNY_N(1); else if (m <= 2) UGB_SKINNY_N(2); else if (m <= 4) UGB_SKINNY_N(4); else UGB_SKINNY_N(8);
+#undef UGB_SKINNY_N
+    return ugb_after_launch(dev, "f32_skinny_n_kernel");
   }
   const dim3 grid((unsigned)((n + 127) / 128), (unsigned)((m + 127) / 128), (unsigned)b);
   UGB_REQUIRE(dev, grid.y <= 65535, UGB_ERR_UNSUPPORTED, "matmul: m too large for the f32 kernel");
