@@ -1439,14 +1439,6 @@ def main():
                 line["configs"] = config_records(dev, group, peaks)
         else:
             for other in ("weak", "tp"):
-                from ug_b200.llama_config import Config
-                n_kv = Config.llama_1b().num_key_value_heads
-                if other == "tp" and world > n_kv:
-                    # more ranks than KV heads replicates a KV head per rank pair: built and covered by
-                    # tests/test_llama_tp_gpu.py, measured on request only (bench.py --tp)
-                    if rank == 0:
-                        line["tp"] = {"skipped": "more ranks than KV heads (%d > %d): run bench.py --tp for this form" % (world, n_kv)}
-                    continue
                 owl, om = run_decode(other, clocks=False)
                 o_step = om["ms"] / 1e3 / args.steps
                 n_seq = owl.total_batch * (world if other == "weak" else 1)
